@@ -1,0 +1,215 @@
+/*
+ * lego_b200 -- C ABI of the B200 (sm_100a) back end for LEGO layouts.
+ *
+ * The reference library (tavakkoliamirmohammad/LEGO) has no native interface:
+ * a layout is turned into index-expression text and pasted into Triton / MLIR /
+ * CUDA templates.  This header is what a binding for that path would call
+ * instead.  Every entry point is extern "C", takes plain pointers and sizes,
+ * returns an int32 status (0 = OK, < 0 = argument rejected on the host before
+ * any launch, > 0 = CUDA runtime error code + LEGO_ERR_CUDA_BASE or a device
+ * status), never throws and never aborts.
+ *
+ * Buffers named "dev" are device pointers owned by the caller.  `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream); all work is
+ * enqueued on it and the call returns without synchronising unless said
+ * otherwise.  The library keeps one small lazily created workspace per device
+ * (tensor maps, a status word), released by lego_shutdown().
+ */
+#ifndef LEGO_B200_H_
+#define LEGO_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LEGO_MAX_RANK    12   /* logical coordinates of a layout / dims of one block   */
+#define LEGO_MAX_BLOCKS   4   /* permutation blocks in one OrderBy                      */
+#define LEGO_MAX_STAGES   8   /* OrderBy stages in one GroupBy                          */
+#define LEGO_MAX_TERMS   32   /* digits of a folded layout                              */
+#define LEGO_MAX_GROUPS 256   /* problems in one grouped GEMM call                      */
+
+/* status codes */
+enum {
+  LEGO_OK                = 0,
+  LEGO_ERR_NULL          = -1,   /* a required pointer is NULL                          */
+  LEGO_ERR_RANK          = -2,   /* rank / count outside the limits above or mismatched */
+  LEGO_ERR_PERM          = -3,   /* perm[] is not a permutation                         */
+  LEGO_ERR_DIM           = -4,   /* a dimension is < 1                                  */
+  LEGO_ERR_NOT_BIJECTIVE = -5,   /* a stage's size differs from the logical size        */
+  LEGO_ERR_SIZE          = -6,   /* sizes inconsistent with the operation               */
+  LEGO_ERR_ALIGN         = -7,   /* pointer or leading dimension not aligned as needed  */
+  LEGO_ERR_UNSUPPORTED   = -8,   /* valid request this build has no kernel for          */
+  LEGO_ERR_DOMAIN        = -9,   /* layouts of one call disagree on the logical domain  */
+  LEGO_ERR_OVERFLOW      = -10,  /* index space does not fit in 63 bits                 */
+  LEGO_ERR_CUDA_BASE     = 1000, /* status = LEGO_ERR_CUDA_BASE + cudaError_t           */
+  LEGO_ERR_DEVICE_TIMEOUT = 2001 /* a bounded wait inside a kernel ran out              */
+};
+
+/* block kinds */
+enum {
+  LEGO_BLOCK_REGP     = 0,  /* regular permutation: flatten(sigma(idx), sigma(dims))    */
+  LEGO_BLOCK_ANTIDIAG = 1,  /* GenP: anti-diagonal enumeration of a square, dims = (n,n)*/
+  LEGO_BLOCK_REVERSE  = 2   /* GenP: (n1-1-i)*n2 + (n2-1-j), dims = (n1,n2)             */
+};
+
+/* One permutation block: RegP / Row / Col of lego/lego.py:197-240, or one of
+ * the GenP bodies of lego/lego.py:490-535.  sigma(v)[i] = v[perm[i]].          */
+typedef struct lego_block {
+  int32_t rank;
+  int32_t kind;
+  int64_t dims[LEGO_MAX_RANK];
+  int32_t perm[LEGO_MAX_RANK];
+} lego_block_t;
+
+/* One OrderBy (lego/lego.py:243-362): blocks concatenated big-endian.          */
+typedef struct lego_stage {
+  int32_t n_blocks;
+  int32_t reserved;
+  lego_block_t blocks[LEGO_MAX_BLOCKS];
+} lego_stage_t;
+
+/* One GroupBy (lego/lego.py:365-404): logical dims and its `objects`, in the
+ * order the reference stores them (apply walks them last to first).            */
+typedef struct lego_layout {
+  int32_t rank;
+  int32_t n_stages;
+  int64_t dims[LEGO_MAX_RANK];
+  lego_stage_t stages[LEGO_MAX_STAGES];
+} lego_layout_t;
+
+/* Folded form: flat = sum_j ((idx[src_j] / div_j) % mod_j) * stride_j, and
+ * idx[k] = sum_{j: src_j = k} ((flat / stride_j) % mod_j) * div_j.             */
+typedef struct lego_term {
+  int32_t src;
+  int32_t reserved;
+  int64_t div;
+  int64_t mod;
+  int64_t stride;
+} lego_term_t;
+
+typedef struct lego_folded {
+  int32_t foldable;   /* 1: terms[] is exact; 0: only the staged form applies   */
+  int32_t n_terms;
+  int64_t size;       /* product of the logical dims                            */
+  lego_term_t terms[LEGO_MAX_TERMS];
+} lego_folded_t;
+
+/* ---- host-side layout services (no GPU needed) ---------------------------- */
+
+/* Validate ranks, permutations, dimensions and that every stage covers exactly
+ * the logical index space (the condition under which GroupBy.apply of
+ * lego/lego.py:388-404 is a bijection).                                        */
+int32_t lego_layout_check(const lego_layout_t* layout);
+
+/* Constant-fold a layout into digit strides.  Replaces the reference's
+ * simplify_ops fix-point (lego/z3_simplifier.py:367-386) for concrete dims.    */
+int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out);
+
+/* Plan of a permute call, for inspection: which kernel lego_permute would pick
+ * (0 generic, 1 run copy, 2 tiled transpose) and its tile extents.             */
+int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
+                          const lego_layout_t* tile_order, int32_t* kernel_kind, int64_t* tile_in,
+                          int64_t* tile_out);
+
+/* ---- index-map evaluator -------------------------------------------------- */
+
+/* flat[i] = layout.apply(idx[i*rank .. i*rank+rank-1]); GroupBy.apply,
+ * lego/lego.py:388-404.  idx, flat: dev int64.                                 */
+int32_t lego_eval_apply(const lego_layout_t* layout, const int64_t* idx, int64_t* flat, int64_t n,
+                        void* stream);
+
+/* idx[i*rank ..] = layout.inv(flat[i]); GroupBy.inv, lego/lego.py:406-433.     */
+int32_t lego_eval_inv(const lego_layout_t* layout, const int64_t* flat, int64_t* idx, int64_t n,
+                      void* stream);
+
+/* flat_out[i] = layout.apply(unflatten(begin + i, dims)) for i in [0, n): the
+ * loop the reference generates with generate_loop over prod(layout.dims())
+ * (lego/lego_mlir.py:85-108).                                                  */
+int32_t lego_eval_range(const lego_layout_t* layout, int64_t begin, int64_t n, int64_t* flat_out,
+                        void* stream);
+
+/* ---- layout reorganisation ------------------------------------------------ */
+
+/* out_flat[dst(idx)] = in_flat[src(idx)] for every idx of the common logical
+ * domain; elem_bytes in {1,2,4,8,16}.  tile_order (nullable) is a layout whose
+ * logical dims equal the leading dims of src/dst: tile_order.inv(cta) names the
+ * tile a CTA moves, as the block-id maps of benchmarks/mlir/transpose_smem.py:
+ * 52-55 do.  Replaces the generated programs mlir_generated/transpose/
+ * transpose_{naive,smem}_N.mlir.                                               */
+int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                     const lego_layout_t* dst, const lego_layout_t* tile_order, void* stream);
+
+/* ---- row-wise kernels ----------------------------------------------------- */
+
+/* y = softmax(x) along the last axis of a contiguous rows x cols matrix, fp32
+ * arithmetic; replaces softmax_kernel, triton_generated/softmax/softmax.py:33-58
+ * and its host softmax(), :97-160.  row_map (nullable) is a layout over `rows`
+ * logical ids whose apply() gives the row a work item processes (the reference
+ * strides rows over persistent programs).                                      */
+int32_t lego_softmax_f16(const void* x, void* y, int64_t rows, int64_t cols,
+                         const lego_layout_t* row_map, void* stream);
+int32_t lego_softmax_f32(const void* x, void* y, int64_t rows, int64_t cols,
+                         const lego_layout_t* row_map, void* stream);
+
+/* LayerNorm forward: y = (x - mean) * rstd * gamma + beta, biased variance,
+ * fp32 statistics written to mean/rstd (dev float[rows]); replaces
+ * _lego_layer_norm_fwd_fused, triton_generated/layernorm/layernorm.py:58-101
+ * and LEGOLayerNorm.forward, :279-307.  x, gamma, beta, y: dev fp16.           */
+int32_t lego_layernorm_fwd_f16(const void* x, const void* gamma, const void* beta, void* y,
+                               float* mean, float* rstd, int64_t rows, int64_t cols, float eps,
+                               const lego_layout_t* row_map, void* stream);
+
+/* LayerNorm backward: dx per row, dgamma/dbeta by a deterministic two-stage
+ * column reduction; replaces _lego_layer_norm_bwd_dx_fused and
+ * _lego_layer_norm_bwd_dwdb, layernorm.py:163-267.  partial: dev float
+ * [2 * lego_layernorm_bwd_partial_rows(rows, cols) * cols] scratch supplied by
+ * the caller.                                                                  */
+int64_t lego_layernorm_bwd_partial_rows(int64_t rows, int64_t cols);
+int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma, const float* mean,
+                               const float* rstd, void* dx, void* dgamma, void* dbeta,
+                               float* partial, int64_t rows, int64_t cols, void* stream);
+
+/* ---- GEMM ----------------------------------------------------------------- */
+
+enum { LEGO_ACT_NONE = 0, LEGO_ACT_LEAKY_RELU = 1 };
+
+/* C[M,N] = act(op(A) . op(B)), fp16 in, fp32 accumulate on tcgen05/TMEM, fp16
+ * out; replaces matmul_kernel / matmul(), triton_generated/matmul/
+ * matmul_NTA_NTB.py:97-145 (and the _TA/_TB variants).  trans_a = 0: A is
+ * row-major [M,K]; 1: A is stored as row-major [K,M].  trans_b = 0: B is
+ * row-major [K,N]; 1: stored as row-major [N,K].  tile_order (nullable) is a
+ * layout with logical dims (M/128, N/256) whose inv(pid) gives (pid_m, pid_n),
+ * the grouped swizzle of benchmarks/triton/matmul_sympy.py:57-65; NULL = row-
+ * major tile order.  M % 128 == 0, N % 256 == 0, K % 64 == 0 (the reference
+ * kernel has no masks either).                                                 */
+int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                      int32_t trans_a, int32_t trans_b, int32_t activation,
+                      const lego_layout_t* tile_order, void* stream);
+
+/* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by
+ * persistent CTAs through the concatenated tile lists; replaces
+ * lego_grouped_matmul_kernel / lego_group_gemm_fn, triton_generated/
+ * grouped_gemm/grouped_gemm.py:39-162.  A, B, C: host arrays of G device
+ * pointers; mnk: host int64 [G,3].  tile_orders (nullable): host array of G
+ * layout pointers, entry g with logical dims (M_g/128, N_g/256).               */
+int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* const* C,
+                              const int64_t* mnk, int32_t G,
+                              const lego_layout_t* const* tile_orders, void* stream);
+
+/* ---- housekeeping --------------------------------------------------------- */
+
+/* Synchronise `stream` and return (then clear) the current device's status word:
+ * LEGO_OK or LEGO_ERR_DEVICE_TIMEOUT; *detail (nullable) receives the raw word. */
+int32_t lego_device_status(void* stream, uint32_t* detail);
+
+const char* lego_status_string(int32_t status);
+
+/* Free every per-device workspace.  Safe to call more than once.               */
+int32_t lego_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEGO_B200_H_ */

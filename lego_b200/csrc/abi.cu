@@ -1,0 +1,134 @@
+// Housekeeping entry points of the C ABI: per-device workspace, status words,
+// and the host-only layout services.
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace lego {
+
+namespace {
+std::mutex g_mu;
+std::vector<DeviceCtx*> g_ctx;  // indexed by device ordinal
+}  // namespace
+
+DeviceCtx* device_ctx(int32_t* err) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    if (err) *err = cuda_status(e);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_mu);
+  if ((int)g_ctx.size() <= dev) g_ctx.resize(dev + 1, nullptr);
+  if (g_ctx[dev]) return g_ctx[dev];
+  DeviceCtx* c = new DeviceCtx();
+  c->device = dev;
+  e = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (e == cudaSuccess) e = cudaMalloc(&c->status_word, 256);
+  if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, 256);
+  c->tmap_table_bytes = (size_t)LEGO_MAX_GROUPS * 448;  // one 448-byte problem record per group
+  if (e == cudaSuccess) e = cudaMalloc(&c->tmap_table, c->tmap_table_bytes);
+  if (e != cudaSuccess) {
+    if (err) *err = cuda_status(e);
+    if (c->status_word) cudaFree(c->status_word);
+    delete c;
+    return nullptr;
+  }
+  g_ctx[dev] = c;
+  return c;
+}
+
+void release_all_ctx() {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int cur = 0;
+  const bool have_cur = cudaGetDevice(&cur) == cudaSuccess;
+  for (DeviceCtx* c : g_ctx) {
+    if (!c) continue;
+    if (cudaSetDevice(c->device) == cudaSuccess) {
+      cudaFree(c->status_word);
+      cudaFree(c->tmap_table);
+    }
+    delete c;
+  }
+  g_ctx.clear();
+  if (have_cur) cudaSetDevice(cur);
+}
+
+}  // namespace lego
+
+using namespace lego;
+
+extern "C" {
+
+int32_t lego_layout_check(const lego_layout_t* layout) { return check_layout(layout, nullptr); }
+
+int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out) {
+  if (!layout || !out) return LEGO_ERR_NULL;
+  int64_t size = 0;
+  int32_t st = check_layout(layout, &size);
+  if (st != LEGO_OK) return st;
+  out->size = size;
+  out->n_terms = 0;
+  out->foldable = 0;
+  std::vector<Digit> dg;
+  st = fold_layout(layout, &dg);
+  if (st == LEGO_ERR_UNSUPPORTED) return LEGO_OK;  // valid layout, staged form only
+  if (st != LEGO_OK) return st;
+  out->foldable = 1;
+  out->n_terms = (int32_t)dg.size();
+  for (size_t j = 0; j < dg.size(); ++j) {
+    out->terms[j].src = dg[j].src;
+    out->terms[j].reserved = 0;
+    out->terms[j].div = dg[j].div;
+    out->terms[j].mod = dg[j].mod;
+    out->terms[j].stride = dg[j].stride;
+  }
+  return LEGO_OK;
+}
+
+int32_t lego_device_status(void* stream, uint32_t* detail) {
+  int32_t err = LEGO_OK;
+  DeviceCtx* c = device_ctx(&err);
+  if (!c) return err;
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t word = 0;
+  LEGO_CUDA_TRY(cudaMemcpyAsync(&word, c->status_word, sizeof(word), cudaMemcpyDeviceToHost, s));
+  LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+  if (detail) *detail = word;
+  if (word) {
+    LEGO_CUDA_TRY(cudaMemsetAsync(c->status_word, 0, sizeof(word), s));
+    LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+    return LEGO_ERR_DEVICE_TIMEOUT;
+  }
+  return LEGO_OK;
+}
+
+const char* lego_status_string(int32_t status) {
+  switch (status) {
+    case LEGO_OK: return "ok";
+    case LEGO_ERR_NULL: return "a required pointer is NULL";
+    case LEGO_ERR_RANK: return "rank or count outside the supported limits, or mismatched";
+    case LEGO_ERR_PERM: return "perm is not a permutation";
+    case LEGO_ERR_DIM: return "a dimension is smaller than 1 or invalid for the block kind";
+    case LEGO_ERR_NOT_BIJECTIVE: return "a stage does not cover the logical index space exactly (layout is not a bijection)";
+    case LEGO_ERR_SIZE: return "sizes are inconsistent with the operation";
+    case LEGO_ERR_ALIGN: return "pointer or leading dimension is not aligned as required";
+    case LEGO_ERR_UNSUPPORTED: return "valid request this build has no kernel for";
+    case LEGO_ERR_DOMAIN: return "layouts disagree on the logical domain";
+    case LEGO_ERR_OVERFLOW: return "index space does not fit in 63 bits";
+    case LEGO_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    default: break;
+  }
+  if (status >= LEGO_ERR_CUDA_BASE && status < LEGO_ERR_DEVICE_TIMEOUT)
+    return cudaGetErrorString((cudaError_t)(status - LEGO_ERR_CUDA_BASE));
+  return "unknown status";
+}
+
+int32_t lego_shutdown(void) {
+  release_all_ctx();
+  return LEGO_OK;
+}
+
+}  // extern "C"

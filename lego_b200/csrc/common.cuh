@@ -1,0 +1,40 @@
+// Shared helpers of the CUDA translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/lego_b200.h"
+#include "layout_host.h"
+
+namespace lego {
+
+inline int32_t cuda_status(cudaError_t e) {
+  return e == cudaSuccess ? LEGO_OK : (int32_t)LEGO_ERR_CUDA_BASE + (int32_t)e;
+}
+
+#define LEGO_CUDA_TRY(expr)                                    \
+  do {                                                         \
+    cudaError_t _e = (expr);                                   \
+    if (_e != cudaSuccess) return ::lego::cuda_status(_e);     \
+  } while (0)
+
+// Per-device facts and the lazily created workspace.
+struct DeviceCtx {
+  int device;
+  int sm_count;
+  int smem_optin;
+  uint32_t* status_word;   // device: first failing wait of a kernel, 0 = none
+  void* tmap_table;        // device: tensor maps of grouped GEMM calls
+  size_t tmap_table_bytes;
+};
+// Context of the current device (created on first use); nullptr + *err on failure.
+DeviceCtx* device_ctx(int32_t* err);
+void release_all_ctx();
+
+__device__ __forceinline__ uint32_t fd_div(uint32_t n, const FastDiv& f) {
+  return f.mul ? (__umulhi(n, f.mul) >> f.shr) : (n >> f.shr);
+}
+
+}  // namespace lego

@@ -1,0 +1,151 @@
+// Index-map evaluator: GroupBy.apply / GroupBy.inv over arrays of indices and
+// over ranges of logical ids, as device-side integer arithmetic.
+//
+// A layout that folds runs as a digit-sum program (a handful of strength-reduced
+// divide / wrap / multiply-add terms, 32-bit when the index space allows); any
+// other layout runs the staged interpreter, which re-cuts and permutes the flat
+// id stage by stage in 64-bit arithmetic exactly as lego/lego.py:388-433 does.
+#include "common.cuh"
+#include "staged.cuh"
+
+namespace lego {
+
+enum { MODE_RANGE = 0, MODE_APPLY = 1, MODE_INV = 2 };
+
+template <bool WIDE>
+__device__ __forceinline__ uint64_t term_value(const DigitTerm& t, uint64_t x) {
+  if (WIDE) {
+    uint64_t q = t.a64 > 1 ? x / t.a64 : x;
+    if (t.m64) q %= t.m64;
+    return q * t.b;
+  } else {
+    uint32_t q = fd_div((uint32_t)x, t.a);
+    if (t.m.d) q -= fd_div(q, t.m) * t.m.d;
+    return (uint64_t)(q * (uint32_t)t.b);
+  }
+}
+
+template <bool WIDE, int MODE>
+__global__ void __launch_bounds__(256)
+digit_eval_kernel(const __grid_constant__ DigitProgram p, const int64_t* __restrict__ in,
+                  int64_t* __restrict__ out, int64_t begin, int64_t n) {
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    if (MODE == MODE_INV) {
+      const uint64_t x = (uint64_t)in[i];
+      uint64_t acc[LEGO_MAX_RANK];
+#pragma unroll
+      for (int k = 0; k < LEGO_MAX_RANK; ++k) acc[k] = 0;
+      for (int j = 0; j < p.n_terms; ++j) {
+        const uint64_t v = term_value<WIDE>(p.t[j], x);
+        const int dst = p.t[j].dst;
+#pragma unroll
+        for (int k = 0; k < LEGO_MAX_RANK; ++k)
+          if (k == dst) acc[k] += v;
+      }
+#pragma unroll
+      for (int k = 0; k < LEGO_MAX_RANK; ++k)
+        if (k < p.n_dst) out[i * p.n_dst + k] = (int64_t)acc[k];
+    } else {
+      uint64_t acc = 0;
+      if (MODE == MODE_RANGE) {
+        const uint64_t x = (uint64_t)(begin + i);
+        for (int j = 0; j < p.n_terms; ++j) acc += term_value<WIDE>(p.t[j], x);
+      } else {
+        const int64_t* row = in + i * p.n_src;
+        for (int j = 0; j < p.n_terms; ++j) acc += term_value<WIDE>(p.t[j], (uint64_t)row[p.t[j].src]);
+      }
+      out[i] = (int64_t)acc;
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+staged_eval_kernel(const __grid_constant__ StagedProgram sp, const int64_t* __restrict__ in,
+                   int64_t* __restrict__ out, int64_t begin, int64_t n) {
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    if (MODE == MODE_INV) {
+      int64_t flat = staged_inv(sp, in[i]);
+      for (int k = sp.rank - 1; k > 0; --k) {
+        out[i * sp.rank + k] = flat % sp.dims[k];
+        flat /= sp.dims[k];
+      }
+      out[i * sp.rank] = flat;
+    } else {
+      int64_t flat;
+      if (MODE == MODE_RANGE) {
+        flat = begin + i;
+      } else {
+        flat = 0;
+        for (int k = 0; k < sp.rank; ++k) flat = flat * sp.dims[k] + in[i * sp.rank + k];
+      }
+      out[i] = staged_apply(sp, flat);
+    }
+  }
+}
+
+template <int MODE>
+static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t* out, int64_t begin,
+                        int64_t n, void* stream) {
+  if (!layout || !out || (MODE != MODE_RANGE && !in)) return LEGO_ERR_NULL;
+  int64_t size = 0;
+  int32_t st = check_layout(layout, &size);
+  if (st != LEGO_OK) return st;
+  if (n < 0) return LEGO_ERR_SIZE;
+  if (MODE == MODE_RANGE && (begin < 0 || begin + n > size)) return LEGO_ERR_SIZE;
+  if (n == 0) return LEGO_OK;
+  int32_t err = LEGO_OK;
+  DeviceCtx* ctx = device_ctx(&err);
+  if (!ctx) return err;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = 256;
+  int64_t blocks64 = (n + threads - 1) / threads;
+  const int64_t cap = (int64_t)ctx->sm_count * 16;
+  const int blocks = (int)(blocks64 < cap ? blocks64 : cap);
+
+  std::vector<Digit> dg;
+  st = fold_layout(layout, &dg);
+  if (st == LEGO_OK) {
+    DigitProgram p;
+    if (MODE == MODE_RANGE) program_range(dg, size, &p);
+    if (MODE == MODE_APPLY) program_apply(dg, layout->rank, size, &p);
+    if (MODE == MODE_INV) program_inv(dg, layout->rank, size, &p);
+    if (p.wide)
+      digit_eval_kernel<true, MODE><<<blocks, threads, 0, s>>>(p, in, out, begin, n);
+    else
+      digit_eval_kernel<false, MODE><<<blocks, threads, 0, s>>>(p, in, out, begin, n);
+  } else if (st == LEGO_ERR_UNSUPPORTED) {
+    StagedProgram sp;
+    st = build_staged(layout, &sp);
+    if (st != LEGO_OK) return st;
+    staged_eval_kernel<MODE><<<blocks, threads, 0, s>>>(sp, in, out, begin, n);
+  } else {
+    return st;
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace lego
+
+using namespace lego;
+
+extern "C" {
+
+int32_t lego_eval_apply(const lego_layout_t* layout, const int64_t* idx, int64_t* flat, int64_t n,
+                        void* stream) {
+  return run_eval<MODE_APPLY>(layout, idx, flat, 0, n, stream);
+}
+
+int32_t lego_eval_inv(const lego_layout_t* layout, const int64_t* flat, int64_t* idx, int64_t n,
+                      void* stream) {
+  return run_eval<MODE_INV>(layout, flat, idx, 0, n, stream);
+}
+
+int32_t lego_eval_range(const lego_layout_t* layout, int64_t begin, int64_t n, int64_t* flat_out,
+                        void* stream) {
+  return run_eval<MODE_RANGE>(layout, nullptr, flat_out, begin, n, stream);
+}
+
+}  // extern "C"

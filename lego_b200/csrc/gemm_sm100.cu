@@ -1,0 +1,445 @@
+// fp16 GEMM and grouped GEMM on tcgen05 tensor cores (sm_100a).
+//
+// One persistent CTA per SM walks a flat tile index; a LEGO layout's inverse maps
+// that index to (tile_m, tile_n) -- the grouped swizzle of the reference's
+// matmul_kernel -- and, for the grouped GEMM, a prefix table maps it to the
+// problem first.  Inside a CTA the warps are specialised:
+//   warp 0      TMA producer: 128x64 A and 256x64 B fp16 tiles, 128-byte swizzle,
+//               4-stage ring in shared memory, completion on mbarriers;
+//   warp 1      MMA issuer: tcgen05.mma kind::f16, M128 N256 K16, fp32
+//               accumulators in TMEM, two 256-column buffers so the epilogue of
+//               tile i overlaps the main loop of tile i+1;
+//   warps 2..5  epilogue: tcgen05.ld -> activation -> fp16 -> global stores.
+// Edges are handled by TMA zero fill on the loads and masks on the stores.
+// Every wait is bounded: on expiry the CTA records a code in the status word,
+// raises a CTA-wide abort flag, drains its own TMA loads, frees TMEM and returns.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace lego {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SUB_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major operand
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr long long WAIT_LIMIT = 2000000000LL;  // SM cycles, about a second
+
+constexpr int kMaxOrderTerms = 8;
+struct TileTerm { uint32_t a, m, b, dst; };  // coord[dst] += ((t / a) % m) * b; m == 0: no wrap
+struct TileOrder { int32_t n_terms; int32_t reserved; TileTerm t[kMaxOrderTerms]; };
+
+struct alignas(64) Problem {
+  CUtensorMap tma_a;
+  CUtensorMap tma_b;
+  __half* c;
+  int32_t m, n, k;
+  int32_t tiles_m, tiles_n;
+  int32_t tile_start;   // first flat tile id of this problem
+  int32_t a_mn_major;   // 1: A stored [K, M] row-major
+  int32_t b_mn_major;   // 1: B stored [K, N] row-major
+  int32_t reserved;
+  TileOrder order;
+};
+static_assert(sizeof(Problem) == 448, "Problem must stay 448 bytes: the device table is sized for it");
+
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ void fail(uint32_t* status, volatile uint32_t* abort_flag, uint32_t code) {
+  *abort_flag = 1;
+  atomicCAS(status, 0u, code);
+}
+
+__device__ __forceinline__ void tile_coords(const Problem& p, int local, int* tm, int* tn) {
+  if (p.order.n_terms == 0) {
+    *tm = local / p.tiles_n;
+    *tn = local % p.tiles_n;
+    return;
+  }
+  uint32_t c0 = 0, c1 = 0;
+  for (int j = 0; j < p.order.n_terms; ++j) {
+    const TileTerm t = p.order.t[j];
+    uint32_t q = (uint32_t)local / t.a;
+    if (t.m) q %= t.m;
+    q *= t.b;
+    if (t.dst == 0) c0 += q; else c1 += q;
+  }
+  *tm = (int)c0;
+  *tn = (int)c1;
+}
+
+template <bool GROUPED>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ table, int n_problems,
+            int total_tiles, int activation, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&bars->tmem_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->tmem_empty[a]), 128);
+    }
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  auto problem_of = [&](int tile, int* cursor) -> const Problem* {
+    if (!GROUPED) return &single;
+    int g = *cursor;
+    while (g + 1 < n_problems && tile >= table[g + 1].tile_start) ++g;
+    *cursor = g;
+    return &table[g];
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued[STAGES] = {0, 0, 0, 0};
+      int cursor = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const Problem* p = problem_of(tile, &cursor);
+        int tm, tn;
+        tile_coords(*p, tile - p->tile_start, &tm, &tn);
+        const int kblocks = (p->k + BK - 1) / BK;
+        const bool a_mn = p->a_mn_major != 0, b_mn = p->b_mn_major != 0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
+            fail(status, abort_flag, 0x10000u | stage);
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&bars->full[stage]);
+          const uint32_t a_dst = ptx::smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_dst = a_dst + A_BYTES;
+          ptx::mbar_arrive_expect_tx(full, STAGE_BYTES);
+          if (a_mn) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_2d(a_dst + j * SUB_BYTES, &p->tma_a, tm * BM + j * 64, kb * BK, full);
+          } else {
+            ptx::tma_load_2d(a_dst, &p->tma_a, kb * BK, tm * BM, full);
+          }
+          if (b_mn) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(b_dst + j * SUB_BYTES, &p->tma_b, tn * BN + j * 64, kb * BK, full);
+          } else {
+            ptx::tma_load_2d(b_dst, &p->tma_b, kb * BK, tn * BN, full);
+          }
+          ++issued[stage];
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // Leave no copy of ours in flight: wait (bounded) for the last load of each stage.
+        uint32_t never = 0;
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s)
+          if (issued[s])
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      int cursor = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        const Problem* p = problem_of(tile, &cursor);
+        const int kblocks = (p->k + BK - 1) / BK;
+        const uint32_t a_mn = p->a_mn_major != 0, b_mn = p->b_mn_major != 0;
+        const uint32_t idesc = ptx::idesc_f16(BM, BN, a_mn, b_mn);
+        const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
+          fail(status, abort_flag, 0x20000u | 0x100u | acc);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
+            fail(status, abort_flag, 0x20000u | stage);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a_base = ptx::smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_base = a_base + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // K-major: 16 k values are 32 bytes inside the 128-byte swizzled row.
+            // MN-major: 16 k values are 16 rows of 128 bytes; 64-wide MN blocks follow at SUB_BYTES.
+            const uint64_t da = a_mn ? ptx::smem_desc_sw128(a_base + kk * 2048, SUB_BYTES, 1024)
+                                     : ptx::smem_desc_sw128(a_base + kk * 32, 16, 1024);
+            const uint64_t db = b_mn ? ptx::smem_desc_sw128(b_base + kk * 2048, SUB_BYTES, 1024)
+                                     : ptx::smem_desc_sw128(b_base + kk * 32, 16, 1024);
+            ptx::mma_f16_ss(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          ptx::mma_commit(ptx::smem_u32(&bars->empty[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) ptx::mma_commit(ptx::smem_u32(&bars->tmem_full[acc]));
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int cursor = 0;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const Problem* p = problem_of(tile, &cursor);
+      int tm, tn;
+      tile_coords(*p, tile - p->tile_start, &tm, &tn);
+      const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
+      bool ok = true;
+      if (lane == 0)
+        ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) fail(status, abort_flag, 0x30000u | acc);
+        break;
+      }
+      ptx::tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const int M = p->m, N = p->n;
+      __half* crow = p->c + (size_t)row * N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        ptx::tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < M && col0 < N) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col0 + j * 8 < N) {
+              uint32_t h[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(r[j * 8 + 2 * e]);
+                float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
+                if (activation == LEGO_ACT_LEAKY_RELU) {
+                  x0 = x0 >= 0.f ? x0 : 0.01f * x0;
+                  x1 = x1 >= 0.f ? x1 : 0.01f * x1;
+                }
+                const __half2 hh = __floats2half2_rn(x0, x1);
+                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+              *reinterpret_cast<uint4*>(crow + col0 + j * 8) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(ptx::smem_u32(&bars->tmem_empty[acc]));
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn(int32_t* err) {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  static int32_t status = LEGO_OK;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess) { status = cuda_status(e); return; }
+    if (q != cudaDriverEntryPointSuccess || !p) { status = LEGO_ERR_UNSUPPORTED; return; }
+    fn = (EncodeFn)p;
+  });
+  if (err) *err = status;
+  return fn;
+}
+
+// 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows.
+int32_t make_tmap(EncodeFn enc, CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                  uint32_t box_inner, uint32_t box_outer) {
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * 2};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LEGO_OK : LEGO_ERR_UNSUPPORTED;
+}
+
+int32_t fill_order(const lego_layout_t* order, int tiles_m, int tiles_n, TileOrder* out) {
+  std::memset(out, 0, sizeof(*out));
+  if (!order) return LEGO_OK;
+  int64_t size = 0;
+  int32_t st = check_layout(order, &size);
+  if (st != LEGO_OK) return st;
+  if (order->rank != 2 || order->dims[0] != tiles_m || order->dims[1] != tiles_n) return LEGO_ERR_DOMAIN;
+  std::vector<Digit> dg;
+  st = fold_layout(order, &dg);
+  if (st != LEGO_OK) return st;  // tile orders must fold to digit strides
+  // identity order (row-major over tiles) needs no terms
+  if ((int)dg.size() > kMaxOrderTerms) return LEGO_ERR_UNSUPPORTED;
+  for (const Digit& d : dg) {
+    TileTerm& t = out->t[out->n_terms++];
+    t.a = (uint32_t)d.stride;
+    t.m = (d.stride * d.mod == size) ? 0u : (uint32_t)d.mod;
+    t.b = (uint32_t)d.div;
+    t.dst = (uint32_t)d.src;
+  }
+  return LEGO_OK;
+}
+
+int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, void* C, int64_t M, int64_t N,
+                     int64_t K, int trans_a, int trans_b, const lego_layout_t* order, int tile_start) {
+  if (!A || !B || !C) return LEGO_ERR_NULL;
+  if (M < 1 || N < 1 || K < 1 || M > 0x3fffffff || N > 0x3fffffff || K > 0x3fffffff) return LEGO_ERR_SIZE;
+  // 16-byte global strides for TMA and 16-byte C stores
+  if (N % 8 || K % 8 || (trans_a && M % 8)) return LEGO_ERR_SIZE;
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return LEGO_ERR_ALIGN;
+  std::memset(p, 0, sizeof(*p));
+  p->c = (__half*)C;
+  p->m = (int32_t)M;
+  p->n = (int32_t)N;
+  p->k = (int32_t)K;
+  p->tiles_m = (int32_t)((M + BM - 1) / BM);
+  p->tiles_n = (int32_t)((N + BN - 1) / BN);
+  p->tile_start = tile_start;
+  p->a_mn_major = trans_a ? 1 : 0;
+  p->b_mn_major = trans_b ? 0 : 1;
+  int32_t st;
+  if (trans_a) st = make_tmap(enc, &p->tma_a, A, (uint64_t)M, (uint64_t)K, 64, BK);   // [K, M], M contiguous
+  else         st = make_tmap(enc, &p->tma_a, A, (uint64_t)K, (uint64_t)M, BK, BM);   // [M, K], K contiguous
+  if (st != LEGO_OK) return st;
+  if (trans_b) st = make_tmap(enc, &p->tma_b, B, (uint64_t)K, (uint64_t)N, BK, BN);   // [N, K], K contiguous
+  else         st = make_tmap(enc, &p->tma_b, B, (uint64_t)N, (uint64_t)K, 64, BK);   // [K, N], N contiguous
+  if (st != LEGO_OK) return st;
+  return fill_order(order, p->tiles_m, p->tiles_n, &p->order);
+}
+
+template <bool GROUPED>
+int32_t configure() {
+  static std::once_flag once;
+  static cudaError_t result = cudaSuccess;
+  std::call_once(once, [] {
+    result = cudaFuncSetAttribute(gemm_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  return cuda_status(result);
+}
+
+}  // namespace
+}  // namespace lego
+
+using namespace lego;
+
+extern "C" {
+
+int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                      int32_t trans_a, int32_t trans_b, int32_t activation,
+                      const lego_layout_t* tile_order, void* stream) {
+  if (activation != LEGO_ACT_NONE && activation != LEGO_ACT_LEAKY_RELU) return LEGO_ERR_UNSUPPORTED;
+  int32_t err = LEGO_OK;
+  DeviceCtx* ctx = device_ctx(&err);
+  if (!ctx) return err;
+  EncodeFn enc = encode_fn(&err);
+  if (!enc) return err;
+  Problem p;
+  int32_t st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0);
+  if (st != LEGO_OK) return st;
+  st = configure<false>();
+  if (st != LEGO_OK) return st;
+  const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
+  if (total > 0x7fffffff) return LEGO_ERR_SIZE;
+  const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+  gemm_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(p, nullptr, 1, (int)total, activation,
+                                                                         ctx->status_word);
+  return cuda_status(cudaGetLastError());
+}
+
+int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* const* C,
+                              const int64_t* mnk, int32_t G,
+                              const lego_layout_t* const* tile_orders, void* stream) {
+  if (!A || !B || !C || !mnk) return LEGO_ERR_NULL;
+  if (G < 0 || G > LEGO_MAX_GROUPS) return LEGO_ERR_RANK;
+  if (G == 0) return LEGO_OK;
+  int32_t err = LEGO_OK;
+  DeviceCtx* ctx = device_ctx(&err);
+  if (!ctx) return err;
+  EncodeFn enc = encode_fn(&err);
+  if (!enc) return err;
+  if ((size_t)G * sizeof(Problem) > ctx->tmap_table_bytes) return LEGO_ERR_RANK;
+  std::vector<Problem> table(G);
+  int64_t total = 0;
+  for (int g = 0; g < G; ++g) {
+    const int32_t st = fill_problem(enc, &table[g], A[g], B[g], C[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2],
+                                    0, 0, tile_orders ? tile_orders[g] : nullptr, (int)total);
+    if (st != LEGO_OK) return st;
+    total += (int64_t)table[g].tiles_m * table[g].tiles_n;
+    if (total > 0x7fffffff) return LEGO_ERR_SIZE;
+  }
+  int32_t st = configure<true>();
+  if (st != LEGO_OK) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  // The table is per device and reused by every call: calls on one stream are
+  // ordered; callers overlapping grouped GEMMs on different streams must serialise.
+  LEGO_CUDA_TRY(cudaMemcpyAsync(ctx->tmap_table, table.data(), (size_t)G * sizeof(Problem),
+                                cudaMemcpyHostToDevice, s));
+  const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+  gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], (const Problem*)ctx->tmap_table, G,
+                                                         (int)total, LEGO_ACT_NONE, ctx->status_word);
+  return cuda_status(cudaGetLastError());
+}
+
+}  // extern "C"

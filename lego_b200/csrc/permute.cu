@@ -1,0 +1,489 @@
+// Layout reorganisation: out_flat[dst(idx)] = in_flat[src(idx)].
+//
+// Both layouts are folded to digit strides on the host and refined to a common
+// digit set, which turns the pair into a digit permutation of the flat index.
+// Three kernels cover it:
+//   tiled  : the unit-stride digit differs between input and output; tiles go
+//            through XOR-swizzled shared memory with 128-bit accesses to HBM on
+//            both sides and conflict-free shared-memory phases;
+//   gather : output-order copy with the widest vector the common unit-stride run
+//            allows (also the fallback for digit sets the tiled kernel rejects);
+//   staged : any layout pair, element by element through the staged interpreter.
+// The tile a CTA moves is named by tile_order.inv(cta) when that layout is given.
+#include <cstring>
+
+#include "common.cuh"
+#include "staged.cuh"
+
+namespace lego {
+
+namespace {
+
+enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2 };
+
+constexpr int kThreads = 256;
+constexpr int kVecPerThread = 4;
+constexpr int kCtaVectors = kThreads * kVecPerThread;  // 16 KiB of 16-byte vectors per CTA
+constexpr int kMaxTilesPerCta = 16;
+
+struct TiledParams {
+  DigitProgram p1;  // tile id -> tile coordinates
+  DigitProgram p2;  // tile coordinates -> (input base, output base), in elements
+  int64_t n_tiles;
+  int64_t s_in_o;   // input stride of the output-fast digit (elements)
+  int64_t s_out_i;  // output stride of the input-fast digit (elements)
+  int32_t tiles_per_cta;
+  int32_t log_ti;   // tile extent along the input-fast digit, log2 elements
+  int32_t log_to;   // tile extent along the output-fast digit, log2 elements
+  int32_t reserved;
+};
+
+struct GatherParams {
+  DigitProgram g;   // output element offset -> input element offset
+  int64_t n_vec;
+  int32_t elems_per_vec;
+  int32_t reserved;
+};
+
+struct Plan {
+  int kind;
+  int elem_bytes;
+  int vec_bytes;
+  int64_t size;
+  int64_t tile_in, tile_out;
+  TiledParams tiled;
+  GatherParams gather;
+  StagedProgram staged_src, staged_dst;
+};
+
+template <bool WIDE>
+__device__ __forceinline__ uint64_t term_eval(const DigitTerm& t, uint64_t x) {
+  if (WIDE) {
+    uint64_t q = t.a64 > 1 ? x / t.a64 : x;
+    if (t.m64) q %= t.m64;
+    return q * t.b;
+  } else {
+    uint32_t q = fd_div((uint32_t)x, t.a);
+    if (t.m.d) q -= fd_div(q, t.m) * t.m.d;
+    return (uint64_t)q * t.b;
+  }
+}
+
+template <int BYTES> struct VecT;
+template <> struct VecT<1> { using type = uint8_t; };
+template <> struct VecT<2> { using type = uint16_t; };
+template <> struct VecT<4> { using type = uint32_t; };
+template <> struct VecT<8> { using type = uint2; };
+template <> struct VecT<16> { using type = uint4; };
+
+// ---- gather: thread per output vector ------------------------------------------
+
+template <int VB, bool WIDE>
+__global__ void __launch_bounds__(kThreads)
+gather_kernel(const __grid_constant__ GatherParams P, const uint8_t* __restrict__ in,
+              uint8_t* __restrict__ out) {
+  using V = typename VecT<VB>::type;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < P.n_vec; v += step) {
+    const uint64_t x = (uint64_t)v * (uint32_t)P.elems_per_vec;
+    uint64_t src = 0;
+    for (int j = 0; j < P.g.n_terms; ++j) src += term_eval<WIDE>(P.g.t[j], x);
+    const V val = reinterpret_cast<const V*>(in)[src / (uint32_t)P.elems_per_vec];
+    reinterpret_cast<V*>(out)[v] = val;
+  }
+}
+
+// ---- staged: any pair of layouts -----------------------------------------------
+
+template <int EB>
+__global__ void __launch_bounds__(kThreads)
+staged_permute_kernel(const __grid_constant__ StagedProgram src, const __grid_constant__ StagedProgram dst,
+                      const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n) {
+  using V = typename VecT<EB>::type;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const int64_t s = staged_apply(src, i);
+    const int64_t d = staged_apply(dst, i);
+    reinterpret_cast<V*>(out)[d] = reinterpret_cast<const V*>(in)[s];
+  }
+}
+
+// ---- tiled transpose -------------------------------------------------------------
+//
+// A tile is TI elements along the digit that is contiguous in the input times TO
+// elements along the digit that is contiguous in the output.  Shared memory holds
+// it output-major: row i (TO contiguous elements), the 16-byte column c of row i
+// stored at column c ^ f(i), f(i) = (i / VE) mod min(8, TO / VE).  Phase one
+// (global -> shared) has each group of 8 lanes read 128 contiguous bytes of one
+// input row and scatter elements down a shared-memory column: the XOR puts the 8
+// lanes of a group on distinct 16-byte bank groups and the 4 rows of a warp on the
+// 4 words inside a bank group.  Phase two reads whole 16-byte columns of a row.
+
+template <int EB, bool WIDE>
+__global__ void __launch_bounds__(kThreads)
+tiled_transpose_kernel(const __grid_constant__ TiledParams P, const uint8_t* __restrict__ in,
+                       uint8_t* __restrict__ out) {
+  using E = typename VecT<EB>::type;
+  constexpr int VE = 16 / EB;
+  constexpr int LOG_VE = (VE == 1) ? 0 : (VE == 2) ? 1 : (VE == 4) ? 2 : (VE == 8) ? 3 : 4;
+  __shared__ uint4 tile_mem[kCtaVectors];
+  __shared__ int64_t base_in[kMaxTilesPerCta];
+  __shared__ int64_t base_out[kMaxTilesPerCta];
+
+  const int tid = threadIdx.x;
+  const int log_ti = P.log_ti, log_to = P.log_to;
+  const int log_nvi = log_ti - LOG_VE;                 // vectors per input row of a tile
+  const int log_nvo = log_to - LOG_VE;                 // vectors per output row of a tile
+  const int log_vpt = log_ti + log_to - LOG_VE;        // vectors per tile
+  const int log_ci = log_nvi < 3 ? log_nvi : 3;        // lanes that walk one input row
+  const int fmask = (log_nvo < 3 ? (1 << log_nvo) : 8) - 1;
+  const int G = P.tiles_per_cta;
+
+  if (tid < G) {
+    const int64_t t = (int64_t)blockIdx.x * G + tid;
+    int64_t bi = -1, bo = -1;
+    if (t < P.n_tiles) {
+      uint64_t coord[LEGO_MAX_RANK];
+      for (int k = 0; k < LEGO_MAX_RANK; ++k) coord[k] = 0;
+      for (int j = 0; j < P.p1.n_terms; ++j) coord[P.p1.t[j].dst] += term_eval<WIDE>(P.p1.t[j], (uint64_t)t);
+      uint64_t b0 = 0, b1 = 0;
+      for (int j = 0; j < P.p2.n_terms; ++j) {
+        const uint64_t v = term_eval<WIDE>(P.p2.t[j], coord[P.p2.t[j].src]);
+        if (P.p2.t[j].dst == 0) b0 += v; else b1 += v;
+      }
+      bi = (int64_t)b0;
+      bo = (int64_t)b1;
+    }
+    base_in[tid] = bi;
+    base_out[tid] = bo;
+  }
+  __syncthreads();
+
+  uint4 reg[kVecPerThread];
+  bool ok[kVecPerThread];
+#pragma unroll
+  for (int k = 0; k < kVecPerThread; ++k) {
+    const int gv = k * kThreads + tid;
+    const int g = gv >> log_vpt;
+    const int vi = gv & ((1 << log_vpt) - 1);
+    ok[k] = (g < G) && (base_in[g < kMaxTilesPerCta ? g : 0] >= 0);
+    if (ok[k]) {
+      const int a = vi & ((1 << log_ci) - 1);
+      const int o = (vi >> log_ci) & ((1 << log_to) - 1);
+      const int c = vi >> (log_ci + log_to);
+      const int iv = (c << log_ci) + a;
+      const int64_t off = base_in[g] + (int64_t)o * P.s_in_o + ((int64_t)iv << LOG_VE);
+      reg[k] = *reinterpret_cast<const uint4*>(in + off * EB);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kVecPerThread; ++k) {
+    if (!ok[k]) continue;
+    const int gv = k * kThreads + tid;
+    const int g = gv >> log_vpt;
+    const int vi = gv & ((1 << log_vpt) - 1);
+    const int a = vi & ((1 << log_ci) - 1);
+    const int o = (vi >> log_ci) & ((1 << log_to) - 1);
+    const int c = vi >> (log_ci + log_to);
+    const int iv = (c << log_ci) + a;
+    E* tile = reinterpret_cast<E*>(tile_mem + ((size_t)g << log_vpt));
+    const E* src = reinterpret_cast<const E*>(&reg[k]);
+    const int f = iv & fmask;  // (i / VE) mod fm is the same for the VE elements of this vector
+    const int col = (((o >> LOG_VE) ^ f) << LOG_VE) + (o & (VE - 1));
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int i = (iv << LOG_VE) + e;
+      tile[(i << log_to) + col] = src[e];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < kVecPerThread; ++k) {
+    const int gv = k * kThreads + tid;
+    const int g = gv >> log_vpt;
+    const int vi = gv & ((1 << log_vpt) - 1);
+    if (g >= G || base_out[g < kMaxTilesPerCta ? g : 0] < 0) continue;
+    const int ov = vi & ((1 << log_nvo) - 1);
+    const int i = vi >> log_nvo;
+    const int f = (i >> LOG_VE) & fmask;
+    const uint4 w = tile_mem[((size_t)g << log_vpt) + ((size_t)i << log_nvo) + (ov ^ f)];
+    const int64_t off = base_out[g] + (int64_t)i * P.s_out_i + ((int64_t)ov << LOG_VE);
+    *reinterpret_cast<uint4*>(out + off * EB) = w;
+  }
+}
+
+// ---- planning --------------------------------------------------------------------
+
+bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
+int ilog2(int64_t x) { int l = 0; while (((int64_t)1 << l) < x) ++l; return l; }
+bool aligned(const void* p, int a) { return ((uintptr_t)p % (uintptr_t)a) == 0; }
+
+int32_t same_domain(const lego_layout_t* a, const lego_layout_t* b) {
+  if (a->rank != b->rank) return LEGO_ERR_DOMAIN;
+  for (int k = 0; k < a->rank; ++k)
+    if (a->dims[k] != b->dims[k]) return LEGO_ERR_DOMAIN;
+  return LEGO_OK;
+}
+
+void plan_gather(const std::vector<PairDigit>& merged, int64_t size, int eb, const void* in,
+                 const void* out, Plan* pl) {
+  // run = length of the stretch that is contiguous on both sides
+  int64_t run = 1;
+  for (const PairDigit& d : merged)
+    if (d.sa == 1 && d.sb == 1) run = d.radix;
+  int vb = 16;
+  while (vb > eb && ((run * eb) % vb != 0 || !aligned(in, vb) || !aligned(out, vb))) vb >>= 1;
+  if (vb < eb) vb = eb;
+  pl->kind = KIND_GATHER;
+  pl->vec_bytes = vb;
+  GatherParams& gp = pl->gather;
+  std::memset(&gp, 0, sizeof(gp));
+  gp.elems_per_vec = vb / eb;
+  gp.n_vec = size / gp.elems_per_vec;
+  gp.g.n_src = 1;
+  gp.g.n_dst = 1;
+  gp.g.wide = size > ((int64_t)1 << 31) ? 1 : 0;
+  for (const PairDigit& d : merged) {
+    if (d.radix == 1) continue;
+    const bool top = (d.sb * d.radix == size);
+    set_term(&gp.g.t[gp.g.n_terms++], 0, 0, d.sb, top ? 0 : d.radix, d.sa);
+  }
+  pl->tile_in = run;
+  pl->tile_out = run;
+}
+
+// Fill the tiled plan for an in-tile pair (I: sa == 1, O: sb == 1) and the outer
+// programs already stored in pl->tiled; false if the shape does not qualify.
+bool finish_tiled(int64_t ti, int64_t to, int64_t s_out_i, int64_t s_in_o, int eb, const void* in,
+                  const void* out, Plan* pl) {
+  const int ve = 16 / eb;
+  if (!is_pow2(ti) || !is_pow2(to) || ti < ve || to < ve) return false;
+  const int64_t vpt = ti * to / ve;
+  if (vpt > kCtaVectors) return false;
+  if (!aligned(in, 16) || !aligned(out, 16)) return false;
+  if ((s_out_i * eb) % 16 || (s_in_o * eb) % 16) return false;
+  TiledParams& tp = pl->tiled;
+  for (int j = 0; j < tp.p2.n_terms; ++j)
+    if ((tp.p2.t[j].b * (uint64_t)eb) % 16) return false;
+  int64_t g = kCtaVectors / vpt;
+  if (g > kMaxTilesPerCta) g = kMaxTilesPerCta;
+  if (g > tp.n_tiles) g = tp.n_tiles;
+  tp.tiles_per_cta = (int32_t)g;
+  tp.log_ti = ilog2(ti);
+  tp.log_to = ilog2(to);
+  tp.s_in_o = s_in_o;
+  tp.s_out_i = s_out_i;
+  pl->kind = KIND_TILED;
+  pl->vec_bytes = 16;
+  pl->tile_in = ti;
+  pl->tile_out = to;
+  return true;
+}
+
+int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
+                  const lego_layout_t* order, const void* in, const void* out, Plan* pl) {
+  if (!src || !dst) return LEGO_ERR_NULL;
+  if (eb != 1 && eb != 2 && eb != 4 && eb != 8 && eb != 16) return LEGO_ERR_SIZE;
+  int64_t size = 0, osize = 0;
+  int32_t st = check_layout(src, &size);
+  if (st != LEGO_OK) return st;
+  st = check_layout(dst, nullptr);
+  if (st != LEGO_OK) return st;
+  st = same_domain(src, dst);
+  if (st != LEGO_OK) return st;
+  if (order) {
+    st = check_layout(order, &osize);
+    if (st != LEGO_OK) return st;
+    if (order->rank > src->rank) return LEGO_ERR_DOMAIN;
+    for (int k = 0; k < order->rank; ++k)
+      if (order->dims[k] != src->dims[k]) return LEGO_ERR_DOMAIN;
+  }
+  pl->elem_bytes = eb;
+  pl->size = size;
+  pl->tile_in = pl->tile_out = 1;
+
+  std::vector<Digit> ds, dd, dor;
+  const int32_t fs = fold_layout(src, &ds);
+  const int32_t fd = fold_layout(dst, &dd);
+  std::vector<PairDigit> pairs;
+  if (fs != LEGO_OK || fd != LEGO_OK || !refine_pair(ds, dd, &pairs)) {
+    if ((fs != LEGO_OK && fs != LEGO_ERR_UNSUPPORTED)) return fs;
+    if ((fd != LEGO_OK && fd != LEGO_ERR_UNSUPPORTED)) return fd;
+    pl->kind = KIND_STAGED;
+    pl->vec_bytes = eb;
+    st = build_staged(src, &pl->staged_src);
+    if (st != LEGO_OK) return st;
+    return build_staged(dst, &pl->staged_dst);
+  }
+  const int32_t wide = size > ((int64_t)1 << 31) ? 1 : 0;
+
+  // (i) tiles named by tile_order: a tile is every index sharing the leading coordinates.
+  if (order && fold_layout(order, &dor) == LEGO_OK) {
+    int64_t tile_elems = 1;
+    for (int k = order->rank; k < src->rank; ++k) tile_elems *= src->dims[k];
+    std::vector<PairDigit> inner;
+    for (const PairDigit& d : pairs)
+      if (d.pos < tile_elems) inner.push_back(d);
+    merge_pairs(&inner);
+    if (inner.size() == 2 && inner[0].sa == 1 && inner[1].sb == 1) {
+      TiledParams& tp = pl->tiled;
+      std::memset(&tp, 0, sizeof(tp));
+      program_inv(dor, order->rank, osize, &tp.p1);
+      tp.p2.n_src = order->rank;
+      tp.p2.n_dst = 2;
+      tp.p2.wide = wide;
+      tp.p1.wide = wide;
+      for (const Digit& d : ds)
+        if (d.src < order->rank) set_term(&tp.p2.t[tp.p2.n_terms++], d.src, 0, d.div, d.mod, d.stride);
+      for (const Digit& d : dd)
+        if (d.src < order->rank) set_term(&tp.p2.t[tp.p2.n_terms++], d.src, 1, d.div, d.mod, d.stride);
+      tp.n_tiles = osize;
+      if (finish_tiled(inner[0].radix, inner[1].radix, inner[0].sb, inner[1].sa, eb, in, out, pl))
+        return LEGO_OK;
+    }
+  }
+
+  // (ii) tiles chosen here from the merged digit permutation.
+  std::vector<PairDigit> merged = pairs;
+  merge_pairs(&merged);
+  int ii = -1, oo = -1;
+  for (size_t j = 0; j < merged.size(); ++j) {
+    if (merged[j].sa == 1) ii = (int)j;
+    if (merged[j].sb == 1) oo = (int)j;
+  }
+  if (ii >= 0 && oo >= 0 && ii != oo && eb <= 16) {
+    const int ve = 16 / eb;
+    int64_t t = ve;
+    while ((t * 2) * (t * 2) / ve <= kCtaVectors) t *= 2;
+    int64_t ti = t, to = t;
+    while (ti > 1 && merged[ii].radix % ti) ti >>= 1;
+    while (to > 1 && merged[oo].radix % to) to >>= 1;
+    // grow the narrower side while the tile still fits
+    while (ti * 2 * to / ve <= kCtaVectors && merged[ii].radix % (ti * 2) == 0 && ti < 4 * t) ti *= 2;
+    while (ti * to * 2 / ve <= kCtaVectors && merged[oo].radix % (to * 2) == 0 && to < 4 * t) to *= 2;
+    // outer digits, input-contiguous tile column fastest
+    struct Outer { int64_t radix, sa, sb; };
+    std::vector<Outer> outer;
+    if (merged[ii].radix / ti > 1) outer.push_back({merged[ii].radix / ti, ti, merged[ii].sb * ti});
+    if (merged[oo].radix / to > 1) outer.push_back({merged[oo].radix / to, merged[oo].sa * to, to});
+    for (size_t j = 0; j < merged.size(); ++j)
+      if ((int)j != ii && (int)j != oo && merged[j].radix > 1)
+        outer.push_back({merged[j].radix, merged[j].sa, merged[j].sb});
+    if ((int)outer.size() <= LEGO_MAX_RANK && 2 * (int)outer.size() <= LEGO_MAX_TERMS) {
+      TiledParams& tp = pl->tiled;
+      std::memset(&tp, 0, sizeof(tp));
+      tp.p1.n_src = 1;
+      tp.p1.n_dst = (int32_t)outer.size();
+      tp.p2.n_src = (int32_t)outer.size();
+      tp.p2.n_dst = 2;
+      tp.p1.wide = tp.p2.wide = wide;
+      int64_t before = 1;
+      for (size_t c = 0; c < outer.size(); ++c) {
+        const bool last = (c + 1 == outer.size());
+        set_term(&tp.p1.t[tp.p1.n_terms++], 0, (int)c, before, last ? 0 : outer[c].radix, 1);
+        set_term(&tp.p2.t[tp.p2.n_terms++], (int)c, 0, 1, 0, outer[c].sa);
+        set_term(&tp.p2.t[tp.p2.n_terms++], (int)c, 1, 1, 0, outer[c].sb);
+        before *= outer[c].radix;
+      }
+      tp.n_tiles = before;
+      if (finish_tiled(ti, to, merged[ii].sb, merged[oo].sa, eb, in, out, pl)) return LEGO_OK;
+    }
+  }
+  plan_gather(merged, size, eb, in, out, pl);
+  return LEGO_OK;
+}
+
+template <int EB>
+int32_t launch(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
+  const uint8_t* pin = (const uint8_t*)in;
+  uint8_t* pout = (uint8_t*)out;
+  if (pl.kind == KIND_TILED) {
+    const TiledParams& tp = pl.tiled;
+    const int64_t ctas = (tp.n_tiles + tp.tiles_per_cta - 1) / tp.tiles_per_cta;
+    if (ctas > 0x7fffffff) return LEGO_ERR_SIZE;
+    if (tp.p1.wide)
+      tiled_transpose_kernel<EB, true><<<(unsigned)ctas, kThreads, 0, s>>>(tp, pin, pout);
+    else
+      tiled_transpose_kernel<EB, false><<<(unsigned)ctas, kThreads, 0, s>>>(tp, pin, pout);
+  } else if (pl.kind == KIND_STAGED) {
+    int64_t blocks = (pl.size + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)ctx->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    staged_permute_kernel<EB><<<(unsigned)blocks, kThreads, 0, s>>>(pl.staged_src, pl.staged_dst, pin, pout,
+                                                                   pl.size);
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+template <int VB>
+int32_t launch_gather(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
+  const GatherParams& gp = pl.gather;
+  int64_t blocks = (gp.n_vec + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)ctx->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (gp.g.wide)
+    gather_kernel<VB, true><<<(unsigned)blocks, kThreads, 0, s>>>(gp, (const uint8_t*)in, (uint8_t*)out);
+  else
+    gather_kernel<VB, false><<<(unsigned)blocks, kThreads, 0, s>>>(gp, (const uint8_t*)in, (uint8_t*)out);
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace lego
+
+using namespace lego;
+
+extern "C" {
+
+int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
+                          const lego_layout_t* tile_order, int32_t* kernel_kind, int64_t* tile_in,
+                          int64_t* tile_out) {
+  Plan* pl = new Plan();
+  // Planning for inspection assumes 16-byte aligned buffers, as torch allocations are.
+  const int32_t st = make_plan(elem_bytes, src, dst, tile_order, nullptr, nullptr, pl);
+  if (st == LEGO_OK) {
+    if (kernel_kind) *kernel_kind = pl->kind;
+    if (tile_in) *tile_in = pl->tile_in;
+    if (tile_out) *tile_out = pl->tile_out;
+  }
+  delete pl;
+  return st;
+}
+
+int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                     const lego_layout_t* dst, const lego_layout_t* tile_order, void* stream) {
+  if (!in || !out) return LEGO_ERR_NULL;
+  if (in == out) return LEGO_ERR_UNSUPPORTED;  // in-place reorganisation is not defined
+  if (!aligned(in, elem_bytes > 0 ? elem_bytes : 1) || !aligned(out, elem_bytes > 0 ? elem_bytes : 1))
+    return LEGO_ERR_ALIGN;
+  Plan* pl = new Plan();
+  int32_t st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl);
+  if (st == LEGO_OK && pl->size > 0) {
+    int32_t err = LEGO_OK;
+    DeviceCtx* ctx = device_ctx(&err);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!ctx) {
+      st = err;
+    } else if (pl->kind == KIND_GATHER) {
+      switch (pl->vec_bytes) {
+        case 1: st = launch_gather<1>(*pl, in, out, ctx, s); break;
+        case 2: st = launch_gather<2>(*pl, in, out, ctx, s); break;
+        case 4: st = launch_gather<4>(*pl, in, out, ctx, s); break;
+        case 8: st = launch_gather<8>(*pl, in, out, ctx, s); break;
+        default: st = launch_gather<16>(*pl, in, out, ctx, s); break;
+      }
+    } else {
+      switch (elem_bytes) {
+        case 1: st = launch<1>(*pl, in, out, ctx, s); break;
+        case 2: st = launch<2>(*pl, in, out, ctx, s); break;
+        case 4: st = launch<4>(*pl, in, out, ctx, s); break;
+        case 8: st = launch<8>(*pl, in, out, ctx, s); break;
+        default: st = launch<16>(*pl, in, out, ctx, s); break;
+      }
+    }
+  }
+  delete pl;
+  return st;
+}
+
+}  // extern "C"

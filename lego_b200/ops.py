@@ -1,0 +1,315 @@
+"""Kernel-level callables: the Python side of the C ABI.
+
+The names and argument meaning follow the callables the reference generates:
+``matmul(a, b, activation="")`` (``triton_generated/matmul/matmul_NTA_NTB.py:129-145``),
+``softmax(x)`` (``triton_generated/softmax/softmax.py:97-160``),
+``LEGOLayerNorm.apply(x, normalized_shape, weight, bias, eps)``
+(``triton_generated/layernorm/layernorm.py:279-340``),
+``lego_group_gemm_fn(group_A, group_B)``
+(``triton_generated/grouped_gemm/grouped_gemm.py:120-162``), plus ``permute`` /
+``transpose`` for the MLIR transpose programs and the index-map evaluator.
+
+Tensors are torch tensors; torch only owns memory and streams here.  A CUDA
+tensor is processed in place on the current stream.  A CPU tensor is staged
+through a device buffer (copy in, kernel, copy out) and a CPU tensor comes back:
+that is the end-to-end path.  Without a GPU or without the built library every
+op raises; there is no CPU implementation behind them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _abi
+from .layout import Col, GroupBy, OrderBy, Row
+from .lowering import lower, lower_optional
+
+__all__ = [
+    "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "transpose", "softmax",
+    "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "matmul", "lego_group_gemm_fn",
+    "grouped_swizzle_layout", "row_tiling_layout", "device_status",
+]
+
+
+def _device() -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("lego_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _to_device(t: torch.Tensor) -> torch.Tensor:
+    if t.is_cuda:
+        return t
+    return t.to(_device(), non_blocking=True)
+
+
+def _like_input(result: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+    """Results follow the residence of the input: CPU in, CPU out."""
+    if ref.is_cuda:
+        return result
+    out = torch.empty(result.shape, dtype=result.dtype, device="cpu", pin_memory=True)
+    out.copy_(result, non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    return out
+
+
+def device_status() -> int:
+    """Synchronise the current stream and return the device status word's verdict;
+    raises if a bounded wait inside a kernel ran out."""
+    detail = C.c_uint32(0)
+    st = _abi.lib().lego_device_status(_stream(), C.byref(detail))
+    if st != 0:
+        raise _abi.LegoError(st, f"device status word 0x{detail.value:x}")
+    return 0
+
+
+# ---- layouts used by the ops --------------------------------------------------------
+
+def grouped_swizzle_layout(num_pid_m: int, num_pid_n: int, group_m: int = 8) -> GroupBy:
+    """Tile order of the reference GEMM (``benchmarks/triton/matmul_sympy.py:57-65``):
+    ``inv(pid)`` gives ``(pid_m, pid_n)`` walking ``group_m`` tile rows at a time."""
+    return OrderBy(Col(max(num_pid_m // group_m, 1), 1),
+                   Col(min(num_pid_m, group_m), num_pid_n)).TileBy([num_pid_m, num_pid_n])
+
+
+def row_tiling_layout(n_rows: int, rows_per_tile: int = 1) -> GroupBy:
+    """1-D tiling of rows, ``OrderBy(Row(n_rows)).TileBy([n_rows / R], [R])``."""
+    if rows_per_tile <= 1 or n_rows % rows_per_tile:
+        return OrderBy(Row(n_rows)).TileBy([n_rows])
+    return OrderBy(Row(n_rows)).TileBy([n_rows // rows_per_tile], [rows_per_tile])
+
+
+# ---- index-map evaluator ------------------------------------------------------------
+
+def eval_apply(layout: GroupBy, idx: torch.Tensor) -> torch.Tensor:
+    """``layout.apply`` over rows of ``idx`` (int64 ``[n, rank]``) -> int64 ``[n]``."""
+    desc = lower(layout)
+    if idx.dtype != torch.int64 or idx.dim() != 2 or idx.shape[1] != desc.rank:
+        raise ValueError(f"idx must be int64 [n, {desc.rank}]")
+    d = _to_device(idx).contiguous()
+    out = torch.empty(d.shape[0], dtype=torch.int64, device=d.device)
+    _abi.check(_abi.lib().lego_eval_apply(C.byref(desc), d.data_ptr(), out.data_ptr(), d.shape[0], _stream()),
+               "lego_eval_apply")
+    return _like_input(out, idx)
+
+
+def eval_inv(layout: GroupBy, flat: torch.Tensor) -> torch.Tensor:
+    """``layout.inv`` over ``flat`` (int64 ``[n]``) -> int64 ``[n, rank]``."""
+    desc = lower(layout)
+    if flat.dtype != torch.int64 or flat.dim() != 1:
+        raise ValueError("flat must be int64 [n]")
+    d = _to_device(flat).contiguous()
+    out = torch.empty((d.shape[0], desc.rank), dtype=torch.int64, device=d.device)
+    _abi.check(_abi.lib().lego_eval_inv(C.byref(desc), d.data_ptr(), out.data_ptr(), d.shape[0], _stream()),
+               "lego_eval_inv")
+    return _like_input(out, flat)
+
+
+def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None) -> torch.Tensor:
+    """``layout.apply`` over logical flat ids ``begin .. begin+count`` -> device int64."""
+    desc = lower(layout)
+    size = layout.size()
+    if count is None:
+        count = size - begin
+    out = torch.empty(count, dtype=torch.int64, device=_device())
+    _abi.check(_abi.lib().lego_eval_range(C.byref(desc), begin, count, out.data_ptr(), _stream()),
+               "lego_eval_range")
+    return out
+
+
+# ---- layout reorganisation ----------------------------------------------------------
+
+def permute_plan(elem_bytes: int, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None):
+    """Which kernel ``permute`` would run: ``(kind, tile_in, tile_out)`` with kind
+    0 staged, 1 gather, 2 tiled transpose.  Host-only; needs no GPU."""
+    kind, ti, to = C.c_int32(0), C.c_int64(0), C.c_int64(0)
+    _abi.check(_abi.lib().lego_permute_plan(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)),
+                                            lower_optional(tile_order), C.byref(kind), C.byref(ti), C.byref(to)),
+               "lego_permute_plan")
+    return kind.value, ti.value, to.value
+
+
+def permute(x: torch.Tensor, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out_flat[dst(idx)] = x_flat[src(idx)]`` over the layouts' common logical
+    domain.  ``x`` is read as a flat contiguous buffer; the result has x's shape."""
+    if src.size() != x.numel():
+        raise ValueError(f"layout covers {src.size()} elements, tensor has {x.numel()}")
+    d = _to_device(x).contiguous()
+    res = out if out is not None else torch.empty_like(d)
+    if not res.is_cuda or not res.is_contiguous() or res.numel() != d.numel() or res.dtype != d.dtype:
+        raise ValueError("out must be a contiguous CUDA tensor of x's size and dtype")
+    _abi.check(_abi.lib().lego_permute(d.data_ptr(), res.data_ptr(), d.element_size(), C.byref(lower(src)),
+                                       C.byref(lower(dst)), lower_optional(tile_order), _stream()),
+               "lego_permute")
+    return _like_input(res, x)
+
+
+def transpose(x: torch.Tensor, tile: int = 32, tile_order: Optional[GroupBy] = None) -> torch.Tensor:
+    """2-D transpose through the tiled layouts of the reference's MLIR programs
+    (``benchmarks/mlir/transpose_smem.py:33-37``): source viewed row-major in
+    ``tile x tile`` tiles, destination column-major, tiles visited in ``tile_order``
+    (default: column-major over tiles)."""
+    if x.dim() != 2:
+        raise ValueError("transpose expects a matrix")
+    r, c = x.shape
+    if r % tile or c % tile:
+        raise ValueError(f"matrix {r}x{c} is not a multiple of the {tile}x{tile} tile")
+    src = OrderBy(Row(r, c)).TileBy([r // tile, c // tile], [tile, tile])
+    dst = OrderBy(Col(r, c)).TileBy([r // tile, c // tile], [tile, tile])
+    if tile_order is None:
+        tile_order = OrderBy(Col(r // tile, c // tile)).TileBy([r // tile, c // tile])
+    return permute(x, src, dst, tile_order).reshape(c, r)
+
+
+# ---- row-wise kernels ---------------------------------------------------------------
+
+def softmax(x: torch.Tensor, row_map: Optional[GroupBy] = None) -> torch.Tensor:
+    """Row-wise softmax of a 2-D fp16 or fp32 tensor (fp32 arithmetic)."""
+    if x.dim() != 2:
+        raise ValueError("softmax expects a 2-D tensor")
+    fn = {torch.float16: "lego_softmax_f16", torch.float32: "lego_softmax_f32"}.get(x.dtype)
+    if fn is None:
+        raise ValueError(f"softmax supports float16 and float32, got {x.dtype}")
+    d = _to_device(x).contiguous()
+    y = torch.empty_like(d)
+    n_rows, n_cols = d.shape
+    _abi.check(getattr(_abi.lib(), fn)(d.data_ptr(), y.data_ptr(), n_rows, n_cols, lower_optional(row_map),
+                                       _stream()), fn)
+    return _like_input(y, x)
+
+
+def layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                   row_map: Optional[GroupBy] = None):
+    """LayerNorm forward over the last axis: ``(y, mean, rstd)``, statistics fp32."""
+    if x.dtype != torch.float16 or weight.dtype != torch.float16 or bias.dtype != torch.float16:
+        raise ValueError("layer norm supports float16 tensors")
+    n = x.shape[-1]
+    if weight.numel() != n or bias.numel() != n:
+        raise ValueError("weight / bias must have the size of the last axis")
+    if n * x.element_size() > 65536:
+        raise RuntimeError("This layer norm doesn't support feature dim >= 64KB.")
+    d = _to_device(x).contiguous()
+    x2 = d.reshape(-1, n)
+    w, b = _to_device(weight).contiguous(), _to_device(bias).contiguous()
+    m = x2.shape[0]
+    y = torch.empty_like(d)
+    mean = torch.empty(m, dtype=torch.float32, device=d.device)
+    rstd = torch.empty(m, dtype=torch.float32, device=d.device)
+    _abi.check(_abi.lib().lego_layernorm_fwd_f16(x2.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(),
+                                                 mean.data_ptr(), rstd.data_ptr(), m, n, float(eps),
+                                                 lower_optional(row_map), _stream()),
+               "lego_layernorm_fwd_f16")
+    return _like_input(y, x), _like_input(mean, x), _like_input(rstd, x)
+
+
+class LEGOLayerNorm(torch.autograd.Function):
+    """``LEGOLayerNorm.apply(x, normalized_shape, weight, bias, eps)``."""
+
+    @staticmethod
+    def forward(ctx, x, normalized_shape, weight, bias, eps):
+        y, mean, rstd = layer_norm_fwd(x, weight, bias, eps)
+        ctx.save_for_backward(x, weight, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, mean, rstd = ctx.saved_tensors
+        n = x.shape[-1]
+        xd = _to_device(x).contiguous().reshape(-1, n)
+        dyd = _to_device(dy).contiguous().reshape(-1, n)
+        wd = _to_device(w).contiguous()
+        md, rd = _to_device(mean), _to_device(rstd)
+        m = xd.shape[0]
+        lib = _abi.lib()
+        prow = lib.lego_layernorm_bwd_partial_rows(m, n)
+        partial = torch.empty((2, prow, n), dtype=torch.float32, device=xd.device)
+        dx = torch.empty_like(xd)
+        dw = torch.empty_like(wd)
+        db = torch.empty_like(wd)
+        _abi.check(lib.lego_layernorm_bwd_f16(dyd.data_ptr(), xd.data_ptr(), wd.data_ptr(), md.data_ptr(),
+                                              rd.data_ptr(), dx.data_ptr(), dw.data_ptr(), db.data_ptr(),
+                                              partial.data_ptr(), m, n, _stream()),
+                   "lego_layernorm_bwd_f16")
+        return _like_input(dx.reshape(x.shape), x), None, _like_input(dw, w), _like_input(db, w), None
+
+
+lego_layer_norm = LEGOLayerNorm.apply
+
+
+# ---- GEMM ---------------------------------------------------------------------------
+
+def _operand(t: torch.Tensor):
+    """(contiguous storage, transposed?) of a 2-D operand that is either
+    contiguous or the ``.T`` view of a contiguous matrix."""
+    if t.is_contiguous():
+        return t, 0
+    if t.t().is_contiguous():
+        return t.t(), 1
+    return t.contiguous(), 0
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: Optional[GroupBy] = None,
+           group_m: int = 8) -> torch.Tensor:
+    """``C = act(A @ B)``: fp16 in, fp32 accumulate, fp16 out.  Either operand may
+    be a ``.T`` view.  Tile order defaults to the reference's grouped swizzle with
+    ``GROUP_M = group_m`` when it is a bijection for the tile grid, row-major otherwise."""
+    if a.dtype != torch.float16 or b.dtype != torch.float16:
+        raise ValueError("matmul supports float16 operands")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError("Incompatible dimensions")
+    act = {"": _abi.ACT_NONE, "leaky_relu": _abi.ACT_LEAKY_RELU}.get(activation)
+    if act is None:
+        raise ValueError(f"unknown activation {activation!r}")
+    m, k = a.shape
+    n = b.shape[1]
+    ad, bd = _to_device(a), _to_device(b)
+    a_st, ta = _operand(ad)
+    b_st, tb = _operand(bd)
+    c = torch.empty((m, n), dtype=torch.float16, device=ad.device)
+    if tile_order is None:
+        npm, npn = -(-m // 128), -(-n // 256)
+        if npm % group_m == 0 or npm <= group_m:
+            tile_order = grouped_swizzle_layout(npm, npn, group_m)
+    _abi.check(_abi.lib().lego_gemm_f16(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
+                                        lower_optional(tile_order), _stream()), "lego_gemm_f16")
+    return _like_input(c, a)
+
+
+def lego_group_gemm_fn(group_A: Sequence[torch.Tensor], group_B: Sequence[torch.Tensor],
+                       tile_orders: Optional[Sequence[Optional[GroupBy]]] = None) -> List[torch.Tensor]:
+    """Grouped GEMM: ``[A_g @ B_g for g]`` in one persistent launch."""
+    assert len(group_A) == len(group_B)
+    g = len(group_A)
+    if g == 0:
+        return []
+    if g > _abi.MAX_GROUPS:
+        raise ValueError(f"at most {_abi.MAX_GROUPS} groups per call")
+    a_dev, b_dev, c_dev, mnk = [], [], [], []
+    for A, B in zip(group_A, group_B):
+        if A.dtype != torch.float16 or B.dtype != torch.float16:
+            raise ValueError("grouped GEMM supports float16 operands")
+        assert A.shape[1] == B.shape[0]
+        ad, bd = _to_device(A).contiguous(), _to_device(B).contiguous()
+        a_dev.append(ad)
+        b_dev.append(bd)
+        c_dev.append(torch.empty((A.shape[0], B.shape[1]), dtype=torch.float16, device=ad.device))
+        mnk += [A.shape[0], B.shape[1], A.shape[1]]
+    PtrArr = C.c_void_p * g
+    ap = PtrArr(*[t.data_ptr() for t in a_dev])
+    bp = PtrArr(*[t.data_ptr() for t in b_dev])
+    cp = PtrArr(*[t.data_ptr() for t in c_dev])
+    sizes = (C.c_int64 * (3 * g))(*mnk)
+    orders = None
+    if tile_orders is not None:
+        keep = [None if o is None else lower(o) for o in tile_orders]
+        orders = (_abi.LayoutP * g)(*[C.cast(None, _abi.LayoutP) if o is None else C.pointer(o) for o in keep])
+    _abi.check(_abi.lib().lego_grouped_gemm_f16(ap, bp, cp, sizes, g, orders, _stream()),
+               "lego_grouped_gemm_f16")
+    return [_like_input(c, A) for c, A in zip(c_dev, group_A)]

@@ -1,0 +1,165 @@
+"""Host-side logic of the product (no GPU): the numeric layout algebra, the
+lowering, and the native constant folding, against the reference's golden
+vectors and printed strings."""
+import numpy as np
+import pytest
+
+import lego_b200 as L
+from lego_b200 import ops
+from lego_b200.lowering import fold, lower
+from helpers import build_layout, eval_reference_string, spec_of, unravel
+from oracle import lego_oracle as O
+
+
+def test_apply_and_inv_match_reference(golden):
+    for name, g in golden["layouts"].items():
+        lay = build_layout(g["src"])
+        assert list(lay.dims()) == g["dims"], name
+        assert spec_of(lay) == g["spec"], name
+        got = lay.apply(*unravel(g["ids"], g["dims"]))
+        assert np.array_equal(np.broadcast_to(got, (len(g["ids"]),)), np.asarray(g["apply"])), name
+        inv = lay.inv(np.asarray(g["inv_flat"], dtype=np.int64))
+        exp = np.asarray(g["inv"], dtype=np.int64).reshape(len(g["inv_flat"]), len(g["dims"]))
+        for k in range(len(g["dims"])):
+            assert np.array_equal(np.broadcast_to(inv[k], exp[:, k].shape), exp[:, k]), (name, k)
+        # scalar calls give plain ints, like the reference's numeric path
+        assert lay.apply(*[int(v[0]) for v in unravel(g["ids"][:1], g["dims"])]) == g["apply"][0]
+
+
+def test_fold_matches_reference(golden):
+    staged = set()
+    for name, g in golden["layouts"].items():
+        lay = build_layout(g["src"])
+        f = fold(lay)
+        assert f.size == int(np.prod(g["dims"]))
+        if not f.foldable:
+            staged.add(name)
+            continue
+        idx = unravel(g["ids"], g["dims"])
+        acc = np.zeros(len(g["ids"]), dtype=np.int64)
+        for t in f.terms:
+            acc += ((idx[t.src] // t.div) % t.mod) * t.stride
+        assert np.array_equal(acc, np.asarray(g["apply"])), name
+        # the same terms invert the map
+        flat = np.asarray(g["apply"], dtype=np.int64)
+        for k in range(len(g["dims"])):
+            back = sum(((flat // t.stride) % t.mod) * t.div for t in f.terms if t.src == k)
+            assert np.array_equal(np.broadcast_to(back, idx[k].shape), idx[k]), (name, k)
+    # cuts that no digit split can realise stay on the staged interpreter
+    assert staged == {"misaligned_col", "misaligned_row", "misaligned_two"}
+
+
+def test_fold_examples():
+    f = fold(L.OrderBy(L.Col(128, 128), L.Row(32, 32)).TileBy([128, 128], [32, 32]))
+    assert [(t.src, t.stride) for t in f.terms] == [(1, 131072), (0, 1024), (2, 32), (3, 1)]
+    f = fold(ops.grouped_swizzle_layout(64, 32, 8))
+    assert [(t.src, t.div, t.mod, t.stride) for t in f.terms] == [(0, 8, 8, 256), (1, 1, 32, 8), (0, 1, 8, 1)]
+
+
+def test_getitem_matches_printed_strings(golden):
+    sizes = dict(M=256, N=512, K=192, BM=64, BN=128, BK=32, pid_m=3, pid_n=2, k=5,
+                 n_rows=37, n_cols=64, BLOCK_SIZE=64, row_idx=11, pid=7, BLOCK_SIZE_N=128,
+                 gm=256, gn=512, gk=192, BLOCK_SIZE_M=64, BLOCK_SIZE_K=32, tile_m_idx=3,
+                 tile_n_idx=2, kk=5, i=1, j=0, w=1, q=1)
+    sizes_ln = dict(sizes, N=512, M=24, k=2)
+    checked = 0
+    for name, s in golden["strings"].items():
+        if "layout" not in s:
+            continue
+        env = sizes_ln if name.startswith("layernorm") else sizes
+        if name == "graphene":
+            env = dict(i=1, j=0, k=1, w=1, q=1)
+        lay = build_layout(s["layout"], env)
+        key = []
+        for item in s["key"]:
+            if item == ":":
+                key.append(slice(None))
+            elif item.startswith("arange("):
+                key.append(np.arange(env[item[7:-1]], dtype=np.int64))   # an expression, not a slice
+            elif item.isdigit():
+                key.append(int(item))
+            else:
+                key.append(env[item])
+        got = np.asarray(lay[tuple(key)])
+        exp = np.asarray(eval_reference_string(s["text"], env))
+        if s.get("flat"):
+            got, exp = got.ravel(), exp.ravel()
+        assert got.shape == exp.shape and np.array_equal(got, exp), name
+        checked += 1
+    assert checked >= 15
+
+
+def test_swizzle_inverse_matches_printed_strings(golden):
+    s = golden["strings"]
+    for npm, npn, gm in [(64, 32, 8), (16, 4, 8), (4, 8, 8)]:
+        pid = np.arange(npm * npn, dtype=np.int64)
+        env = {"pid": pid, "num_pid_m": npm, "num_pid_n": npn, "GM": gm}
+        lay = ops.grouped_swizzle_layout(npm, npn, gm)
+        pm, pn = lay.inv(pid)
+        assert np.array_equal(pm, eval_reference_string(s["matmul_pid_m"]["text"], env))
+        assert np.array_equal(pn, eval_reference_string(s["matmul_pid_n"]["text"], env))
+
+
+def test_errors_follow_the_reference():
+    lay = L.OrderBy(L.Row(4, 4)).TileBy([2, 2], [2, 2])
+    with pytest.raises(ValueError):
+        lay.apply(1, 2, 3)                      # lego/lego.py:394-396
+    with pytest.raises(ValueError):
+        L.flatten_index((1, 2), (3,))           # lego/lego.py:99-100
+    with pytest.raises(ValueError):
+        L.Row(4, 4).apply((1,))                 # lego/lego.py:216-217
+    with pytest.raises(ValueError):
+        L.OrderBy(L.Row(2), L.Row(3)).apply((1,))   # lego/lego.py:294-296
+    with pytest.raises(ValueError):
+        L.RegP([2, 2], [0, 0])
+    # the grouped swizzle for 10 tile rows in groups of 8 is not a bijection: rejected at lowering
+    with pytest.raises(ValueError, match="bijection"):
+        lower(ops.grouped_swizzle_layout(10, 4, 8))
+    with pytest.raises(ValueError):
+        lower(L.OrderBy(L.GenP((4, 4), lambda i: i[0] * 4 + i[1], lambda f: (f // 4, f % 4))).GroupBy([(4, 4)]))
+    with pytest.raises(TypeError):
+        lay["bi", 0, 0, 0]
+
+
+def test_genp_bodies_round_trip():
+    n = 7
+    lay = L.OrderBy(L.GenP((n, n), lambda i: L.antidiag(n, i), lambda f: L.antidiag_inv(n, f),
+                           kind="antidiag")).GroupBy([(n, n)])
+    ii, jj = np.indices((n, n))
+    flat = lay.apply(ii.ravel(), jj.ravel())
+    assert np.array_equal(np.sort(flat), np.arange(n * n))
+    assert np.array_equal(flat, O.groupby_apply(spec_of(lay), [ii.ravel(), jj.ravel()]))
+    bi, bj = lay.inv(flat)
+    assert np.array_equal(bi, ii.ravel()) and np.array_equal(bj, jj.ravel())
+    assert lower(lay).stages[0].blocks[0].kind == 1
+    assert not fold(lay).foldable
+
+
+def test_permute_plans():
+    n = 4096
+    src = L.OrderBy(L.Row(n, n)).TileBy([128, 128], [32, 32])
+    dst = L.OrderBy(L.Col(n, n)).TileBy([128, 128], [32, 32])
+    order = L.OrderBy(L.Col(128, 128)).TileBy([128, 128])
+    assert ops.permute_plan(4, src, dst, order) == (2, 32, 32)       # tiles named by the layout
+    kind, ti, to = ops.permute_plan(4, src, dst)
+    assert kind == 2 and ti == 64 and to == 64                         # free choice: 64 x 64 fp32
+    kind, ti, to = ops.permute_plan(2, src, dst)
+    assert kind == 2 and ti * to * 2 <= 16384
+    tm = L.OrderBy(L.Col(128, 128), L.Row(32, 32)).TileBy([128, 128], [32, 32])
+    rm = L.OrderBy(L.Row(n, n)).TileBy([128, 128], [32, 32])
+    assert ops.permute_plan(4, rm, tm) == (1, 32, 32)                  # common 32-element runs: gather
+    a = L.OrderBy(L.Col(3, 2)).GroupBy([(2, 3)])
+    b = L.OrderBy(L.Row(2, 3)).GroupBy([(2, 3)])
+    assert ops.permute_plan(4, a, b)[0] == 0                           # staged interpreter
+    with pytest.raises(ValueError):
+        ops.permute_plan(4, src, L.OrderBy(L.Row(8, 8)).TileBy([8, 8]))
+    with pytest.raises(ValueError):
+        ops.permute_plan(3, src, dst)
+
+
+def test_ops_fail_loudly_without_a_gpu():
+    torch = pytest.importorskip("torch")
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.softmax(torch.zeros(4, 8, dtype=torch.float16))
