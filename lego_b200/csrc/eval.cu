@@ -89,13 +89,13 @@ staged_eval_kernel(const __grid_constant__ StagedProgram sp, const int64_t* __re
 template <int MODE>
 static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t* out, int64_t begin,
                         int64_t n, void* stream) {
-  if (!layout || !out || (MODE != MODE_RANGE && !in)) return LEGO_ERR_NULL;
   int64_t size = 0;
   int32_t st = check_layout(layout, &size);
   if (st != LEGO_OK) return st;
   if (n < 0) return LEGO_ERR_SIZE;
   if (MODE == MODE_RANGE && (begin < 0 || begin + n > size)) return LEGO_ERR_SIZE;
-  if (n == 0) return LEGO_OK;
+  if (n == 0) return LEGO_OK;  // nothing to do; empty buffers may be NULL
+  if (!out || (MODE != MODE_RANGE && !in)) return LEGO_ERR_NULL;
   int32_t err = LEGO_OK;
   DeviceCtx* ctx = device_ctx(&err);
   if (!ctx) return err;

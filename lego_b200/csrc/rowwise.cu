@@ -174,9 +174,9 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 template <int OP, typename T>
 int32_t run_rows(RowParams& P, const lego_layout_t* row_map, void* stream) {
-  if (!P.x || !P.y) return LEGO_ERR_NULL;
-  if (OP == OP_LAYERNORM && (!P.gamma || !P.beta || !P.mean || !P.rstd)) return LEGO_ERR_NULL;
   if (P.rows < 0 || P.cols < 1) return LEGO_ERR_SIZE;
+  if (P.rows > 0 && (!P.x || !P.y)) return LEGO_ERR_NULL;  // empty buffers may be NULL
+  if (P.rows > 0 && OP == OP_LAYERNORM && (!P.gamma || !P.beta || !P.mean || !P.rstd)) return LEGO_ERR_NULL;
   if (((uintptr_t)P.x % sizeof(T)) || ((uintptr_t)P.y % sizeof(T))) return LEGO_ERR_ALIGN;
   P.has_map = 0;
   if (row_map) {

@@ -1,0 +1,115 @@
+"""fp16 GEMM and grouped GEMM on tcgen05, through the C ABI, against the oracle
+(fp32 CPU product of the fp16 inputs).  Tolerance: relative Frobenius error
+<= 1e-3; the reference's own allclose(atol=1e-2) checks are repeated too."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import lego_b200 as L
+from lego_b200 import ops
+from inputs import gemm_input, grouped_input, grouped_sizes
+from oracle import lego_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_FRO = 1e-3
+
+
+def rel_fro(got, ref):
+    return ((got.float() - ref).norm() / ref.norm()).item()
+
+
+def test_matmul_512_like_the_reference_check():
+    torch.manual_seed(0)
+    a = torch.randn(512, 512).half()
+    b = torch.randn(512, 512).half()
+    c = ops.matmul(a.cuda(), b.cuda()).cpu()
+    ops.device_status()
+    ref = O.matmul(a, b)
+    assert rel_fro(c, ref) <= REL_FRO
+    assert torch.allclose(c.float(), ref.half().float(), atol=1e-2 * 8, rtol=1e-2)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_operand_layout_variants(ta, tb):
+    g = torch.Generator().manual_seed(7 + 2 * ta + tb)
+    m, n, k = 384, 768, 320
+    a = (torch.randn(m, k, generator=g) / math.sqrt(k)).half()
+    b = (torch.randn(k, n, generator=g) / math.sqrt(k)).half()
+    ad = a.t().contiguous().cuda().t() if ta else a.cuda()       # .T view of a [K, M] buffer
+    bd = b.t().contiguous().cuda().t() if tb else b.cuda()
+    c = ops.matmul(ad, bd).cpu()
+    ops.device_status()
+    assert rel_fro(c, O.matmul(a, b)) <= REL_FRO
+
+
+def test_edges_activation_and_tile_orders():
+    g = torch.Generator().manual_seed(9)
+    for m, n, k in [(128, 256, 64), (1, 8, 8), (130, 264, 72), (1000, 520, 136), (256, 512, 4096)]:
+        a = (torch.randn(m, k, generator=g) / math.sqrt(k)).half()
+        b = (torch.randn(k, n, generator=g) / math.sqrt(k)).half()
+        ref = O.matmul(a, b)
+        c = ops.matmul(a.cuda(), b.cuda()).cpu()
+        ops.device_status()
+        assert rel_fro(c, ref) <= REL_FRO, (m, n, k)
+    a, b = gemm_input(1024, 1024, 512)
+    ref = O.matmul(a, b, "leaky_relu")
+    assert rel_fro(ops.matmul(a.cuda(), b.cuda(), activation="leaky_relu").cpu(), ref) <= REL_FRO
+    base = ops.matmul(a.cuda(), b.cuda())
+    for order in (L.OrderBy(L.Row(8, 4)).TileBy([8, 4]), L.OrderBy(L.Col(8, 4)).TileBy([8, 4]),
+                  ops.grouped_swizzle_layout(8, 4, 2)):
+        assert torch.equal(ops.matmul(a.cuda(), b.cuda(), tile_order=order), base)   # order never changes bits
+    with pytest.raises(ValueError):
+        ops.matmul(a.cuda(), b.cuda(), tile_order=L.OrderBy(L.Row(4, 4)).TileBy([4, 4]))
+    with pytest.raises(ValueError):
+        ops.matmul(a.cuda()[:, :100].contiguous(), b.cuda()[:100].contiguous())     # K % 8 != 0
+    ops.device_status()
+
+
+def test_config4_8192_cubed():
+    a, b = gemm_input()
+    ad, bd = a.cuda(), b.cuda()
+    c = ops.matmul(ad, bd)
+    ops.device_status()
+    # oracle on sampled rows: C[r, :] = A[r, :] @ B in fp32 on the CPU
+    rows = torch.tensor([0, 1, 127, 128, 4095, 5000, 8191])
+    ref = a[rows].float() @ b.float()
+    assert rel_fro(c[rows.cuda()].cpu(), ref) <= REL_FRO
+    # full size, size-independent property: (A B) v == A (B v) for a random v, in fp64 on the device
+    v = torch.randn(8192, 1, dtype=torch.float64, device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    lhs = c.double() @ v
+    rhs = ad.double() @ (bd.double() @ v)
+    assert ((lhs - rhs).norm() / rhs.norm()).item() <= REL_FRO
+
+
+def test_grouped_reference_sizes_and_config5():
+    torch.manual_seed(0)
+    sizes = [1024, 512, 256, 128]
+    A = [torch.rand(s, s).half() for s in sizes]
+    B = [torch.rand(s, s).half() for s in sizes]
+    out = ops.lego_group_gemm_fn([t.cuda() for t in A], [t.cuda() for t in B])
+    ops.device_status()
+    for c, r in zip(out, O.grouped_matmul(A, B)):
+        assert rel_fro(c.cpu(), r) <= REL_FRO
+    # config 5 shapes with M shrunk 8x for the CPU oracle; then full size with the product property
+    A, B = grouped_input(scale_rows=8)
+    out = ops.lego_group_gemm_fn([t.cuda() for t in A], [t.cuda() for t in B])
+    ops.device_status()
+    for c, r in zip(out, O.grouped_matmul(A, B)):
+        assert rel_fro(c.cpu(), r) <= REL_FRO
+    sizes5, _ = grouped_sizes()
+    assert sizes5[0] == (2048, 1024, 4096) and sizes5[13] == (4096, 4096, 4096)
+    A, B = grouped_input()
+    Ad, Bd = [t.cuda() for t in A], [t.cuda() for t in B]
+    orders = [L.OrderBy(L.Row(-(-a.shape[0] // 128), -(-b.shape[1] // 256))).TileBy(
+        [-(-a.shape[0] // 128), -(-b.shape[1] // 256)]) for a, b in zip(A, B)]
+    out = ops.lego_group_gemm_fn(Ad, Bd, orders)
+    ops.device_status()
+    gen = torch.Generator("cuda").manual_seed(2)
+    for c, a, b in zip(out, Ad, Bd):
+        v = torch.randn(b.shape[1], 1, dtype=torch.float64, device="cuda", generator=gen)
+        rhs = a.double() @ (b.double() @ v)
+        assert (((c.double() @ v) - rhs).norm() / rhs.norm()).item() <= REL_FRO
+    assert ops.lego_group_gemm_fn([], []) == []

@@ -1,0 +1,115 @@
+"""Layout reorganisation on the GPU, through the C ABI, bit-exact against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import lego_b200 as L
+from lego_b200 import ops
+from helpers import spec_of
+from inputs import transpose_input
+from oracle import lego_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(x):
+    """Flat numpy view of a tensor's elements as unsigned integers of their size."""
+    kind = {1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[x.element_size()]
+    return x.contiguous().reshape(-1).view(torch.uint8).numpy().view(kind)
+
+
+def _check(x, src, dst, order=None, kind=None):
+    if kind is not None:
+        assert ops.permute_plan(x.element_size(), src, dst, order)[0] == kind
+    got = ops.permute(x.cuda(), src, dst, order).cpu()
+    exp = O.permute(_bits(x), spec_of(src), spec_of(dst))
+    assert np.array_equal(_bits(got), exp)
+    return got
+
+
+def test_config1_transpose_4096_bit_exact():
+    n = 4096
+    a = transpose_input(n)
+    src = L.OrderBy(L.Row(n, n)).TileBy([128, 128], [32, 32])
+    dst = L.OrderBy(L.Col(n, n)).TileBy([128, 128], [32, 32])
+    order = L.OrderBy(L.Col(128, 128)).TileBy([128, 128])
+    for o in (order, None, L.OrderBy(L.Row(128, 128)).TileBy([128, 128])):
+        out = ops.permute(a.cuda(), src, dst, o).cpu()
+        assert torch.equal(out.reshape(n, n), a.t().contiguous())
+    assert torch.equal(ops.transpose(a.cuda()).cpu(), a.t().contiguous())
+    # second reading of the configuration: re-layout into tile-major order
+    tm = L.OrderBy(L.Col(128, 128), L.Row(32, 32)).TileBy([128, 128], [32, 32])
+    got = ops.permute(a.cuda(), src, tm).cpu().reshape(128, 128, 32, 32)
+    exp = a.reshape(128, 32, 128, 32).permute(2, 0, 1, 3).contiguous()
+    assert torch.equal(got, exp)
+    # and back: round trip is the identity
+    assert torch.equal(ops.permute(got.cuda(), tm, src).cpu().reshape(n, n), a)
+
+
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.float16, torch.float32, torch.float64])
+def test_tiled_transposes_against_oracle(dtype):
+    g = torch.Generator().manual_seed(11)
+    for r, c, t in [(96, 160, 32), (256, 128, 64), (64, 64, 16), (128, 384, 32)]:
+        x = torch.randint(0, 255, (r * c * torch.empty(0, dtype=dtype).element_size(),), generator=g,
+                          dtype=torch.uint8).view(dtype).reshape(r, c)
+        src = L.OrderBy(L.Row(r, c)).TileBy([r // t, c // t], [t, t])
+        dst = L.OrderBy(L.Col(r, c)).TileBy([r // t, c // t], [t, t])
+        order = L.OrderBy(L.Col(r // t, c // t)).TileBy([r // t, c // t])
+        got = _check(x, src, dst, order)
+        assert torch.equal(got.reshape(c, r).view(torch.uint8), x.t().contiguous().view(torch.uint8))
+        _check(x, src, dst, None)
+
+
+def test_three_level_layouts_of_the_mlir_programs():
+    n = 256
+    x = torch.arange(n * n, dtype=torch.float32).reshape(n, n)       # the reference fills with float(i)
+    a = L.OrderBy(L.Row(n, n)).TileBy([8, 8], [4, 1], [8, 32])
+    b = L.OrderBy(L.Col(n, n)).TileBy([8, 8], [4, 1], [8, 32])
+    got = _check(x, a, b)
+    assert torch.equal(got.reshape(n, n), x.t().contiguous())
+
+
+def test_batched_and_brick_permutations():
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(6 * 64 * 128, generator=g)
+    # 3-D brick re-layout (row-major volume -> 2x2x4 bricks), a pure gather
+    vol = L.OrderBy(L.Row(8, 12, 128)).TileBy([4, 6, 2], [2, 2, 64])
+    brick = L.OrderBy(L.Row(4, 6, 2), L.Row(2, 2, 64)).TileBy([4, 6, 2], [2, 2, 64])
+    _check(x[:8 * 12 * 128], vol, brick, kind=1)
+    # batched transpose: (b, i, j) -> (b, j, i)
+    src = L.OrderBy(L.Row(6, 64, 128)).GroupBy([(6, 64, 128)])
+    dst = L.OrderBy(L.RegP([6, 64, 128], [0, 2, 1])).GroupBy([(6, 64, 128)])
+    got = _check(x, src, dst, kind=2)
+    assert torch.equal(got.reshape(6, 128, 64), x.reshape(6, 64, 128).transpose(1, 2).contiguous())
+
+
+def test_staged_and_ragged_layouts():
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(6, generator=g)
+    a = L.OrderBy(L.Col(3, 2)).GroupBy([(2, 3)])
+    b = L.OrderBy(L.Row(2, 3)).GroupBy([(2, 3)])
+    _check(x, a, b, kind=0)
+    y = torch.randn(120, generator=g).half()
+    c = L.OrderBy(L.Col(6, 4), L.Row(5)).GroupBy([(4, 5, 6)])
+    d = L.OrderBy(L.Row(4, 5, 6)).GroupBy([(4, 5, 6)])
+    _check(y, c, d, kind=0)
+    # odd sizes: no 16-byte structure anywhere -> scalar gather
+    z = torch.randn(7 * 9, generator=g)
+    e = L.OrderBy(L.Row(7, 9)).TileBy([7, 9])
+    f = L.OrderBy(L.Col(7, 9)).TileBy([7, 9])
+    got = _check(z, e, f, kind=1)
+    assert torch.equal(got.reshape(9, 7), z.reshape(7, 9).t().contiguous())
+    one = torch.randn(1)
+    s = L.OrderBy(L.Row(1)).TileBy([1])
+    assert torch.equal(ops.permute(one.cuda(), s, s).cpu(), one)
+
+
+def test_argument_errors():
+    x = torch.zeros(64, device="cuda")
+    a = L.OrderBy(L.Row(8, 8)).TileBy([8, 8])
+    with pytest.raises(ValueError):
+        ops.permute(x, a, L.OrderBy(L.Row(4, 16)).TileBy([4, 16]))
+    with pytest.raises(ValueError):
+        ops.permute(x[:32], a, a)
+    with pytest.raises(ValueError):
+        ops.permute(x, a, a, out=x)        # in place is refused

@@ -1,0 +1,147 @@
+"""Row-wise softmax and LayerNorm on the GPU, through the C ABI, against the
+oracle (torch CPU fp32, what the reference's own checks compare with).
+Tolerances: softmax / LayerNorm output max-abs 1e-3 in fp16, statistics
+relative 1e-5; fp32 softmax 1e-6."""
+import pytest
+import torch
+
+import lego_b200 as L
+from lego_b200 import ops
+from inputs import layernorm_input, softmax_input
+from oracle import lego_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_F16 = 1e-3
+
+
+def ln_error_ok(y16, ref32):
+    """LayerNorm output check against the un-rounded fp32 oracle: max-abs 1e-3
+    wherever fp16 can represent it (|y| < 2, half an ulp is below 1e-3); beyond
+    that the output grid itself is coarser, so the bound is half an fp16 ulp of
+    the value (2^-11 |y|) plus 1e-4 of arithmetic slack."""
+    err = (y16.float() - ref32).abs()
+    small = ref32.abs() < 2
+    ok_small = (err[small] <= TOL_F16).all().item() if small.any() else True
+    ok_large = (err[~small] <= ref32[~small].abs() * 2.0 ** -11 + 1e-4).all().item() if (~small).any() else True
+    return ok_small and ok_large
+
+
+def ln_ref32(x, w, b, eps):
+    return O.layernorm_fwd(x, w, b, eps, round_output=False)[0]
+
+
+def test_softmax_config2_rows_subset_and_full_properties():
+    x = softmax_input(16384, 8192)
+    y = ops.softmax(x.cuda(), ops.row_tiling_layout(16384, 4))
+    # oracle on a bounded sample of rows (CPU softmax of the whole matrix takes a while)
+    sel = torch.arange(0, 16384, 37)
+    assert (y[sel.cuda()].cpu().float() - O.softmax(x[sel]).float()).abs().max().item() <= TOL_F16
+    # full size: rows sum to one, order of every row is preserved, nothing negative / NaN
+    s = y.float().sum(dim=1)
+    assert (s - 1).abs().max().item() < 2e-2
+    assert torch.isfinite(y).all() and (y >= 0).all()
+    assert torch.equal(y.argmax(dim=1).cpu(), x.float().argmax(dim=1))
+
+
+@pytest.mark.parametrize("rows,cols", [(1823, 781), (4, 8), (1, 1), (33, 256), (7, 1024), (5, 1032),
+                                       (3, 4096), (2, 8192), (2, 8200), (1, 32768), (9, 2047)])
+def test_softmax_shapes_f16_f32(rows, cols):
+    g = torch.Generator().manual_seed(rows * 131 + cols)
+    x32 = torch.randn(rows, cols, generator=g)                     # the reference's own case is 1823 x 781 fp32
+    y32 = ops.softmax(x32.cuda()).cpu()
+    assert (y32 - torch.softmax(x32, dim=-1)).abs().max().item() <= 1e-6
+    x16 = (x32 * 2).half()
+    y16 = ops.softmax(x16.cuda()).cpu()
+    assert (y16.float() - O.softmax(x16).float()).abs().max().item() <= TOL_F16
+
+
+def test_softmax_row_maps_and_extremes():
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(60, 512, generator=g).half()
+    ref = O.softmax(x)
+    for rm in (L.OrderBy(L.Col(12, 5)).TileBy([12, 5]), L.OrderBy(L.Row(60)).TileBy([15], [4]), None):
+        assert torch.equal(ops.softmax(x.cuda(), rm).cpu(), ops.softmax(x.cuda()).cpu())
+        assert (ops.softmax(x.cuda(), rm).cpu().float() - ref.float()).abs().max().item() <= TOL_F16
+    big = torch.full((2, 64), 60000.0).half()
+    big[0, 3] = -60000.0
+    out = ops.softmax(big.cuda()).cpu()
+    assert torch.isfinite(out).all() and abs(out[1].float().sum().item() - 1) < 1e-2
+    ninf = torch.full((1, 16), float("-inf")).half()
+    ninf[0, 5] = 1.0
+    assert ops.softmax(ninf.cuda()).cpu()[0, 5].item() == 1.0
+    with pytest.raises(ValueError):
+        ops.softmax(x.cuda(), L.OrderBy(L.Row(59)).TileBy([59]))       # map over the wrong number of rows
+    assert ops.softmax(torch.zeros(0, 8, dtype=torch.float16).cuda()).shape == (0, 8)
+
+
+def test_softmax_host_buffers_end_to_end():
+    x = softmax_input(64, 8192)
+    y = ops.softmax(x.pin_memory())
+    assert not y.is_cuda
+    assert (y.float() - O.softmax(x).float()).abs().max().item() <= TOL_F16
+
+
+def test_layernorm_config3_sample_and_full_properties():
+    x, gamma, beta = layernorm_input(16384, 8192)
+    y, mean, rstd = ops.layer_norm_fwd(x.cuda(), gamma.cuda(), beta.cuda(), 1e-5, ops.row_tiling_layout(16384, 4))
+    sel = torch.arange(0, 16384, 41)
+    ry, rm, rr = O.layernorm_fwd(x[sel], gamma, beta, 1e-5)
+    assert ln_error_ok(y[sel.cuda()].cpu(), ln_ref32(x[sel], gamma, beta, 1e-5))
+    assert (y[sel.cuda()].cpu().float() - ry.float()).abs().max().item() <= 2.0 ** -8   # one fp16 ulp at |y| < 8
+    assert ((mean[sel.cuda()].cpu() - rm).abs() <= 1e-5 * rm.abs() + 1e-6).all()
+    assert ((rstd[sel.cuda()].cpu() - rr).abs() <= 1e-5 * rr.abs()).all()
+    # full size: undoing the affine part gives rows of zero mean and unit variance
+    z = (y.float() - beta.cuda().float()) / gamma.cuda().float()
+    assert z.mean(dim=1).abs().max().item() < 5e-3
+    assert (z.var(dim=1, unbiased=False) - 1).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(1151, 8192), (5, 8), (3, 100), (17, 1000), (4, 4096), (2, 16384),
+                                       (1, 32768), (6, 777)])
+def test_layernorm_shapes(rows, cols):
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (-2.3 + 0.5 * torch.randn(rows, cols, generator=g)).half()      # the reference test's distribution
+    w = torch.rand(cols, generator=g).half()
+    b = torch.rand(cols, generator=g).half()
+    y, mean, rstd = ops.layer_norm_fwd(x.cuda(), w.cuda(), b.cuda(), 1e-5)
+    ry, rm, rr = O.layernorm_fwd(x, w, b, 1e-5)
+    assert ln_error_ok(y.cpu(), ln_ref32(x, w, b, 1e-5))
+    assert ((mean.cpu() - rm).abs() <= 1e-5 * rm.abs() + 1e-6).all()
+    assert ((rstd.cpu() - rr).abs() <= 2e-5 * rr.abs()).all()
+
+
+def test_layernorm_backward_matches_reference_test():
+    # test_lego_layer_norm(1151, 8192, fp16) of the reference: atol 1e-2 on y, dx, dw, db
+    rows, cols = 1151, 8192
+    g = torch.Generator().manual_seed(0)
+    w = torch.rand(cols, generator=g).half()
+    b = torch.rand(cols, generator=g).half()
+    x = (-2.3 + 0.5 * torch.randn(rows, cols, generator=g)).half()
+    dy = (0.1 * torch.randn(rows, cols, generator=g)).half()
+    xd = x.cuda().requires_grad_(True)
+    wd = w.cuda().requires_grad_(True)
+    bd = b.cuda().requires_grad_(True)
+    y = ops.lego_layer_norm(xd, (cols,), wd, bd, 1e-5)
+    y.backward(dy.cuda())
+    ry, rm, rr = O.layernorm_fwd(x, w, b, 1e-5)
+    rdx, rdw, rdb = O.layernorm_bwd(dy, x, w, rm, rr)
+    assert torch.allclose(y.detach().cpu().float(), ry.float(), atol=1e-2, rtol=0)
+    assert torch.allclose(xd.grad.cpu().float(), rdx.float(), atol=1e-2, rtol=0)
+    # dw / db sum 1151 rows: compare relative to their magnitude
+    assert (wd.grad.cpu().float() - rdw.float()).abs().max().item() <= 1e-2 * rdw.float().abs().max().item()
+    assert (bd.grad.cpu().float() - rdb.float()).abs().max().item() <= 1e-2 * rdb.float().abs().max().item()
+    # deterministic: a second run gives the same bits
+    xd.grad = wd.grad = bd.grad = None
+    ops.lego_layer_norm(xd, (cols,), wd, bd, 1e-5).backward(dy.cuda())
+    y2 = ops.lego_layer_norm(xd, (cols,), wd, bd, 1e-5)
+    assert torch.equal(y2, y)
+
+
+def test_layernorm_errors():
+    x = torch.zeros(2, 40000, dtype=torch.float16, device="cuda")
+    w = torch.zeros(40000, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="64KB"):
+        ops.layer_norm_fwd(x, w, w, 1e-5)
+    with pytest.raises(ValueError):
+        ops.layer_norm_fwd(x[:, :64].contiguous(), w[:32], w[:32], 1e-5)
