@@ -108,7 +108,8 @@ int32_t lego_layout_check(const lego_layout_t* layout);
 int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out);
 
 /* Plan of a permute call, for inspection: which kernel lego_permute would pick
- * (0 generic, 1 run copy, 2 tiled transpose) and its tile extents.             */
+ * (0 staged interpreter, 1 output-order gather, 2 shared-memory tiled transpose,
+ * 3 TMA-fed tiled transpose) and its tile extents.             */
 int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
                           const lego_layout_t* tile_order, int32_t* kernel_kind, int64_t* tile_in,
                           int64_t* tile_out);

@@ -17,7 +17,10 @@ inline int32_t cuda_status(cudaError_t e) {
 #define LEGO_CUDA_TRY(expr)                                    \
   do {                                                         \
     cudaError_t _e = (expr);                                   \
-    if (_e != cudaSuccess) return ::lego::cuda_status(_e);     \
+    if (_e != cudaSuccess) {                                   \
+      (void)cudaGetLastError(); /* do not leak into later calls */ \
+      return ::lego::cuda_status(_e);                          \
+    }                                                          \
   } while (0)
 
 // Per-device facts and the lazily created workspace.

@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "tma_host.cuh"
 
 namespace lego {
 namespace {
@@ -287,37 +288,11 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
 
 // ---- host side ---------------------------------------------------------------------------
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn(int32_t* err) {
-  static EncodeFn fn = nullptr;
-  static std::once_flag once;
-  static int32_t status = LEGO_OK;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
-    if (e != cudaSuccess) { status = cuda_status(e); return; }
-    if (q != cudaDriverEntryPointSuccess || !p) { status = LEGO_ERR_UNSUPPORTED; return; }
-    fn = (EncodeFn)p;
-  });
-  if (err) *err = status;
-  return fn;
-}
-
 // 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows.
 int32_t make_tmap(EncodeFn enc, CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                   uint32_t box_inner, uint32_t box_outer) {
-  const cuuint64_t dims[2] = {inner, outer};
-  const cuuint64_t strides[1] = {inner * 2};
-  const cuuint32_t box[2] = {box_inner, box_outer};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? LEGO_OK : LEGO_ERR_UNSUPPORTED;
+  return make_tmap_2d(enc, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, inner, outer, inner * 2, box_inner,
+                      box_outer);
 }
 
 int32_t fill_order(const lego_layout_t* order, int tiles_m, int tiles_n, TileOrder* out) {

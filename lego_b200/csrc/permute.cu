@@ -13,13 +13,15 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 #include "staged.cuh"
+#include "tma_host.cuh"
 
 namespace lego {
 
 namespace {
 
-enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2 };
+enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2, KIND_TMA = 3 };
 
 constexpr int kThreads = 256;
 constexpr int kVecPerThread = 4;
@@ -45,6 +47,16 @@ struct GatherParams {
   int32_t reserved;
 };
 
+struct TmaParams {
+  DigitProgram p1;  // tile id -> tile coordinates
+  DigitProgram p2;  // tile coordinates -> (input base, output base), in elements
+  int64_t n_tiles;
+  int64_t pitch;    // elements between consecutive rows of the input tensor map
+  int64_t s_out_i;  // output stride of the input-contiguous digit (elements)
+  int32_t stages;   // ring slots per CTA
+  int32_t reserved;
+};
+
 struct Plan {
   int kind;
   int elem_bytes;
@@ -52,6 +64,7 @@ struct Plan {
   int64_t size;
   int64_t tile_in, tile_out;
   TiledParams tiled;
+  TmaParams tma;
   GatherParams gather;
   StagedProgram staged_src, staged_dst;
 };
@@ -212,6 +225,244 @@ tiled_transpose_kernel(const __grid_constant__ TiledParams P, const uint8_t* __r
   }
 }
 
+
+// ---- TMA-fed transpose ---------------------------------------------------------------
+//
+// Persistent CTAs of ten warps.  A tile is 128 bytes along the input-contiguous digit
+// times 8 * (16 / EB) rows (32 x 32 fp32, 64 x 64 fp16, 16 x 16 fp64).
+//   planner   (1 warp)  evaluates tile_order.inv and both layouts' strides for 32
+//             tiles at a time, one tile per lane, fully converged, into a queue;
+//   producer  (1 lane)  takes queue entries in order: waits for the ring slot,
+//             publishes the tile's output offset and issues 16/EB TMA loads (128-byte
+//             swizzle) through a 3-D map that gathers every (16/EB)-th row, so loads
+//             cost no thread instructions and up to kTmaStages tiles per CTA are in
+//             flight;
+//   consumers (8 warps, in pairs)  read a (16/EB) x (16/EB) block per thread with
+//             conflict-free 128-bit shared-memory loads, transpose it in registers
+//             and write 128-bit vectors; a quarter-warp fills one whole output line.
+// Tiles are dealt to CTAs round-robin in tile-order sequence.
+
+constexpr int kTmaStages = 16;
+constexpr int kTmaConsumerWarps = 8;
+constexpr int kTmaThreads = 32 * (2 + kTmaConsumerWarps);
+constexpr int kPlanBatch = 32;
+constexpr long long kTmaWaitLimit = 2000000000LL;  // SM cycles, about a second
+
+struct PlanEntry {
+  int64_t out_base;
+  int32_t cx, cy;   // tensor-map coordinates of the tile; cx < 0: no tile (ragged end)
+};
+
+struct TmaCtl {
+  uint64_t full[kTmaStages];
+  uint64_t empty[kTmaStages];
+  uint64_t plan_full[2];
+  uint64_t plan_empty[2];
+  int64_t out_base[kTmaStages];
+  PlanEntry plan[2][kPlanBatch];
+  uint32_t abort_flag;
+};
+
+template <int EB, bool WIDE>
+__global__ void __launch_bounds__(kTmaThreads)
+tma_transpose_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ TmaParams P,
+                     uint8_t* __restrict__ out, uint32_t* status) {
+  constexpr int VE = 16 / EB;            // elements per 16-byte vector
+  constexpr int ROWS = 8 * VE;           // tile rows (along the output-contiguous digit)
+  constexpr int TILE_BYTES = ROWS * 128;
+  extern __shared__ uint8_t tsm_raw[];
+  const uint32_t raw = ptx::smem_u32(tsm_raw);
+  uint8_t* tiles = tsm_raw + (((raw + 1023u) & ~1023u) - raw);
+  TmaCtl* ctl = reinterpret_cast<TmaCtl*>(tiles + P.stages * TILE_BYTES);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = P.stages;  // ring slots in use (<= kTmaStages)
+  // tiles are dealt round-robin: the n-th tile of this CTA has id blockIdx.x + n * gridDim.x
+  const int64_t my_tiles =
+      P.n_tiles > blockIdx.x ? (P.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  auto tile_id = [&](int64_t n) { return blockIdx.x + n * (int64_t)gridDim.x; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 2);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->plan_full[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->plan_empty[b]), 1);
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  __syncthreads();
+
+  if (warp == kTmaConsumerWarps + 1) {
+    // ---------------- planner: one tile per lane, 32 tiles per batch ----------------
+    const int64_t batches = (my_tiles + kPlanBatch - 1) / kPlanBatch;
+    for (int64_t k = 0; k < batches; ++k) {
+      const int b = (int)(k & 1);
+      bool ok = true;
+      if (lane == 0)
+        ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->plan_empty[b]), (uint32_t)(((k >> 1) & 1) ^ 1), abort_flag,
+                                    kTmaWaitLimit);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) { *abort_flag = 1; atomicCAS(status, 0u, 0x80000u | (uint32_t)b); }
+        break;
+      }
+      const int64_t n = k * kPlanBatch + lane;
+      PlanEntry e;
+      e.out_base = 0;
+      e.cx = -1;
+      e.cy = 0;
+      const int64_t t = tile_id(n);
+      if (n < my_tiles && t < P.n_tiles) {
+        uint64_t coord[LEGO_MAX_RANK];
+#pragma unroll
+        for (int c = 0; c < LEGO_MAX_RANK; ++c) coord[c] = 0;
+        for (int j = 0; j < P.p1.n_terms; ++j) {
+          const uint64_t v = term_eval<WIDE>(P.p1.t[j], (uint64_t)t);
+          const int dst = P.p1.t[j].dst;
+#pragma unroll
+          for (int c = 0; c < LEGO_MAX_RANK; ++c)
+            if (c == dst) coord[c] += v;
+        }
+        uint64_t b_in = 0, b_out = 0;
+        for (int j = 0; j < P.p2.n_terms; ++j) {
+          const int src = P.p2.t[j].src;
+          uint64_t x = 0;
+#pragma unroll
+          for (int c = 0; c < LEGO_MAX_RANK; ++c)
+            if (c == src) x = coord[c];
+          const uint64_t v = term_eval<WIDE>(P.p2.t[j], x);
+          if (P.p2.t[j].dst == 0) b_in += v; else b_out += v;
+        }
+        e.out_base = (int64_t)b_out;
+        if (WIDE) {
+          e.cx = (int32_t)(b_in % (uint64_t)P.pitch);
+          e.cy = (int32_t)(b_in / (uint64_t)P.pitch);
+        } else {
+          e.cy = (int32_t)((uint32_t)b_in / (uint32_t)P.pitch);
+          e.cx = (int32_t)((uint32_t)b_in - (uint32_t)e.cy * (uint32_t)P.pitch);
+        }
+      }
+      ctl->plan[b][lane] = e;
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->plan_full[b]));
+    }
+    return;
+  }
+
+  if (warp == kTmaConsumerWarps) {
+    // ---------------- producer: one lane, slots in order ----------------
+    if (lane == 0) {
+      int64_t issued = 0;
+      for (int64_t n = 0; n < my_tiles; ++n) {
+        const int64_t k = n / kPlanBatch;
+        const int b = (int)(k & 1), q = (int)(n % kPlanBatch);
+        if (q == 0 &&
+            !ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->plan_full[b]), (uint32_t)((k >> 1) & 1), abort_flag,
+                                    kTmaWaitLimit)) {
+          *abort_flag = 1;
+          atomicCAS(status, 0u, 0x90000u | (uint32_t)b);
+          break;
+        }
+        const PlanEntry e = ctl->plan[b][q];
+        const bool last_of_batch = (q == kPlanBatch - 1) || (n + 1 == my_tiles);
+        if (e.cx >= 0) {
+          const int s = (int)(n % stages);
+          const uint32_t use = (uint32_t)(n / stages);
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kTmaWaitLimit)) {
+            *abort_flag = 1;
+            atomicCAS(status, 0u, 0x60000u | (uint32_t)s);
+            break;
+          }
+          ctl->out_base[s] = e.out_base;
+          const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+          ptx::mbar_arrive_expect_tx(full, TILE_BYTES);
+          // rows k, k + VE, k + 2 VE, ... of the tile go to the k-th 8-row group of the slot
+#pragma unroll
+          for (int k = 0; k < VE; ++k)
+            ptx::tma_load_3d(ptx::smem_u32(tiles + s * TILE_BYTES + k * 1024), &tmap, e.cx, k, e.cy / VE, full);
+          ++issued;
+        }
+        if (last_of_batch) ptx::mbar_arrive(ptx::smem_u32(&ctl->plan_empty[b]));
+      }
+      if (*abort_flag) {
+        // leave no copy of ours in flight: the last use of every slot that was filled
+        uint32_t never = 0;
+        for (int s = 0; s < stages; ++s) {
+          const int64_t uses = issued > s ? (issued - s + stages - 1) / stages : 0;
+          if (uses)
+            ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kTmaWaitLimit);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers: warp pair p takes tiles n = p, p + 4, ... ----------------
+  const int pair = warp >> 1;
+  // Thread (rb, cb) owns rows rb * VE .. rb * VE + VE - 1 of the tile and its cb-th
+  // 16-byte column.  Row rb * VE + k sits at row rb of the slot's k-th group, stored at
+  // 16-byte position cb ^ rb, so the eight lanes of a quarter-warp (same cb, rb = 0..7)
+  // read eight distinct bank groups; the same eight lanes then write one whole
+  // 128-byte line of the output.
+  const int rb = lane & 7;
+  const int cb = ((warp & 1) << 2) + (lane >> 3);
+  for (int64_t n = pair; n < my_tiles; n += kTmaConsumerWarps / 2) {
+    const int s = (int)(n % stages);
+    const uint32_t use = (uint32_t)(n / stages);
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kTmaWaitLimit)) {
+      *abort_flag = 1;
+      atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
+      break;
+    }
+    const int64_t ob = ctl->out_base[s];
+    const uint4* tile = reinterpret_cast<const uint4*>(tiles + s * TILE_BYTES);
+    uint4 r[VE];
+#pragma unroll
+    for (int k = 0; k < VE; ++k) r[k] = tile[(k * 8 + rb) * 8 + (cb ^ rb)];
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));
+    uint4 w[VE];
+    if (EB == 4) {
+      const uint32_t* a0 = reinterpret_cast<const uint32_t*>(&r[0]);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        uint32_t* d = reinterpret_cast<uint32_t*>(&w[e]);
+#pragma unroll
+        for (int k = 0; k < VE; ++k) d[k] = a0[k * 4 + e];
+      }
+    } else if (EB == 8) {
+      const uint2* a0 = reinterpret_cast<const uint2*>(&r[0]);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        uint2* d = reinterpret_cast<uint2*>(&w[e]);
+#pragma unroll
+        for (int k = 0; k < VE; ++k) d[k] = a0[k * 2 + e];
+      }
+    } else {  // EB == 2: 8 x 8 block of 16-bit elements, two source rows per output word
+      const uint32_t* a0 = reinterpret_cast<const uint32_t*>(&r[0]);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        uint32_t* d = reinterpret_cast<uint32_t*>(&w[e]);
+#pragma unroll
+        for (int k2 = 0; k2 < VE / 2; ++k2)
+          d[k2] = __byte_perm(a0[(2 * k2) * 4 + e / 2], a0[(2 * k2 + 1) * 4 + e / 2], (e & 1) ? 0x7632 : 0x5410);
+      }
+    }
+    uint8_t* obase = out + (ob + (int64_t)rb * VE) * EB;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const int i = cb * VE + e;
+      __stcs(reinterpret_cast<uint4*>(obase + (int64_t)i * P.s_out_i * EB), w[e]);
+    }
+  }
+}
+
 // ---- planning --------------------------------------------------------------------
 
 bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
@@ -277,6 +528,16 @@ bool finish_tiled(int64_t ti, int64_t to, int64_t s_out_i, int64_t s_in_o, int e
   pl->vec_bytes = 16;
   pl->tile_in = ti;
   pl->tile_out = to;
+  // The TMA-fed kernel takes tiles of exactly 128 bytes x 8 vectors.
+  if ((eb == 2 || eb == 4 || eb == 8) && ti * eb == 128 && to == 8 * ve && s_in_o < ((int64_t)1 << 31) &&
+      pl->size / s_in_o < ((int64_t)1 << 31)) {
+    pl->kind = KIND_TMA;
+    pl->tma.p1 = tp.p1;
+    pl->tma.p2 = tp.p2;
+    pl->tma.n_tiles = tp.n_tiles;
+    pl->tma.pitch = s_in_o;
+    pl->tma.s_out_i = s_out_i;
+  }
   return true;
 }
 
@@ -356,11 +617,17 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
     int64_t t = ve;
     while ((t * 2) * (t * 2) / ve <= kCtaVectors) t *= 2;
     int64_t ti = t, to = t;
-    while (ti > 1 && merged[ii].radix % ti) ti >>= 1;
-    while (to > 1 && merged[oo].radix % to) to >>= 1;
-    // grow the narrower side while the tile still fits
-    while (ti * 2 * to / ve <= kCtaVectors && merged[ii].radix % (ti * 2) == 0 && ti < 4 * t) ti *= 2;
-    while (ti * to * 2 / ve <= kCtaVectors && merged[oo].radix % (to * 2) == 0 && to < 4 * t) to *= 2;
+    const int64_t tma_ti = 128 / eb, tma_to = 8 * ve;
+    if ((eb == 2 || eb == 4 || eb == 8) && merged[ii].radix % tma_ti == 0 && merged[oo].radix % tma_to == 0) {
+      ti = tma_ti;  // the shape the TMA-fed kernel moves
+      to = tma_to;
+    } else {
+      while (ti > 1 && merged[ii].radix % ti) ti >>= 1;
+      while (to > 1 && merged[oo].radix % to) to >>= 1;
+      // grow the narrower side while the tile still fits
+      while (ti * 2 * to / ve <= kCtaVectors && merged[ii].radix % (ti * 2) == 0 && ti < 4 * t) ti *= 2;
+      while (ti * to * 2 / ve <= kCtaVectors && merged[oo].radix % (to * 2) == 0 && to < 4 * t) to *= 2;
+    }
     // outer digits, input-contiguous tile column fastest
     struct Outer { int64_t radix, sa, sb; };
     std::vector<Outer> outer;
@@ -412,6 +679,50 @@ int32_t launch(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaSt
     staged_permute_kernel<EB><<<(unsigned)blocks, kThreads, 0, s>>>(pl.staged_src, pl.staged_dst, pin, pout,
                                                                    pl.size);
   }
+  return cuda_status(cudaGetLastError());
+}
+
+template <int EB>
+int32_t launch_tma(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
+  constexpr int TILE_BYTES = 8 * (16 / EB) * 128;
+  int32_t err = LEGO_OK;
+  EncodeFn enc = encode_fn(&err);
+  if (!enc) return err;
+  TmaParams tp = pl.tma;
+  // Measured on B200 (fp32 4096^2 and 8192^2, column- and row-major tile orders):
+  // three CTAs per SM; a shallow ring (4 tiles) for large problems and 8 tiles below
+  // 32 Ki tiles were the best of a sweep over 2..6 CTAs x 4..16 slots; deeper rings
+  // lose up to 20 %.  A slot must always be drained by the same consumer pair (a
+  // waiter two uses ahead of an mbarrier cannot tell its phase from the one two
+  // back), so the slot count is a multiple of the number of pairs.
+  const int ctas_per_sm = 3;
+  const int stages = tp.n_tiles >= 32768 ? 4 : 8;
+  static_assert(kTmaStages % (kTmaConsumerWarps / 2) == 0, "slots per consumer pair");
+  tp.stages = stages;
+  const size_t SMEM = (size_t)stages * TILE_BYTES + sizeof(TmaCtl) + 1024;
+  CUtensorMap tmap;
+  const CUtensorMapDataType dt = EB == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                               : EB == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT64;
+  err = make_tmap_row_groups(enc, &tmap, dt, in, (uint64_t)tp.pitch, (uint64_t)(pl.size / tp.pitch),
+                             (uint64_t)tp.pitch * EB, 16 / EB, 128 / EB, 8);
+  if (err != LEGO_OK) return err;
+  static bool configured[2] = {false, false};
+  const int wide = tp.p1.wide ? 1 : 0;
+  if (!configured[wide]) {
+    const int max_smem = kTmaStages * TILE_BYTES + (int)sizeof(TmaCtl) + 1024;
+    if (wide) LEGO_CUDA_TRY(cudaFuncSetAttribute(tma_transpose_kernel<EB, true>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    else LEGO_CUDA_TRY(cudaFuncSetAttribute(tma_transpose_kernel<EB, false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    configured[wide] = true;
+  }
+  int64_t grid = (int64_t)ctx->sm_count * ctas_per_sm;
+  if (grid > tp.n_tiles) grid = tp.n_tiles;
+  if (grid < 1) grid = 1;
+  if (wide)
+    tma_transpose_kernel<EB, true><<<(unsigned)grid, kTmaThreads, SMEM, s>>>(tmap, tp, (uint8_t*)out, ctx->status_word);
+  else
+    tma_transpose_kernel<EB, false><<<(unsigned)grid, kTmaThreads, SMEM, s>>>(tmap, tp, (uint8_t*)out, ctx->status_word);
   return cuda_status(cudaGetLastError());
 }
 
@@ -471,6 +782,12 @@ int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_l
         case 4: st = launch_gather<4>(*pl, in, out, ctx, s); break;
         case 8: st = launch_gather<8>(*pl, in, out, ctx, s); break;
         default: st = launch_gather<16>(*pl, in, out, ctx, s); break;
+      }
+    } else if (pl->kind == KIND_TMA) {
+      switch (elem_bytes) {
+        case 2: st = launch_tma<2>(*pl, in, out, ctx, s); break;
+        case 4: st = launch_tma<4>(*pl, in, out, ctx, s); break;
+        default: st = launch_tma<8>(*pl, in, out, ctx, s); break;
       }
     } else {
       switch (elem_bytes) {

@@ -93,6 +93,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int3
       : "memory");
 }
 
+// 3-D tile load into this CTA's shared memory, completion on an mbarrier.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int32_t c0, int32_t c1, int32_t c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+// 1-D bulk copy global -> this CTA's shared memory (16-byte aligned, size % 16 == 0).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// Barrier among a subset of the CTA's warps (id 1..15; `threads` a multiple of 32).
+template <int ID, int THREADS>
+__device__ __forceinline__ void named_barrier() {
+  asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(THREADS) : "memory");
+}
+
 // ---- tcgen05 / TMEM --------------------------------------------------------------------
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

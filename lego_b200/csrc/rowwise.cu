@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 #include "rowwise.cuh"
 
 namespace lego {
@@ -143,6 +144,245 @@ row_kernel(const __grid_constant__ RowParams P) {
   }
 }
 
+
+// ---- bulk-copy pipelined kernel ------------------------------------------------------
+//
+// For rows of 1 Ki .. 8 Ki elements whose bytes are a multiple of 16: a producer
+// warp streams whole rows into a shared-memory ring with 1-D bulk copies
+// (cp.async.bulk, completion on mbarriers) while 256 consumer threads pull a row
+// into registers with 128-bit shared-memory loads, free the slot at once, reduce
+// and write the result with 128-bit streaming stores.  The ring keeps several rows
+// per CTA in flight without spending registers or load instructions on them; the
+// row a slot holds is named by the producer next to the data.  gamma / beta of
+// LayerNorm are staged in shared memory once per CTA.
+
+constexpr int kRing = 8;          // most ring slots a CTA may use
+constexpr int kConsumers = 256;
+constexpr long long kWaitLimit = 2000000000LL;  // SM cycles, about a second
+
+struct RingCtl {
+  uint64_t full[kRing];
+  uint64_t empty[kRing];
+  int64_t row[kRing];
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int OP, typename T, int EPT>
+__global__ void __launch_bounds__(kConsumers + 32)
+row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* status) {
+  constexpr int VEC = Elem<T>::VEC;
+  constexpr int NV = EPT / VEC;
+  extern __shared__ __align__(128) uint8_t ring_smem[];
+  const int cols = P.cols;
+  const uint32_t row_bytes = (uint32_t)cols * sizeof(T);
+  const uint32_t slot_bytes = (row_bytes + 127u) & ~127u;
+  uint8_t* params_smem = ring_smem + (size_t)stages * slot_bytes;  // gamma | beta (LayerNorm)
+  RingCtl* ctl = reinterpret_cast<RingCtl*>(params_smem + (OP == OP_LAYERNORM ? 2 * slot_bytes : 0));
+  __shared__ float slots[2][32];
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  const int tid = threadIdx.x;
+  const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), kConsumers / 32);
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (OP == OP_LAYERNORM) {
+    const uint4* g = reinterpret_cast<const uint4*>(P.gamma);
+    const uint4* b = reinterpret_cast<const uint4*>(P.beta);
+    uint4* sg = reinterpret_cast<uint4*>(params_smem);
+    uint4* sb = reinterpret_cast<uint4*>(params_smem + slot_bytes);
+    for (int i = tid; i < (int)(row_bytes / 16); i += blockDim.x) {
+      sg[i] = __ldg(g + i);
+      sb[i] = __ldg(b + i);
+    }
+  }
+  __syncthreads();
+
+  if (tid >= kConsumers) {
+    // ---------------- producer ----------------
+    if (tid == kConsumers) {
+      const T* __restrict__ x = reinterpret_cast<const T*>(P.x);
+      int64_t issued = 0;
+      for (int64_t n = 0; n < my_rows; ++n) {
+        const int s = (int)(n % stages);
+        const uint32_t use = (uint32_t)(n / stages);
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kWaitLimit)) {
+          *abort_flag = 1;
+          atomicCAS(status, 0u, 0x40000u | (uint32_t)s);
+          break;
+        }
+        const int64_t w = blockIdx.x + n * (int64_t)gridDim.x;
+        const int64_t row = P.has_map ? (int64_t)map_eval(P.map, (uint64_t)w) : w;
+        ctl->row[s] = row;
+        const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+        ptx::mbar_arrive_expect_tx(full, row_bytes);
+        ptx::bulk_load(ptx::smem_u32(ring_smem + (size_t)s * slot_bytes), x + row * cols, row_bytes, full);
+        ++issued;
+      }
+      if (*abort_flag) {
+        // leave no copy of ours in flight
+        uint32_t never = 0;
+        for (int s = 0; s < stages; ++s) {
+          const int64_t uses = issued > s ? (issued - s + stages - 1) / stages : 0;
+          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kWaitLimit);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  T* __restrict__ y = reinterpret_cast<T*>(P.y);
+  const int lane = tid & 31;
+  for (int64_t n = 0; n < my_rows; ++n) {
+    const int s = (int)(n % stages);
+    const uint32_t use = (uint32_t)(n / stages);
+    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kWaitLimit);
+    if (!ok) {
+      *abort_flag = 1;
+      atomicCAS(status, 0u, 0x50000u | (uint32_t)s);
+    }
+    const int64_t row = ok ? ctl->row[s] : 0;
+    const uint4* slot = reinterpret_cast<const uint4*>(ring_smem + (size_t)s * slot_bytes);
+    float v[EPT];
+    const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * kConsumers + tid) * VEC;
+      if (ok && c < cols) {
+        Elem<T>::unpack(slot[k * kConsumers + tid], v + k * VEC);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[k * VEC + e] = fill;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
+
+    if (OP == OP_SOFTMAX) {
+      float m = v[0];
+#pragma unroll
+      for (int k = 1; k < EPT; ++k) m = fmaxf(m, v[k]);
+      m = row_reduce<kConsumers, true, 1>(m, slots[0]);
+      if (*abort_flag) break;  // uniform: every flag write of this row precedes the barrier above
+      const float ms = m * 1.4426950408889634f;
+      float sum = 0.f;
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) {
+        v[k] = fast_exp2(fmaf(v[k], 1.4426950408889634f, -ms));
+        sum += v[k];
+      }
+      sum = row_reduce<kConsumers, false, 1>(sum, slots[1]);
+      const float inv = 1.0f / sum;
+      T* __restrict__ yrow = y + row * cols;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * kConsumers + tid) * VEC;
+        if (c < cols) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[k * VEC + e] *= inv;
+          __stcs(reinterpret_cast<uint4*>(yrow + c), Elem<T>::pack(v + k * VEC));
+        }
+      }
+    } else {
+      float sum = 0.f;
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) sum += v[k];
+      sum = row_reduce<kConsumers, false, 1>(sum, slots[0]);
+      if (*abort_flag) break;
+      const float mean = sum / (float)cols;
+      float q = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const bool in = (k * kConsumers + tid) * VEC < cols;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float d = in ? v[k * VEC + e] - mean : 0.f;
+          v[k * VEC + e] = d;
+          q = fmaf(d, d, q);
+        }
+      }
+      q = row_reduce<kConsumers, false, 1>(q, slots[1]);
+      const float rstd = 1.0f / sqrtf(q / (float)cols + P.eps);
+      if (tid == 0) {
+        P.mean[row] = mean;
+        P.rstd[row] = rstd;
+      }
+      const uint4* sg = reinterpret_cast<const uint4*>(params_smem);
+      const uint4* sb = reinterpret_cast<const uint4*>(params_smem + slot_bytes);
+      T* __restrict__ yrow = y + row * cols;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * kConsumers + tid) * VEC;
+        if (c < cols) {
+          float g[VEC], b[VEC];
+          Elem<T>::unpack(sg[k * kConsumers + tid], g);
+          Elem<T>::unpack(sb[k * kConsumers + tid], b);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[k * VEC + e] = fmaf(v[k * VEC + e] * rstd, g[e], b[e]);
+          __stcs(reinterpret_cast<uint4*>(yrow + c), Elem<T>::pack(v + k * VEC));
+        }
+      }
+    }
+  }
+}
+
+template <int OP, typename T, int EPT>
+int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
+  auto kern = row_ring_kernel<OP, T, EPT>;
+  const size_t row_bytes = (size_t)P.cols * sizeof(T);
+  const size_t slot = (row_bytes + 127) & ~(size_t)127;
+  const size_t fixed = (OP == OP_LAYERNORM ? 2 * slot : 0) + sizeof(RingCtl) + 128;
+  // CTAs per SM by registers / threads, then as many ring slots as shared memory allows
+  static int per_sm_regs = 0;
+  if (!per_sm_regs) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));  // static part: reduction slots
+    LEGO_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_regs, kern, kConsumers + 32, 0));
+    if (per_sm_regs < 1) per_sm_regs = 1;
+  }
+  // Measured on B200 (16384 x 8192 fp16): one CTA turns a row around in about 2500
+  // cycles, so two (softmax) or three (LayerNorm) per SM saturate HBM; more CTAs only
+  // add contention on the special-function pipe and lower the achieved bandwidth.
+  int per_sm = per_sm_regs;
+  const int want = OP == OP_SOFTMAX ? 2 : 3;
+  if (per_sm > want) per_sm = want;
+  int stages = 0;
+  for (; per_sm >= 1; --per_sm) {
+    const size_t budget = (size_t)(228 * 1024) / per_sm - 1024 - 1024;  // per-CTA share minus static and reserved
+    if (budget <= fixed) continue;
+    stages = (int)((budget - fixed) / slot);
+    if (stages > 4) stages = 4;
+    if (stages >= 2) break;
+  }
+  if (per_sm < 1 || stages < 2) return LEGO_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)stages * slot + fixed;
+  if (smem > (size_t)ctx->smem_optin - 1024) return LEGO_ERR_UNSUPPORTED;
+  int64_t grid = (int64_t)ctx->sm_count * per_sm;
+  if (grid > P.rows) grid = P.rows;
+  kern<<<(unsigned)grid, kConsumers + 32, smem, s>>>(P, stages, ctx->status_word);
+  return cuda_status(cudaGetLastError());
+}
+
+template <int OP, typename T>
+int32_t launch_ring_by_cols(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
+  if (P.cols <= kConsumers * 8) return launch_ring<OP, T, 8>(P, ctx, s);
+  if (P.cols <= kConsumers * 16) return launch_ring<OP, T, 16>(P, ctx, s);
+  return launch_ring<OP, T, 32>(P, ctx, s);
+}
+
 template <int OP, typename T, int TPR, int EPT, bool VECTOR>
 int32_t launch_cfg(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   constexpr int BLOCK = TPR < 256 ? 256 : TPR;
@@ -201,6 +441,11 @@ int32_t run_rows(RowParams& P, const lego_layout_t* row_map, void* stream) {
   constexpr int VEC = Elem<T>::VEC;
   bool vec = (P.cols % VEC == 0) && aligned16(P.x) && aligned16(P.y);
   if (OP == OP_LAYERNORM) vec = vec && aligned16(P.gamma) && aligned16(P.beta);
+  // long aligned rows, enough of them to fill the machine: the bulk-copy pipeline
+  if (vec && P.cols > 1024 && P.cols <= kConsumers * 32 && P.rows >= 2 * (int64_t)ctx->sm_count) {
+    const int32_t st = launch_ring_by_cols<OP, T>(P, ctx, s);
+    if (st != LEGO_ERR_UNSUPPORTED) return st;
+  }
   return vec ? launch_vec<OP, T, true>(P, ctx, s) : launch_vec<OP, T, false>(P, ctx, s);
 }
 

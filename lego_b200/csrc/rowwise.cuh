@@ -120,14 +120,17 @@ __device__ __forceinline__ float warp_reduce(float v) {
   return v;
 }
 
-template <int TPR, bool IS_MAX>
+// BAR == 0 synchronises the whole CTA; BAR > 0 uses that named barrier over TPR threads
+// (for kernels whose CTA has extra warps that do not take part).
+template <int TPR, bool IS_MAX, int BAR = 0>
 __device__ __forceinline__ float row_reduce(float v, float* slots) {
   v = warp_reduce<IS_MAX>(v);
   if (TPR == 32) return v;
   constexpr int NW = TPR / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (lane == 0) slots[warp] = v;
-  __syncthreads();
+  if (BAR == 0) __syncthreads();
+  else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(TPR) : "memory");
   if (NW <= 8) {
     float r = slots[0];
 #pragma unroll

@@ -127,7 +127,8 @@ def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None) -> 
 
 def permute_plan(elem_bytes: int, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None):
     """Which kernel ``permute`` would run: ``(kind, tile_in, tile_out)`` with kind
-    0 staged, 1 gather, 2 tiled transpose.  Host-only; needs no GPU."""
+    0 staged, 1 gather, 2 shared-memory tiled transpose, 3 TMA-fed tiled transpose.
+    Host-only; needs no GPU."""
     kind, ti, to = C.c_int32(0), C.c_int64(0), C.c_int64(0)
     _abi.check(_abi.lib().lego_permute_plan(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)),
                                             lower_optional(tile_order), C.byref(kind), C.byref(ti), C.byref(to)),

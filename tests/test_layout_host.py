@@ -140,11 +140,15 @@ def test_permute_plans():
     src = L.OrderBy(L.Row(n, n)).TileBy([128, 128], [32, 32])
     dst = L.OrderBy(L.Col(n, n)).TileBy([128, 128], [32, 32])
     order = L.OrderBy(L.Col(128, 128)).TileBy([128, 128])
-    assert ops.permute_plan(4, src, dst, order) == (2, 32, 32)       # tiles named by the layout
-    kind, ti, to = ops.permute_plan(4, src, dst)
-    assert kind == 2 and ti == 64 and to == 64                         # free choice: 64 x 64 fp32
-    kind, ti, to = ops.permute_plan(2, src, dst)
-    assert kind == 2 and ti * to * 2 <= 16384
+    assert ops.permute_plan(4, src, dst, order) == (3, 32, 32)       # tiles named by the layout, TMA-fed
+    assert ops.permute_plan(4, src, dst) == (3, 32, 32)              # free choice: 128 B x 8 vectors
+    assert ops.permute_plan(2, src, dst) == (3, 64, 64)
+    assert ops.permute_plan(8, src, dst) == (3, 16, 16)
+    kind, ti, to = ops.permute_plan(1, src, dst)
+    assert kind == 2 and ti * to <= 16384                              # bytes: shared-memory tiled kernel
+    small = L.OrderBy(L.Row(48, 80)).TileBy([3, 5], [16, 16])
+    small_t = L.OrderBy(L.Col(48, 80)).TileBy([3, 5], [16, 16])
+    assert ops.permute_plan(4, small, small_t, L.OrderBy(L.Row(3, 5)).TileBy([3, 5])) == (2, 16, 16)
     tm = L.OrderBy(L.Col(128, 128), L.Row(32, 32)).TileBy([128, 128], [32, 32])
     rm = L.OrderBy(L.Row(n, n)).TileBy([128, 128], [32, 32])
     assert ops.permute_plan(4, rm, tm) == (1, 32, 32)                  # common 32-element runs: gather

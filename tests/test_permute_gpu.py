@@ -79,7 +79,7 @@ def test_batched_and_brick_permutations():
     # batched transpose: (b, i, j) -> (b, j, i)
     src = L.OrderBy(L.Row(6, 64, 128)).GroupBy([(6, 64, 128)])
     dst = L.OrderBy(L.RegP([6, 64, 128], [0, 2, 1])).GroupBy([(6, 64, 128)])
-    got = _check(x, src, dst, kind=2)
+    got = _check(x, src, dst, kind=3)
     assert torch.equal(got.reshape(6, 128, 64), x.reshape(6, 64, 128).transpose(1, 2).contiguous())
 
 
