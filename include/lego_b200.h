@@ -199,6 +199,38 @@ int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* 
                               const int64_t* mnk, int32_t G,
                               const lego_layout_t* const* tile_orders, void* stream);
 
+/* Grouped GEMM for callers that must not allocate.  No counterpart in the
+ * reference: its lego_group_gemm_fn allocates freely through torch.
+ *
+ * Who needs it: code that runs where a device allocation is impossible or
+ * unwelcome -- inside a serving loop whose memory is entirely owned by a
+ * framework's caching allocator (a cudaMalloc there can fail or stall every
+ * stream of the device while the driver maps memory), or in a process that has
+ * handed all free memory to other libraries.  lego_grouped_gemm_f16 creates a
+ * per-device workspace with cudaMalloc on its first use; this variant calls no
+ * cudaMalloc / cudaFree and no allocating library routine at all.  Its scratch
+ * (the problem table the persistent CTAs read, and a status word) is a
+ * file-scope __device__ array of LEGO_STATIC_SCRATCH_BYTES that every GPU
+ * loading the library holds until the process exits; the host-side records are
+ * built on the stack.
+ *
+ * Same arguments and results as lego_grouped_gemm_f16, plus dev_status: a
+ * device uint32 owned and zeroed by the caller that receives the code of a
+ * bounded wait that ran out, or NULL to use (and clear) a word inside the
+ * array.  G > LEGO_STATIC_MAX_GROUPS is rejected with LEGO_ERR_SIZE.
+ *
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and the SM count; make that
+ * first call before any stream capture begins.  Every call on a device shares
+ * the one array and overwrites what the previous call left there, so two calls
+ * whose kernels may overlap on the GPU (different streams) race: order them.  */
+#define LEGO_STATIC_MAX_GROUPS     64
+#define LEGO_STATIC_SCRATCH_BYTES  (256 + LEGO_STATIC_MAX_GROUPS * 448)
+int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B, void* const* C,
+                                     const int64_t* mnk, int32_t G,
+                                     const lego_layout_t* const* tile_orders, uint32_t* dev_status,
+                                     void* stream);
+
 /* ---- housekeeping --------------------------------------------------------- */
 
 /* Synchronise `stream` and return (then clear) the current device's status word:

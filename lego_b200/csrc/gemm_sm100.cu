@@ -344,6 +344,43 @@ int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, voi
   return fill_order(order, p->tiles_m, p->tiles_n, &p->order);
 }
 
+// Scratch of lego_grouped_gemm_f16_static: a 256-byte status area followed by the
+// problem table.  Lives in the library's device image: every GPU that loads the
+// library holds these 28.25 KiB until the process exits.
+constexpr int kStaticGroups = 64;
+constexpr size_t kStaticStatusBytes = 256;
+constexpr size_t kStaticScratchBytes = kStaticStatusBytes + (size_t)kStaticGroups * sizeof(Problem);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratch {
+  unsigned char* dev;  // device address of g_static_scratch on this device
+  int sm_count;
+  bool ready;
+};
+constexpr int kMaxDevices = 64;
+StaticScratch g_static[kMaxDevices];
+std::mutex g_static_mu;
+
+// In host code `g_static_scratch` is only a stand-in for the symbol; the address a
+// kernel may use comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+int32_t static_scratch(StaticScratch** out) {
+  int dev = 0;
+  LEGO_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return LEGO_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticScratch& sc = g_static[dev];
+  if (!sc.ready) {
+    void* p = nullptr;
+    LEGO_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    LEGO_CUDA_TRY(cudaDeviceGetAttribute(&sc.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    sc.dev = (unsigned char*)p;
+    sc.ready = true;
+  }
+  *out = &sc;
+  return LEGO_OK;
+}
+
 template <bool GROUPED>
 int32_t configure() {
   static std::once_flag once;
@@ -414,6 +451,45 @@ int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* 
   const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
   gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], (const Problem*)ctx->tmap_table, G,
                                                          (int)total, LEGO_ACT_NONE, ctx->status_word);
+  return cuda_status(cudaGetLastError());
+}
+
+int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B, void* const* C,
+                                     const int64_t* mnk, int32_t G,
+                                     const lego_layout_t* const* tile_orders, uint32_t* dev_status,
+                                     void* stream) {
+  if (!A || !B || !C || !mnk) return LEGO_ERR_NULL;
+  if (G < 0) return LEGO_ERR_RANK;
+  if (G > kStaticGroups) return LEGO_ERR_SIZE;  // the built-in table holds LEGO_STATIC_MAX_GROUPS records
+  if (G == 0) return LEGO_OK;
+  int32_t err = LEGO_OK;
+  StaticScratch* sc = nullptr;
+  err = static_scratch(&sc);
+  if (err != LEGO_OK) return err;
+  EncodeFn enc = encode_fn(&err);
+  if (!enc) return err;
+  Problem table[kStaticGroups];  // host stack: no heap, no device allocation anywhere in this call
+  int64_t total = 0;
+  for (int g = 0; g < G; ++g) {
+    const int32_t st = fill_problem(enc, &table[g], A[g], B[g], C[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2],
+                                    0, 0, tile_orders ? tile_orders[g] : nullptr, (int)total);
+    if (st != LEGO_OK) return st;
+    total += (int64_t)table[g].tiles_m * table[g].tiles_n;
+    if (total > 0x7fffffff) return LEGO_ERR_SIZE;
+  }
+  const int32_t st = configure<true>();
+  if (st != LEGO_OK) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t* status = dev_status;
+  if (!status) {
+    // the array keeps whatever the previous call left: the status word must start at zero
+    status = reinterpret_cast<uint32_t*>(sc->dev);
+    LEGO_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(uint32_t), s));
+  }
+  Problem* dev_table = reinterpret_cast<Problem*>(sc->dev + kStaticStatusBytes);
+  LEGO_CUDA_TRY(cudaMemcpyAsync(dev_table, table, (size_t)G * sizeof(Problem), cudaMemcpyHostToDevice, s));
+  const int grid = (int)(total < sc->sm_count ? total : sc->sm_count);
+  gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], dev_table, G, (int)total, LEGO_ACT_NONE, status);
   return cuda_status(cudaGetLastError());
 }
 
