@@ -69,7 +69,7 @@ __device__ __forceinline__ void fail(uint32_t* status, volatile uint32_t* abort_
   atomicCAS(status, 0u, code);
 }
 
-__device__ __forceinline__ void tile_coords(const Problem& p, int local, int* tm, int* tn) {
+__host__ __device__ __forceinline__ void tile_coords(const Problem& p, int local, int* tm, int* tn) {
   if (p.order.n_terms == 0) {
     *tm = local / p.tiles_n;
     *tn = local % p.tiles_n;
@@ -192,6 +192,12 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
         const int kblocks = (p->k + BK - 1) / BK;
         const uint32_t a_mn = p->a_mn_major != 0, b_mn = p->b_mn_major != 0;
         const uint32_t idesc = ptx::idesc_f16(BM, BN, a_mn, b_mn);
+        // K-major: 16 k values are 32 bytes inside the 128-byte swizzled row.
+        // MN-major: 16 k values are 16 rows of 128 bytes; 64-wide MN blocks follow at SUB_BYTES.
+        const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? SUB_BYTES : 16, 1024);
+        const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? SUB_BYTES : 16, 1024);
+        const uint32_t a_kstep = a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = b_mn ? (2048 >> 4) : (32 >> 4);
+        const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
           fail(status, abort_flag, 0x20000u | 0x100u | acc);
@@ -206,18 +212,13 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t a_base = ptx::smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t b_base = a_base + A_BYTES;
+          // Only the 14-bit start-address field of a descriptor changes from MMA to MMA.
+          const uint32_t a_enc = smem_enc + stage * (STAGE_BYTES >> 4);
+          const uint32_t b_enc = a_enc + (A_BYTES >> 4);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            // K-major: 16 k values are 32 bytes inside the 128-byte swizzled row.
-            // MN-major: 16 k values are 16 rows of 128 bytes; 64-wide MN blocks follow at SUB_BYTES.
-            const uint64_t da = a_mn ? ptx::smem_desc_sw128(a_base + kk * 2048, SUB_BYTES, 1024)
-                                     : ptx::smem_desc_sw128(a_base + kk * 32, 16, 1024);
-            const uint64_t db = b_mn ? ptx::smem_desc_sw128(b_base + kk * 2048, SUB_BYTES, 1024)
-                                     : ptx::smem_desc_sw128(b_base + kk * 32, 16, 1024);
-            ptx::mma_f16_ss(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
-          }
+          for (int kk = 0; kk < BK / 16; ++kk)
+            ptx::mma_f16_ss(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep), db_fixed | (uint64_t)(b_enc + kk * b_kstep),
+                            idesc, (kb | kk) != 0 ? 1u : 0u);
           ptx::mma_commit(ptx::smem_u32(&bars->empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -286,6 +287,222 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
   }
 }
 
+// ---- CTA-pair kernel ---------------------------------------------------------------------
+//
+// Two CTAs on neighbouring SMs (a cluster of two) compute a 256 x 256 block of C with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own 128
+// columns of B, so an SM pulls 32 KiB per 64-deep k-step from L2 instead of 48 KiB
+// and the ring holds 6 stages.  CTA r of pair p works on flat tile id 2p + r; the host
+// only selects this kernel when the tile order puts ids 2p and 2p + 1 on vertically
+// adjacent tiles of the same tile column.  The leader (rank 0) issues the MMAs; TMA
+// loads of both CTAs complete on the leader's "full" barrier, MMA completion is
+// committed to the "empty" / "accumulator full" barriers of both CTAs, and both
+// epilogues report to the leader's "accumulator empty" barrier.  No load is multicast.
+
+constexpr int P_STAGES = 6;
+constexpr int P_BN_HALF = BN / 2;                    // B columns staged per CTA
+constexpr int P_A_BYTES = BM * BK * 2;
+constexpr int P_B_BYTES = P_BN_HALF * BK * 2;
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+
+struct PairBarriers {
+  uint64_t full[P_STAGES];
+  uint64_t empty[P_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int activation, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + P_STAGES * P_STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const int n_pairs_grid = gridDim.x >> 1;
+  const int first_pair = blockIdx.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&bars->tmem_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->tmem_empty[a]), 256);  // 128 epilogue threads of each CTA
+    }
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // the peer's barriers exist before anything arrives on them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int kblocks = (prob.k + BK - 1) / BK;
+  const bool a_mn = prob.a_mn_major != 0, b_mn = prob.b_mn_major != 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued[P_STAGES] = {0, 0, 0, 0, 0, 0};
+      bool ok = true;
+      for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid) {
+        int tm, tn;
+        tile_coords(prob, 2 * pair + (int)rank, &tm, &tn);
+        const int n0 = tn * BN + (int)rank * P_BN_HALF;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
+            fail(status, abort_flag, 0x110000u | stage);
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = ptx::smem_u32(&bars->full[stage]);
+          const uint32_t full_leader = ptx::mapa(full_local, 0);
+          const uint32_t a_dst = ptx::smem_u32(smem + stage * P_STAGE_BYTES);
+          const uint32_t b_dst = a_dst + P_A_BYTES;
+          if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * P_STAGE_BYTES);  // both CTAs' bytes
+          if (a_mn) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_2d_pair(a_dst + j * SUB_BYTES, &prob.tma_a, tm * BM + j * 64, kb * BK, full_leader);
+          } else {
+            ptx::tma_load_2d_pair(a_dst, &prob.tma_a, kb * BK, tm * BM, full_leader);
+          }
+          if (b_mn) {
+#pragma unroll
+            for (int j = 0; j < P_BN_HALF / 64; ++j)
+              ptx::tma_load_2d_pair(b_dst + j * SUB_BYTES, &prob.tma_b, n0 + j * 64, kb * BK, full_leader);
+          } else {
+            ptx::tma_load_2d_pair(b_dst, &prob.tma_b, kb * BK, n0, full_leader);
+          }
+          ++issued[stage];
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag && rank == 0) {
+        // Leave no copy in flight on the barrier we own: wait (bounded) for each stage's last load.
+        uint32_t never = 0;
+#pragma unroll
+        for (int s = 0; s < P_STAGES; ++s)
+          if (issued[s])
+            ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      const uint32_t idesc = ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+      // Only the 14-bit start-address field of a descriptor changes from MMA to MMA.
+      const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? SUB_BYTES : 16, 1024);
+      const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? SUB_BYTES : 16, 1024);
+      const uint32_t a_kstep = a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = b_mn ? (2048 >> 4) : (32 >> 4);
+      const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
+      for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid, ++it) {
+        const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
+          fail(status, abort_flag, 0x120000u | 0x100u | acc);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
+            fail(status, abort_flag, 0x120000u | stage);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a_enc = smem_enc + stage * (P_STAGE_BYTES >> 4);
+          const uint32_t b_enc = a_enc + (P_A_BYTES >> 4);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)
+            ptx::mma_f16_ss_pair(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
+                                 db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (kb | kk) != 0 ? 1u : 0u);
+          ptx::mma_commit_pair(ptx::smem_u32(&bars->empty[stage]), 3);  // frees the slot in both CTAs
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) ptx::mma_commit_pair(ptx::smem_u32(&bars->tmem_full[acc]), 3);
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    const int q = warp & 3;
+    uint32_t it = 0;
+    for (int pair = first_pair; pair < total_pairs; pair += n_pairs_grid, ++it) {
+      int tm, tn;
+      tile_coords(prob, 2 * pair + (int)rank, &tm, &tn);
+      const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
+      bool ok = true;
+      if (lane == 0)
+        ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) fail(status, abort_flag, 0x130000u | acc);
+        break;
+      }
+      ptx::tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const int M = prob.m, N = prob.n;
+      __half* crow = prob.c + (size_t)row * N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        ptx::tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < M && col0 < N) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col0 + j * 8 < N) {
+              uint32_t h[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(r[j * 8 + 2 * e]);
+                float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
+                if (activation == LEGO_ACT_LEAKY_RELU) {
+                  x0 = x0 >= 0.f ? x0 : 0.01f * x0;
+                  x1 = x1 >= 0.f ? x1 : 0.01f * x1;
+                }
+                const __half2 hh = __floats2half2_rn(x0, x1);
+                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+              *reinterpret_cast<uint4*>(crow + col0 + j * 8) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0));
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // neither CTA leaves while the other may still touch its shared memory
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------
 
 // 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows.
@@ -318,7 +535,8 @@ int32_t fill_order(const lego_layout_t* order, int tiles_m, int tiles_n, TileOrd
 }
 
 int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, void* C, int64_t M, int64_t N,
-                     int64_t K, int trans_a, int trans_b, const lego_layout_t* order, int tile_start) {
+                     int64_t K, int trans_a, int trans_b, const lego_layout_t* order, int tile_start,
+                     int b_box_rows = BN) {
   if (!A || !B || !C) return LEGO_ERR_NULL;
   if (M < 1 || N < 1 || K < 1 || M > 0x3fffffff || N > 0x3fffffff || K > 0x3fffffff) return LEGO_ERR_SIZE;
   // 16-byte global strides for TMA and 16-byte C stores
@@ -338,7 +556,7 @@ int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, voi
   if (trans_a) st = make_tmap(enc, &p->tma_a, A, (uint64_t)M, (uint64_t)K, 64, BK);   // [K, M], M contiguous
   else         st = make_tmap(enc, &p->tma_a, A, (uint64_t)K, (uint64_t)M, BK, BM);   // [M, K], K contiguous
   if (st != LEGO_OK) return st;
-  if (trans_b) st = make_tmap(enc, &p->tma_b, B, (uint64_t)K, (uint64_t)N, BK, BN);   // [N, K], K contiguous
+  if (trans_b) st = make_tmap(enc, &p->tma_b, B, (uint64_t)K, (uint64_t)N, BK, b_box_rows);   // [N, K], K contiguous
   else         st = make_tmap(enc, &p->tma_b, B, (uint64_t)N, (uint64_t)K, 64, BK);   // [K, N], N contiguous
   if (st != LEGO_OK) return st;
   return fill_order(order, p->tiles_m, p->tiles_n, &p->order);
@@ -391,6 +609,34 @@ int32_t configure() {
   return cuda_status(result);
 }
 
+// One-time set-up of the CTA-pair kernel: shared-memory limit and how many pairs
+// the device can hold at once.
+int32_t configure_pair(int* max_clusters) {
+  static std::once_flag once;
+  static int32_t result = LEGO_OK;
+  static int clusters = 0;
+  std::call_once(once, [] {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    if (e == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = P_SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel, &cfg);
+    }
+    if (e != cudaSuccess) { (void)cudaGetLastError(); result = cuda_status(e); }
+  });
+  *max_clusters = clusters;
+  return result;
+}
+
 }  // namespace
 }  // namespace lego
 
@@ -410,10 +656,33 @@ int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t 
   Problem p;
   int32_t st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0);
   if (st != LEGO_OK) return st;
-  st = configure<false>();
-  if (st != LEGO_OK) return st;
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
   if (total > 0x7fffffff) return LEGO_ERR_SIZE;
+  // CTA pairs: tile ids 2p and 2p + 1 must share their tile column (they share B).
+  bool pairs = total >= 2 && total % 2 == 0 && total <= (1 << 22);
+  for (int64_t t = 0; pairs && t < total; t += 2) {
+    int m0, n0, m1, n1;
+    tile_coords(p, (int)t, &m0, &n0);
+    tile_coords(p, (int)t + 1, &m1, &n1);
+    pairs = (n0 == n1);
+  }
+  if (pairs) {
+    st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF);
+    if (st != LEGO_OK) return st;
+    int max_clusters = 0;
+    st = configure_pair(&max_clusters);
+    if (st == LEGO_OK && max_clusters >= 1) {
+      const int64_t n_pairs = total / 2;
+      const int clusters = (int)(n_pairs < max_clusters ? n_pairs : max_clusters);
+      gemm_pair_kernel<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, (cudaStream_t)stream>>>(p, (int)n_pairs, activation,
+                                                                                   ctx->status_word);
+      return cuda_status(cudaGetLastError());
+    }
+    st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0);
+    if (st != LEGO_OK) return st;
+  }
+  st = configure<false>();
+  if (st != LEGO_OK) return st;
   const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
   gemm_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(p, nullptr, 1, (int)total, activation,
                                                                          ctx->status_word);
