@@ -53,7 +53,7 @@ class Workload:
 
     def metric(self) -> str:
         kind = "HBM GB/s" if self.unit == "GB/s" else "TFLOP/s"
-        return f"{self.name.split('_f')[0]} {kind}"
+        return f"{getattr(self, 'short', self.name.split('_f')[0])} {kind}"
 
     def setup(self, dev):
         raise NotImplementedError
@@ -275,7 +275,7 @@ class GroupedGemm(Workload):
     unit = "TFLOP/s"
     bound = "tensor"
     description = ("16 independent fp16 GEMMs, M,N drawn from {1024,2048,4096} seed 4, K = 4096, inputs ~ N(0,1/64), "
-                   "fp32 accumulate; persistent CTAs walk (group, tile_m, tile_n); operands larger than L2")
+                   "fp32 accumulate; persistent CTA pairs walk (group, tile_m, tile_n), per-group order OrderBy(Col(M/128, N/256)); operands larger than L2")
 
     def work(self):
         return float(sum(2 * m * n * k for m, n, k in self.sizes))
@@ -288,7 +288,7 @@ class GroupedGemm(Workload):
         self.A_host, self.B_host = inputs.grouped_input()
         self.A = [t.to(dev) for t in self.A_host]
         self.B = [t.to(dev) for t in self.B_host]
-        self.orders = [L.OrderBy(L.Row(m // 128, n // 256)).TileBy([m // 128, n // 256]) for m, n, _ in self.sizes]
+        self.orders = [L.OrderBy(L.Col(m // 128, n // 256)).TileBy([m // 128, n // 256]) for m, n, _ in self.sizes]
 
     def step(self, i):
         self.C = self.ops.lego_group_gemm_fn(self.A, self.B, self.orders)
@@ -325,8 +325,54 @@ class GroupedGemm(Workload):
         return 2.0 * m * nn * k * n, dt, f"{n} x group 4 ({m}x{nn}x{k}) as a.float() @ b.float()"
 
 
+class IndexMap(Workload):
+    graph_ok = True
+    name = "index_map_range_i64_4096x4096"
+    short = "index_map"
+    dtype = "int64"
+    description = ("index-map evaluator: layout.apply over all 2^24 logical ids of OrderBy(Col(4096,4096))"
+                   ".TileBy([128,128],[32,32]) (the transpose's destination layout), int64 results (128 MiB, larger than L2)")
+
+    def work(self):
+        return 8.0 * (1 << 24)
+
+    def setup(self, dev):
+        import lego_b200 as L
+        from lego_b200 import ops
+        self.ops = ops
+        self.layout = L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])
+
+    def step(self, i):
+        self.flat = self.ops.eval_range(self.layout)
+
+    def check(self):
+        from oracle import lego_oracle as O
+        from helpers import spec_of
+        ids = torch.arange(0, 1 << 24, 4099)
+        idx = [v.numpy() for v in torch.unravel_index(ids, self.layout.dims())]
+        ref = O.groupby_apply(spec_of(self.layout), idx)
+        ok = bool((self.flat[ids.to(self.flat.device)].cpu().numpy() == ref).all())
+        return ok, f"bit-exact on {len(ids)} sampled ids vs oracle"
+
+    def e2e_setup(self):
+        return 0, 8 * (1 << 24)
+
+    def e2e_step(self, i):
+        return self.ops.eval_range(self.layout).cpu()
+
+    def cpu_sample(self, threads, budget=4.0):
+        from oracle import lego_oracle as O
+        from helpers import spec_of
+        n = 1 << 22
+        t0 = time.perf_counter()
+        ids = np.arange(n, dtype=np.int64)
+        O.groupby_apply(spec_of(self.layout), O.unflatten_index(ids, list(self.layout.dims())))
+        dt = time.perf_counter() - t0
+        return 8.0 * n, dt, "1 x numpy GroupBy.apply over 2^22 of the 2^24 ids (single thread)"
+
+
 WORKLOADS = {"softmax": Softmax, "layernorm": LayerNorm, "transpose": Transpose, "gemm": Gemm,
-             "grouped_gemm": GroupedGemm}
+             "grouped_gemm": GroupedGemm, "index_map": IndexMap}
 
 
 # --------------------------------------------------------------------------------------

@@ -225,7 +225,7 @@ int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* 
  * the one array and overwrites what the previous call left there, so two calls
  * whose kernels may overlap on the GPU (different streams) race: order them.  */
 #define LEGO_STATIC_MAX_GROUPS     64
-#define LEGO_STATIC_SCRATCH_BYTES  (256 + LEGO_STATIC_MAX_GROUPS * 448)
+#define LEGO_STATIC_SCRATCH_BYTES  (256 + LEGO_STATIC_MAX_GROUPS * 640)
 int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B, void* const* C,
                                      const int64_t* mnk, int32_t G,
                                      const lego_layout_t* const* tile_orders, uint32_t* dev_status,

@@ -28,7 +28,7 @@ DeviceCtx* device_ctx(int32_t* err) {
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   if (e == cudaSuccess) e = cudaMalloc(&c->status_word, 256);
   if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, 256);
-  c->tmap_table_bytes = (size_t)LEGO_MAX_GROUPS * 448;  // one 448-byte problem record per group
+  c->tmap_table_bytes = (size_t)LEGO_MAX_GROUPS * 640;  // one 640-byte problem record per group
   if (e == cudaSuccess) e = cudaMalloc(&c->tmap_table, c->tmap_table_bytes);
   if (e != cudaSuccess) {
     if (err) *err = cuda_status(e);

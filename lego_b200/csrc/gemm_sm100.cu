@@ -34,16 +34,21 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SUB_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major operand
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_STAGE_TOTAL = 4 * 2 * 32 * 64 * 2;  // epilogue staging, see EPI_BYTES
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_TOTAL + 1024 + 256;
 constexpr long long WAIT_LIMIT = 2000000000LL;  // SM cycles, about a second
 
 constexpr int kMaxOrderTerms = 8;
 struct TileTerm { uint32_t a, m, b, dst; };  // coord[dst] += ((t / a) % m) * b; m == 0: no wrap
 struct TileOrder { int32_t n_terms; int32_t reserved; TileTerm t[kMaxOrderTerms]; };
 
-struct alignas(64) Problem {
+// Tensor maps that TMA reads from global memory must sit on 128-byte boundaries: with a
+// 64-byte aligned record the maps of every second problem were fetched from the wrong
+// line (results depended on the neighbouring record).  Hence the alignment and size.
+struct alignas(128) Problem {
   CUtensorMap tma_a;
   CUtensorMap tma_b;
+  CUtensorMap tma_c;    // C as [M rows][N contiguous], box 64 columns x 32 rows
   __half* c;
   int32_t m, n, k;
   int32_t tiles_m, tiles_n;
@@ -53,7 +58,7 @@ struct alignas(64) Problem {
   int32_t reserved;
   TileOrder order;
 };
-static_assert(sizeof(Problem) == 448, "Problem must stay 448 bytes: the device table is sized for it");
+static_assert(sizeof(Problem) == 640, "Problem must stay 640 bytes: the device tables are sized for it");
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -87,6 +92,67 @@ __host__ __device__ __forceinline__ void tile_coords(const Problem& p, int local
   *tn = (int)c1;
 }
 
+// Epilogue staging: each of the four epilogue warps owns two 4 KiB buffers (32 rows x
+// 128 bytes, 128-byte swizzle) and writes C with TMA stores, 64 columns at a time.
+constexpr int EPI_CHUNK_COLS = 64;
+constexpr int EPI_BUF_BYTES = 32 * EPI_CHUNK_COLS * 2;   // 4 KiB
+constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;          // 32 KiB per CTA
+static_assert(EPI_BYTES == EPI_STAGE_TOTAL, "staging size");
+
+// One accumulator tile (this warp's 32 rows x 256 columns) -> activation -> fp16 ->
+// swizzled shared memory -> TMA store.  Thread `lane` holds row q * 32 + lane; its eight
+// 16-byte pieces of a 64-column chunk go to positions j ^ (lane & 7) of its row, so a
+// quarter-warp writes eight distinct bank groups.  Full 128-byte lines reach L2, where the
+// direct per-thread stores this replaces wrote 16-byte pieces of 32 different rows per
+// instruction and cost about 40 us per 8192 x 8192 output.  `chunk_no` counts the chunks
+// this warp has stored so far (selects the buffer; lane 0 keeps at most one store pending
+// before a buffer is rewritten).
+__device__ __forceinline__ void epilogue_store_tile(const Problem* p, int tm, int tn, int q, int lane,
+                                                    uint32_t tmem_tile, uint8_t* warp_stage, int activation,
+                                                    uint32_t* chunk_no, bool map_in_global) {
+  const int row0 = tm * BM + q * 32;
+  if (row0 >= p->m) return;  // nothing of this warp's rows exists (warp-uniform)
+  if (map_in_global && lane == 0) ptx::tensormap_acquire(&p->tma_c);
+#pragma unroll 1
+  for (int c = 0; c < BN / EPI_CHUNK_COLS; ++c) {
+    // Chunks past the last column are not staged at all: every staged chunk commits
+    // exactly one bulk group, which is what the "at most one pending" wait below counts.
+    const int col0 = tn * BN + c * EPI_CHUNK_COLS;
+    if (col0 >= p->n) break;
+    uint32_t r[64];
+    ptx::tmem_ld_32x32(tmem_tile + c * EPI_CHUNK_COLS, r);
+    ptx::tmem_ld_32x32(tmem_tile + c * EPI_CHUNK_COLS + 32, r + 32);
+    uint8_t* buf = warp_stage + ((*chunk_no) & 1u) * EPI_BUF_BYTES;
+    if (lane == 0) ptx::bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+    __syncwarp();
+    ptx::tmem_ld_wait();
+    uint4* dst = reinterpret_cast<uint4*>(buf + lane * 128);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t h[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float x0 = __uint_as_float(r[j * 8 + 2 * e]);
+        float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
+        if (activation == LEGO_ACT_LEAKY_RELU) {
+          x0 = x0 >= 0.f ? x0 : 0.01f * x0;
+          x1 = x1 >= 0.f ? x1 : 0.01f * x1;
+        }
+        const __half2 hh = __floats2half2_rn(x0, x1);
+        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+      }
+      dst[j ^ (lane & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+    ptx::fence_proxy_async();  // generic-proxy writes above -> visible to the TMA engine
+    __syncwarp();
+    if (lane == 0) {
+      ptx::tma_store_2d(&p->tma_c, col0, row0, ptx::smem_u32(buf));
+      ptx::bulk_commit_group();
+    }
+    ++(*chunk_no);
+  }
+}
+
 template <bool GROUPED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ table, int n_problems,
@@ -94,7 +160,8 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(epi_stage + EPI_BYTES);
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -139,6 +206,10 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const Problem* p = problem_of(tile, &cursor);
+        if (GROUPED) {
+          ptx::tensormap_acquire(&p->tma_a);
+          ptx::tensormap_acquire(&p->tma_b);
+        }
         int tm, tn;
         tile_coords(*p, tile - p->tile_start, &tm, &tn);
         const int kblocks = (p->k + BK - 1) / BK;
@@ -228,6 +299,7 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
   } else {
     // ---------------- epilogue ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t chunk_no = 0;
     int cursor = 0;
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
@@ -244,39 +316,12 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
         break;
       }
       ptx::tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
-      const int M = p->m, N = p->n;
-      __half* crow = p->c + (size_t)row * N;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-        ptx::tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
-        if (row < M && col0 < N) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (col0 + j * 8 < N) {
-              uint32_t h[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float x0 = __uint_as_float(r[j * 8 + 2 * e]);
-                float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
-                if (activation == LEGO_ACT_LEAKY_RELU) {
-                  x0 = x0 >= 0.f ? x0 : 0.01f * x0;
-                  x1 = x1 >= 0.f ? x1 : 0.01f * x1;
-                }
-                const __half2 hh = __floats2half2_rn(x0, x1);
-                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-              }
-              *reinterpret_cast<uint4*>(crow + col0 + j * 8) = make_uint4(h[0], h[1], h[2], h[3]);
-            }
-          }
-        }
-      }
+      epilogue_store_tile(p, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
+                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED);
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&bars->tmem_empty[acc]));
     }
+    if (lane == 0) ptx::bulk_wait_group_read<0>();  // staging must outlive the stores that read it
   }
 
   ptx::tc_fence_before();
@@ -292,19 +337,19 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
 // Two CTAs on neighbouring SMs (a cluster of two) compute a 256 x 256 block of C with
 // tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own 128
 // columns of B, so an SM pulls 32 KiB per 64-deep k-step from L2 instead of 48 KiB
-// and the ring holds 6 stages.  CTA r of pair p works on flat tile id 2p + r; the host
+// and the ring holds 5 stages next to the epilogue staging.  CTA r of pair p works on flat tile id 2p + r; the host
 // only selects this kernel when the tile order puts ids 2p and 2p + 1 on vertically
 // adjacent tiles of the same tile column.  The leader (rank 0) issues the MMAs; TMA
 // loads of both CTAs complete on the leader's "full" barrier, MMA completion is
 // committed to the "empty" / "accumulator full" barriers of both CTAs, and both
 // epilogues report to the leader's "accumulator empty" barrier.  No load is multicast.
 
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = 5;
 constexpr int P_BN_HALF = BN / 2;                    // B columns staged per CTA
 constexpr int P_A_BYTES = BM * BK * 2;
 constexpr int P_B_BYTES = P_BN_HALF * BK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + EPI_STAGE_TOTAL + 1024 + 256;
 
 struct PairBarriers {
   uint64_t full[P_STAGES];
@@ -315,12 +360,15 @@ struct PairBarriers {
   uint32_t abort_flag;
 };
 
+template <bool GROUPED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int activation, uint32_t* status) {
+gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict__ table, int n_problems,
+                 int total_pairs, int activation, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint8_t* epi_stage = smem + P_STAGES * P_STAGE_BYTES;
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(epi_stage + EPI_BYTES);
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -352,18 +400,32 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int acti
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  const int kblocks = (prob.k + BK - 1) / BK;
-  const bool a_mn = prob.a_mn_major != 0, b_mn = prob.b_mn_major != 0;
+  // problem owning flat tile id `tile` (ids of one pair always belong to one problem)
+  auto problem_of = [&](int tile, int* cursor) -> const Problem* {
+    if (!GROUPED) return &prob;
+    int g = *cursor;
+    while (g + 1 < n_problems && tile >= table[g + 1].tile_start) ++g;
+    *cursor = g;
+    return &table[g];
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      uint32_t issued[P_STAGES] = {0, 0, 0, 0, 0, 0};
+      uint32_t issued[P_STAGES] = {0, 0, 0, 0, 0};
       bool ok = true;
+      int cursor = 0;
       for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid) {
+        const Problem* pr = problem_of(2 * pair, &cursor);
+        if (GROUPED) {
+          ptx::tensormap_acquire(&pr->tma_a);
+          ptx::tensormap_acquire(&pr->tma_b);
+        }
+        const int kblocks = (pr->k + BK - 1) / BK;
+        const bool a_mn = pr->a_mn_major != 0, b_mn = pr->b_mn_major != 0;
         int tm, tn;
-        tile_coords(prob, 2 * pair + (int)rank, &tm, &tn);
+        tile_coords(*pr, 2 * pair + (int)rank - pr->tile_start, &tm, &tn);
         const int n0 = tn * BN + (int)rank * P_BN_HALF;
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
@@ -379,16 +441,16 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int acti
           if (a_mn) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              ptx::tma_load_2d_pair(a_dst + j * SUB_BYTES, &prob.tma_a, tm * BM + j * 64, kb * BK, full_leader);
+              ptx::tma_load_2d_pair(a_dst + j * SUB_BYTES, &pr->tma_a, tm * BM + j * 64, kb * BK, full_leader);
           } else {
-            ptx::tma_load_2d_pair(a_dst, &prob.tma_a, kb * BK, tm * BM, full_leader);
+            ptx::tma_load_2d_pair(a_dst, &pr->tma_a, kb * BK, tm * BM, full_leader);
           }
           if (b_mn) {
 #pragma unroll
             for (int j = 0; j < P_BN_HALF / 64; ++j)
-              ptx::tma_load_2d_pair(b_dst + j * SUB_BYTES, &prob.tma_b, n0 + j * 64, kb * BK, full_leader);
+              ptx::tma_load_2d_pair(b_dst + j * SUB_BYTES, &pr->tma_b, n0 + j * 64, kb * BK, full_leader);
           } else {
-            ptx::tma_load_2d_pair(b_dst, &prob.tma_b, kb * BK, n0, full_leader);
+            ptx::tma_load_2d_pair(b_dst, &pr->tma_b, kb * BK, n0, full_leader);
           }
           ++issued[stage];
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
@@ -409,13 +471,17 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int acti
       uint32_t stage = 0, phase = 0;
       uint32_t it = 0;
       bool ok = true;
-      const uint32_t idesc = ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
-      // Only the 14-bit start-address field of a descriptor changes from MMA to MMA.
-      const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? SUB_BYTES : 16, 1024);
-      const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? SUB_BYTES : 16, 1024);
-      const uint32_t a_kstep = a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = b_mn ? (2048 >> 4) : (32 >> 4);
+      int cursor = 0;
       const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
       for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid, ++it) {
+        const Problem* pr = problem_of(2 * pair, &cursor);
+        const int kblocks = (pr->k + BK - 1) / BK;
+        const bool a_mn = pr->a_mn_major != 0, b_mn = pr->b_mn_major != 0;
+        const uint32_t idesc = ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+        // Only the 14-bit start-address field of a descriptor changes from MMA to MMA.
+        const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? SUB_BYTES : 16, 1024);
+        const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? SUB_BYTES : 16, 1024);
+        const uint32_t a_kstep = a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = b_mn ? (2048 >> 4) : (32 >> 4);
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
           fail(status, abort_flag, 0x120000u | 0x100u | acc);
@@ -445,10 +511,13 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int acti
   } else {
     // ---------------- epilogue (both CTAs, own 128 rows) ----------------
     const int q = warp & 3;
+    uint32_t chunk_no = 0;
     uint32_t it = 0;
+    int cursor = 0;
     for (int pair = first_pair; pair < total_pairs; pair += n_pairs_grid, ++it) {
+      const Problem* pr = problem_of(2 * pair, &cursor);
       int tm, tn;
-      tile_coords(prob, 2 * pair + (int)rank, &tm, &tn);
+      tile_coords(*pr, 2 * pair + (int)rank - pr->tile_start, &tm, &tn);
       const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
       bool ok = true;
       if (lane == 0)
@@ -459,39 +528,12 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, int total_pairs, int acti
         break;
       }
       ptx::tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
-      const int M = prob.m, N = prob.n;
-      __half* crow = prob.c + (size_t)row * N;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-        ptx::tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
-        if (row < M && col0 < N) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (col0 + j * 8 < N) {
-              uint32_t h[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float x0 = __uint_as_float(r[j * 8 + 2 * e]);
-                float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
-                if (activation == LEGO_ACT_LEAKY_RELU) {
-                  x0 = x0 >= 0.f ? x0 : 0.01f * x0;
-                  x1 = x1 >= 0.f ? x1 : 0.01f * x1;
-                }
-                const __half2 hh = __floats2half2_rn(x0, x1);
-                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-              }
-              *reinterpret_cast<uint4*>(crow + col0 + j * 8) = make_uint4(h[0], h[1], h[2], h[3]);
-            }
-          }
-        }
-      }
+      epilogue_store_tile(pr, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
+                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED);
       ptx::tc_fence_before();
       ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0));
     }
+    if (lane == 0) ptx::bulk_wait_group_read<0>();  // staging must outlive the stores that read it
   }
 
   ptx::tc_fence_before();
@@ -559,12 +601,14 @@ int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, voi
   if (trans_b) st = make_tmap(enc, &p->tma_b, B, (uint64_t)K, (uint64_t)N, BK, b_box_rows);   // [N, K], K contiguous
   else         st = make_tmap(enc, &p->tma_b, B, (uint64_t)N, (uint64_t)K, 64, BK);   // [K, N], N contiguous
   if (st != LEGO_OK) return st;
+  st = make_tmap(enc, &p->tma_c, C, (uint64_t)N, (uint64_t)M, EPI_CHUNK_COLS, 32);      // [M, N], N contiguous
+  if (st != LEGO_OK) return st;
   return fill_order(order, p->tiles_m, p->tiles_n, &p->order);
 }
 
 // Scratch of lego_grouped_gemm_f16_static: a 256-byte status area followed by the
 // problem table.  Lives in the library's device image: every GPU that loads the
-// library holds these 28.25 KiB until the process exits.
+// library holds these 40.25 KiB until the process exits.
 constexpr int kStaticGroups = 64;
 constexpr size_t kStaticStatusBytes = 256;
 constexpr size_t kStaticScratchBytes = kStaticStatusBytes + (size_t)kStaticGroups * sizeof(Problem);
@@ -611,12 +655,13 @@ int32_t configure() {
 
 // One-time set-up of the CTA-pair kernel: shared-memory limit and how many pairs
 // the device can hold at once.
+template <bool GROUPED>
 int32_t configure_pair(int* max_clusters) {
   static std::once_flag once;
   static int32_t result = LEGO_OK;
   static int clusters = 0;
   std::call_once(once, [] {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
     if (e == cudaSuccess) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2, 1, 1);
@@ -629,12 +674,67 @@ int32_t configure_pair(int* max_clusters) {
       attr.val.clusterDim.z = 1;
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
-      e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel, &cfg);
+      e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<GROUPED>, &cfg);
     }
     if (e != cudaSuccess) { (void)cudaGetLastError(); result = cuda_status(e); }
   });
   *max_clusters = clusters;
   return result;
+}
+
+// Do tile ids 2p and 2p + 1 of this problem share a tile column (they would share B)?
+bool pairs_share_columns(const Problem& p) {
+  const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
+  if (total % 2 || total > (1 << 22)) return false;
+  for (int64_t t = 0; t < total; t += 2) {
+    int m0, n0, m1, n1;
+    tile_coords(p, (int)t, &m0, &n0);
+    tile_coords(p, (int)t + 1, &m1, &n1);
+    if (n0 != n1) return false;
+  }
+  return true;
+}
+
+// Build the problem records of a grouped GEMM into `table` (host), copy them to
+// `dev_table` and launch on `s`.  A group without a tile order gets column-major
+// tiles when it has an even number of tile rows (so that CTA pairs apply), row-major
+// otherwise.  Allocates nothing.
+int32_t run_grouped(EncodeFn enc, Problem* table, const void* const* A, const void* const* B, void* const* C,
+                    const int64_t* mnk, int32_t G, const lego_layout_t* const* tile_orders, Problem* dev_table,
+                    uint32_t* status, int sm_count, cudaStream_t s) {
+  int64_t total = 0;
+  bool pairs = true;
+  for (int g = 0; g < G; ++g) {
+    const lego_layout_t* order = tile_orders ? tile_orders[g] : nullptr;
+    const int32_t st = fill_problem(enc, &table[g], A[g], B[g], C[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2],
+                                    0, 0, order, (int)total);
+    if (st != LEGO_OK) return st;
+    Problem& p = table[g];
+    if (!order && p.tiles_m % 2 == 0) {
+      p.order.n_terms = 2;  // tile_m = t % tiles_m, tile_n = t / tiles_m
+      p.order.t[0] = TileTerm{1u, (uint32_t)p.tiles_m, 1u, 0u};
+      p.order.t[1] = TileTerm{(uint32_t)p.tiles_m, 0u, 1u, 1u};
+    }
+    pairs = pairs && pairs_share_columns(p);
+    total += (int64_t)p.tiles_m * p.tiles_n;
+    if (total > 0x7fffffff) return LEGO_ERR_SIZE;
+  }
+  LEGO_CUDA_TRY(cudaMemcpyAsync(dev_table, table, (size_t)G * sizeof(Problem), cudaMemcpyHostToDevice, s));
+  if (pairs) {
+    int max_clusters = 0;
+    if (configure_pair<true>(&max_clusters) == LEGO_OK && max_clusters >= 1) {
+      const int64_t n_pairs = total / 2;
+      const int clusters = (int)(n_pairs < max_clusters ? n_pairs : max_clusters);
+      gemm_pair_kernel<true><<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, s>>>(table[0], dev_table, G, (int)n_pairs,
+                                                                            LEGO_ACT_NONE, status);
+      return cuda_status(cudaGetLastError());
+    }
+  }
+  const int32_t st = configure<true>();
+  if (st != LEGO_OK) return st;
+  const int grid = (int)(total < sm_count ? total : sm_count);
+  gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], dev_table, G, (int)total, LEGO_ACT_NONE, status);
+  return cuda_status(cudaGetLastError());
 }
 
 }  // namespace
@@ -670,11 +770,11 @@ int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t 
     st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF);
     if (st != LEGO_OK) return st;
     int max_clusters = 0;
-    st = configure_pair(&max_clusters);
+    st = configure_pair<false>(&max_clusters);
     if (st == LEGO_OK && max_clusters >= 1) {
       const int64_t n_pairs = total / 2;
       const int clusters = (int)(n_pairs < max_clusters ? n_pairs : max_clusters);
-      gemm_pair_kernel<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, (cudaStream_t)stream>>>(p, (int)n_pairs, activation,
+      gemm_pair_kernel<false><<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, (cudaStream_t)stream>>>(p, nullptr, 1, (int)n_pairs, activation,
                                                                                    ctx->status_word);
       return cuda_status(cudaGetLastError());
     }
@@ -702,25 +802,10 @@ int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* 
   if (!enc) return err;
   if ((size_t)G * sizeof(Problem) > ctx->tmap_table_bytes) return LEGO_ERR_RANK;
   std::vector<Problem> table(G);
-  int64_t total = 0;
-  for (int g = 0; g < G; ++g) {
-    const int32_t st = fill_problem(enc, &table[g], A[g], B[g], C[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2],
-                                    0, 0, tile_orders ? tile_orders[g] : nullptr, (int)total);
-    if (st != LEGO_OK) return st;
-    total += (int64_t)table[g].tiles_m * table[g].tiles_n;
-    if (total > 0x7fffffff) return LEGO_ERR_SIZE;
-  }
-  int32_t st = configure<true>();
-  if (st != LEGO_OK) return st;
-  cudaStream_t s = (cudaStream_t)stream;
-  // The table is per device and reused by every call: calls on one stream are
+  // The device table is per device and reused by every call: calls on one stream are
   // ordered; callers overlapping grouped GEMMs on different streams must serialise.
-  LEGO_CUDA_TRY(cudaMemcpyAsync(ctx->tmap_table, table.data(), (size_t)G * sizeof(Problem),
-                                cudaMemcpyHostToDevice, s));
-  const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-  gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], (const Problem*)ctx->tmap_table, G,
-                                                         (int)total, LEGO_ACT_NONE, ctx->status_word);
-  return cuda_status(cudaGetLastError());
+  return run_grouped(enc, table.data(), A, B, C, mnk, G, tile_orders, (Problem*)ctx->tmap_table, ctx->status_word,
+                     ctx->sm_count, (cudaStream_t)stream);
 }
 
 int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B, void* const* C,
@@ -738,16 +823,6 @@ int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B,
   EncodeFn enc = encode_fn(&err);
   if (!enc) return err;
   Problem table[kStaticGroups];  // host stack: no heap, no device allocation anywhere in this call
-  int64_t total = 0;
-  for (int g = 0; g < G; ++g) {
-    const int32_t st = fill_problem(enc, &table[g], A[g], B[g], C[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2],
-                                    0, 0, tile_orders ? tile_orders[g] : nullptr, (int)total);
-    if (st != LEGO_OK) return st;
-    total += (int64_t)table[g].tiles_m * table[g].tiles_n;
-    if (total > 0x7fffffff) return LEGO_ERR_SIZE;
-  }
-  const int32_t st = configure<true>();
-  if (st != LEGO_OK) return st;
   cudaStream_t s = (cudaStream_t)stream;
   uint32_t* status = dev_status;
   if (!status) {
@@ -756,10 +831,7 @@ int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B,
     LEGO_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(uint32_t), s));
   }
   Problem* dev_table = reinterpret_cast<Problem*>(sc->dev + kStaticStatusBytes);
-  LEGO_CUDA_TRY(cudaMemcpyAsync(dev_table, table, (size_t)G * sizeof(Problem), cudaMemcpyHostToDevice, s));
-  const int grid = (int)(total < sc->sm_count ? total : sc->sm_count);
-  gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], dev_table, G, (int)total, LEGO_ACT_NONE, status);
-  return cuda_status(cudaGetLastError());
+  return run_grouped(enc, table, A, B, C, mnk, G, tile_orders, dev_table, status, sc->sm_count, s);
 }
 
 }  // extern "C"

@@ -79,6 +79,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 // ---- TMA -----------------------------------------------------------------------------
 
+// A tensor map that lives in global memory and was (re)written before the launch --
+// e.g. a table refreshed by cudaMemcpyAsync for every call -- must be acquired by the
+// thread that is about to use it: descriptor fetches go through their own proxy and may
+// otherwise see what the same address held for an earlier launch.
+__device__ __forceinline__ void tensormap_acquire(const void* tmap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(tmap) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -101,6 +109,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int3
       " [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
+}
+
+// 2-D tile store shared -> global (bulk async group); boxes reaching past the tensor's
+// extents are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t c0, int32_t c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(tmap), "r"(c0), "r"(c1), "r"(src)
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Wait until at most N of this thread's bulk groups still have to read their source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
 // 1-D bulk copy global -> this CTA's shared memory (16-byte aligned, size % 16 == 0).

@@ -113,3 +113,26 @@ def test_grouped_reference_sizes_and_config5():
         rhs = a.double() @ (b.double() @ v)
         assert (((c.double() @ v) - rhs).norm() / rhs.norm()).item() <= REL_FRO
     assert ops.lego_group_gemm_fn([], []) == []
+
+
+def test_narrow_outputs_next_to_wide_ones():
+    """Problems narrower than one 256-column tile stage fewer epilogue chunks than they
+    skip; mixed with wide problems in one launch they once had their staging buffers
+    overwritten before the pending TMA store had read them."""
+    g = torch.Generator().manual_seed(31)
+    for shapes in ([(128, 256, 64), (128, 64, 64)], [(1, 8, 8)] * 3, [(128, 128, 64)] * 2,
+                   [(640, 512, 1024), (1, 8, 8)], [(128, 256, 64), (1, 8, 8), (128, 256, 64)],
+                   [(384, 512, 64), (128, 8, 8), (256, 192, 128)]):
+        A = [(torch.randn(m, k, generator=g) / 16).half() for m, n, k in shapes]
+        B = [(torch.randn(k, n, generator=g) / 16).half() for m, n, k in shapes]
+        for _ in range(3):
+            out = ops.lego_group_gemm_fn([t.cuda() for t in A], [t.cuda() for t in B])
+            ops.device_status()
+            for c, r in zip(out, O.grouped_matmul(A, B)):
+                assert rel_fro(c.cpu(), r) <= REL_FRO, shapes
+    for m, n, k in [(256, 128, 64), (512, 64, 128), (128, 192, 320), (1024, 8, 8)]:
+        a = (torch.randn(m, k, generator=g) / 16).half()
+        b = (torch.randn(k, n, generator=g) / 16).half()
+        for _ in range(3):
+            assert rel_fro(ops.matmul(a.cuda(), b.cuda()).cpu(), O.matmul(a, b)) <= REL_FRO, (m, n, k)
+    ops.device_status()
