@@ -60,6 +60,54 @@ digit_eval_kernel(const __grid_constant__ DigitProgram p, const int64_t* __restr
   }
 }
 
+// Range evaluation for the common case (32-bit index space, at most kFastTerms digits):
+// the terms live in registers, every thread produces two consecutive ids and writes them
+// as one 16-byte store, so the kernel is bound by the int64 output stream, not by
+// fetching term fields from the parameter bank for every index.
+constexpr int kFastTerms = 6;
+
+__global__ void __launch_bounds__(256)
+digit_range_fast_kernel(const __grid_constant__ DigitProgram p, int64_t* __restrict__ out, int64_t begin, int64_t n) {
+  uint32_t a_mul[kFastTerms], a_shr[kFastTerms], m_mul[kFastTerms], m_shr[kFastTerms], m_d[kFastTerms], b[kFastTerms];
+#pragma unroll
+  for (int j = 0; j < kFastTerms; ++j) {
+    const bool on = j < p.n_terms;
+    a_mul[j] = on ? p.t[j].a.mul : 0u;
+    a_shr[j] = on ? p.t[j].a.shr : 0u;
+    m_mul[j] = on ? p.t[j].m.mul : 0u;
+    m_shr[j] = on ? p.t[j].m.shr : 0u;
+    m_d[j] = on ? p.t[j].m.d : 0u;
+    b[j] = on ? (uint32_t)p.t[j].b : 0u;   // a disabled term multiplies by zero
+  }
+  auto eval = [&](uint32_t x) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int j = 0; j < kFastTerms; ++j) {
+      uint32_t q = a_mul[j] ? (__umulhi(x, a_mul[j]) >> a_shr[j]) : (x >> a_shr[j]);
+      if (m_d[j]) {
+        const uint32_t w = m_mul[j] ? (__umulhi(q, m_mul[j]) >> m_shr[j]) : (q >> m_shr[j]);
+        q -= w * m_d[j];
+      }
+      acc += q * b[j];
+    }
+    return (int64_t)acc;
+  };
+  const int64_t pairs = n >> 1;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += step) {
+    const uint32_t x = (uint32_t)(begin + 2 * i);
+    const int64_t v0 = eval(x), v1 = eval(x + 1);
+    if (aligned) {
+      *reinterpret_cast<longlong2*>(out + 2 * i) = make_longlong2(v0, v1);
+    } else {
+      out[2 * i] = v0;
+      out[2 * i + 1] = v1;
+    }
+  }
+  if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) out[n - 1] = eval((uint32_t)(begin + n - 1));
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(256)
 staged_eval_kernel(const __grid_constant__ StagedProgram sp, const int64_t* __restrict__ in,
@@ -112,7 +160,9 @@ static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t*
     if (MODE == MODE_RANGE) program_range(dg, size, &p);
     if (MODE == MODE_APPLY) program_apply(dg, layout->rank, size, &p);
     if (MODE == MODE_INV) program_inv(dg, layout->rank, size, &p);
-    if (p.wide)
+    if (MODE == MODE_RANGE && !p.wide && p.n_terms <= kFastTerms)
+      digit_range_fast_kernel<<<blocks, threads, 0, s>>>(p, out, begin, n);
+    else if (p.wide)
       digit_eval_kernel<true, MODE><<<blocks, threads, 0, s>>>(p, in, out, begin, n);
     else
       digit_eval_kernel<false, MODE><<<blocks, threads, 0, s>>>(p, in, out, begin, n);
