@@ -109,10 +109,13 @@ static_assert(EPI_BYTES == EPI_STAGE_TOTAL, "staging size");
 // before a buffer is rewritten).
 __device__ __forceinline__ void epilogue_store_tile(const Problem* p, int tm, int tn, int q, int lane,
                                                     uint32_t tmem_tile, uint8_t* warp_stage, int activation,
-                                                    uint32_t* chunk_no, bool map_in_global) {
+                                                    uint32_t* chunk_no, const Problem** fenced) {
   const int row0 = tm * BM + q * 32;
   if (row0 >= p->m) return;  // nothing of this warp's rows exists (warp-uniform)
-  if (map_in_global && lane == 0) ptx::tensormap_acquire(&p->tma_c);
+  if (fenced && *fenced != p) {  // table-resident map: acquire once per problem
+    if (lane == 0) ptx::tensormap_acquire(&p->tma_c);
+    *fenced = p;
+  }
 #pragma unroll 1
   for (int c = 0; c < BN / EPI_CHUNK_COLS; ++c) {
     // Chunks past the last column are not staged at all: every staged chunk commits
@@ -203,12 +206,14 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
       uint32_t stage = 0, phase = 0;
       uint32_t issued[STAGES] = {0, 0, 0, 0};
       int cursor = 0;
+      const Problem* fenced = nullptr;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const Problem* p = problem_of(tile, &cursor);
-        if (GROUPED) {
+        if (GROUPED && p != fenced) {  // once per problem this CTA meets, not per tile
           ptx::tensormap_acquire(&p->tma_a);
           ptx::tensormap_acquire(&p->tma_b);
+          fenced = p;
         }
         int tm, tn;
         tile_coords(*p, tile - p->tile_start, &tm, &tn);
@@ -300,6 +305,7 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
     // ---------------- epilogue ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t chunk_no = 0;
+    const Problem* epi_fenced = nullptr;
     int cursor = 0;
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
@@ -317,7 +323,7 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
       }
       ptx::tc_fence_after();
       epilogue_store_tile(p, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
-                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED);
+                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED ? &epi_fenced : nullptr);
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&bars->tmem_empty[acc]));
     }
@@ -413,49 +419,70 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      uint32_t issued[P_STAGES] = {0, 0, 0, 0, 0};
+      uint32_t issued[P_STAGES] = {};
       bool ok = true;
-      int cursor = 0;
-      for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid) {
-        const Problem* pr = problem_of(2 * pair, &cursor);
-        if (GROUPED) {
+      const Problem* fenced = nullptr;
+      // One k-step of this CTA's share of the pair's tile: the boxes of A and B to fetch.
+      struct Step {
+        int pair, kb, kblocks, cursor, tm, n0;
+        const Problem* pr;
+      };
+      auto enter = [&](Step& st) {  // position `st` on the first k-step of st.pair
+        if (st.pair >= total_pairs) return;
+        st.pr = problem_of(2 * st.pair, &st.cursor);
+        st.kblocks = (st.pr->k + BK - 1) / BK;
+        st.kb = 0;
+        int tn;
+        tile_coords(*st.pr, 2 * st.pair + (int)rank - st.pr->tile_start, &st.tm, &tn);
+        st.n0 = tn * BN + (int)rank * P_BN_HALF;
+      };
+      auto advance = [&](Step& st) {
+        if (++st.kb == st.kblocks) {
+          st.pair += n_pairs_grid;
+          enter(st);
+        }
+      };
+      auto acquire = [&](const Problem* pr) {  // once per problem this CTA meets, not per tile
+        if (GROUPED && pr != fenced) {
           ptx::tensormap_acquire(&pr->tma_a);
           ptx::tensormap_acquire(&pr->tma_b);
+          fenced = pr;
         }
-        const int kblocks = (pr->k + BK - 1) / BK;
-        const bool a_mn = pr->a_mn_major != 0, b_mn = pr->b_mn_major != 0;
-        int tm, tn;
-        tile_coords(*pr, 2 * pair + (int)rank - pr->tile_start, &tm, &tn);
-        const int n0 = tn * BN + (int)rank * P_BN_HALF;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
-            fail(status, abort_flag, 0x110000u | stage);
-            ok = false;
-            break;
-          }
-          const uint32_t full_local = ptx::smem_u32(&bars->full[stage]);
-          const uint32_t full_leader = ptx::mapa(full_local, 0);
-          const uint32_t a_dst = ptx::smem_u32(smem + stage * P_STAGE_BYTES);
-          const uint32_t b_dst = a_dst + P_A_BYTES;
-          if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * P_STAGE_BYTES);  // both CTAs' bytes
-          if (a_mn) {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              ptx::tma_load_2d_pair(a_dst + j * SUB_BYTES, &pr->tma_a, tm * BM + j * 64, kb * BK, full_leader);
-          } else {
-            ptx::tma_load_2d_pair(a_dst, &pr->tma_a, kb * BK, tm * BM, full_leader);
-          }
-          if (b_mn) {
-#pragma unroll
-            for (int j = 0; j < P_BN_HALF / 64; ++j)
-              ptx::tma_load_2d_pair(b_dst + j * SUB_BYTES, &pr->tma_b, n0 + j * 64, kb * BK, full_leader);
-          } else {
-            ptx::tma_load_2d_pair(b_dst, &pr->tma_b, kb * BK, n0, full_leader);
-          }
-          ++issued[stage];
-          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+      };
+      Step ld = {first_pair, 0, 0, 0, 0, 0, nullptr};
+      enter(ld);
+      while (ld.pair < total_pairs) {
+        const Problem* pr = ld.pr;
+        acquire(pr);
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
+          fail(status, abort_flag, 0x110000u | stage);
+          ok = false;
+          break;
         }
+        const uint32_t full_local = ptx::smem_u32(&bars->full[stage]);
+        const uint32_t full_leader = ptx::mapa(full_local, 0);
+        const uint32_t a_dst = ptx::smem_u32(smem + stage * P_STAGE_BYTES);
+        const uint32_t b_dst = a_dst + P_A_BYTES;
+        if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * P_STAGE_BYTES);  // both CTAs' bytes
+        if (pr->a_mn_major) {
+#pragma unroll
+          for (int j = 0; j < BM / 64; ++j)
+            ptx::tma_load_2d_pair(a_dst + j * SUB_BYTES, &pr->tma_a, ld.tm * BM + j * 64, ld.kb * BK, full_leader);
+        } else {
+          ptx::tma_load_2d_pair(a_dst, &pr->tma_a, ld.kb * BK, ld.tm * BM, full_leader);
+        }
+        if (pr->b_mn_major) {
+#pragma unroll
+          for (int j = 0; j < P_BN_HALF / 64; ++j)
+            ptx::tma_load_2d_pair(b_dst + j * SUB_BYTES, &pr->tma_b, ld.n0 + j * 64, ld.kb * BK, full_leader);
+        } else {
+          ptx::tma_load_2d_pair(b_dst, &pr->tma_b, ld.kb * BK, ld.n0, full_leader);
+        }
+        ++issued[stage];
+        if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        advance(ld);
       }
+      (void)ok;
       if (*abort_flag && rank == 0) {
         // Leave no copy in flight on the barrier we own: wait (bounded) for each stage's last load.
         uint32_t never = 0;
@@ -512,6 +539,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
     // ---------------- epilogue (both CTAs, own 128 rows) ----------------
     const int q = warp & 3;
     uint32_t chunk_no = 0;
+    const Problem* epi_fenced = nullptr;
     uint32_t it = 0;
     int cursor = 0;
     for (int pair = first_pair; pair < total_pairs; pair += n_pairs_grid, ++it) {
@@ -529,7 +557,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
       }
       ptx::tc_fence_after();
       epilogue_store_tile(pr, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
-                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED);
+                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED ? &epi_fenced : nullptr);
       ptx::tc_fence_before();
       ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0));
     }
