@@ -59,6 +59,68 @@ def _like_input(result: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
     return out
 
 
+# Host-resident operands.  A host tensor is staged through the device in row blocks on
+# three streams: block i + 1 is copied in while block i is computed and block i - 1 is
+# copied out, so that a call on host buffers costs about one PCIe direction's time, not
+# the sum of both.  Pinned inputs overlap; pageable ones still work, serialised by the
+# driver's own staging.
+_HOST_BLOCK_BYTES = 16 << 20   # measured best on PCIe 5 x16 (8 and 32 MiB are within 4 %)
+_side_streams = {}
+
+
+def _copy_streams(dev: torch.device):
+    key = (dev.index, torch.cuda.current_stream().cuda_stream)
+    if key not in _side_streams:
+        _side_streams[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return _side_streams[key]
+
+
+class _HostPipeline:
+    """Copy-in / compute / copy-out over row blocks.  ``feed(dst, src)`` copies a host
+    block to the device on the inbound stream, ``ready()`` makes the compute stream wait
+    for everything fed so far, ``drain(dst, src)`` sends a device block back once the
+    compute stream has reached this point, ``finish()`` waits for the last block."""
+
+    def __init__(self):
+        self.dev = _device()
+        self.main = torch.cuda.current_stream()
+        self.inbound, self.outbound = _copy_streams(self.dev)
+        self.inbound.wait_stream(self.main)
+        self.outbound.wait_stream(self.main)
+
+    def feed(self, dst: torch.Tensor, src: torch.Tensor) -> None:
+        with torch.cuda.stream(self.inbound):
+            dst.copy_(src, non_blocking=True)
+
+    def ready(self) -> None:
+        ev = torch.cuda.Event()
+        ev.record(self.inbound)
+        self.main.wait_event(ev)
+
+    def drain(self, dst: torch.Tensor, src: torch.Tensor) -> None:
+        ev = torch.cuda.Event()
+        ev.record(self.main)
+        self.outbound.wait_event(ev)
+        with torch.cuda.stream(self.outbound):
+            dst.copy_(src, non_blocking=True)
+
+    def finish(self) -> None:
+        # device blocks were allocated on the compute stream: order their reuse after both copy streams
+        self.main.wait_stream(self.inbound)
+        self.main.wait_stream(self.outbound)
+        self.outbound.synchronize()
+
+
+def _row_blocks(rows: int, row_bytes: int, multiple: int = 1):
+    step = max(1, _HOST_BLOCK_BYTES // max(1, row_bytes))
+    step = max(multiple, step // multiple * multiple)
+    return [(r0, min(rows, r0 + step)) for r0 in range(0, rows, step)]
+
+
+def _pinned_like(shape, dtype) -> torch.Tensor:
+    return torch.empty(tuple(shape), dtype=dtype, device="cpu", pin_memory=True)
+
+
 def device_status() -> int:
     """Synchronise the current stream and return the device status word's verdict;
     raises if a bounded wait inside a kernel ran out."""
@@ -178,11 +240,26 @@ def softmax(x: torch.Tensor, row_map: Optional[GroupBy] = None) -> torch.Tensor:
     fn = {torch.float16: "lego_softmax_f16", torch.float32: "lego_softmax_f32"}.get(x.dtype)
     if fn is None:
         raise ValueError(f"softmax supports float16 and float32, got {x.dtype}")
+    call = getattr(_abi.lib(), fn)
+    if not x.is_cuda and x.is_contiguous() and x.numel() * x.element_size() > 2 * _HOST_BLOCK_BYTES:
+        # Host rows: staged block by block.  A row map only decides which CTA takes which
+        # row, never the result, so the blocks run in arrival order without it.
+        lower_optional(row_map)
+        pipe = _HostPipeline()
+        d = torch.empty(x.shape, dtype=x.dtype, device=pipe.dev)
+        y = torch.empty_like(d)
+        out = _pinned_like(x.shape, x.dtype)
+        for r0, r1 in _row_blocks(x.shape[0], x.shape[1] * x.element_size()):
+            pipe.feed(d[r0:r1], x[r0:r1])
+            pipe.ready()
+            _abi.check(call(d[r0:r1].data_ptr(), y[r0:r1].data_ptr(), r1 - r0, x.shape[1], None, _stream()), fn)
+            pipe.drain(out[r0:r1], y[r0:r1])
+        pipe.finish()
+        return out
     d = _to_device(x).contiguous()
     y = torch.empty_like(d)
     n_rows, n_cols = d.shape
-    _abi.check(getattr(_abi.lib(), fn)(d.data_ptr(), y.data_ptr(), n_rows, n_cols, lower_optional(row_map),
-                                       _stream()), fn)
+    _abi.check(call(d.data_ptr(), y.data_ptr(), n_rows, n_cols, lower_optional(row_map), _stream()), fn)
     return _like_input(y, x)
 
 
@@ -196,6 +273,30 @@ def layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, ep
         raise ValueError("weight / bias must have the size of the last axis")
     if n * x.element_size() > 65536:
         raise RuntimeError("This layer norm doesn't support feature dim >= 64KB.")
+    call = _abi.lib().lego_layernorm_fwd_f16
+    if not x.is_cuda and x.is_contiguous() and x.numel() * x.element_size() > 2 * _HOST_BLOCK_BYTES:
+        # host rows: staged block by block (a row map never changes the result, see softmax)
+        lower_optional(row_map)
+        pipe = _HostPipeline()
+        xh = x.reshape(-1, n)
+        m = xh.shape[0]
+        w, b = _to_device(weight).contiguous(), _to_device(bias).contiguous()
+        d = torch.empty(xh.shape, dtype=x.dtype, device=pipe.dev)
+        y = torch.empty_like(d)
+        mean = torch.empty(m, dtype=torch.float32, device=pipe.dev)
+        rstd = torch.empty(m, dtype=torch.float32, device=pipe.dev)
+        y_h, mean_h, rstd_h = _pinned_like(xh.shape, x.dtype), _pinned_like((m,), torch.float32), _pinned_like((m,), torch.float32)
+        for r0, r1 in _row_blocks(m, n * x.element_size()):
+            pipe.feed(d[r0:r1], xh[r0:r1])
+            pipe.ready()
+            _abi.check(call(d[r0:r1].data_ptr(), w.data_ptr(), b.data_ptr(), y[r0:r1].data_ptr(),
+                            mean[r0:r1].data_ptr(), rstd[r0:r1].data_ptr(), r1 - r0, n, float(eps), None, _stream()),
+                       "lego_layernorm_fwd_f16")
+            pipe.drain(y_h[r0:r1], y[r0:r1])
+        pipe.drain(mean_h, mean)
+        pipe.drain(rstd_h, rstd)
+        pipe.finish()
+        return y_h.reshape(x.shape), mean_h, rstd_h
     d = _to_device(x).contiguous()
     x2 = d.reshape(-1, n)
     w, b = _to_device(weight).contiguous(), _to_device(bias).contiguous()
@@ -270,6 +371,34 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         raise ValueError(f"unknown activation {activation!r}")
     m, k = a.shape
     n = b.shape[1]
+    lib = _abi.lib()
+    if (not a.is_cuda and not b.is_cuda and a.is_contiguous() and tile_order is None
+            and a.numel() * 2 > 2 * _HOST_BLOCK_BYTES and m % 256 == 0):
+        # Host operands: B goes in first, then A in blocks of rows; each block's rows of C
+        # leave while the next block arrives.  Every block is its own GEMM with its own
+        # default tile order.
+        pipe = _HostPipeline()
+        if not b.is_contiguous() and b.t().is_contiguous():  # a .T view: copy the storage, keep the view
+            store = torch.empty(b.t().shape, dtype=b.dtype, device=pipe.dev)
+            pipe.feed(store, b.t())
+            bd = store.t()
+        else:
+            bd = torch.empty(b.shape, dtype=b.dtype, device=pipe.dev)
+            pipe.feed(bd, b)
+        b_st, tb = _operand(bd)
+        ad = torch.empty(a.shape, dtype=a.dtype, device=pipe.dev)
+        c = torch.empty((m, n), dtype=torch.float16, device=pipe.dev)
+        c_h = _pinned_like((m, n), torch.float16)
+        for r0, r1 in _row_blocks(m, max(k, n) * 2, multiple=256):
+            pipe.feed(ad[r0:r1], a[r0:r1])
+            pipe.ready()
+            npm, npn = -(-(r1 - r0) // 128), -(-n // 256)
+            order = grouped_swizzle_layout(npm, npn, group_m) if (npm % group_m == 0 or npm <= group_m) else None
+            _abi.check(lib.lego_gemm_f16(ad[r0:r1].data_ptr(), b_st.data_ptr(), c[r0:r1].data_ptr(), r1 - r0, n, k,
+                                         0, tb, act, lower_optional(order), _stream()), "lego_gemm_f16")
+            pipe.drain(c_h[r0:r1], c[r0:r1])
+        pipe.finish()
+        return c_h
     ad, bd = _to_device(a), _to_device(b)
     a_st, ta = _operand(ad)
     b_st, tb = _operand(bd)
@@ -278,8 +407,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         npm, npn = -(-m // 128), -(-n // 256)
         if npm % group_m == 0 or npm <= group_m:
             tile_order = grouped_swizzle_layout(npm, npn, group_m)
-    _abi.check(_abi.lib().lego_gemm_f16(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
-                                        lower_optional(tile_order), _stream()), "lego_gemm_f16")
+    _abi.check(lib.lego_gemm_f16(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
+                               lower_optional(tile_order), _stream()), "lego_gemm_f16")
     return _like_input(c, a)
 
 
@@ -292,11 +421,14 @@ def lego_group_gemm_fn(group_A: Sequence[torch.Tensor], group_B: Sequence[torch.
         return []
     if g > _abi.MAX_GROUPS:
         raise ValueError(f"at most {_abi.MAX_GROUPS} groups per call")
-    a_dev, b_dev, c_dev, mnk = [], [], [], []
     for A, B in zip(group_A, group_B):
         if A.dtype != torch.float16 or B.dtype != torch.float16:
             raise ValueError("grouped GEMM supports float16 operands")
         assert A.shape[1] == B.shape[0]
+    if all(not t.is_cuda for t in list(group_A) + list(group_B)) and g > 1:
+        return _group_gemm_from_host(group_A, group_B, tile_orders)
+    a_dev, b_dev, c_dev, mnk = [], [], [], []
+    for A, B in zip(group_A, group_B):
         ad, bd = _to_device(A).contiguous(), _to_device(B).contiguous()
         a_dev.append(ad)
         b_dev.append(bd)
@@ -314,3 +446,30 @@ def lego_group_gemm_fn(group_A: Sequence[torch.Tensor], group_B: Sequence[torch.
     _abi.check(_abi.lib().lego_grouped_gemm_f16(ap, bp, cp, sizes, g, orders, _stream()),
                "lego_grouped_gemm_f16")
     return [_like_input(c, A) for c, A in zip(c_dev, group_A)]
+
+
+def _group_gemm_from_host(group_A, group_B, tile_orders) -> List[torch.Tensor]:
+    """Grouped GEMM on host operands: group g + 1 is copied in while group g is computed
+    (one single-problem launch each) and group g - 1 is copied out."""
+    pipe = _HostPipeline()
+    lib = _abi.lib()
+    outs, keep = [], []
+    for i, (A, B) in enumerate(zip(group_A, group_B)):
+        ad = torch.empty(A.shape, dtype=A.dtype, device=pipe.dev)
+        bd = torch.empty(B.shape, dtype=B.dtype, device=pipe.dev)
+        cd = torch.empty((A.shape[0], B.shape[1]), dtype=torch.float16, device=pipe.dev)
+        keep += [ad, bd, cd]
+        pipe.feed(ad, A)
+        pipe.feed(bd, B)
+        pipe.ready()
+        order = None if tile_orders is None or tile_orders[i] is None else lower(tile_orders[i])
+        orders = None if order is None else (_abi.LayoutP * 1)(C.pointer(order))
+        _abi.check(lib.lego_grouped_gemm_f16((C.c_void_p * 1)(ad.data_ptr()), (C.c_void_p * 1)(bd.data_ptr()),
+                                             (C.c_void_p * 1)(cd.data_ptr()),
+                                             (C.c_int64 * 3)(A.shape[0], B.shape[1], A.shape[1]), 1, orders, _stream()),
+                   "lego_grouped_gemm_f16")
+        out = _pinned_like(cd.shape, torch.float16)
+        pipe.drain(out, cd)
+        outs.append(out)
+    pipe.finish()
+    return outs

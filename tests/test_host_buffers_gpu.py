@@ -1,0 +1,77 @@
+"""Host-resident operands: the calls a user makes with CPU tensors stage the data
+through the device in blocks (copy-in / compute / copy-out on three streams).  The
+results must be bit-identical to the same call on device-resident tensors, pinned or
+pageable input alike, and must come back on the host."""
+import pytest
+import torch
+
+import lego_b200 as L
+from lego_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def small_blocks(monkeypatch):
+    """8 MiB blocks so that inputs of some 20 MiB already take the staged route"""
+    monkeypatch.setattr(ops, "_HOST_BLOCK_BYTES", 8 << 20)
+
+
+def _both(x):
+    """the tensor as pageable and as pinned host memory"""
+    return (("pageable", x), ("pinned", x.pin_memory()))
+
+
+def test_softmax_host_rows_match_device_rows():
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(2600, 4096, generator=g) * 2).half()   # 20 MiB: three blocks, the last one ragged
+    want = ops.softmax(x.cuda()).cpu()
+    for name, xh in _both(x):
+        got = ops.softmax(xh, ops.row_tiling_layout(2600, 4))
+        assert not got.is_cuda, name
+        assert torch.equal(got, want), name
+    # small inputs take the one-shot route and agree as well
+    small = x[:64].contiguous()
+    assert torch.equal(ops.softmax(small), ops.softmax(small.cuda()).cpu())
+
+
+def test_layernorm_host_rows_match_device_rows():
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(3, 900, 4096, generator=g).half()       # leading axes are flattened into rows
+    w = (1 + 0.1 * torch.randn(4096, generator=g)).half()
+    b = (0.1 * torch.randn(4096, generator=g)).half()
+    y_d, mean_d, rstd_d = ops.layer_norm_fwd(x.cuda(), w.cuda(), b.cuda(), 1e-5)
+    for name, xh in _both(x):
+        y, mean, rstd = ops.layer_norm_fwd(xh, w, b, 1e-5)
+        assert y.shape == x.shape and not y.is_cuda, name
+        assert torch.equal(y, y_d.cpu()), name
+        assert torch.equal(mean, mean_d.cpu()) and torch.equal(rstd, rstd_d.cpu()), name
+
+
+def test_matmul_host_operands_match_device_operands():
+    g = torch.Generator().manual_seed(13)
+    m, n, k = 2304, 1024, 4096                               # A is 18 MiB: blocks of 1024, 1024 and 256 rows
+    a = (torch.randn(m, k, generator=g) / 64).half()
+    b = (torch.randn(k, n, generator=g) / 64).half()
+    want = ops.matmul(a.cuda(), b.cuda()).cpu()
+    for name, ah in _both(a):
+        got = ops.matmul(ah, b)
+        assert not got.is_cuda and torch.equal(got, want), name
+    # B given as the .T view of an [n, k] matrix, and the fused activation
+    bt = b.t().contiguous()
+    got = ops.matmul(a.pin_memory(), bt.t(), activation="leaky_relu")
+    assert torch.equal(got, ops.matmul(a.cuda(), b.cuda(), activation="leaky_relu").cpu())
+
+
+def test_grouped_gemm_host_groups_match_device_groups():
+    g = torch.Generator().manual_seed(14)
+    sizes = [(256, 512, 1024), (1024, 256, 512), (384, 768, 256)]
+    A = [(torch.randn(m, k, generator=g) / 16).half() for m, n, k in sizes]
+    B = [(torch.randn(k, n, generator=g) / 16).half() for m, n, k in sizes]
+    want = [c.cpu() for c in ops.lego_group_gemm_fn([t.cuda() for t in A], [t.cuda() for t in B])]
+    got = ops.lego_group_gemm_fn([t.pin_memory() for t in A], B)
+    assert all(not c.is_cuda for c in got)
+    assert all(torch.equal(c, w) for c, w in zip(got, want))
+    orders = [L.OrderBy(L.Row(-(-m // 128), -(-n // 256))).TileBy([-(-m // 128), -(-n // 256)]) for m, n, _ in sizes]
+    got = ops.lego_group_gemm_fn(A, B, orders)
+    assert all(torch.equal(c, w) for c, w in zip(got, want))
