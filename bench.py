@@ -255,7 +255,7 @@ class Gemm(Workload):
         return (self.ap.numel() + self.bp.numel()) * 2, self.m * self.n * 2
 
     def e2e_step(self, i):
-        return self.ops.matmul(self.ap, self.bp, tile_order=self.order)
+        return self.ops.matmul(self.ap, self.bp)  # default tile order = the same swizzle, per row block
 
     def cpu_sample(self, threads, budget=4.0):
         m = 1024
@@ -358,7 +358,7 @@ class IndexMap(Workload):
         return 0, 8 * (1 << 24)
 
     def e2e_step(self, i):
-        return self.ops.eval_range(self.layout).cpu()
+        return self.ops.eval_range(self.layout, host=True)
 
     def cpu_sample(self, threads, budget=4.0):
         from oracle import lego_oracle as O

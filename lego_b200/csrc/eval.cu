@@ -108,6 +108,77 @@ digit_range_fast_kernel(const __grid_constant__ DigitProgram p, int64_t* __restr
   if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) out[n - 1] = eval((uint32_t)(begin + n - 1));
 }
 
+// Range evaluation, one warp per 1024 consecutive ids.  Terms whose divisor is a multiple
+// of 32 ("slow" terms) are constant over a 32-aligned run of ids: lane L evaluates their
+// sum once for run L of the warp's 32 runs, and the sums travel by shuffle.  Only the
+// remaining "fast" terms (normally just the innermost digit) are evaluated per id.  Each
+// store instruction writes 64 consecutive int64 (512 contiguous bytes per warp).
+constexpr int kWarpFast = 2;
+constexpr int kWarpSlow = 6;
+
+struct TermRegs {
+  uint32_t a_mul, a_shr, m_mul, m_shr, m_d, b;
+};
+
+__device__ __forceinline__ TermRegs load_term(const DigitProgram& p, int j, bool on) {
+  TermRegs r;
+  r.a_mul = on ? p.t[j].a.mul : 0u;
+  r.a_shr = on ? p.t[j].a.shr : 0u;
+  r.m_mul = on ? p.t[j].m.mul : 0u;
+  r.m_shr = on ? p.t[j].m.shr : 0u;
+  r.m_d = on ? p.t[j].m.d : 0u;
+  r.b = on ? (uint32_t)p.t[j].b : 0u;  // a disabled term multiplies by zero
+  return r;
+}
+
+__device__ __forceinline__ uint32_t eval_term(const TermRegs& r, uint32_t x) {
+  uint32_t q = r.a_mul ? (__umulhi(x, r.a_mul) >> r.a_shr) : (x >> r.a_shr);
+  if (r.m_d) {
+    const uint32_t w = r.m_mul ? (__umulhi(q, r.m_mul) >> r.m_shr) : (q >> r.m_shr);
+    q -= w * r.m_d;
+  }
+  return q * r.b;
+}
+
+// `p` holds the fast terms first (n_fast of them), then the slow ones.
+__global__ void __launch_bounds__(256)
+digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int64_t* __restrict__ out, int64_t begin,
+                        int64_t n, int vec) {
+  TermRegs fast[kWarpFast], slow[kWarpSlow];
+#pragma unroll
+  for (int j = 0; j < kWarpFast; ++j) fast[j] = load_term(p, j, j < n_fast);
+#pragma unroll
+  for (int j = 0; j < kWarpSlow; ++j) slow[j] = load_term(p, n_fast + j, n_fast + j < p.n_terms);
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t block_end = (begin + n + 1023) >> 10;
+  for (int64_t blk = (begin >> 10) + warp; blk < block_end; blk += n_warps) {
+    const uint32_t base = (uint32_t)(blk << 10);
+    uint32_t run_sum = 0;
+#pragma unroll
+    for (int j = 0; j < kWarpSlow; ++j) run_sum += eval_term(slow[j], base + 32u * lane);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const uint32_t s = __shfl_sync(0xffffffffu, run_sum, 2 * k + (lane >> 4));
+      const uint32_t x = base + 64u * k + 2u * lane;
+      uint32_t v0 = s, v1 = s;
+#pragma unroll
+      for (int j = 0; j < kWarpFast; ++j) {
+        v0 += eval_term(fast[j], x);
+        v1 += eval_term(fast[j], x + 1);
+      }
+      const int64_t i = (int64_t)x - begin;
+      if (vec && i >= 0 && i + 1 < n) {
+        *reinterpret_cast<longlong2*>(out + i) = make_longlong2((int64_t)v0, (int64_t)v1);
+      } else {
+        if (i >= 0 && i < n) out[i] = (int64_t)v0;
+        if (i + 1 >= 0 && i + 1 < n) out[i + 1] = (int64_t)v1;
+      }
+    }
+  }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(256)
 staged_eval_kernel(const __grid_constant__ StagedProgram sp, const int64_t* __restrict__ in,
@@ -160,6 +231,23 @@ static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t*
     if (MODE == MODE_RANGE) program_range(dg, size, &p);
     if (MODE == MODE_APPLY) program_apply(dg, layout->rank, size, &p);
     if (MODE == MODE_INV) program_inv(dg, layout->rank, size, &p);
+    if (MODE == MODE_RANGE && !p.wide && n >= 4096) {
+      // fast terms first; a term is slow when its divisor is a multiple of 32
+      DigitProgram w = p;
+      int n_fast = 0, k = 0;
+      for (int j = 0; j < p.n_terms; ++j)
+        if (p.t[j].a.d % 32 != 0) w.t[k++] = p.t[j];
+      n_fast = k;
+      for (int j = 0; j < p.n_terms; ++j)
+        if (p.t[j].a.d % 32 == 0) w.t[k++] = p.t[j];
+      if (n_fast <= kWarpFast && p.n_terms - n_fast <= kWarpSlow) {
+        const int64_t id_blocks = ((begin + n + 1023) >> 10) - (begin >> 10);
+        const int64_t want = (id_blocks + 7) / 8, most = (int64_t)ctx->sm_count * 64;
+        const int vec = (begin % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) ? 1 : 0;
+        digit_range_warp_kernel<<<(int)(want < most ? want : most), threads, 0, s>>>(w, n_fast, out, begin, n, vec);
+        return cuda_status(cudaGetLastError());
+      }
+    }
     if (MODE == MODE_RANGE && !p.wide && p.n_terms <= kFastTerms)
       digit_range_fast_kernel<<<blocks, threads, 0, s>>>(p, out, begin, n);
     else if (p.wide)

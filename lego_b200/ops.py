@@ -173,16 +173,33 @@ def eval_inv(layout: GroupBy, flat: torch.Tensor) -> torch.Tensor:
     return _like_input(out, flat)
 
 
-def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None) -> torch.Tensor:
-    """``layout.apply`` over logical flat ids ``begin .. begin+count`` -> device int64."""
+def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None, host: bool = False) -> torch.Tensor:
+    """``layout.apply`` over logical flat ids ``begin .. begin+count`` -> int64, on the
+    device, or with ``host=True`` in pinned host memory (evaluated block by block, each
+    block leaving the device while the next is computed)."""
     desc = lower(layout)
     size = layout.size()
     if count is None:
         count = size - begin
+    call = _abi.lib().lego_eval_range
+    if host and count * 8 > 2 * _HOST_BLOCK_BYTES:
+        pipe = _HostPipeline()
+        res = _pinned_like((count,), torch.int64)
+        bufs = [torch.empty(_HOST_BLOCK_BYTES // 8, dtype=torch.int64, device=pipe.dev) for _ in range(2)]
+        done = [None, None]  # the copy-out that last read each buffer
+        for i, (r0, r1) in enumerate(_row_blocks(count, 8)):
+            buf = bufs[i & 1][: r1 - r0]
+            if done[i & 1] is not None:
+                pipe.main.wait_event(done[i & 1])
+            _abi.check(call(C.byref(desc), begin + r0, r1 - r0, buf.data_ptr(), _stream()), "lego_eval_range")
+            pipe.drain(res[r0:r1], buf)
+            done[i & 1] = torch.cuda.Event()
+            done[i & 1].record(pipe.outbound)
+        pipe.finish()
+        return res
     out = torch.empty(count, dtype=torch.int64, device=_device())
-    _abi.check(_abi.lib().lego_eval_range(C.byref(desc), begin, count, out.data_ptr(), _stream()),
-               "lego_eval_range")
-    return out
+    _abi.check(call(C.byref(desc), begin, count, out.data_ptr(), _stream()), "lego_eval_range")
+    return _like_input(out, torch.empty(0)) if host else out
 
 
 # ---- layout reorganisation ----------------------------------------------------------

@@ -88,3 +88,20 @@ def test_empty_and_bad_arguments():
         ops.eval_range(lay, 60, 10)
     with pytest.raises(ValueError):
         ops.eval_apply(lay, torch.zeros((4, 3), dtype=torch.int64).cuda())
+
+
+def test_range_windows_odd_offsets_and_term_mixes():
+    """Windows that start and end anywhere (odd offsets, a few ids past a 1024-id block,
+    unaligned output pointers) over layouts with one, two and many digits that change
+    inside a run of 32 ids."""
+    cases = (L.OrderBy(L.Col(512, 512)).TileBy([16, 16], [32, 32]),          # one fast digit (32 wide)
+             L.OrderBy(L.Col(960, 400)).TileBy([80, 50], [12, 8]),           # innermost digits 8 and 12 wide: two fast
+             L.OrderBy(L.Col(6, 10, 14, 18)).TileBy([3, 5, 7, 9], [2, 2, 2, 2]),  # many narrow digits
+             L.OrderBy(L.Row(70000)).TileBy([17500], [4]))                   # identity map, one term
+    for lay in cases:
+        size = lay.size()
+        want = O.groupby_apply_all(spec_of(lay))
+        assert np.array_equal(ops.eval_range(lay).cpu().numpy(), want)
+        for begin, count in ((1, size - 1), (1023, 4097), (size - 5001, 5001), (2048, 4096), (31, 8191)):
+            got = ops.eval_range(lay, begin, count).cpu().numpy()
+            assert np.array_equal(got, want[begin:begin + count]), (lay.dims(), begin, count)

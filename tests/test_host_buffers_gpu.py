@@ -75,3 +75,13 @@ def test_grouped_gemm_host_groups_match_device_groups():
     orders = [L.OrderBy(L.Row(-(-m // 128), -(-n // 256))).TileBy([-(-m // 128), -(-n // 256)]) for m, n, _ in sizes]
     got = ops.lego_group_gemm_fn(A, B, orders)
     assert all(torch.equal(c, w) for c, w in zip(got, want))
+
+
+def test_eval_range_into_host_memory():
+    lay = L.OrderBy(L.Col(2048, 2048)).TileBy([64, 64], [32, 32])   # 2^22 ids = 32 MiB of int64
+    want = ops.eval_range(lay).cpu()
+    got = ops.eval_range(lay, host=True)
+    assert not got.is_cuda and torch.equal(got, want)
+    part = ops.eval_range(lay, begin=12345, count=3 * (1 << 20) + 17, host=True)
+    assert torch.equal(part, want[12345:12345 + 3 * (1 << 20) + 17])
+    assert torch.equal(ops.eval_range(lay, count=1000, host=True), want[:1000])
