@@ -10,6 +10,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 #include "rowwise.cuh"
 
 namespace lego {
@@ -110,6 +111,270 @@ ln_bwd_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dga
   }
 }
 
+// ---- bulk-copy pipelined dx kernel -------------------------------------------------
+//
+// One CTA per SM.  A producer thread streams the rows of x and dy (and the 16-byte
+// chunks holding the row's mean and rstd) into a shared-memory ring with 1-D bulk
+// copies; 512 consumer threads own 8 or 16 fixed columns each: gamma and the two
+// column accumulators of those columns stay in registers for the whole kernel, a row
+// costs one two-value reduction over the CTA, and dx leaves in 128-bit streaming
+// stores.  Memory-level parallelism comes from the ring (up to 6 rows of x and dy in
+// flight per SM), not from occupancy.
+
+constexpr int kBwdConsumers = 512;
+constexpr int kBwdRing = 6;
+constexpr long long kBwdWaitLimit = 2000000000LL;  // SM cycles, about a second
+
+struct BwdRingCtl {
+  uint64_t full[kBwdRing];
+  uint64_t empty[kBwdRing];
+  int64_t row[kBwdRing];
+  uint32_t abort_flag;
+};
+
+template <int EPT>
+__global__ void __launch_bounds__(kBwdConsumers + 32, 1)
+ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
+  constexpr int NV = EPT / 8;
+  constexpr int NW = kBwdConsumers / 32;
+  extern __shared__ __align__(128) uint8_t bwd_smem[];
+  __shared__ __align__(8) float red[2][NW][2];  // [row parity][warp] -> (s1, s2)
+  const int cols = P.cols;
+  const uint32_t row_bytes = (uint32_t)cols * 2u;
+  const uint32_t half_slot = (row_bytes + 127u) & ~127u;
+  const uint32_t slot_bytes = 2u * half_slot + 128u;  // x | dy | mean chunk, rstd chunk
+  BwdRingCtl* ctl = reinterpret_cast<BwdRingCtl*>(bwd_smem + (size_t)stages * slot_bytes);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const int tid = threadIdx.x;
+  const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), NW);
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  __syncthreads();
+
+  if (tid >= kBwdConsumers) {
+    // ---------------- producer ----------------
+    if (tid == kBwdConsumers) {
+      int64_t issued = 0;
+      // s walks the ring, use counts the laps (no 64-bit division per row)
+      int s = 0;
+      uint32_t use = 0;
+      for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kBwdWaitLimit)) {
+          *abort_flag = 1;
+          atomicCAS(status, 0u, 0x60000u | (uint32_t)s);
+          break;
+        }
+        const int64_t row = blockIdx.x + n * (int64_t)gridDim.x;
+        ctl->row[s] = row;
+        const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+        const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)s * slot_bytes);
+        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+        ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
+        ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
+        ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+        ptx::bulk_load(dst + 2u * half_slot + 16u, P.rstd + (row & ~3LL), 16u, full);
+        ++issued;
+      }
+      if (*abort_flag) {
+        // leave no copy of ours in flight
+        uint32_t never = 0;
+        for (int s = 0; s < stages; ++s) {
+          const int64_t uses = issued > s ? (issued - s + stages - 1) / stages : 0;
+          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kBwdWaitLimit);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  // All element-wise fp32 work runs as packed pairs (f32x2): P = EPT / 2 pairs per thread.
+  constexpr int P2 = EPT / 2;
+  const int lane = tid & 31, warp = tid >> 5;
+  float2 g[P2], acc_w[P2], acc_b[P2];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = (k * kBwdConsumers + tid) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (c < cols) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
+    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) g[k * 4 + e] = __half22float2(hp[e]);
+  }
+#pragma unroll
+  for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
+  const float inv_cols = 1.0f / (float)cols;
+  float2* red2 = reinterpret_cast<float2*>(&red[0][0][0]);  // [row parity][warp] -> (s1, s2)
+
+  int s = 0;
+  uint32_t use = 0;
+  for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
+    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwdWaitLimit);
+    if (!ok) {
+      *abort_flag = 1;
+      atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
+    }
+    const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
+    const int64_t row = ok ? ctl->row[s] : 0;
+    const float mean = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3] : 0.f;
+    const float rstd = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3] : 0.f;
+    uint4 xr[NV], dr[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int v = k * kBwdConsumers + tid;
+      xr[k] = dr[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (ok && v * 8 < cols) {
+        xr[k] = reinterpret_cast<const uint4*>(slot)[v];
+        dr[k] = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
+
+    // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
+    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
+    float2 h[P2], w[P2];
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < P2; ++k) {
+      const __half2 xh2 = reinterpret_cast<const __half2*>(&xr[k / 4])[k % 4];
+      const __half2 dh2 = reinterpret_cast<const __half2*>(&dr[k / 4])[k % 4];
+      const float2 d = __half22float2(dh2);
+      h[k] = ptx::fma2(__half22float2(xh2), rstd2, shift2);
+      acc_w[k] = ptx::fma2(d, h[k], acc_w[k]);
+      acc_b[k] = ptx::add2(acc_b[k], d);
+      w[k] = ptx::mul2(d, g[k]);
+      s1 = ptx::fma2(h[k], w[k], s1);
+      s2 = ptx::add2(s2, w[k]);
+    }
+    float2 ss = make_float2(s1.x + s1.y, s2.x + s2.y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+      ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+    }
+    float2* r = red2 + (n & 1) * NW;
+    if (lane == 0) r[warp] = ss;
+    ptx::named_barrier<1, kBwdConsumers>();
+    if (*abort_flag) break;  // uniform: every flag write of this row precedes the barrier above
+    ss = lane < NW ? r[lane] : make_float2(0.f, 0.f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {  // all 32 lanes end up with the total
+      ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+      ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+    }
+    // dx = (wdy - (xhat * c1 + c2)) * rstd, as two fused steps per pair
+    const float c1r = ss.x * inv_cols * rstd, c2r = ss.y * inv_cols * rstd;
+    const float2 nc1 = make_float2(-c1r, -c1r), nc2 = make_float2(-c2r, -c2r);
+    __half* __restrict__ dx = P.dx + row * cols;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * kBwdConsumers + tid) * 8;
+      uint4 outv;
+      __half2* o2 = reinterpret_cast<__half2*>(&outv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 t = ptx::fma2(h[k * 4 + e], nc1, ptx::fma2(w[k * 4 + e], rstd2, nc2));
+        o2[e] = __floats2half2_rn(t.x, t.y);
+      }
+      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv);
+    }
+  }
+  if (*abort_flag) return;
+  float* pw = P.partial + (size_t)blockIdx.x * cols;
+  float* pb = P.partial + ((size_t)P.partial_rows + blockIdx.x) * cols;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = (k * kBwdConsumers + tid) * 8;
+    if (c < cols) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = k * 4 + 2 * e;
+        *reinterpret_cast<float4*>(pw + c + 4 * e) = make_float4(acc_w[j].x, acc_w[j].y, acc_w[j + 1].x, acc_w[j + 1].y);
+        *reinterpret_cast<float4*>(pb + c + 4 * e) = make_float4(acc_b[j].x, acc_b[j].y, acc_b[j + 1].x, acc_b[j + 1].y);
+      }
+    }
+  }
+}
+
+// Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
+template <int EPT>
+int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
+  auto kern = ln_bwd_ring_kernel<EPT>;
+  const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
+  const size_t slot = 2 * half_slot + 128;
+  static bool configured = false;
+  if (!configured) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
+    configured = true;
+  }
+  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRingCtl) - 128;
+  int stages = (int)(budget / slot);
+  if (stages > kBwdRing) stages = kBwdRing;
+  if (stages < 2) return LEGO_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
+  const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
+  P.partial_rows = grid;
+  kern<<<grid, kBwdConsumers + 32, smem, s>>>(P, stages, ctx->status_word);
+  return cuda_status(cudaGetLastError());
+}
+
+// Column reduction for widths that are a multiple of 4: a CTA sums 32 columns; lane
+// (q, r) of warp w reads the 16 bytes of column quad q in partial rows r + 4 w, + 32, ...
+// (a warp reads four whole 128-byte lines per step), the 32 row lanes are folded by
+// shuffles and one pass through shared memory, always in the same order.
+__global__ void __launch_bounds__(256)
+ln_bwd_reduce4_kernel(const float* __restrict__ partial, __half* __restrict__ dgamma, __half* __restrict__ dbeta,
+                      int cols, int partial_rows) {
+  __shared__ float4 sw[8][8], sb[8][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q = lane & 7, rl = (lane >> 3) + 4 * warp;
+  const int c = blockIdx.x * 32 + q * 4;
+  float4 w = make_float4(0.f, 0.f, 0.f, 0.f), b = w;
+  if (c < cols) {
+    for (int r = rl; r < partial_rows; r += 32) {
+      const float4 pw = __ldcs(reinterpret_cast<const float4*>(partial + (size_t)r * cols + c));
+      const float4 pb = __ldcs(reinterpret_cast<const float4*>(partial + ((size_t)partial_rows + r) * cols + c));
+      w.x += pw.x; w.y += pw.y; w.z += pw.z; w.w += pw.w;
+      b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+    }
+  }
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+    w.x += __shfl_xor_sync(0xffffffffu, w.x, o); w.y += __shfl_xor_sync(0xffffffffu, w.y, o);
+    w.z += __shfl_xor_sync(0xffffffffu, w.z, o); w.w += __shfl_xor_sync(0xffffffffu, w.w, o);
+    b.x += __shfl_xor_sync(0xffffffffu, b.x, o); b.y += __shfl_xor_sync(0xffffffffu, b.y, o);
+    b.z += __shfl_xor_sync(0xffffffffu, b.z, o); b.w += __shfl_xor_sync(0xffffffffu, b.w, o);
+  }
+  if (lane < 8) {
+    sw[warp][q] = w;
+    sb[warp][q] = b;
+  }
+  __syncthreads();
+  if (warp == 0 && lane < 8 && c < cols) {
+    float4 tw = sw[0][q], tb = sb[0][q];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      tw.x += sw[k][q].x; tw.y += sw[k][q].y; tw.z += sw[k][q].z; tw.w += sw[k][q].w;
+      tb.x += sb[k][q].x; tb.y += sb[k][q].y; tb.z += sb[k][q].z; tb.w += sb[k][q].w;
+    }
+    __half2* dg = reinterpret_cast<__half2*>(dgamma + c);
+    __half2* dbp = reinterpret_cast<__half2*>(dbeta + c);
+    dg[0] = __floats2half2_rn(tw.x, tw.y);
+    dg[1] = __floats2half2_rn(tw.z, tw.w);
+    dbp[0] = __floats2half2_rn(tb.x, tb.y);
+    dbp[1] = __floats2half2_rn(tb.z, tb.w);
+  }
+}
+
 template <int TPR, int EPT, bool VECTOR>
 int32_t launch_dx(const BwdParams& P, cudaStream_t s) {
   ln_bwd_dx_kernel<TPR, EPT, VECTOR><<<P.partial_rows, TPR, 0, s>>>(P);
@@ -151,10 +416,24 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   cudaStream_t s = (cudaStream_t)stream;
   auto a16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   const bool vec = cols % 8 == 0 && a16(dy) && a16(x) && a16(gamma) && a16(dx);
-  int32_t st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
+  int32_t st = LEGO_ERR_UNSUPPORTED;
+  // Ring-fed kernel: 16-byte aligned rows of 1 Ki .. 8 Ki columns, enough rows to fill the
+  // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
+  if (vec && cols > 1024 && cols <= kBwdConsumers * 16 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
+      a16(partial) && rows >= 2 * 148) {
+    int32_t err = LEGO_OK;
+    DeviceCtx* ctx = device_ctx(&err);
+    if (!ctx) return err;
+    st = cols <= kBwdConsumers * 8 ? launch_ring_dx<8>(P, ctx, s) : launch_ring_dx<16>(P, ctx, s);
+  }
+  if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
   if (st != LEGO_OK) return st;
-  ln_bwd_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
-                                                                 (int)cols, P.partial_rows);
+  if (cols % 4 == 0 && a16(partial) && ((uintptr_t)dgamma & 3) == 0 && ((uintptr_t)dbeta & 3) == 0)
+    ln_bwd_reduce4_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
+                                                                    (int)cols, P.partial_rows);
+  else
+    ln_bwd_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
+                                                                   (int)cols, P.partial_rows);
   return cuda_status(cudaGetLastError());
 }
 

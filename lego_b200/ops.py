@@ -28,7 +28,7 @@ from .lowering import lower, lower_optional
 
 __all__ = [
     "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "transpose", "softmax",
-    "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "matmul", "lego_group_gemm_fn",
+    "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "layer_norm_bwd", "matmul", "lego_group_gemm_fn",
     "grouped_swizzle_layout", "row_tiling_layout", "device_status",
 ]
 
@@ -340,23 +340,35 @@ class LEGOLayerNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w, mean, rstd = ctx.saved_tensors
-        n = x.shape[-1]
-        xd = _to_device(x).contiguous().reshape(-1, n)
-        dyd = _to_device(dy).contiguous().reshape(-1, n)
-        wd = _to_device(w).contiguous()
-        md, rd = _to_device(mean), _to_device(rstd)
-        m = xd.shape[0]
-        lib = _abi.lib()
-        prow = lib.lego_layernorm_bwd_partial_rows(m, n)
-        partial = torch.empty((2, prow, n), dtype=torch.float32, device=xd.device)
-        dx = torch.empty_like(xd)
-        dw = torch.empty_like(wd)
-        db = torch.empty_like(wd)
-        _abi.check(lib.lego_layernorm_bwd_f16(dyd.data_ptr(), xd.data_ptr(), wd.data_ptr(), md.data_ptr(),
-                                              rd.data_ptr(), dx.data_ptr(), dw.data_ptr(), db.data_ptr(),
-                                              partial.data_ptr(), m, n, _stream()),
-                   "lego_layernorm_bwd_f16")
-        return _like_input(dx.reshape(x.shape), x), None, _like_input(dw, w), _like_input(db, w), None
+        dx, dw, db = layer_norm_bwd(dy, x, w, mean, rstd)
+        return dx, None, dw, db, None
+
+
+def layer_norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor):
+    """LayerNorm backward over the last axis: ``(dx, dweight, dbias)`` from the saved
+    row statistics; dweight / dbias come from a fixed-order two-stage column reduction
+    (same bits on every run)."""
+    n = x.shape[-1]
+    xd = _to_device(x).contiguous().reshape(-1, n)
+    dyd = _to_device(dy).contiguous().reshape(-1, n)
+    wd = _to_device(weight).contiguous()
+    md, rd = _to_device(mean).contiguous(), _to_device(rstd).contiguous()
+    m = xd.shape[0]
+    if dyd.shape != xd.shape or wd.numel() != n or md.numel() != m or rd.numel() != m:
+        raise ValueError("layer norm backward: shapes of dy, x, weight, mean, rstd do not agree")
+    if xd.dtype != torch.float16 or dyd.dtype != torch.float16 or wd.dtype != torch.float16:
+        raise ValueError("layer norm supports float16 tensors")
+    lib = _abi.lib()
+    prow = lib.lego_layernorm_bwd_partial_rows(m, n)
+    partial = torch.empty((2, prow, n), dtype=torch.float32, device=xd.device)
+    dx = torch.empty_like(xd)
+    dw = torch.empty_like(wd)
+    db = torch.empty_like(wd)
+    _abi.check(lib.lego_layernorm_bwd_f16(dyd.data_ptr(), xd.data_ptr(), wd.data_ptr(), md.data_ptr(),
+                                          rd.data_ptr(), dx.data_ptr(), dw.data_ptr(), db.data_ptr(),
+                                          partial.data_ptr(), m, n, _stream()),
+               "lego_layernorm_bwd_f16")
+    return _like_input(dx.reshape(x.shape), x), _like_input(dw, weight), _like_input(db, weight)
 
 
 lego_layer_norm = LEGOLayerNorm.apply

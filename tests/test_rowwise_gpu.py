@@ -138,6 +138,29 @@ def test_layernorm_backward_matches_reference_test():
     assert torch.equal(y2, y)
 
 
+def test_layernorm_backward_shapes_of_both_kernels():
+    """dx / dweight / dbias against the oracle for row counts and widths that take the
+    ring-fed kernel (row count a multiple of 4, 1 Ki < cols <= 8 Ki, 16-byte rows) and
+    for neighbours that take the register kernel; tolerances of the reference's own test
+    (atol 1e-2) for dx, 1e-2 of the largest entry for the column sums."""
+    for rows, cols in ((1152, 8192), (600, 4096), (2048, 2056), (1152, 1032), (1150, 8192), (512, 8200), (300, 1024)):
+        g = torch.Generator().manual_seed(rows + cols)
+        w = torch.rand(cols, generator=g).half()
+        b = torch.rand(cols, generator=g).half()
+        x = (-2.3 + 0.5 * torch.randn(rows, cols, generator=g)).half()
+        dy = (0.1 * torch.randn(rows, cols, generator=g)).half()
+        _, mean, rstd = O.layernorm_fwd(x, w, b, 1e-5)
+        rdx, rdw, rdb = O.layernorm_bwd(dy, x, w, mean, rstd)
+        dx, dw, db = ops.layer_norm_bwd(dy.cuda(), x.cuda(), w.cuda(), mean.cuda(), rstd.cuda())
+        assert torch.allclose(dx.cpu().float(), rdx.float(), atol=1e-2, rtol=0), (rows, cols)
+        assert (dx.cpu().float() - rdx.float()).abs().max().item() <= 2e-3, (rows, cols)
+        assert (dw.cpu().float() - rdw.float()).abs().max().item() <= 1e-2 * rdw.float().abs().max().item(), (rows, cols)
+        assert (db.cpu().float() - rdb.float()).abs().max().item() <= 1e-2 * rdb.float().abs().max().item(), (rows, cols)
+        again = ops.layer_norm_bwd(dy.cuda(), x.cuda(), w.cuda(), mean.cuda(), rstd.cuda())
+        assert all(torch.equal(a, b) for a, b in zip(again, (dx, dw, db))), (rows, cols)
+    ops.device_status()
+
+
 def test_layernorm_errors():
     x = torch.zeros(2, 40000, dtype=torch.float16, device="cuda")
     w = torch.zeros(40000, dtype=torch.float16, device="cuda")
