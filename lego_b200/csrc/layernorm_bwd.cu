@@ -327,20 +327,22 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   return cuda_status(cudaGetLastError());
 }
 
-// Column reduction for widths that are a multiple of 4: a CTA sums 32 columns; lane
-// (q, r) of warp w reads the 16 bytes of column quad q in partial rows r + 4 w, + 32, ...
-// (a warp reads four whole 128-byte lines per step), the 32 row lanes are folded by
-// shuffles and one pass through shared memory, always in the same order.
-__global__ void __launch_bounds__(256)
+// Column reduction for widths that are a multiple of 4: a CTA of 32 warps sums 32 columns;
+// lane (q, r) of warp w reads the 16 bytes of column quad q in partial rows r + 4 w,
+// + 128, ... (a warp reads four whole 128-byte lines per step, and with the usual 148
+// partial rows no thread waits for more than two loads in a row), the 128 row lanes are
+// folded by shuffles and one pass through shared memory, always in the same order.
+__global__ void __launch_bounds__(1024)
 ln_bwd_reduce4_kernel(const float* __restrict__ partial, __half* __restrict__ dgamma, __half* __restrict__ dbeta,
                       int cols, int partial_rows) {
-  __shared__ float4 sw[8][8], sb[8][8];
+  __shared__ float4 sw[32][8], sb[32][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int q = lane & 7, rl = (lane >> 3) + 4 * warp;
   const int c = blockIdx.x * 32 + q * 4;
   float4 w = make_float4(0.f, 0.f, 0.f, 0.f), b = w;
   if (c < cols) {
-    for (int r = rl; r < partial_rows; r += 32) {
+#pragma unroll 2
+    for (int r = rl; r < partial_rows; r += 128) {
       const float4 pw = __ldcs(reinterpret_cast<const float4*>(partial + (size_t)r * cols + c));
       const float4 pb = __ldcs(reinterpret_cast<const float4*>(partial + ((size_t)partial_rows + r) * cols + c));
       w.x += pw.x; w.y += pw.y; w.z += pw.z; w.w += pw.w;
@@ -362,7 +364,7 @@ ln_bwd_reduce4_kernel(const float* __restrict__ partial, __half* __restrict__ dg
   if (warp == 0 && lane < 8 && c < cols) {
     float4 tw = sw[0][q], tb = sb[0][q];
 #pragma unroll
-    for (int k = 1; k < 8; ++k) {
+    for (int k = 1; k < 32; ++k) {
       tw.x += sw[k][q].x; tw.y += sw[k][q].y; tw.z += sw[k][q].z; tw.w += sw[k][q].w;
       tb.x += sb[k][q].x; tb.y += sb[k][q].y; tb.z += sb[k][q].z; tb.w += sb[k][q].w;
     }
@@ -429,7 +431,7 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
   if (st != LEGO_OK) return st;
   if (cols % 4 == 0 && a16(partial) && ((uintptr_t)dgamma & 3) == 0 && ((uintptr_t)dbeta & 3) == 0)
-    ln_bwd_reduce4_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
+    ln_bwd_reduce4_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
                                                                     (int)cols, P.partial_rows);
   else
     ln_bwd_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
