@@ -183,11 +183,22 @@ enum { LEGO_ACT_NONE = 0, LEGO_ACT_LEAKY_RELU = 1 };
  * row-major [K,N]; 1: stored as row-major [N,K].  tile_order (nullable) is a
  * layout with logical dims (M/128, N/256) whose inv(pid) gives (pid_m, pid_n),
  * the grouped swizzle of benchmarks/triton/matmul_sympy.py:57-65; NULL = row-
- * major tile order.  M % 128 == 0, N % 256 == 0, K % 64 == 0 (the reference
- * kernel has no masks either).                                                 */
+ * major tile order.  Any M; N % 8 == 0, K % 8 == 0 (M % 8 == 0 with trans_a):
+ * rows are 16-byte multiples; tile edges are masked (the reference kernel has no
+ * masks and needs M % 128 == N % 256 == K % 64 == 0).                           */
 int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                       int32_t trans_a, int32_t trans_b, int32_t activation,
                       const lego_layout_t* tile_order, void* stream);
+
+/* The same GEMM with 8-bit floating-point operands (e5m2: 1 sign, 5 exponent, 2
+ * mantissa bits; torch.float8_e5m2), fp32 accumulate (tcgen05 kind::f8f6f4), fp16
+ * C; replaces matmul() called on fp8 tensors, benchmarks/triton/
+ * matmul_sympy.py:346-364 (TORCH_HAS_FP8 branch).  Arguments as lego_gemm_f16;
+ * operand rows are 16-byte multiples: K % 16 == 0, N % 16 == 0 unless trans_b,
+ * M % 16 == 0 with trans_a; N % 8 == 0 always (C is fp16).                      */
+int32_t lego_gemm_e5m2(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                       int32_t trans_a, int32_t trans_b, int32_t activation,
+                       const lego_layout_t* tile_order, void* stream);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by
  * persistent CTAs through the concatenated tile lists; replaces

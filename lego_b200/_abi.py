@@ -71,6 +71,8 @@ SIGNATURES = {
     "lego_layernorm_bwd_f16": (C.c_int32, [C.c_void_p] * 9 + [C.c_int64, C.c_int64, C.c_void_p]),
     "lego_gemm_f16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                   C.c_int32, C.c_int32, C.c_int32, LayoutP, C.c_void_p]),
+    "lego_gemm_e5m2": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                   C.c_int32, C.c_int32, C.c_int32, LayoutP, C.c_void_p]),
     "lego_grouped_gemm_f16": (C.c_int32, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                           C.POINTER(C.c_int64), C.c_int32, C.POINTER(LayoutP), C.c_void_p]),
     "lego_grouped_gemm_f16_static": (C.c_int32, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),

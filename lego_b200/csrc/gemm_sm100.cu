@@ -31,7 +31,24 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SUB_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major operand
+constexpr int SUB_BYTES = 64 * BK * 2;  // one 64 x 64 box of an MN-major fp16 operand
+
+// A stage always holds 128 bytes of K per row: 64 fp16 or 128 fp8 values.  What depends
+// on the element width: K values per stage, elements per 128-byte line of an MN-major
+// box, the size of such a box (k rows x 128 bytes), and the descriptor step from one MMA
+// to the next in an MN-major operand (MMA K rows x 128 bytes; 32 bytes when K-major).
+struct Geometry {
+  int bk, mn_box, sub_bytes;
+  uint32_t mn_kstep;
+};
+__host__ __device__ __forceinline__ Geometry geometry_of(int elem8) {
+  Geometry g;
+  g.bk = elem8 ? 2 * BK : BK;
+  g.mn_box = elem8 ? 128 : 64;
+  g.sub_bytes = g.bk * 128;
+  g.mn_kstep = (elem8 ? 4096u : 2048u) >> 4;
+  return g;
+}
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_STAGE_TOTAL = 4 * 2 * 32 * 64 * 2;  // epilogue staging, see EPI_BYTES
@@ -55,7 +72,7 @@ struct alignas(128) Problem {
   int32_t tile_start;   // first flat tile id of this problem
   int32_t a_mn_major;   // 1: A stored [K, M] row-major
   int32_t b_mn_major;   // 1: B stored [K, N] row-major
-  int32_t reserved;
+  int32_t elem8;        // 1: A and B hold 8-bit floats (e5m2), 0: fp16
   TileOrder order;
 };
 static_assert(sizeof(Problem) == 640, "Problem must stay 640 bytes: the device tables are sized for it");
@@ -217,7 +234,8 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
         }
         int tm, tn;
         tile_coords(*p, tile - p->tile_start, &tm, &tn);
-        const int kblocks = (p->k + BK - 1) / BK;
+        const Geometry geo = geometry_of(p->elem8);
+        const int kblocks = (p->k + geo.bk - 1) / geo.bk;
         const bool a_mn = p->a_mn_major != 0, b_mn = p->b_mn_major != 0;
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
@@ -230,18 +248,16 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
           const uint32_t b_dst = a_dst + A_BYTES;
           ptx::mbar_arrive_expect_tx(full, STAGE_BYTES);
           if (a_mn) {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              ptx::tma_load_2d(a_dst + j * SUB_BYTES, &p->tma_a, tm * BM + j * 64, kb * BK, full);
+            for (int j = 0; j < BM / geo.mn_box; ++j)
+              ptx::tma_load_2d(a_dst + j * geo.sub_bytes, &p->tma_a, tm * BM + j * geo.mn_box, kb * geo.bk, full);
           } else {
-            ptx::tma_load_2d(a_dst, &p->tma_a, kb * BK, tm * BM, full);
+            ptx::tma_load_2d(a_dst, &p->tma_a, kb * geo.bk, tm * BM, full);
           }
           if (b_mn) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              ptx::tma_load_2d(b_dst + j * SUB_BYTES, &p->tma_b, tn * BN + j * 64, kb * BK, full);
+            for (int j = 0; j < BN / geo.mn_box; ++j)
+              ptx::tma_load_2d(b_dst + j * geo.sub_bytes, &p->tma_b, tn * BN + j * geo.mn_box, kb * geo.bk, full);
           } else {
-            ptx::tma_load_2d(b_dst, &p->tma_b, kb * BK, tn * BN, full);
+            ptx::tma_load_2d(b_dst, &p->tma_b, kb * geo.bk, tn * BN, full);
           }
           ++issued[stage];
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -265,14 +281,17 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
         const Problem* p = problem_of(tile, &cursor);
-        const int kblocks = (p->k + BK - 1) / BK;
+        const Geometry geo = geometry_of(p->elem8);
+        const bool f8 = p->elem8 != 0;
+        const int kblocks = (p->k + geo.bk - 1) / geo.bk;
         const uint32_t a_mn = p->a_mn_major != 0, b_mn = p->b_mn_major != 0;
-        const uint32_t idesc = ptx::idesc_f16(BM, BN, a_mn, b_mn);
-        // K-major: 16 k values are 32 bytes inside the 128-byte swizzled row.
-        // MN-major: 16 k values are 16 rows of 128 bytes; 64-wide MN blocks follow at SUB_BYTES.
-        const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? SUB_BYTES : 16, 1024);
-        const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? SUB_BYTES : 16, 1024);
-        const uint32_t a_kstep = a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = b_mn ? (2048 >> 4) : (32 >> 4);
+        const uint32_t idesc = f8 ? ptx::idesc_f8(BM, BN, a_mn, b_mn, 1u) : ptx::idesc_f16(BM, BN, a_mn, b_mn);
+        // K-major: the K values of one MMA (16 fp16 / 32 fp8) are 32 bytes inside the 128-byte
+        // swizzled row.  MN-major: they are that many rows of 128 bytes; the next box of 128
+        // bytes of MN follows at sub_bytes.
+        const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? geo.sub_bytes : 16, 1024);
+        const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? geo.sub_bytes : 16, 1024);
+        const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
         const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
@@ -291,10 +310,17 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
           // Only the 14-bit start-address field of a descriptor changes from MMA to MMA.
           const uint32_t a_enc = smem_enc + stage * (STAGE_BYTES >> 4);
           const uint32_t b_enc = a_enc + (A_BYTES >> 4);
+          if (f8) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            ptx::mma_f16_ss(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep), db_fixed | (uint64_t)(b_enc + kk * b_kstep),
-                            idesc, (kb | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < BK / 16; ++kk)
+              ptx::mma_f8_ss(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep), db_fixed | (uint64_t)(b_enc + kk * b_kstep),
+                             idesc, (kb | kk) != 0 ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+              ptx::mma_f16_ss(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep), db_fixed | (uint64_t)(b_enc + kk * b_kstep),
+                              idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
           ptx::mma_commit(ptx::smem_u32(&bars->empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -430,7 +456,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
       auto enter = [&](Step& st) {  // position `st` on the first k-step of st.pair
         if (st.pair >= total_pairs) return;
         st.pr = problem_of(2 * st.pair, &st.cursor);
-        st.kblocks = (st.pr->k + BK - 1) / BK;
+        st.kblocks = (st.pr->k + geometry_of(st.pr->elem8).bk - 1) / geometry_of(st.pr->elem8).bk;
         st.kb = 0;
         int tn;
         tile_coords(*st.pr, 2 * st.pair + (int)rank - st.pr->tile_start, &st.tm, &tn);
@@ -464,19 +490,20 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         const uint32_t a_dst = ptx::smem_u32(smem + stage * P_STAGE_BYTES);
         const uint32_t b_dst = a_dst + P_A_BYTES;
         if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * P_STAGE_BYTES);  // both CTAs' bytes
+        const Geometry geo = geometry_of(pr->elem8);
         if (pr->a_mn_major) {
-#pragma unroll
-          for (int j = 0; j < BM / 64; ++j)
-            ptx::tma_load_2d_pair(a_dst + j * SUB_BYTES, &pr->tma_a, ld.tm * BM + j * 64, ld.kb * BK, full_leader);
+          for (int j = 0; j < BM / geo.mn_box; ++j)
+            ptx::tma_load_2d_pair(a_dst + j * geo.sub_bytes, &pr->tma_a, ld.tm * BM + j * geo.mn_box, ld.kb * geo.bk,
+                                  full_leader);
         } else {
-          ptx::tma_load_2d_pair(a_dst, &pr->tma_a, ld.kb * BK, ld.tm * BM, full_leader);
+          ptx::tma_load_2d_pair(a_dst, &pr->tma_a, ld.kb * geo.bk, ld.tm * BM, full_leader);
         }
         if (pr->b_mn_major) {
-#pragma unroll
-          for (int j = 0; j < P_BN_HALF / 64; ++j)
-            ptx::tma_load_2d_pair(b_dst + j * SUB_BYTES, &pr->tma_b, ld.n0 + j * 64, ld.kb * BK, full_leader);
+          for (int j = 0; j < P_BN_HALF / geo.mn_box; ++j)
+            ptx::tma_load_2d_pair(b_dst + j * geo.sub_bytes, &pr->tma_b, ld.n0 + j * geo.mn_box, ld.kb * geo.bk,
+                                  full_leader);
         } else {
-          ptx::tma_load_2d_pair(b_dst, &pr->tma_b, ld.kb * BK, ld.n0, full_leader);
+          ptx::tma_load_2d_pair(b_dst, &pr->tma_b, ld.kb * geo.bk, ld.n0, full_leader);
         }
         ++issued[stage];
         if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
@@ -502,13 +529,16 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
       const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
       for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid, ++it) {
         const Problem* pr = problem_of(2 * pair, &cursor);
-        const int kblocks = (pr->k + BK - 1) / BK;
+        const Geometry geo = geometry_of(pr->elem8);
+        const bool f8 = pr->elem8 != 0;
+        const int kblocks = (pr->k + geo.bk - 1) / geo.bk;
         const bool a_mn = pr->a_mn_major != 0, b_mn = pr->b_mn_major != 0;
-        const uint32_t idesc = ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+        const uint32_t idesc = f8 ? ptx::idesc_f8(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u, 1u)
+                                  : ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
         // Only the 14-bit start-address field of a descriptor changes from MMA to MMA.
-        const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? SUB_BYTES : 16, 1024);
-        const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? SUB_BYTES : 16, 1024);
-        const uint32_t a_kstep = a_mn ? (2048 >> 4) : (32 >> 4), b_kstep = b_mn ? (2048 >> 4) : (32 >> 4);
+        const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? geo.sub_bytes : 16, 1024);
+        const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? geo.sub_bytes : 16, 1024);
+        const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
           fail(status, abort_flag, 0x120000u | 0x100u | acc);
@@ -525,10 +555,17 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
           ptx::tc_fence_after();
           const uint32_t a_enc = smem_enc + stage * (P_STAGE_BYTES >> 4);
           const uint32_t b_enc = a_enc + (P_A_BYTES >> 4);
+          if (f8) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            ptx::mma_f16_ss_pair(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
-                                 db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (kb | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < BK / 16; ++kk)
+              ptx::mma_f8_ss_pair(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
+                                  db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (kb | kk) != 0 ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+              ptx::mma_f16_ss_pair(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
+                                   db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
           ptx::mma_commit_pair(ptx::smem_u32(&bars->empty[stage]), 3);  // frees the slot in both CTAs
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -575,11 +612,12 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
 
 // ---- host side ---------------------------------------------------------------------------
 
-// 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows.
+// 2-D tensor map of fp16 (elem_bytes 2) or 8-bit (elem_bytes 1) elements: `inner`
+// contiguous elements per row, `outer` rows.
 int32_t make_tmap(EncodeFn enc, CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
-                  uint32_t box_inner, uint32_t box_outer) {
-  return make_tmap_2d(enc, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, inner, outer, inner * 2, box_inner,
-                      box_outer);
+                  uint32_t box_inner, uint32_t box_outer, int elem_bytes = 2) {
+  return make_tmap_2d(enc, out, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base,
+                      inner, outer, inner * (uint64_t)elem_bytes, box_inner, box_outer);
 }
 
 int32_t fill_order(const lego_layout_t* order, int tiles_m, int tiles_n, TileOrder* out) {
@@ -606,11 +644,12 @@ int32_t fill_order(const lego_layout_t* order, int tiles_m, int tiles_n, TileOrd
 
 int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, void* C, int64_t M, int64_t N,
                      int64_t K, int trans_a, int trans_b, const lego_layout_t* order, int tile_start,
-                     int b_box_rows = BN) {
+                     int b_box_rows = BN, int elem8 = 0) {
   if (!A || !B || !C) return LEGO_ERR_NULL;
   if (M < 1 || N < 1 || K < 1 || M > 0x3fffffff || N > 0x3fffffff || K > 0x3fffffff) return LEGO_ERR_SIZE;
-  // 16-byte global strides for TMA and 16-byte C stores
-  if (N % 8 || K % 8 || (trans_a && M % 8)) return LEGO_ERR_SIZE;
+  // 16-byte global strides for TMA (8 fp16 or 16 fp8 values) and 16-byte rows of the fp16 C
+  const int per16 = elem8 ? 16 : 8;
+  if (N % 8 || K % per16 || (trans_a && M % per16) || (!trans_b && N % per16)) return LEGO_ERR_SIZE;
   if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return LEGO_ERR_ALIGN;
   std::memset(p, 0, sizeof(*p));
   p->c = (__half*)C;
@@ -622,12 +661,15 @@ int32_t fill_problem(EncodeFn enc, Problem* p, const void* A, const void* B, voi
   p->tile_start = tile_start;
   p->a_mn_major = trans_a ? 1 : 0;
   p->b_mn_major = trans_b ? 0 : 1;
+  p->elem8 = elem8 ? 1 : 0;
+  const Geometry geo = geometry_of(p->elem8);
+  const int eb = elem8 ? 1 : 2;
   int32_t st;
-  if (trans_a) st = make_tmap(enc, &p->tma_a, A, (uint64_t)M, (uint64_t)K, 64, BK);   // [K, M], M contiguous
-  else         st = make_tmap(enc, &p->tma_a, A, (uint64_t)K, (uint64_t)M, BK, BM);   // [M, K], K contiguous
+  if (trans_a) st = make_tmap(enc, &p->tma_a, A, (uint64_t)M, (uint64_t)K, geo.mn_box, geo.bk, eb);   // [K, M], M contiguous
+  else         st = make_tmap(enc, &p->tma_a, A, (uint64_t)K, (uint64_t)M, geo.bk, BM, eb);           // [M, K], K contiguous
   if (st != LEGO_OK) return st;
-  if (trans_b) st = make_tmap(enc, &p->tma_b, B, (uint64_t)K, (uint64_t)N, BK, b_box_rows);   // [N, K], K contiguous
-  else         st = make_tmap(enc, &p->tma_b, B, (uint64_t)N, (uint64_t)K, 64, BK);   // [K, N], N contiguous
+  if (trans_b) st = make_tmap(enc, &p->tma_b, B, (uint64_t)K, (uint64_t)N, geo.bk, b_box_rows, eb);   // [N, K], K contiguous
+  else         st = make_tmap(enc, &p->tma_b, B, (uint64_t)N, (uint64_t)K, geo.mn_box, geo.bk, eb);   // [K, N], N contiguous
   if (st != LEGO_OK) return st;
   st = make_tmap(enc, &p->tma_c, C, (uint64_t)N, (uint64_t)M, EPI_CHUNK_COLS, 32);      // [M, N], N contiguous
   if (st != LEGO_OK) return st;
@@ -772,9 +814,10 @@ using namespace lego;
 
 extern "C" {
 
-int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
-                      int32_t trans_a, int32_t trans_b, int32_t activation,
-                      const lego_layout_t* tile_order, void* stream) {
+// One GEMM, fp16 or e5m2 operands: CTA pairs when the tile order allows, else one CTA per tile.
+static int32_t run_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int32_t trans_a,
+                        int32_t trans_b, int32_t activation, const lego_layout_t* tile_order, int elem8,
+                        void* stream) {
   if (activation != LEGO_ACT_NONE && activation != LEGO_ACT_LEAKY_RELU) return LEGO_ERR_UNSUPPORTED;
   int32_t err = LEGO_OK;
   DeviceCtx* ctx = device_ctx(&err);
@@ -782,7 +825,7 @@ int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t 
   EncodeFn enc = encode_fn(&err);
   if (!enc) return err;
   Problem p;
-  int32_t st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0);
+  int32_t st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, BN, elem8);
   if (st != LEGO_OK) return st;
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
   if (total > 0x7fffffff) return LEGO_ERR_SIZE;
@@ -795,7 +838,7 @@ int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t 
     pairs = (n0 == n1);
   }
   if (pairs) {
-    st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF);
+    st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF, elem8);
     if (st != LEGO_OK) return st;
     int max_clusters = 0;
     st = configure_pair<false>(&max_clusters);
@@ -806,7 +849,7 @@ int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t 
                                                                                    ctx->status_word);
       return cuda_status(cudaGetLastError());
     }
-    st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0);
+    st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, BN, elem8);
     if (st != LEGO_OK) return st;
   }
   st = configure<false>();
@@ -815,6 +858,18 @@ int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t 
   gemm_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(p, nullptr, 1, (int)total, activation,
                                                                          ctx->status_word);
   return cuda_status(cudaGetLastError());
+}
+
+int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                      int32_t trans_a, int32_t trans_b, int32_t activation,
+                      const lego_layout_t* tile_order, void* stream) {
+  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 0, stream);
+}
+
+int32_t lego_gemm_e5m2(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                       int32_t trans_a, int32_t trans_b, int32_t activation,
+                       const lego_layout_t* tile_order, void* stream) {
+  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 1, stream);
 }
 
 int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* const* C,

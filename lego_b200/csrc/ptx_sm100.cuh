@@ -199,6 +199,19 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uin
       : "memory");
 }
 
+// Same with 8-bit floating-point inputs (kind::f8f6f4; K = 32 per instruction).
+__device__ __forceinline__ void mma_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // mbarrier arrives once every tcgen05 operation issued so far by this thread is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -273,6 +286,18 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a
       : "memory");
 }
 
+__device__ __forceinline__ void mma_f8_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // The mbarrier at this offset in every CTA of `cta_mask` arrives once the tcgen05
 // operations issued so far by this thread are done.
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask) {
@@ -311,6 +336,13 @@ __host__ __device__ __forceinline__ uint32_t idesc_f16(uint32_t m, uint32_t n, u
   d |= ((n >> 3) & 0x3Fu) << 17;
   d |= ((m >> 4) & 0x1Fu) << 24;
   return d;
+}
+
+// Instruction descriptor of kind::f8f6f4 with fp32 D: same fields; the A / B format codes
+// are 0 = e4m3, 1 = e5m2.
+__host__ __device__ __forceinline__ uint32_t idesc_f8(uint32_t m, uint32_t n, uint32_t a_mn_major, uint32_t b_mn_major,
+                                                      uint32_t format) {
+  return idesc_f16(m, n, a_mn_major, b_mn_major) | ((format & 7u) << 7) | ((format & 7u) << 10);
 }
 
 }  // namespace ptx

@@ -391,8 +391,9 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
     """``C = act(A @ B)``: fp16 in, fp32 accumulate, fp16 out.  Either operand may
     be a ``.T`` view.  Tile order defaults to the reference's grouped swizzle with
     ``GROUP_M = group_m`` when it is a bijection for the tile grid, row-major otherwise."""
-    if a.dtype != torch.float16 or b.dtype != torch.float16:
-        raise ValueError("matmul supports float16 operands")
+    if a.dtype != b.dtype or a.dtype not in (torch.float16, torch.float8_e5m2):
+        raise ValueError("matmul supports float16 operands, or float8_e5m2 operands (fp16 result)")
+    fn = "lego_gemm_f16" if a.dtype == torch.float16 else "lego_gemm_e5m2"
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
         raise ValueError("Incompatible dimensions")
     act = {"": _abi.ACT_NONE, "leaky_relu": _abi.ACT_LEAKY_RELU}.get(activation)
@@ -402,7 +403,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
     n = b.shape[1]
     lib = _abi.lib()
     if (not a.is_cuda and not b.is_cuda and a.is_contiguous() and tile_order is None
-            and a.numel() * 2 > 2 * _HOST_BLOCK_BYTES and m % 256 == 0):
+            and a.numel() * a.element_size() > 2 * _HOST_BLOCK_BYTES and m % 256 == 0):
         # Host operands: B goes in first, then A in blocks of rows; each block's rows of C
         # leave while the next block arrives.  Every block is its own GEMM with its own
         # default tile order.
@@ -418,13 +419,14 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         ad = torch.empty(a.shape, dtype=a.dtype, device=pipe.dev)
         c = torch.empty((m, n), dtype=torch.float16, device=pipe.dev)
         c_h = _pinned_like((m, n), torch.float16)
-        for r0, r1 in _row_blocks(m, max(k, n) * 2, multiple=256):
+        call = getattr(lib, fn)
+        for r0, r1 in _row_blocks(m, max(k * a.element_size(), n * 2), multiple=256):
             pipe.feed(ad[r0:r1], a[r0:r1])
             pipe.ready()
             npm, npn = -(-(r1 - r0) // 128), -(-n // 256)
             order = grouped_swizzle_layout(npm, npn, group_m) if (npm % group_m == 0 or npm <= group_m) else None
-            _abi.check(lib.lego_gemm_f16(ad[r0:r1].data_ptr(), b_st.data_ptr(), c[r0:r1].data_ptr(), r1 - r0, n, k,
-                                         0, tb, act, lower_optional(order), _stream()), "lego_gemm_f16")
+            _abi.check(call(ad[r0:r1].data_ptr(), b_st.data_ptr(), c[r0:r1].data_ptr(), r1 - r0, n, k,
+                            0, tb, act, lower_optional(order), _stream()), fn)
             pipe.drain(c_h[r0:r1], c[r0:r1])
         pipe.finish()
         return c_h
@@ -436,8 +438,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         npm, npn = -(-m // 128), -(-n // 256)
         if npm % group_m == 0 or npm <= group_m:
             tile_order = grouped_swizzle_layout(npm, npn, group_m)
-    _abi.check(lib.lego_gemm_f16(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
-                               lower_optional(tile_order), _stream()), "lego_gemm_f16")
+    _abi.check(getattr(lib, fn)(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
+                                lower_optional(tile_order), _stream()), fn)
     return _like_input(c, a)
 
 

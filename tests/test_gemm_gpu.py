@@ -136,3 +136,43 @@ def test_narrow_outputs_next_to_wide_ones():
         for _ in range(3):
             assert rel_fro(ops.matmul(a.cuda(), b.cuda()).cpu(), O.matmul(a, b)) <= REL_FRO, (m, n, k)
     ops.device_status()
+
+
+def _e5m2_pair(m, n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).half().to(torch.float8_e5m2)
+    b = torch.randn(k, n, generator=g).half().to(torch.float8_e5m2)
+    return a, b
+
+
+def test_e5m2_512_like_the_reference_check():
+    # the TORCH_HAS_FP8 branch of the reference's check: randn -> e5m2, allclose(atol=0.125)
+    # against the fp16 product of the same 8-bit values
+    a, b = _e5m2_pair(512, 512, 512, 0)
+    c = ops.matmul(a.cuda(), b.cuda()).cpu()
+    ops.device_status()
+    assert c.dtype == torch.float16
+    ref = O.matmul(a.float(), b.float())
+    assert rel_fro(c, ref) <= REL_FRO
+    assert torch.allclose(c.float(), ref.half().float(), atol=0.125, rtol=0)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_e5m2_operand_layouts_edges_and_both_kernels(ta, tb):
+    # (384, 768, 320): even tile rows -> CTA pairs, K not a multiple of the 128-wide stage;
+    # (400, 528, 144): ragged M and N, odd tile count -> one CTA per tile
+    for m, n, k in ((384, 768, 320), (400, 528, 144), (128, 256, 4096)):
+        a, b = _e5m2_pair(m, n, k, 31 + 2 * ta + tb + m)
+        ad = a.cuda().t().contiguous().t() if ta else a.cuda()
+        bd = b.cuda().t().contiguous().t() if tb else b.cuda()
+        c = ops.matmul(ad, bd).cpu()
+        ops.device_status()
+        ref = O.matmul(a.float(), b.float())
+        assert rel_fro(c, ref) <= REL_FRO, (ta, tb, m, n, k)
+    a, b = _e5m2_pair(256, 256, 256, 77)
+    got = ops.matmul(a.cuda(), b.cuda(), activation="leaky_relu").cpu()
+    assert rel_fro(got, O.matmul(a.float(), b.float(), "leaky_relu")) <= REL_FRO
+    with pytest.raises(ValueError):
+        ops.matmul(a.cuda(), b.cuda().half())                      # mixed operand types
+    with pytest.raises(ValueError):
+        ops.matmul(a.cuda()[:, :200].contiguous(), b.cuda()[:200])  # K = 200 is not a multiple of 16
