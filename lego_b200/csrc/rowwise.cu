@@ -147,25 +147,42 @@ row_kernel(const __grid_constant__ RowParams P) {
 
 // ---- bulk-copy pipelined kernel ------------------------------------------------------
 //
-// For rows of 1 Ki .. 8 Ki elements whose bytes are a multiple of 16: a producer
-// warp streams whole rows into a shared-memory ring with 1-D bulk copies
-// (cp.async.bulk, completion on mbarriers) while 256 consumer threads pull a row
-// into registers with 128-bit shared-memory loads, free the slot at once, reduce
-// and write the result with 128-bit streaming stores.  The ring keeps several rows
-// per CTA in flight without spending registers or load instructions on them; the
-// row a slot holds is named by the producer next to the data.  gamma / beta of
-// LayerNorm are staged in shared memory once per CTA.
+// For rows of 1 Ki .. 8 Ki elements whose bytes are a multiple of 16.  One CTA per SM:
+// a producer thread streams whole rows into a shared-memory ring with 1-D bulk copies
+// (cp.async.bulk, completion on mbarriers); two or three groups of 256 consumer threads
+// each take every second / third row: pull it into registers with 128-bit shared-memory
+// loads, free the slot at once, reduce within the group (named barrier) and write the
+// result with 128-bit streaming stores.  One CTA with several consumer groups instead of
+// several CTAs per SM because the memory system prefers few row streams per SM: a plain
+// copy through this ring ran at 0.955 of the copy peak with one CTA per SM, 0.915 with
+// two and 0.89 with three.  The row a slot holds is named by the producer next to the
+// data.  gamma / beta of LayerNorm are staged in shared memory once per CTA.
 
 constexpr int kRing = 8;          // most ring slots a CTA may use
-constexpr int kConsumers = 256;
+constexpr int kConsumers = 256;   // threads of one consumer group
+constexpr int kMaxGroups = 3;
 constexpr long long kWaitLimit = 2000000000LL;  // SM cycles, about a second
 
 struct RingCtl {
   uint64_t full[kRing];
   uint64_t empty[kRing];
   int64_t row[kRing];
-  uint32_t abort_flag;
+  uint32_t abort_flag;               // any role gave up: polled inside every bounded wait
+  uint32_t group_abort[kMaxGroups];  // written only by the group's own threads, read after its barrier
 };
+
+// Reduction over the 256 threads of one consumer group (named barrier `bar`).
+template <bool IS_MAX>
+__device__ __forceinline__ float group_reduce(float v, float* slots, int bar) {
+  v = warp_reduce<IS_MAX>(v);
+  const int warp = (threadIdx.x >> 5) & 7, lane = threadIdx.x & 31;
+  if (lane == 0) slots[warp] = v;
+  asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(kConsumers) : "memory");
+  float r = slots[0];
+#pragma unroll
+  for (int w = 1; w < kConsumers / 32; ++w) r = IS_MAX ? fmaxf(r, slots[w]) : r + slots[w];
+  return r;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -174,8 +191,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int OP, typename T, int EPT>
-__global__ void __launch_bounds__(kConsumers + 32)
-row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* status) {
+__global__ void __launch_bounds__(kMaxGroups * kConsumers + 32, 1)
+row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uint32_t* status) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int NV = EPT / VEC;
   extern __shared__ __align__(128) uint8_t ring_smem[];
@@ -184,10 +201,11 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
   const uint32_t slot_bytes = (row_bytes + 127u) & ~127u;
   uint8_t* params_smem = ring_smem + (size_t)stages * slot_bytes;  // gamma | beta (LayerNorm)
   RingCtl* ctl = reinterpret_cast<RingCtl*>(params_smem + (OP == OP_LAYERNORM ? 2 * slot_bytes : 0));
-  __shared__ float slots[2][32];
+  __shared__ float slots_all[kMaxGroups][2][8];
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
   const int tid = threadIdx.x;
+  const int n_consumers = groups * kConsumers;
   const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (tid == 0) {
@@ -196,6 +214,7 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
       ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), kConsumers / 32);
     }
     ctl->abort_flag = 0;
+    for (int g = 0; g < kMaxGroups; ++g) ctl->group_abort[g] = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
   }
@@ -211,9 +230,9 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
   }
   __syncthreads();
 
-  if (tid >= kConsumers) {
+  if (tid >= n_consumers) {
     // ---------------- producer ----------------
-    if (tid == kConsumers) {
+    if (tid == n_consumers) {
       const T* __restrict__ x = reinterpret_cast<const T*>(P.x);
       int64_t issued = 0;
       for (int64_t n = 0; n < my_rows; ++n) {
@@ -244,15 +263,23 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
     return;
   }
 
-  // ---------------- consumers ----------------
+  // ---------------- consumers: group g takes rows g, g + groups, ... of this CTA ----------------
+  // The slot count is a multiple of the group count, so a slot is always drained by the same
+  // group (a waiter two uses ahead of an mbarrier could not tell its phase from the one two back).
   T* __restrict__ y = reinterpret_cast<T*>(P.y);
+  const int group = tid / kConsumers;
+  const int gtid = tid - group * kConsumers;  // thread within the group
   const int lane = tid & 31;
-  for (int64_t n = 0; n < my_rows; ++n) {
+  const int bar = 1 + group;
+  float (*slots)[8] = slots_all[group];
+  volatile uint32_t* group_abort = &ctl->group_abort[group];
+  for (int64_t n = group; n < my_rows; n += groups) {
     const int s = (int)(n % stages);
     const uint32_t use = (uint32_t)(n / stages);
     const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kWaitLimit);
     if (!ok) {
       *abort_flag = 1;
+      *group_abort = 1;
       atomicCAS(status, 0u, 0x50000u | (uint32_t)s);
     }
     const int64_t row = ok ? ctl->row[s] : 0;
@@ -261,9 +288,9 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int c = (k * kConsumers + tid) * VEC;
+      const int c = (k * kConsumers + gtid) * VEC;
       if (ok && c < cols) {
-        Elem<T>::unpack(slot[k * kConsumers + tid], v + k * VEC);
+        Elem<T>::unpack(slot[k * kConsumers + gtid], v + k * VEC);
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) v[k * VEC + e] = fill;
@@ -276,8 +303,8 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
       float m = v[0];
 #pragma unroll
       for (int k = 1; k < EPT; ++k) m = fmaxf(m, v[k]);
-      m = row_reduce<kConsumers, true, 1>(m, slots[0]);
-      if (*abort_flag) break;  // uniform: every flag write of this row precedes the barrier above
+      m = group_reduce<true>(m, slots[0], bar);
+      if (*group_abort) break;  // uniform: the group's own flag writes of this row precede the barrier above
       const float ms = m * 1.4426950408889634f;
       float sum = 0.f;
 #pragma unroll
@@ -285,12 +312,12 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
         v[k] = fast_exp2(fmaf(v[k], 1.4426950408889634f, -ms));
         sum += v[k];
       }
-      sum = row_reduce<kConsumers, false, 1>(sum, slots[1]);
+      sum = group_reduce<false>(sum, slots[1], bar);
       const float inv = 1.0f / sum;
       T* __restrict__ yrow = y + row * cols;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const int c = (k * kConsumers + tid) * VEC;
+        const int c = (k * kConsumers + gtid) * VEC;
         if (c < cols) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) v[k * VEC + e] *= inv;
@@ -301,13 +328,13 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
       float sum = 0.f;
 #pragma unroll
       for (int k = 0; k < EPT; ++k) sum += v[k];
-      sum = row_reduce<kConsumers, false, 1>(sum, slots[0]);
-      if (*abort_flag) break;
+      sum = group_reduce<false>(sum, slots[0], bar);
+      if (*group_abort) break;
       const float mean = sum / (float)cols;
       float q = 0.f;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const bool in = (k * kConsumers + tid) * VEC < cols;
+        const bool in = (k * kConsumers + gtid) * VEC < cols;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float d = in ? v[k * VEC + e] - mean : 0.f;
@@ -315,9 +342,9 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
           q = fmaf(d, d, q);
         }
       }
-      q = row_reduce<kConsumers, false, 1>(q, slots[1]);
+      q = group_reduce<false>(q, slots[1], bar);
       const float rstd = 1.0f / sqrtf(q / (float)cols + P.eps);
-      if (tid == 0) {
+      if (gtid == 0) {
         P.mean[row] = mean;
         P.rstd[row] = rstd;
       }
@@ -326,11 +353,11 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, uint32_t* statu
       T* __restrict__ yrow = y + row * cols;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const int c = (k * kConsumers + tid) * VEC;
+        const int c = (k * kConsumers + gtid) * VEC;
         if (c < cols) {
           float g[VEC], b[VEC];
-          Elem<T>::unpack(sg[k * kConsumers + tid], g);
-          Elem<T>::unpack(sb[k * kConsumers + tid], b);
+          Elem<T>::unpack(sg[k * kConsumers + gtid], g);
+          Elem<T>::unpack(sb[k * kConsumers + gtid], b);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) v[k * VEC + e] = fmaf(v[k * VEC + e] * rstd, g[e], b[e]);
           __stcs(reinterpret_cast<uint4*>(yrow + c), Elem<T>::pack(v + k * VEC));
@@ -346,33 +373,26 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const size_t row_bytes = (size_t)P.cols * sizeof(T);
   const size_t slot = (row_bytes + 127) & ~(size_t)127;
   const size_t fixed = (OP == OP_LAYERNORM ? 2 * slot : 0) + sizeof(RingCtl) + 128;
-  // CTAs per SM by registers / threads, then as many ring slots as shared memory allows
-  static int per_sm_regs = 0;
-  if (!per_sm_regs) {
+  static bool configured = false;
+  if (!configured) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));  // static part: reduction slots
-    LEGO_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_regs, kern, kConsumers + 32, 0));
-    if (per_sm_regs < 1) per_sm_regs = 1;
+    configured = true;
   }
-  // Measured on B200 (16384 x 8192 fp16): one CTA turns a row around in about 2500
-  // cycles, so two (softmax) or three (LayerNorm) per SM saturate HBM; more CTAs only
-  // add contention on the special-function pipe and lower the achieved bandwidth.
-  int per_sm = per_sm_regs;
-  const int want = OP == OP_SOFTMAX ? 2 : 3;
-  if (per_sm > want) per_sm = want;
-  int stages = 0;
-  for (; per_sm >= 1; --per_sm) {
-    const size_t budget = (size_t)(228 * 1024) / per_sm - 1024 - 1024;  // per-CTA share minus static and reserved
-    if (budget <= fixed) continue;
-    stages = (int)((budget - fixed) / slot);
-    if (stages > 4) stages = 4;
-    if (stages >= 2) break;
-  }
-  if (per_sm < 1 || stages < 2) return LEGO_ERR_UNSUPPORTED;
+  // Measured on B200 (16384 x 8192 fp16), same box, GB/s: one group turns a row around in
+  // about 2500 cycles, so two groups (softmax: 6260; three: 5580, they fight over the
+  // special-function pipe) or three (LayerNorm: 6390; two: 5410) keep up with HBM.  Six ring
+  // slots are the sweet spot for both (softmax 4 / 6 / 8 slots: 6170 / 6260 / 6260;
+  // LayerNorm 3 / 6 / 9 / 12 slots: 5930 / 6390 / 6060 / 5930).
+  const int groups = OP == OP_SOFTMAX ? 2 : 3;
+  const size_t budget = (size_t)ctx->smem_optin - 1024 - fixed;
+  int stages = (int)(budget / slot);
+  if (stages > 6) stages = 6;
+  stages -= stages % groups;  // a slot always belongs to one group
+  if (stages < groups) return LEGO_ERR_UNSUPPORTED;
   const size_t smem = (size_t)stages * slot + fixed;
-  if (smem > (size_t)ctx->smem_optin - 1024) return LEGO_ERR_UNSUPPORTED;
-  int64_t grid = (int64_t)ctx->sm_count * per_sm;
+  int64_t grid = ctx->sm_count;
   if (grid > P.rows) grid = P.rows;
-  kern<<<(unsigned)grid, kConsumers + 32, smem, s>>>(P, stages, ctx->status_word);
+  kern<<<(unsigned)grid, groups * kConsumers + 32, smem, s>>>(P, stages, groups, ctx->status_word);
   return cuda_status(cudaGetLastError());
 }
 
