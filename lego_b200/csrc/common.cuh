@@ -1,6 +1,8 @@
 // Shared helpers of the CUDA translation units.
 #pragma once
 
+#include <utility>
+
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -22,6 +24,26 @@ inline int32_t cuda_status(cudaError_t e) {
       return ::lego::cuda_status(_e);                          \
     }                                                          \
   } while (0)
+
+// Launch with programmatic stream serialization: the grid may become resident, and run
+// everything before its ptx::grid_dependency_wait(), while the previous grid in the
+// stream (if it called ptx::launch_dependents()) is still draining.  Kernels launched this
+// way touch global memory only after that wait.  Also valid under stream capture.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // Per-device facts and the lazily created workspace.
 struct DeviceCtx {

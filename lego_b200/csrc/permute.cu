@@ -54,7 +54,7 @@ struct TmaParams {
   int64_t pitch;    // elements between consecutive rows of the input tensor map
   int64_t s_out_i;  // output stride of the input-contiguous digit (elements)
   int32_t stages;   // ring slots per CTA
-  int32_t reserved;
+  int32_t one_load; // 1: the tensor map is group-major, one TMA load fetches a whole tile
 };
 
 struct Plan {
@@ -232,17 +232,17 @@ tiled_transpose_kernel(const __grid_constant__ TiledParams P, const uint8_t* __r
 // times 8 * (16 / EB) rows (32 x 32 fp32, 64 x 64 fp16, 16 x 16 fp64).
 //   planner   (1 warp)  evaluates tile_order.inv and both layouts' strides for 32
 //             tiles at a time, one tile per lane, fully converged, into a queue;
-//   producer  (1 lane)  takes queue entries in order: waits for the ring slot,
-//             publishes the tile's output offset and issues 16/EB TMA loads (128-byte
-//             swizzle) through a 3-D map that gathers every (16/EB)-th row, so loads
-//             cost no thread instructions and up to kTmaStages tiles per CTA are in
-//             flight;
+//   producer  (1 warp, lane l owns ring slot l, lanes in lock step)  takes queue entries
+//             a round of slots at a time: waits for the slot, publishes the tile's output
+//             offset and issues one TMA load (128-byte swizzle) through a 3-D map whose
+//             box gathers every (16/EB)-th row into one 8-row block of the slot (or
+//             16/EB loads through the row-group map if the driver refuses that map);
 //   consumers (8 warps, in pairs)  read a (16/EB) x (16/EB) block per thread with
 //             conflict-free 128-bit shared-memory loads, transpose it in registers
 //             and write 128-bit vectors; a quarter-warp fills one whole output line.
 // Tiles are dealt to CTAs round-robin in tile-order sequence.
 
-constexpr int kTmaStages = 16;
+constexpr int kTmaStages = 32;   // one producer lane per slot
 constexpr int kTmaConsumerWarps = 8;
 constexpr int kTmaThreads = 32 * (2 + kTmaConsumerWarps);
 constexpr int kPlanBatch = 32;
@@ -297,6 +297,11 @@ tma_transpose_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_cons
     ptx::fence_proxy_async();
   }
   __syncthreads();
+  // Let the next grid of the stream start its own set-up now; and touch global memory only
+  // once the previous grid is complete.  The planner warp works from kernel parameters and
+  // shared memory alone, so it runs ahead of that wait.
+  ptx::launch_dependents();
+  if (warp != kTmaConsumerWarps + 1) ptx::grid_dependency_wait();
 
   if (warp == kTmaConsumerWarps + 1) {
     // ---------------- planner: one tile per lane, 32 tiles per batch ----------------
@@ -356,49 +361,55 @@ tma_transpose_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_cons
   }
 
   if (warp == kTmaConsumerWarps) {
-    // ---------------- producer: one lane, slots in order ----------------
-    if (lane == 0) {
-      int64_t issued = 0;
-      for (int64_t n = 0; n < my_tiles; ++n) {
-        const int64_t k = n / kPlanBatch;
-        const int b = (int)(k & 1), q = (int)(n % kPlanBatch);
-        if (q == 0 &&
-            !ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->plan_full[b]), (uint32_t)((k >> 1) & 1), abort_flag,
+    // ---------------- producer: lane l owns ring slot l ----------------
+    // The lanes work in lock step, one round of `stages` tiles at a time, so the latencies of
+    // the plan read, the barrier polls and the TMA issue overlap across up to 32 tiles
+    // instead of adding up in one thread; no per-tile division is needed either.
+    uint32_t uses = 0;       // loads this lane has issued into its slot
+    bool failed = false;
+    for (int64_t base = 0; base < my_tiles; base += stages) {
+      const int64_t n = base + lane;
+      const bool active = lane < stages && n < my_tiles;
+      const int64_t k = n / kPlanBatch;
+      const int b = (int)(k & 1), q = (int)(n % kPlanBatch);
+      if (active) {
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->plan_full[b]), (uint32_t)((k >> 1) & 1), abort_flag,
                                     kTmaWaitLimit)) {
           *abort_flag = 1;
           atomicCAS(status, 0u, 0x90000u | (uint32_t)b);
-          break;
+          failed = true;
         }
+      }
+      if (__any_sync(0xffffffffu, failed)) break;
+      if (active) {
         const PlanEntry e = ctl->plan[b][q];
-        const bool last_of_batch = (q == kPlanBatch - 1) || (n + 1 == my_tiles);
-        if (e.cx >= 0) {
-          const int s = (int)(n % stages);
-          const uint32_t use = (uint32_t)(n / stages);
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kTmaWaitLimit)) {
-            *abort_flag = 1;
-            atomicCAS(status, 0u, 0x60000u | (uint32_t)s);
-            break;
-          }
-          ctl->out_base[s] = e.out_base;
-          const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[lane]), (uses & 1) ^ 1, abort_flag, kTmaWaitLimit)) {
+          *abort_flag = 1;
+          atomicCAS(status, 0u, 0x60000u | (uint32_t)lane);
+          failed = true;
+        } else {
+          ctl->out_base[lane] = e.out_base;
+          const uint32_t full = ptx::smem_u32(&ctl->full[lane]);
           ptx::mbar_arrive_expect_tx(full, TILE_BYTES);
           // rows k, k + VE, k + 2 VE, ... of the tile go to the k-th 8-row group of the slot
+          if (P.one_load) {
+            ptx::tma_load_3d(ptx::smem_u32(tiles + lane * TILE_BYTES), &tmap, e.cx, e.cy / VE, 0, full);
+          } else {
 #pragma unroll
-          for (int k = 0; k < VE; ++k)
-            ptx::tma_load_3d(ptx::smem_u32(tiles + s * TILE_BYTES + k * 1024), &tmap, e.cx, k, e.cy / VE, full);
-          ++issued;
-        }
-        if (last_of_batch) ptx::mbar_arrive(ptx::smem_u32(&ctl->plan_empty[b]));
-      }
-      if (*abort_flag) {
-        // leave no copy of ours in flight: the last use of every slot that was filled
-        uint32_t never = 0;
-        for (int s = 0; s < stages; ++s) {
-          const int64_t uses = issued > s ? (issued - s + stages - 1) / stages : 0;
-          if (uses)
-            ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kTmaWaitLimit);
+            for (int kk = 0; kk < VE; ++kk)
+              ptx::tma_load_3d(ptx::smem_u32(tiles + lane * TILE_BYTES + kk * 1024), &tmap, e.cx, kk, e.cy / VE, full);
+          }
+          ++uses;
         }
       }
+      __syncwarp();  // every lane has read its plan entry before a batch is handed back
+      if (active && (q == kPlanBatch - 1 || n + 1 == my_tiles)) ptx::mbar_arrive(ptx::smem_u32(&ctl->plan_empty[b]));
+      if (__any_sync(0xffffffffu, failed)) break;
+    }
+    if (*abort_flag && uses) {
+      // leave no copy of ours in flight: the last load into this lane's slot
+      uint32_t never = 0;
+      ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[lane]), (uses - 1) & 1, &never, kTmaWaitLimit);
     }
     return;
   }
@@ -412,9 +423,14 @@ tma_transpose_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_cons
   // 128-byte line of the output.
   const int rb = lane & 7;
   const int cb = ((warp & 1) << 2) + (lane >> 3);
-  for (int64_t n = pair; n < my_tiles; n += kTmaConsumerWarps / 2) {
-    const int s = (int)(n % stages);
-    const uint32_t use = (uint32_t)(n / stages);
+  // The slot count is a multiple of the pair count: this pair walks slots pair, pair + pairs, ...
+  int s = pair;
+  uint32_t use = 0;
+  for (int64_t n = pair; n < my_tiles; n += kTmaConsumerWarps / 2, s += kTmaConsumerWarps / 2) {
+    if (s >= stages) {
+      s -= stages;
+      ++use;
+    }
     if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kTmaWaitLimit)) {
       *abort_flag = 1;
       atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
@@ -689,41 +705,53 @@ int32_t launch_tma(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cu
   EncodeFn enc = encode_fn(&err);
   if (!enc) return err;
   TmaParams tp = pl.tma;
-  // Measured on B200 (fp32 4096^2 and 8192^2, column- and row-major tile orders):
-  // three CTAs per SM; a shallow ring (4 tiles) for large problems and 8 tiles below
-  // 32 Ki tiles were the best of a sweep over 2..6 CTAs x 4..16 slots; deeper rings
-  // lose up to 20 %.  A slot must always be drained by the same consumer pair (a
-  // waiter two uses ahead of an mbarrier cannot tell its phase from the one two
-  // back), so the slot count is a multiple of the number of pairs.
-  const int ctas_per_sm = 3;
-  const int stages = tp.n_tiles >= 32768 ? 4 : 8;
+  if (tp.n_tiles >= ((int64_t)1 << 31)) return LEGO_ERR_SIZE;
+  // Measured on B200 (fp32 4096^2, back-to-back launches): two CTAs per SM with eight ring
+  // slots each (5.74 TB/s); 1 x 16 or 1 x 32 slots 5.45, 3 x 4 slots 5.40, 3 x 8 slots 5.2,
+  // 2 x 4 slots 4.8, 2 x 16 slots 5.0; 4, 8 or 16 consumer warps make no difference.  About 64 KiB
+  // of tiles in flight per SM is enough, and leaving half of the SM's shared memory and
+  // thread slots free lets the next grid of the stream become resident and plan its first
+  // tiles while this one drains (programmatic dependent launch).  The tile order (row-,
+  // column-major, 2 x 2 .. 16 x 16 blocks) moves the result by less than 3 %.  A slot must
+  // always be drained by the same consumer pair (a waiter two uses ahead of an mbarrier
+  // cannot tell its phase from the one two back), so the slot count is a multiple of the
+  // number of pairs.
+  const int ctas_per_sm = 2;
+  const int stages = 8;
   static_assert(kTmaStages % (kTmaConsumerWarps / 2) == 0, "slots per consumer pair");
   tp.stages = stages;
   const size_t SMEM = (size_t)stages * TILE_BYTES + sizeof(TmaCtl) + 1024;
   CUtensorMap tmap;
   const CUtensorMapDataType dt = EB == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
                                : EB == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT64;
-  err = make_tmap_row_groups(enc, &tmap, dt, in, (uint64_t)tp.pitch, (uint64_t)(pl.size / tp.pitch),
-                             (uint64_t)tp.pitch * EB, 16 / EB, 128 / EB, 8);
+  err = make_tmap_group_major(enc, &tmap, dt, in, (uint64_t)tp.pitch, (uint64_t)(pl.size / tp.pitch),
+                              (uint64_t)tp.pitch * EB, 16 / EB, 128 / EB, 8);
+  tp.one_load = err == LEGO_OK ? 1 : 0;
+  if (err != LEGO_OK)
+    err = make_tmap_row_groups(enc, &tmap, dt, in, (uint64_t)tp.pitch, (uint64_t)(pl.size / tp.pitch),
+                               (uint64_t)tp.pitch * EB, 16 / EB, 128 / EB, 8);
   if (err != LEGO_OK) return err;
-  static bool configured[2] = {false, false};
+  static size_t configured[2] = {0, 0};  // dynamic shared memory each instantiation is set up for
   const int wide = tp.p1.wide ? 1 : 0;
-  if (!configured[wide]) {
-    const int max_smem = kTmaStages * TILE_BYTES + (int)sizeof(TmaCtl) + 1024;
+  if (configured[wide] < SMEM) {
     if (wide) LEGO_CUDA_TRY(cudaFuncSetAttribute(tma_transpose_kernel<EB, true>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     else LEGO_CUDA_TRY(cudaFuncSetAttribute(tma_transpose_kernel<EB, false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    configured[wide] = true;
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    configured[wide] = SMEM;
   }
   int64_t grid = (int64_t)ctx->sm_count * ctas_per_sm;
   if (grid > tp.n_tiles) grid = tp.n_tiles;
   if (grid < 1) grid = 1;
+  cudaError_t e;
   if (wide)
-    tma_transpose_kernel<EB, true><<<(unsigned)grid, kTmaThreads, SMEM, s>>>(tmap, tp, (uint8_t*)out, ctx->status_word);
+    e = launch_overlapped(tma_transpose_kernel<EB, true>, dim3((unsigned)grid), dim3(kTmaThreads), SMEM, s, tmap, tp,
+                          (uint8_t*)out, ctx->status_word);
   else
-    tma_transpose_kernel<EB, false><<<(unsigned)grid, kTmaThreads, SMEM, s>>>(tmap, tp, (uint8_t*)out, ctx->status_word);
-  return cuda_status(cudaGetLastError());
+    e = launch_overlapped(tma_transpose_kernel<EB, false>, dim3((unsigned)grid), dim3(kTmaThreads), SMEM, s, tmap, tp,
+                          (uint8_t*)out, ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
 }
 
 template <int VB>

@@ -157,6 +157,12 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return *reinterpret_cast<float2*>(&d);
 }
 
+// Programmatic dependent launch.  launch_dependents: the next grid in the stream may start
+// becoming resident now.  grid_dependency_wait: block until every grid this one depends on
+// has completed and its memory is visible (returns at once for an ordinary launch).
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Barrier among a subset of the CTA's warps (id 1..15; `threads` a multiple of 32).
 template <int ID, int THREADS>
 __device__ __forceinline__ void named_barrier() {

@@ -63,4 +63,22 @@ inline int32_t make_tmap_row_groups(EncodeFn enc, CUtensorMap* out, CUtensorMapD
   return r == CUDA_SUCCESS ? LEGO_OK : LEGO_ERR_UNSUPPORTED;
 }
 
+// The same rows seen as (x, g, k): the group index before the row-in-group index, so that
+// one box {box_inner, box_groups, group} lands in shared memory as `group` blocks of
+// box_groups rows each: block k holds rows k, k + group, k + 2 group, ...  The stride of
+// the last dimension (one row) is smaller than that of the middle one (one group); the
+// driver may refuse such a map, in which case the caller gathers with one load per k.
+inline int32_t make_tmap_group_major(EncodeFn enc, CUtensorMap* out, CUtensorMapDataType dt, const void* base,
+                                     uint64_t inner, uint64_t rows, uint64_t pitch_bytes, uint32_t group,
+                                     uint32_t box_inner, uint32_t box_groups) {
+  const cuuint64_t dims[3] = {inner, rows / group, group};
+  const cuuint64_t strides[2] = {pitch_bytes * group, pitch_bytes};
+  const cuuint32_t box[3] = {box_inner, box_groups, group};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LEGO_OK : LEGO_ERR_UNSUPPORTED;
+}
+
 }  // namespace lego
