@@ -6,6 +6,7 @@
 // other layout runs the staged interpreter, which re-cuts and permutes the flat
 // id stage by stage in 64-bit arithmetic exactly as lego/lego.py:388-433 does.
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 #include "staged.cuh"
 
 namespace lego {
@@ -153,6 +154,8 @@ digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int6
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t block_end = (begin + n + 1023) >> 10;
+  ptx::launch_dependents();   // the next grid of the stream may set itself up now
+  ptx::grid_dependency_wait();  // stores only once the previous grid is complete
   for (int64_t blk = (begin >> 10) + warp; blk < block_end; blk += n_warps) {
     const uint32_t base = (uint32_t)(blk << 10);
     uint32_t run_sum = 0;
@@ -244,8 +247,10 @@ static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t*
         const int64_t id_blocks = ((begin + n + 1023) >> 10) - (begin >> 10);
         const int64_t want = (id_blocks + 7) / 8, most = (int64_t)ctx->sm_count * 64;
         const int vec = (begin % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) ? 1 : 0;
-        digit_range_warp_kernel<<<(int)(want < most ? want : most), threads, 0, s>>>(w, n_fast, out, begin, n, vec);
-        return cuda_status(cudaGetLastError());
+        const cudaError_t e = launch_overlapped(digit_range_warp_kernel, dim3((unsigned)(want < most ? want : most)),
+                                                dim3(threads), 0, s, w, n_fast, out, begin, n, vec);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        return cuda_status(e);
       }
     }
     if (MODE == MODE_RANGE && !p.wide && p.n_terms <= kFastTerms)

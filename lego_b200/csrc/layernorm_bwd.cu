@@ -158,6 +158,8 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
     ptx::fence_proxy_async();
   }
   __syncthreads();
+  ptx::launch_dependents();     // the column reduction (or the next op) may set itself up now
+  ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
 
   if (tid >= kBwdConsumers) {
     // ---------------- producer ----------------
@@ -323,8 +325,9 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
   const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
   P.partial_rows = grid;
-  kern<<<grid, kBwdConsumers + 32, smem, s>>>(P, stages, ctx->status_word);
-  return cuda_status(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(kBwdConsumers + 32), smem, s, P, stages, ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
 }
 
 // Column reduction for widths that are a multiple of 4: a CTA of 32 warps sums 32 columns;
@@ -340,6 +343,8 @@ ln_bwd_reduce4_kernel(const float* __restrict__ partial, __half* __restrict__ dg
   const int q = lane & 7, rl = (lane >> 3) + 4 * warp;
   const int c = blockIdx.x * 32 + q * 4;
   float4 w = make_float4(0.f, 0.f, 0.f, 0.f), b = w;
+  ptx::launch_dependents();
+  ptx::grid_dependency_wait();  // the partial rows are complete and visible after this
   if (c < cols) {
 #pragma unroll 2
     for (int r = rl; r < partial_rows; r += 128) {
@@ -430,12 +435,15 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   }
   if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
   if (st != LEGO_OK) return st;
-  if (cols % 4 == 0 && a16(partial) && ((uintptr_t)dgamma & 3) == 0 && ((uintptr_t)dbeta & 3) == 0)
-    ln_bwd_reduce4_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
-                                                                    (int)cols, P.partial_rows);
-  else
-    ln_bwd_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
-                                                                   (int)cols, P.partial_rows);
+  if (cols % 4 == 0 && a16(partial) && ((uintptr_t)dgamma & 3) == 0 && ((uintptr_t)dbeta & 3) == 0) {
+    const cudaError_t e = launch_overlapped(ln_bwd_reduce4_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(1024), 0, s,
+                                            (const float*)partial, (__half*)dgamma, (__half*)dbeta, (int)cols,
+                                            (int)P.partial_rows);
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    return cuda_status(e);
+  }
+  ln_bwd_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, s>>>(partial, (__half*)dgamma, (__half*)dbeta,
+                                                                 (int)cols, P.partial_rows);
   return cuda_status(cudaGetLastError());
 }
 

@@ -218,6 +218,10 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
   }
+  // The next grid of the stream may set itself up now; global memory is touched only once
+  // the previous grid is complete (programmatic dependent launch).
+  ptx::launch_dependents();
+  ptx::grid_dependency_wait();
   if (OP == OP_LAYERNORM) {
     const uint4* g = reinterpret_cast<const uint4*>(P.gamma);
     const uint4* b = reinterpret_cast<const uint4*>(P.beta);
@@ -392,8 +396,10 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const size_t smem = (size_t)stages * slot + fixed;
   int64_t grid = ctx->sm_count;
   if (grid > P.rows) grid = P.rows;
-  kern<<<(unsigned)grid, groups * kConsumers + 32, smem, s>>>(P, stages, groups, ctx->status_word);
-  return cuda_status(cudaGetLastError());
+  const cudaError_t e = launch_overlapped(kern, dim3((unsigned)grid), dim3(groups * kConsumers + 32), smem, s, P, stages,
+                                          groups, ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
 }
 
 template <int OP, typename T>
