@@ -49,14 +49,17 @@ def _to_device(t: torch.Tensor) -> torch.Tensor:
     return t.to(_device(), non_blocking=True)
 
 
-def _like_input(result: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
-    """Results follow the residence of the input: CPU in, CPU out."""
-    if ref.is_cuda:
-        return result
+def _to_host(result: torch.Tensor) -> torch.Tensor:
+    """A device result as a pinned host tensor (synchronises the current stream)."""
     out = torch.empty(result.shape, dtype=result.dtype, device="cpu", pin_memory=True)
     out.copy_(result, non_blocking=True)
     torch.cuda.current_stream().synchronize()
     return out
+
+
+def _like_input(result: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+    """Results follow the residence of the input: CPU in, CPU out."""
+    return result if ref.is_cuda else _to_host(result)
 
 
 # Host-resident operands.  A host tensor is staged through the device in row blocks on
@@ -199,7 +202,7 @@ def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None, hos
         return res
     out = torch.empty(count, dtype=torch.int64, device=_device())
     _abi.check(call(C.byref(desc), begin, count, out.data_ptr(), _stream()), "lego_eval_range")
-    return _like_input(out, torch.empty(0)) if host else out
+    return _to_host(out) if host else out
 
 
 # ---- layout reorganisation ----------------------------------------------------------
