@@ -238,7 +238,7 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
         const int kblocks = (p->k + geo.bk - 1) / geo.bk;
         const bool a_mn = p->a_mn_major != 0, b_mn = p->b_mn_major != 0;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
+          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
             fail(status, abort_flag, 0x10000u | stage);
             ok = false;
             break;
@@ -269,7 +269,7 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
 #pragma unroll
         for (int s = 0; s < STAGES; ++s)
           if (issued[s])
-            ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
+            ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
       }
     }
   } else if (warp == 1) {
@@ -294,14 +294,14 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
         const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
         const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
+        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
           fail(status, abort_flag, 0x20000u | 0x100u | acc);
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
+          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
             fail(status, abort_flag, 0x20000u | stage);
             ok = false;
             break;
@@ -341,7 +341,7 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
       const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
       bool ok = true;
       if (lane == 0)
-        ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
+        ok = ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) {
         if (lane == 0) fail(status, abort_flag, 0x30000u | acc);
@@ -480,7 +480,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
       while (ld.pair < total_pairs) {
         const Problem* pr = ld.pr;
         acquire(pr);
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
+        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
           fail(status, abort_flag, 0x110000u | stage);
           ok = false;
           break;
@@ -516,7 +516,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
 #pragma unroll
         for (int s = 0; s < P_STAGES; ++s)
           if (issued[s])
-            ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
+            ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
       }
     }
   } else if (warp == 1) {
@@ -540,14 +540,14 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? geo.sub_bytes : 16, 1024);
         const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
+        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
           fail(status, abort_flag, 0x120000u | 0x100u | acc);
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
+          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
             fail(status, abort_flag, 0x120000u | stage);
             ok = false;
             break;
@@ -586,7 +586,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
       const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
       bool ok = true;
       if (lane == 0)
-        ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
+        ok = ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) {
         if (lane == 0) fail(status, abort_flag, 0x130000u | acc);

@@ -48,6 +48,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// One try of a parity wait: the thread may be suspended by the hardware until the phase
+// completes or a short system-dependent time has passed.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -62,15 +64,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same with a suspend-time hint of kSuspendNs instead of the system default, for roles
+// that wait long (the epilogue warps of a GEMM wait a whole k-loop): they stop burning
+// issue slots and power on polling.  Measured A/B on one box: +9 % on the power-capped
+// 8192^3 GEMM, +5 % on the grouped GEMM; -1 % on the bandwidth-bound row kernels, whose
+// waits are short, so those keep the plain form.
+constexpr uint32_t kSuspendNs = 20000;
+__device__ __forceinline__ bool mbar_try_wait_long(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kSuspendNs)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: gives up after `limit_cycles` of the SM clock, or as soon as
 // *abort_flag (shared memory) is non-zero.  Returns false when it gave up.
+template <bool LONG = false>
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag, long long limit_cycles) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (LONG ? mbar_try_wait_long(bar, parity) : mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
+    if (LONG ? mbar_try_wait_long(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (LONG || (it & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > limit_cycles) return false;
     }
