@@ -147,20 +147,23 @@ row_kernel(const __grid_constant__ RowParams P) {
 
 // ---- bulk-copy pipelined kernel ------------------------------------------------------
 //
-// For rows of 1 Ki .. 8 Ki elements whose bytes are a multiple of 16.  One CTA per SM:
-// a producer thread streams whole rows into a shared-memory ring with 1-D bulk copies
-// (cp.async.bulk, completion on mbarriers); two or three groups of 256 consumer threads
-// each take every second / third row: pull it into registers with 128-bit shared-memory
-// loads, free the slot at once, reduce within the group (named barrier) and write the
-// result with 128-bit streaming stores.  One CTA with several consumer groups instead of
-// several CTAs per SM because the memory system prefers few row streams per SM: a plain
-// copy through this ring ran at 0.955 of the copy peak with one CTA per SM, 0.915 with
-// two and 0.89 with three.  The row a slot holds is named by the producer next to the
-// data.  gamma / beta of LayerNorm are staged in shared memory once per CTA.
+// For rows of at least 2 KiB whose bytes are a multiple of 16.  One CTA per SM: a producer
+// warp streams whole rows into a shared-memory ring with 1-D bulk copies (cp.async.bulk,
+// completion on mbarriers; lane l owns ring slot l and the lanes work in lock step, so the
+// per-row latencies of barrier polls and copy issue overlap); several groups of consumer
+// threads each take every groups-th row: pull it into registers with 128-bit
+// shared-memory loads (32 values per thread, so a group has cols / 32 threads: 32 .. 512),
+// free the slot at once, reduce within the group (named barrier) and write the result
+// with 128-bit streaming stores.  One CTA with several consumer groups instead of several
+// CTAs per SM because the memory system prefers few row streams per SM: a plain copy
+// through this ring ran at 0.955 of the copy peak with one CTA per SM, 0.915 with two and
+// 0.89 with three.  The row a slot holds is named by the producer next to the data.
+// gamma / beta of LayerNorm are staged in shared memory once per CTA.
 
-constexpr int kRing = 8;          // most ring slots a CTA may use
-constexpr int kConsumers = 256;   // threads of one consumer group
-constexpr int kMaxGroups = 3;
+constexpr int kRing = 32;         // most ring slots a CTA may use (one producer lane each)
+constexpr int kRingEpt = 32;      // values per consumer thread
+constexpr int kMaxGroups = 15;    // named barriers 1 .. 15
+constexpr int kMaxConsumers = 768;
 constexpr long long kWaitLimit = 2000000000LL;  // SM cycles, about a second
 
 struct RingCtl {
@@ -171,16 +174,26 @@ struct RingCtl {
   uint32_t group_abort[kMaxGroups];  // written only by the group's own threads, read after its barrier
 };
 
-// Reduction over the 256 threads of one consumer group (named barrier `bar`).
+// Reduction over the `gsize` threads (nw warps) of one consumer group (named barrier `bar`).
+// `slots` holds 16 partials; entries of warps the group does not have were set to the
+// operation's identity once, so the fold is a fixed tree over two or four 128-bit loads
+// whatever the group size.
 template <bool IS_MAX>
-__device__ __forceinline__ float group_reduce(float v, float* slots, int bar) {
+__device__ __forceinline__ float group_reduce(float v, float* slots, int bar, int gsize, int nw, int warp_in_group) {
   v = warp_reduce<IS_MAX>(v);
-  const int warp = (threadIdx.x >> 5) & 7, lane = threadIdx.x & 31;
-  if (lane == 0) slots[warp] = v;
-  asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(kConsumers) : "memory");
-  float r = slots[0];
-#pragma unroll
-  for (int w = 1; w < kConsumers / 32; ++w) r = IS_MAX ? fmaxf(r, slots[w]) : r + slots[w];
+  if (nw == 1) return v;
+  if ((threadIdx.x & 31) == 0) slots[warp_in_group] = v;
+  asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(gsize) : "memory");
+  const float4* q = reinterpret_cast<const float4*>(slots);
+  const float4 a = q[0], b = q[1];
+  float r;
+  if (IS_MAX) r = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+  else r = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+  if (nw > 8) {
+    const float4 c = q[2], d = q[3];
+    if (IS_MAX) r = fmaxf(r, fmaxf(fmaxf(fmaxf(c.x, c.y), fmaxf(c.z, c.w)), fmaxf(fmaxf(d.x, d.y), fmaxf(d.z, d.w))));
+    else r += ((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w));
+  }
   return r;
 }
 
@@ -190,9 +203,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-template <int OP, typename T, int EPT>
-__global__ void __launch_bounds__(kMaxGroups * kConsumers + 32, 1)
-row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uint32_t* status) {
+template <int OP, typename T>
+__global__ void __launch_bounds__(kMaxConsumers + 32, 1)
+row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int gsize, uint32_t* status) {
+  constexpr int EPT = kRingEpt;
   constexpr int VEC = Elem<T>::VEC;
   constexpr int NV = EPT / VEC;
   extern __shared__ __align__(128) uint8_t ring_smem[];
@@ -201,23 +215,27 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
   const uint32_t slot_bytes = (row_bytes + 127u) & ~127u;
   uint8_t* params_smem = ring_smem + (size_t)stages * slot_bytes;  // gamma | beta (LayerNorm)
   RingCtl* ctl = reinterpret_cast<RingCtl*>(params_smem + (OP == OP_LAYERNORM ? 2 * slot_bytes : 0));
-  __shared__ float slots_all[kMaxGroups][2][8];
+  __shared__ __align__(16) float slots_all[kMaxGroups][2][16];
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
   const int tid = threadIdx.x;
-  const int n_consumers = groups * kConsumers;
+  const int n_consumers = groups * gsize;
+  const int nw = gsize >> 5;  // warps per group
   const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), kConsumers / 32);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), nw);
     }
     ctl->abort_flag = 0;
     for (int g = 0; g < kMaxGroups; ++g) ctl->group_abort[g] = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
   }
+  // partials of warps a group does not have: the identity of the reduction that uses the array
+  for (int i = tid; i < kMaxGroups * 2 * 16; i += blockDim.x)
+    (&slots_all[0][0][0])[i] = (OP == OP_SOFTMAX && ((i >> 4) & 1) == 0) ? -INFINITY : 0.f;
   // The next grid of the stream may set itself up now; global memory is touched only once
   // the previous grid is complete (programmatic dependent launch).
   ptx::launch_dependents();
@@ -235,33 +253,47 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
   __syncthreads();
 
   if (tid >= n_consumers) {
-    // ---------------- producer ----------------
-    if (tid == n_consumers) {
-      const T* __restrict__ x = reinterpret_cast<const T*>(P.x);
-      int64_t issued = 0;
-      for (int64_t n = 0; n < my_rows; ++n) {
-        const int s = (int)(n % stages);
-        const uint32_t use = (uint32_t)(n / stages);
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kWaitLimit)) {
+    // ---------------- producer warp ----------------
+    // A round feeds one row to every group: lanes 0 .. groups-1 work in lock step (their
+    // barrier polls and copy issues overlap), and a round only waits for slots that the
+    // groups free at about the same time, so the ring never drains while a round waits.
+    const int lane = tid & 31;
+    const T* __restrict__ x = reinterpret_cast<const T*>(P.x);
+    int slot0 = 0;       // first slot of this round (the slot count is a multiple of the group count)
+    uint32_t lap = 0;    // how often the ring has wrapped
+    int64_t issued = 0;  // rows requested so far
+    bool failed = false;
+    for (int64_t base = 0; base < my_rows; base += groups) {
+      const int64_t n = base + lane;
+      const int sl = slot0 + lane;
+      if (lane < groups && n < my_rows) {
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[sl]), (lap & 1) ^ 1, abort_flag, kWaitLimit)) {
           *abort_flag = 1;
-          atomicCAS(status, 0u, 0x40000u | (uint32_t)s);
-          break;
+          atomicCAS(status, 0u, 0x40000u | (uint32_t)sl);
+          failed = true;
+        } else {
+          const int64_t w = blockIdx.x + n * (int64_t)gridDim.x;
+          const int64_t row = P.has_map ? (int64_t)map_eval(P.map, (uint64_t)w) : w;
+          ctl->row[sl] = row;
+          const uint32_t full = ptx::smem_u32(&ctl->full[sl]);
+          ptx::mbar_arrive_expect_tx(full, row_bytes);
+          ptx::bulk_load(ptx::smem_u32(ring_smem + (size_t)sl * slot_bytes), x + row * cols, row_bytes, full);
         }
-        const int64_t w = blockIdx.x + n * (int64_t)gridDim.x;
-        const int64_t row = P.has_map ? (int64_t)map_eval(P.map, (uint64_t)w) : w;
-        ctl->row[s] = row;
-        const uint32_t full = ptx::smem_u32(&ctl->full[s]);
-        ptx::mbar_arrive_expect_tx(full, row_bytes);
-        ptx::bulk_load(ptx::smem_u32(ring_smem + (size_t)s * slot_bytes), x + row * cols, row_bytes, full);
-        ++issued;
       }
-      if (*abort_flag) {
-        // leave no copy of ours in flight
-        uint32_t never = 0;
-        for (int s = 0; s < stages; ++s) {
-          const int64_t uses = issued > s ? (issued - s + stages - 1) / stages : 0;
-          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kWaitLimit);
-        }
+      if (__any_sync(0xffffffffu, failed)) break;
+      issued = base + groups < my_rows ? base + groups : my_rows;
+      slot0 += groups;
+      if (slot0 == stages) {
+        slot0 = 0;
+        ++lap;
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      // leave no copy of ours in flight: the last request into every slot
+      uint32_t never = 0;
+      for (int sl = 0; sl < stages; ++sl) {
+        const int64_t uses = issued > sl ? (issued - sl + stages - 1) / stages : 0;
+        if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[sl]), (uint32_t)((uses - 1) & 1), &never, kWaitLimit);
       }
     }
     return;
@@ -271,15 +303,25 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
   // The slot count is a multiple of the group count, so a slot is always drained by the same
   // group (a waiter two uses ahead of an mbarrier could not tell its phase from the one two back).
   T* __restrict__ y = reinterpret_cast<T*>(P.y);
-  const int group = tid / kConsumers;
-  const int gtid = tid - group * kConsumers;  // thread within the group
+  const int group = tid / gsize;
+  const int gtid = tid - group * gsize;  // thread within the group
   const int lane = tid & 31;
+  const int warp_in_group = gtid >> 5;
   const int bar = 1 + group;
-  float (*slots)[8] = slots_all[group];
+  float (*slots)[16] = slots_all[group];
   volatile uint32_t* group_abort = &ctl->group_abort[group];
-  for (int64_t n = group; n < my_rows; n += groups) {
-    const int s = (int)(n % stages);
-    const uint32_t use = (uint32_t)(n / stages);
+  int s = group;       // this group walks slots group, group + groups, ...
+  uint32_t use = 0;    // laps of the ring
+  for (int64_t n = group; n < my_rows; n += groups, s += groups) {
+#ifdef EXP_DIV
+    s = (int)(n % stages);
+    use = (uint32_t)(n / stages);
+#else
+    if (s >= stages) {
+      s -= stages;
+      ++use;
+    }
+#endif
     const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kWaitLimit);
     if (!ok) {
       *abort_flag = 1;
@@ -292,9 +334,9 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int c = (k * kConsumers + gtid) * VEC;
+      const int c = (k * gsize + gtid) * VEC;
       if (ok && c < cols) {
-        Elem<T>::unpack(slot[k * kConsumers + gtid], v + k * VEC);
+        Elem<T>::unpack(slot[k * gsize + gtid], v + k * VEC);
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) v[k * VEC + e] = fill;
@@ -307,7 +349,7 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
       float m = v[0];
 #pragma unroll
       for (int k = 1; k < EPT; ++k) m = fmaxf(m, v[k]);
-      m = group_reduce<true>(m, slots[0], bar);
+      m = group_reduce<true>(m, slots[0], bar, gsize, nw, warp_in_group);
       if (*group_abort) break;  // uniform: the group's own flag writes of this row precede the barrier above
       const float ms = m * 1.4426950408889634f;
       float sum = 0.f;
@@ -316,12 +358,12 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
         v[k] = fast_exp2(fmaf(v[k], 1.4426950408889634f, -ms));
         sum += v[k];
       }
-      sum = group_reduce<false>(sum, slots[1], bar);
+      sum = group_reduce<false>(sum, slots[1], bar, gsize, nw, warp_in_group);
       const float inv = 1.0f / sum;
       T* __restrict__ yrow = y + row * cols;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const int c = (k * kConsumers + gtid) * VEC;
+        const int c = (k * gsize + gtid) * VEC;
         if (c < cols) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) v[k * VEC + e] *= inv;
@@ -332,13 +374,13 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
       float sum = 0.f;
 #pragma unroll
       for (int k = 0; k < EPT; ++k) sum += v[k];
-      sum = group_reduce<false>(sum, slots[0], bar);
+      sum = group_reduce<false>(sum, slots[0], bar, gsize, nw, warp_in_group);
       if (*group_abort) break;
       const float mean = sum / (float)cols;
       float q = 0.f;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const bool in = (k * kConsumers + gtid) * VEC < cols;
+        const bool in = (k * gsize + gtid) * VEC < cols;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float d = in ? v[k * VEC + e] - mean : 0.f;
@@ -346,7 +388,7 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
           q = fmaf(d, d, q);
         }
       }
-      q = group_reduce<false>(q, slots[1], bar);
+      q = group_reduce<false>(q, slots[1], bar, gsize, nw, warp_in_group);
       const float rstd = 1.0f / sqrtf(q / (float)cols + P.eps);
       if (gtid == 0) {
         P.mean[row] = mean;
@@ -357,11 +399,11 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
       T* __restrict__ yrow = y + row * cols;
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        const int c = (k * kConsumers + gtid) * VEC;
+        const int c = (k * gsize + gtid) * VEC;
         if (c < cols) {
           float g[VEC], b[VEC];
-          Elem<T>::unpack(sg[k * kConsumers + gtid], g);
-          Elem<T>::unpack(sb[k * kConsumers + gtid], b);
+          Elem<T>::unpack(sg[k * gsize + gtid], g);
+          Elem<T>::unpack(sb[k * gsize + gtid], b);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) v[k * VEC + e] = fmaf(v[k * VEC + e] * rstd, g[e], b[e]);
           __stcs(reinterpret_cast<uint4*>(yrow + c), Elem<T>::pack(v + k * VEC));
@@ -371,42 +413,46 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, uin
   }
 }
 
-template <int OP, typename T, int EPT>
+template <int OP, typename T>
 int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
-  auto kern = row_ring_kernel<OP, T, EPT>;
+  auto kern = row_ring_kernel<OP, T>;
+  constexpr int VEC = Elem<T>::VEC;
   const size_t row_bytes = (size_t)P.cols * sizeof(T);
   const size_t slot = (row_bytes + 127) & ~(size_t)127;
   const size_t fixed = (OP == OP_LAYERNORM ? 2 * slot : 0) + sizeof(RingCtl) + 128;
+  // threads per row: 32 values each, whole warps
+  const int per_thread = kRingEpt / VEC;  // vectors per thread
+  const int vectors = P.cols / VEC;
+  int gsize = ((vectors + per_thread - 1) / per_thread + 31) & ~31;
+  if (gsize > 512) return LEGO_ERR_UNSUPPORTED;
   static bool configured = false;
   if (!configured) {
-    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));  // static part: reduction slots
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 4096));  // static part: reduction slots
     configured = true;
   }
-  // Measured on B200 (16384 x 8192 fp16), same box, GB/s: one group turns a row around in
-  // about 2500 cycles, so two groups (softmax: 6260; three: 5580, they fight over the
-  // special-function pipe) or three (LayerNorm: 6390; two: 5410) keep up with HBM.  Six ring
-  // slots are the sweet spot for both (softmax 4 / 6 / 8 slots: 6170 / 6260 / 6260;
-  // LayerNorm 3 / 6 / 9 / 12 slots: 5930 / 6390 / 6060 / 5930).
-  const int groups = OP == OP_SOFTMAX ? 2 : 3;
-  const size_t budget = (size_t)ctx->smem_optin - 1024 - fixed;
-  int stages = (int)(budget / slot);
-  if (stages > 6) stages = 6;
+  // Measured on B200 (16384 x 8192 fp16, 256 threads per row), same box, GB/s: one group turns
+  // a row around in about 2500 cycles, so two groups (softmax: 6260; three: 5580, they fight
+  // over the special-function pipe) or three (LayerNorm: 6390; two: 5410) keep up with HBM;
+  // other widths keep the same number of consumer threads (512 / 768).  About 96 KiB of rows in
+  // flight is the sweet spot (softmax 64 / 96 / 128 KiB: 6170 / 6260 / 6260; LayerNorm 48 / 96 /
+  // 144 / 192 KiB: 5930 / 6390 / 6060 / 5930).
+  int groups = (OP == OP_SOFTMAX ? 512 : kMaxConsumers) / gsize;
+  if (groups < 1) groups = 1;
+  if (groups > kMaxGroups) groups = kMaxGroups;
+  const size_t budget = (size_t)ctx->smem_optin - 4096 - fixed;
+  int stages = (int)((96 * 1024 + slot / 2) / slot);
+  if (stages < 2 * groups) stages = 2 * groups;
+  if (stages > kRing) stages = kRing;
+  if ((size_t)stages > budget / slot) stages = (int)(budget / slot);
   stages -= stages % groups;  // a slot always belongs to one group
   if (stages < groups) return LEGO_ERR_UNSUPPORTED;
   const size_t smem = (size_t)stages * slot + fixed;
   int64_t grid = ctx->sm_count;
   if (grid > P.rows) grid = P.rows;
-  const cudaError_t e = launch_overlapped(kern, dim3((unsigned)grid), dim3(groups * kConsumers + 32), smem, s, P, stages,
-                                          groups, ctx->status_word);
+  const cudaError_t e = launch_overlapped(kern, dim3((unsigned)grid), dim3(groups * gsize + 32), smem, s, P, stages,
+                                          groups, gsize, ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
-}
-
-template <int OP, typename T>
-int32_t launch_ring_by_cols(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
-  if (P.cols <= kConsumers * 8) return launch_ring<OP, T, 8>(P, ctx, s);
-  if (P.cols <= kConsumers * 16) return launch_ring<OP, T, 16>(P, ctx, s);
-  return launch_ring<OP, T, 32>(P, ctx, s);
 }
 
 template <int OP, typename T, int TPR, int EPT, bool VECTOR>
@@ -468,8 +514,8 @@ int32_t run_rows(RowParams& P, const lego_layout_t* row_map, void* stream) {
   bool vec = (P.cols % VEC == 0) && aligned16(P.x) && aligned16(P.y);
   if (OP == OP_LAYERNORM) vec = vec && aligned16(P.gamma) && aligned16(P.beta);
   // long aligned rows, enough of them to fill the machine: the bulk-copy pipeline
-  if (vec && P.cols > 1024 && P.cols <= kConsumers * 32 && P.rows >= 2 * (int64_t)ctx->sm_count) {
-    const int32_t st = launch_ring_by_cols<OP, T>(P, ctx, s);
+  if (vec && (size_t)P.cols * sizeof(T) >= 2048 && P.rows >= 2 * (int64_t)ctx->sm_count) {
+    const int32_t st = launch_ring<OP, T>(P, ctx, s);
     if (st != LEGO_ERR_UNSUPPORTED) return st;
   }
   return vec ? launch_vec<OP, T, true>(P, ctx, s) : launch_vec<OP, T, false>(P, ctx, s);
