@@ -203,10 +203,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-template <int OP, typename T>
+// G: threads per consumer group when it is one of the common sizes (constants for the
+// address arithmetic and the barrier), 0 = taken from `gsize_rt`.
+template <int OP, typename T, int G>
 __global__ void __launch_bounds__(kMaxConsumers + 32, 1)
-row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int gsize, uint32_t* status) {
+row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int gsize_rt, uint32_t* status) {
   constexpr int EPT = kRingEpt;
+  const int gsize = G > 0 ? G : gsize_rt;
   constexpr int VEC = Elem<T>::VEC;
   constexpr int NV = EPT / VEC;
   extern __shared__ __align__(128) uint8_t ring_smem[];
@@ -254,19 +257,25 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
 
   if (tid >= n_consumers) {
     // ---------------- producer warp ----------------
-    // A round feeds one row to every group: lanes 0 .. groups-1 work in lock step (their
-    // barrier polls and copy issues overlap), and a round only waits for slots that the
-    // groups free at about the same time, so the ring never drains while a round waits.
+    // Rows are requested in order, `chunk` at a time by as many lanes in lock step (their
+    // barrier polls and copy issues overlap).  With many small groups a round feeds one row
+    // to every group: it only waits for slots that the groups free at about the same time,
+    // so the ring never drains while a round waits.  With few large groups (long rows) one
+    // lane does it all: the per-row cost is negligible there and a round of three would hold
+    // back the first copy until the third slot is free.
+    // (16384 x 8192 fp16, same box: one lane / lock-step rounds: softmax 6450 / 6470 GB/s,
+    // LayerNorm 6480 / 6300.)
+    const int chunk = groups > 4 ? groups : 1;
     const int lane = tid & 31;
     const T* __restrict__ x = reinterpret_cast<const T*>(P.x);
     int slot0 = 0;       // first slot of this round (the slot count is a multiple of the group count)
     uint32_t lap = 0;    // how often the ring has wrapped
     int64_t issued = 0;  // rows requested so far
     bool failed = false;
-    for (int64_t base = 0; base < my_rows; base += groups) {
+    for (int64_t base = 0; base < my_rows; base += chunk) {
       const int64_t n = base + lane;
       const int sl = slot0 + lane;
-      if (lane < groups && n < my_rows) {
+      if (lane < chunk && n < my_rows) {
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[sl]), (lap & 1) ^ 1, abort_flag, kWaitLimit)) {
           *abort_flag = 1;
           atomicCAS(status, 0u, 0x40000u | (uint32_t)sl);
@@ -281,8 +290,8 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
         }
       }
       if (__any_sync(0xffffffffu, failed)) break;
-      issued = base + groups < my_rows ? base + groups : my_rows;
-      slot0 += groups;
+      issued = base + chunk < my_rows ? base + chunk : my_rows;
+      slot0 += chunk;
       if (slot0 == stages) {
         slot0 = 0;
         ++lap;
@@ -313,15 +322,10 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
   int s = group;       // this group walks slots group, group + groups, ...
   uint32_t use = 0;    // laps of the ring
   for (int64_t n = group; n < my_rows; n += groups, s += groups) {
-#ifdef EXP_DIV
-    s = (int)(n % stages);
-    use = (uint32_t)(n / stages);
-#else
     if (s >= stages) {
       s -= stages;
       ++use;
     }
-#endif
     const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kWaitLimit);
     if (!ok) {
       *abort_flag = 1;
@@ -413,9 +417,24 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
   }
 }
 
+template <int OP, typename T, int G>
+int32_t launch_ring_g(const RowParams& P, DeviceCtx* ctx, cudaStream_t s, int stages, int groups, int gsize, size_t smem) {
+  auto kern = row_ring_kernel<OP, T, G>;
+  static bool configured = false;
+  if (!configured) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 4096));  // static part: reduction slots
+    configured = true;
+  }
+  int64_t grid = ctx->sm_count;
+  if (grid > P.rows) grid = P.rows;
+  const cudaError_t e = launch_overlapped(kern, dim3((unsigned)grid), dim3(groups * gsize + 32), smem, s, P, stages,
+                                          groups, gsize, ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
+}
+
 template <int OP, typename T>
 int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
-  auto kern = row_ring_kernel<OP, T>;
   constexpr int VEC = Elem<T>::VEC;
   const size_t row_bytes = (size_t)P.cols * sizeof(T);
   const size_t slot = (row_bytes + 127) & ~(size_t)127;
@@ -425,11 +444,6 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const int vectors = P.cols / VEC;
   int gsize = ((vectors + per_thread - 1) / per_thread + 31) & ~31;
   if (gsize > 512) return LEGO_ERR_UNSUPPORTED;
-  static bool configured = false;
-  if (!configured) {
-    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 4096));  // static part: reduction slots
-    configured = true;
-  }
   // Measured on B200 (16384 x 8192 fp16, 256 threads per row), same box, GB/s: one group turns
   // a row around in about 2500 cycles, so two groups (softmax: 6260; three: 5580, they fight
   // over the special-function pipe) or three (LayerNorm: 6390; two: 5410) keep up with HBM;
@@ -447,12 +461,12 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   stages -= stages % groups;  // a slot always belongs to one group
   if (stages < groups) return LEGO_ERR_UNSUPPORTED;
   const size_t smem = (size_t)stages * slot + fixed;
-  int64_t grid = ctx->sm_count;
-  if (grid > P.rows) grid = P.rows;
-  const cudaError_t e = launch_overlapped(kern, dim3((unsigned)grid), dim3(groups * gsize + 32), smem, s, P, stages,
-                                          groups, gsize, ctx->status_word);
-  if (e != cudaSuccess) (void)cudaGetLastError();
-  return cuda_status(e);
+  switch (gsize) {
+    case 64: return launch_ring_g<OP, T, 64>(P, ctx, s, stages, groups, gsize, smem);
+    case 128: return launch_ring_g<OP, T, 128>(P, ctx, s, stages, groups, gsize, smem);
+    case 256: return launch_ring_g<OP, T, 256>(P, ctx, s, stages, groups, gsize, smem);
+    default: return launch_ring_g<OP, T, 0>(P, ctx, s, stages, groups, gsize, smem);
+  }
 }
 
 template <int OP, typename T, int TPR, int EPT, bool VECTOR>

@@ -56,6 +56,34 @@ def test_softmax_shapes_f16_f32(rows, cols):
     assert (y16.float() - O.softmax(x16).float()).abs().max().item() <= TOL_F16
 
 
+@pytest.mark.parametrize("cols", [1024, 1536, 2048, 4096, 5120, 8192, 12288, 16384])
+def test_ring_kernel_group_sizes(cols):
+    """Enough rows (>= 2 per SM) of 2 KiB or more for the bulk-copy ring kernel, at widths that
+    give every consumer-group size from one warp (1024 fp16 values) to sixteen (16384), a width
+    that leaves part of a group idle (1536, 5120, 12288), fp16 and fp32, with and without a row
+    map; softmax and LayerNorm against the oracle on every row."""
+    rows = 332
+    g = torch.Generator().manual_seed(cols)
+    x32 = torch.randn(rows, cols, generator=g) * 3
+    x16 = x32.half()
+    rm = L.OrderBy(L.Col(83, 4)).TileBy([83, 4])
+    y16 = ops.softmax(x16.cuda()).cpu()
+    assert (y16.float() - O.softmax(x16).float()).abs().max().item() <= TOL_F16
+    assert torch.equal(ops.softmax(x16.cuda(), rm).cpu(), y16)
+    if cols * 4 <= 65536:
+        y32 = ops.softmax(x32.cuda()).cpu()
+        # the reference's own criterion for its fp32 softmax (torch.allclose defaults) plus 1e-6
+        assert torch.allclose(y32, torch.softmax(x32, dim=-1), rtol=1e-5, atol=1e-6)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).half()
+    b = (0.1 * torch.randn(cols, generator=g)).half()
+    y, mean, rstd = ops.layer_norm_fwd(x16.cuda(), w.cuda(), b.cuda(), 1e-5, rm)
+    ry, rmean, rrstd = O.layernorm_fwd(x16, w, b, 1e-5)
+    assert ln_error_ok(y.cpu(), ln_ref32(x16, w, b, 1e-5))
+    assert ((mean.cpu() - rmean).abs() <= 1e-5 * rmean.abs() + 1e-6).all()
+    assert ((rstd.cpu() - rrstd).abs() <= 2e-5 * rrstd.abs()).all()
+    ops.device_status()
+
+
 def test_softmax_row_maps_and_extremes():
     g = torch.Generator().manual_seed(3)
     x = torch.randn(60, 512, generator=g).half()
