@@ -111,7 +111,7 @@ ln_bwd_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dga
   }
 }
 
-// ---- bulk-copy pipelined dx kernel -------------------------------------------------
+// ---- bulk-copy pipelined dx kernel, one group (rows of more than 3 Ki columns) -------
 //
 // One CTA per SM.  A producer thread streams the rows of x and dy (and the 16-byte
 // chunks holding the row's mean and rstd) into a shared-memory ring with 1-D bulk
@@ -121,29 +121,29 @@ ln_bwd_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dga
 // stores.  Memory-level parallelism comes from the ring (up to 6 rows of x and dy in
 // flight per SM), not from occupancy.
 
-constexpr int kBwdConsumers = 512;
-constexpr int kBwdRing = 6;
-constexpr long long kBwdWaitLimit = 2000000000LL;  // SM cycles, about a second
+constexpr int kBwd1Consumers = 512;
+constexpr int kBwd1Ring = 6;
+constexpr long long kBwd1WaitLimit = 2000000000LL;  // SM cycles, about a second
 
-struct BwdRingCtl {
-  uint64_t full[kBwdRing];
-  uint64_t empty[kBwdRing];
-  int64_t row[kBwdRing];
+struct BwdRing1Ctl {
+  uint64_t full[kBwd1Ring];
+  uint64_t empty[kBwd1Ring];
+  int64_t row[kBwd1Ring];
   uint32_t abort_flag;
 };
 
 template <int EPT>
-__global__ void __launch_bounds__(kBwdConsumers + 32, 1)
-ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
+__global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
+ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
   constexpr int NV = EPT / 8;
-  constexpr int NW = kBwdConsumers / 32;
-  extern __shared__ __align__(128) uint8_t bwd_smem[];
+  constexpr int NW = kBwd1Consumers / 32;
+  extern __shared__ __align__(128) uint8_t bwd1_smem[];
   __shared__ __align__(8) float red[2][NW][2];  // [row parity][warp] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
   const uint32_t half_slot = (row_bytes + 127u) & ~127u;
   const uint32_t slot_bytes = 2u * half_slot + 128u;  // x | dy | mean chunk, rstd chunk
-  BwdRingCtl* ctl = reinterpret_cast<BwdRingCtl*>(bwd_smem + (size_t)stages * slot_bytes);
+  BwdRing1Ctl* ctl = reinterpret_cast<BwdRing1Ctl*>(bwd1_smem + (size_t)stages * slot_bytes);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   const int tid = threadIdx.x;
   const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -161,15 +161,15 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
   ptx::launch_dependents();     // the column reduction (or the next op) may set itself up now
   ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
 
-  if (tid >= kBwdConsumers) {
+  if (tid >= kBwd1Consumers) {
     // ---------------- producer ----------------
-    if (tid == kBwdConsumers) {
+    if (tid == kBwd1Consumers) {
       int64_t issued = 0;
       // s walks the ring, use counts the laps (no 64-bit division per row)
       int s = 0;
       uint32_t use = 0;
       for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kBwdWaitLimit)) {
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kBwd1WaitLimit)) {
           *abort_flag = 1;
           atomicCAS(status, 0u, 0x60000u | (uint32_t)s);
           break;
@@ -177,7 +177,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
         const int64_t row = blockIdx.x + n * (int64_t)gridDim.x;
         ctl->row[s] = row;
         const uint32_t full = ptx::smem_u32(&ctl->full[s]);
-        const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)s * slot_bytes);
+        const uint32_t dst = ptx::smem_u32(bwd1_smem + (size_t)s * slot_bytes);
         ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
         ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
         ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
@@ -190,7 +190,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
         uint32_t never = 0;
         for (int s = 0; s < stages; ++s) {
           const int64_t uses = issued > s ? (issued - s + stages - 1) / stages : 0;
-          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kBwdWaitLimit);
+          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), (uint32_t)((uses - 1) & 1), &never, kBwd1WaitLimit);
         }
       }
     }
@@ -204,7 +204,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
   float2 g[P2], acc_w[P2], acc_b[P2];
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
-    const int c = (k * kBwdConsumers + tid) * 8;
+    const int c = (k * kBwd1Consumers + tid) * 8;
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (c < cols) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
     const __half2* hp = reinterpret_cast<const __half2*>(&raw);
@@ -219,19 +219,19 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
   int s = 0;
   uint32_t use = 0;
   for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
-    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwdWaitLimit);
+    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwd1WaitLimit);
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
     }
-    const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
+    const uint8_t* slot = bwd1_smem + (size_t)s * slot_bytes;
     const int64_t row = ok ? ctl->row[s] : 0;
     const float mean = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3] : 0.f;
     const float rstd = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3] : 0.f;
     uint4 xr[NV], dr[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int v = k * kBwdConsumers + tid;
+      const int v = k * kBwd1Consumers + tid;
       xr[k] = dr[k] = make_uint4(0u, 0u, 0u, 0u);
       if (ok && v * 8 < cols) {
         xr[k] = reinterpret_cast<const uint4*>(slot)[v];
@@ -265,7 +265,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
     }
     float2* r = red2 + (n & 1) * NW;
     if (lane == 0) r[warp] = ss;
-    ptx::named_barrier<1, kBwdConsumers>();
+    ptx::named_barrier<1, kBwd1Consumers>();
     if (*abort_flag) break;  // uniform: every flag write of this row precedes the barrier above
     ss = lane < NW ? r[lane] : make_float2(0.f, 0.f);
 #pragma unroll
@@ -279,7 +279,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
     __half* __restrict__ dx = P.dx + row * cols;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int c = (k * kBwdConsumers + tid) * 8;
+      const int c = (k * kBwd1Consumers + tid) * 8;
       uint4 outv;
       __half2* o2 = reinterpret_cast<__half2*>(&outv);
 #pragma unroll
@@ -295,7 +295,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
   float* pb = P.partial + ((size_t)P.partial_rows + blockIdx.x) * cols;
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
-    const int c = (k * kBwdConsumers + tid) * 8;
+    const int c = (k * kBwd1Consumers + tid) * 8;
     if (c < cols) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
@@ -309,8 +309,8 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* st
 
 // Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
 template <int EPT>
-int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
-  auto kern = ln_bwd_ring_kernel<EPT>;
+int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
+  auto kern = ln_bwd_ring1_kernel<EPT>;
   const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
   static bool configured = false;
@@ -318,16 +318,286 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
     configured = true;
   }
-  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRingCtl) - 128;
+  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128;
   int stages = (int)(budget / slot);
-  if (stages > kBwdRing) stages = kBwdRing;
+  if (stages > kBwd1Ring) stages = kBwd1Ring;
   if (stages < 2) return LEGO_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
+  const size_t smem = (size_t)stages * slot + sizeof(BwdRing1Ctl) + 128;
   const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
   P.partial_rows = grid;
-  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(kBwdConsumers + 32), smem, s, P, stages, ctx->status_word);
+  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(kBwd1Consumers + 32), smem, s, P, stages, ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
+}
+
+// ---- bulk-copy pipelined dx kernel, several groups (rows of up to 3 Ki columns) ------
+//
+// One CTA per SM.  A producer thread streams the rows of x and dy (and the 16-byte
+// chunks holding the row's mean and rstd) into a shared-memory ring with 1-D bulk
+// copies; up to 512 consumer threads in 1 .. 4 groups: a group of cols / 16 threads
+// (cols / 8 for the narrowest rows) takes every groups-th row of the CTA, each of its
+// threads owning 16 (8) fixed columns: gamma and the two column accumulators of those
+// columns stay in registers for the whole kernel, a row costs one two-value reduction
+// over the group (named barrier), and dx leaves in 128-bit streaming stores.  Every
+// group ends with its own partial row of column sums.  All element-wise fp32 work is
+// packed (f32x2).  Memory-level parallelism comes from the ring, not from occupancy.
+
+constexpr int kBwdConsumers = 512;
+constexpr int kBwdMaxGroups = 4;   // partial rows: 4 per SM (kMaxPartialRows)
+constexpr int kBwdRing = 16;
+constexpr long long kBwdWaitLimit = 2000000000LL;  // SM cycles, about a second
+
+struct BwdRingCtl {
+  uint64_t full[kBwdRing];
+  uint64_t empty[kBwdRing];
+  int64_t row[kBwdRing];
+  uint32_t abort_flag;                  // any role gave up: polled inside every bounded wait
+  uint32_t group_abort[kBwdMaxGroups];  // written only by the group's own threads, read after its barrier
+};
+
+// G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
+template <int EPT, int G>
+__global__ void __launch_bounds__(kBwdConsumers + 32, 1)
+ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, uint32_t* status) {
+  constexpr int NV = EPT / 8;
+  const int gsize = G > 0 ? G : gsize_rt;
+  const int groups = G == kBwdConsumers ? 1 : groups_rt;
+  constexpr int P2 = EPT / 2;  // packed pairs per thread and row
+  extern __shared__ __align__(128) uint8_t bwd_smem[];
+  __shared__ __align__(16) float2 red_all[kBwdMaxGroups][2][16];  // [group][row parity][warp] -> (s1, s2)
+  const int cols = P.cols;
+  const uint32_t row_bytes = (uint32_t)cols * 2u;
+  const uint32_t half_slot = (row_bytes + 127u) & ~127u;
+  const uint32_t slot_bytes = 2u * half_slot + 128u;  // x | dy | mean chunk, rstd chunk
+  BwdRingCtl* ctl = reinterpret_cast<BwdRingCtl*>(bwd_smem + (size_t)stages * slot_bytes);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const int tid = threadIdx.x;
+  const int n_consumers = groups * gsize;
+  const int nw = gsize >> 5;  // warps per group
+  const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), nw);
+    }
+    ctl->abort_flag = 0;
+    for (int g = 0; g < kBwdMaxGroups; ++g) ctl->group_abort[g] = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  // partials of warps a group does not have: zero, so the fold below is a fixed tree
+  for (int i = tid; i < kBwdMaxGroups * 2 * 16; i += blockDim.x) (&red_all[0][0][0])[i] = make_float2(0.f, 0.f);
+  __syncthreads();
+  ptx::launch_dependents();     // the column reduction (or the next op) may set itself up now
+  ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
+
+  if (tid >= n_consumers) {
+    // ---------------- producer: rows in order, row n of this CTA into slot n mod stages ----------------
+    if (tid == n_consumers) {
+      int64_t issued = 0;
+      int s = 0;
+      uint32_t use = 0;
+      for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kBwdWaitLimit)) {
+          *abort_flag = 1;
+          atomicCAS(status, 0u, 0x60000u | (uint32_t)s);
+          break;
+        }
+        const int64_t row = blockIdx.x + n * (int64_t)gridDim.x;
+        ctl->row[s] = row;
+        const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+        const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)s * slot_bytes);
+        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+        ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
+        ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
+        ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+        ptx::bulk_load(dst + 2u * half_slot + 16u, P.rstd + (row & ~3LL), 16u, full);
+        ++issued;
+      }
+      if (*abort_flag) {
+        // leave no copy of ours in flight
+        uint32_t never = 0;
+        for (int sl = 0; sl < stages; ++sl) {
+          const int64_t uses = issued > sl ? (issued - sl + stages - 1) / stages : 0;
+          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[sl]), (uint32_t)((uses - 1) & 1), &never, kBwdWaitLimit);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers: group g takes rows g, g + groups, ... of this CTA ----------------
+  // The slot count is a multiple of the group count, so a slot is always drained by the same group.
+  const int group = tid / gsize;
+  const int gtid = tid - group * gsize;
+  const int lane = tid & 31, warp_in_group = gtid >> 5;
+  const int bar = 1 + group;
+  volatile uint32_t* group_abort = &ctl->group_abort[group];
+  float2 g[P2], acc_w[P2], acc_b[P2];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = (k * gsize + gtid) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (c < cols) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
+    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) g[k * 4 + e] = __half22float2(hp[e]);
+  }
+#pragma unroll
+  for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
+  const float inv_cols = 1.0f / (float)cols;
+
+  int s = group;
+  uint32_t use = 0;
+  uint32_t parity = 0;
+  for (int64_t n = group; n < my_rows; n += groups, s += groups, parity ^= 1u) {
+    if (s >= stages) {
+      s -= stages;
+      ++use;
+    }
+    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwdWaitLimit);
+    if (!ok) {
+      *abort_flag = 1;
+      *group_abort = 1;
+      atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
+    }
+    const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
+    const int64_t row = ok ? ctl->row[s] : 0;
+    const float mean = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3] : 0.f;
+    const float rstd = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3] : 0.f;
+    uint4 xr[NV], dr[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int v = k * gsize + gtid;
+      xr[k] = dr[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (ok && v * 8 < cols) {
+        xr[k] = reinterpret_cast<const uint4*>(slot)[v];
+        dr[k] = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
+
+    // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
+    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
+    float2 h[P2], w[P2];
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < P2; ++k) {
+      const __half2 xh2 = reinterpret_cast<const __half2*>(&xr[k / 4])[k % 4];
+      const __half2 dh2 = reinterpret_cast<const __half2*>(&dr[k / 4])[k % 4];
+      const float2 d = __half22float2(dh2);
+      h[k] = ptx::fma2(__half22float2(xh2), rstd2, shift2);
+      acc_w[k] = ptx::fma2(d, h[k], acc_w[k]);
+      acc_b[k] = ptx::add2(acc_b[k], d);
+      w[k] = ptx::mul2(d, g[k]);
+      s1 = ptx::fma2(h[k], w[k], s1);
+      s2 = ptx::add2(s2, w[k]);
+    }
+    float2 ss = make_float2(s1.x + s1.y, s2.x + s2.y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+      ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+    }
+    if (nw > 1) {
+      float2* r = red_all[group][parity];
+      if (lane == 0) r[warp_in_group] = ss;
+      asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(gsize) : "memory");
+      if (nw > 8) {
+        // 16 partials: both half-warps fold the same 16 values by shuffles (few registers)
+        ss = r[lane & 15];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+          ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+          ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+        }
+      } else {
+        // up to 8 partials (absent warps hold zeros): a fixed tree over four 128-bit loads
+        const float4* q = reinterpret_cast<const float4*>(r);
+        const float4 a0 = q[0], a1 = q[1], a2 = q[2], a3 = q[3];
+        ss.x = ((a0.x + a0.z) + (a1.x + a1.z)) + ((a2.x + a2.z) + (a3.x + a3.z));
+        ss.y = ((a0.y + a0.w) + (a1.y + a1.w)) + ((a2.y + a2.w) + (a3.y + a3.w));
+      }
+    }
+    if (*group_abort) break;  // uniform: the group's own flag writes of this row precede the barrier / __syncwarp above
+    // dx = (wdy - (xhat * c1 + c2)) * rstd, as two fused steps per pair
+    const float c1r = ss.x * inv_cols * rstd, c2r = ss.y * inv_cols * rstd;
+    const float2 nc1 = make_float2(-c1r, -c1r), nc2 = make_float2(-c2r, -c2r);
+    __half* __restrict__ dx = P.dx + row * cols;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * gsize + gtid) * 8;
+      uint4 outv;
+      __half2* o2 = reinterpret_cast<__half2*>(&outv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 t = ptx::fma2(h[k * 4 + e], nc1, ptx::fma2(w[k * 4 + e], rstd2, nc2));
+        o2[e] = __floats2half2_rn(t.x, t.y);
+      }
+      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv);
+    }
+  }
+  if (*group_abort) return;
+  // this group's partial row of column sums
+  const size_t prow = (size_t)blockIdx.x * groups + group;
+  float* pw = P.partial + prow * cols;
+  float* pb = P.partial + ((size_t)P.partial_rows + prow) * cols;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = (k * gsize + gtid) * 8;
+    if (c < cols) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = k * 4 + 2 * e;
+        *reinterpret_cast<float4*>(pw + c + 4 * e) = make_float4(acc_w[j].x, acc_w[j].y, acc_w[j + 1].x, acc_w[j + 1].y);
+        *reinterpret_cast<float4*>(pb + c + 4 * e) = make_float4(acc_b[j].x, acc_b[j].y, acc_b[j + 1].x, acc_b[j + 1].y);
+      }
+    }
+  }
+}
+
+// Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
+template <int EPT, int G>
+int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int grid, int stages, int groups, int gsize,
+                         size_t smem) {
+  auto kern = ln_bwd_ring_kernel<EPT, G>;
+  static bool configured = false;
+  if (!configured) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 2048));
+    configured = true;
+  }
+  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32), smem, s, P, stages, groups, gsize,
+                                          ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
+}
+
+template <int EPT>
+int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
+  const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
+  const size_t slot = 2 * half_slot + 128;
+  // threads per row: EPT columns each, whole warps; as many groups as fit into 512 threads
+  int gsize = (((P.cols + EPT - 1) / EPT) + 31) & ~31;
+  if (gsize > kBwdConsumers) return LEGO_ERR_UNSUPPORTED;
+  const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
+  int groups = kBwdConsumers / gsize;
+  if (groups > kBwdMaxGroups) groups = kBwdMaxGroups;
+  // one partial row per group and CTA: no more than the caller's scratch holds
+  const int64_t room = (P.rows < kMaxPartialRows ? P.rows : kMaxPartialRows) / grid;
+  if (groups > room) groups = (int)room;
+  if (groups < 1) return LEGO_ERR_UNSUPPORTED;
+  const size_t budget = (size_t)ctx->smem_optin - 2048 - sizeof(BwdRingCtl) - 128;
+  int stages = (int)((192 * 1024 + slot / 2) / slot);  // about 192 KiB of x and dy in flight
+  if (stages < 2 * groups) stages = 2 * groups;
+  if (stages > kBwdRing) stages = kBwdRing;
+  if ((size_t)stages > budget / slot) stages = (int)(budget / slot);
+  stages -= stages % groups;
+  if (stages < 2 || stages < groups) return LEGO_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
+  P.partial_rows = grid * groups;  // every group writes its row, all zeros if it saw no row of x
+  return launch_ring_dx_g<EPT, 0>(P, ctx, s, grid, stages, groups, gsize, smem);
 }
 
 // Column reduction for widths that are a multiple of 4: a CTA of 32 warps sums 32 columns;
@@ -431,7 +701,10 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
     int32_t err = LEGO_OK;
     DeviceCtx* ctx = device_ctx(&err);
     if (!ctx) return err;
-    st = cols <= kBwdConsumers * 8 ? launch_ring_dx<8>(P, ctx, s) : launch_ring_dx<16>(P, ctx, s);
+    // Same box, GB/s, 16384 rows: one group of 512 threads / groups of cols/16 threads:
+    // N = 2048: 2440 / 3890, N = 4096: 4430 / 4260, N = 8192: 4730 / 4490.
+    if (cols > 3072) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
+    else st = cols <= 1536 ? launch_ring_dx<8>(P, ctx, s) : launch_ring_dx<16>(P, ctx, s);
   }
   if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
   if (st != LEGO_OK) return st;
