@@ -1,6 +1,6 @@
 """Generate ``tests/golden/layouts.json`` by running the reference itself.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference (tavakkoliamirmohammad/LEGO) is pure Python + SymPy + Z3 and
 imports on a CPU-only machine.  It cannot travel to the machine the GPU tests
@@ -25,7 +25,9 @@ import os
 import random
 import sys
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/reference (a checkout of tavakkoliamirmohammad/LEGO)")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 import sympy as sp  # noqa: E402
