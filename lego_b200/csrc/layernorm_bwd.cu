@@ -662,6 +662,7 @@ template <bool VECTOR>
 int32_t launch_dx_by_cols(const BwdParams& P, cudaStream_t s) {
   if (P.cols <= 256 * 8) return launch_dx<256, 8, VECTOR>(P, s);
   if (P.cols <= 256 * 32) return launch_dx<256, 32, VECTOR>(P, s);
+  if (P.cols <= 1024 * 16) return launch_dx<1024, 16, VECTOR>(P, s);  // half the registers of the next one
   if (P.cols <= 1024 * 32) return launch_dx<1024, 32, VECTOR>(P, s);
   return LEGO_ERR_UNSUPPORTED;
 }
