@@ -4,6 +4,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 from lego_b200 import _abi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -41,3 +43,19 @@ def test_status_strings_and_host_only_calls():
     assert lib.lego_layout_check(None) == -1
     assert lib.lego_layernorm_bwd_partial_rows(10, 64) == 10
     assert lib.lego_layernorm_bwd_partial_rows(100000, 64) == 592
+
+
+def test_device_timeout_status_maps_to_lego_error():
+    """The status a caller sees when a bounded wait inside a kernel ran out (2001), and a CUDA
+    runtime error (1000 + cudaError_t), surface as LegoError with the library's text; argument
+    errors (negative) as ValueError."""
+    lib = _abi.lib()
+    assert b"wait" in lib.lego_status_string(2001).lower() or b"timeout" in lib.lego_status_string(2001).lower()
+    with pytest.raises(_abi.LegoError) as e:
+        _abi.check(2001, "lego_device_status")
+    assert e.value.status == 2001 and "lego_device_status" in str(e.value)
+    with pytest.raises(_abi.LegoError):
+        _abi.check(1000 + 2, "lego_softmax_f16")
+    with pytest.raises(ValueError):
+        _abi.check(-5, "lego_layout_check")
+    _abi.check(0, "anything")
