@@ -379,7 +379,7 @@ class GroupedGemm(Workload):
     unit = "TFLOP/s"
     bound = "tensor"
     description = ("16 independent fp16 GEMMs, M,N drawn from {1024,2048,4096} seed 4, K = 4096, inputs ~ N(0,1/64), "
-                   "fp32 accumulate; persistent CTA pairs walk (group, tile_m, tile_n), per-group order OrderBy(Col(M/128, N/256)); operands larger than L2")
+                   "fp32 accumulate; persistent CTAs walk (group, tile_m, tile_n), per-group order OrderBy(Row(M/128, N/256)) as in the reference; operands larger than L2")
 
     def work(self):
         return float(sum(2 * m * n * k for m, n, k in self.sizes))
@@ -392,7 +392,7 @@ class GroupedGemm(Workload):
         self.A_host, self.B_host = inputs.grouped_input()
         self.A = [t.to(dev) for t in self.A_host]
         self.B = [t.to(dev) for t in self.B_host]
-        self.orders = [L.OrderBy(L.Col(m // 128, n // 256)).TileBy([m // 128, n // 256]) for m, n, _ in self.sizes]
+        self.orders = [L.OrderBy(L.Row(m // 128, n // 256)).TileBy([m // 128, n // 256]) for m, n, _ in self.sizes]
 
     def step(self, i):
         self.C = self.ops.lego_group_gemm_fn(self.A, self.B, self.orders)
