@@ -11,8 +11,8 @@ The names and argument meaning follow the callables the reference generates:
 
 Tensors are torch tensors; torch only owns memory and streams here.  A CUDA
 tensor is processed in place on the current stream.  A CPU tensor is staged
-through a device buffer (copy in, kernel, copy out) and a CPU tensor comes back:
-that is the end-to-end path.  Without a GPU or without the built library every
+through the device (large ones in row blocks, so that copy-in, kernel and copy-out
+overlap) and a CPU tensor comes back: that is the end-to-end path.  Without a GPU or without the built library every
 op raises; there is no CPU implementation behind them.
 """
 from __future__ import annotations
@@ -352,6 +352,10 @@ def layer_norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, mean
     row statistics; dweight / dbias come from a fixed-order two-stage column reduction
     (same bits on every run)."""
     n = x.shape[-1]
+    if (not x.is_cuda and not dy.is_cuda and x.is_contiguous() and dy.is_contiguous() and x.shape == dy.shape
+            and x.dtype == torch.float16 and dy.dtype == torch.float16 and weight.dtype == torch.float16
+            and x.numel() * 2 > 2 * _HOST_BLOCK_BYTES):
+        return _layer_norm_bwd_from_host(dy, x, weight, mean, rstd)
     xd = _to_device(x).contiguous().reshape(-1, n)
     dyd = _to_device(dy).contiguous().reshape(-1, n)
     wd = _to_device(weight).contiguous()
@@ -372,6 +376,46 @@ def layer_norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, mean
                                           partial.data_ptr(), m, n, _stream()),
                "lego_layernorm_bwd_f16")
     return _like_input(dx.reshape(x.shape), x), _like_input(dw, weight), _like_input(db, weight)
+
+
+def _layer_norm_bwd_from_host(dy, x, weight, mean, rstd):
+    """Host rows of x and dy: staged block by block (copy-in / compute / copy-out overlap).  Every
+    block yields its own dweight / dbias (fp16, as the entry point rounds them); they are summed
+    in fp32 on the device and rounded once more at the end, so these two results may differ in
+    the last bit from one call on device-resident rows."""
+    n = x.shape[-1]
+    xh, dyh = x.reshape(-1, n), dy.reshape(-1, n)
+    m = xh.shape[0]
+    if weight.numel() != n or mean.numel() != m or rstd.numel() != m:
+        raise ValueError("layer norm backward: shapes of dy, x, weight, mean, rstd do not agree")
+    pipe = _HostPipeline()
+    lib = _abi.lib()
+    wd = _to_device(weight).contiguous()
+    md, rd = _to_device(mean).contiguous(), _to_device(rstd).contiguous()
+    xd = torch.empty(xh.shape, dtype=x.dtype, device=pipe.dev)
+    dyd = torch.empty_like(xd)
+    dx = torch.empty_like(xd)
+    dx_h = _pinned_like(xh.shape, x.dtype)
+    dw32 = torch.zeros(n, dtype=torch.float32, device=pipe.dev)
+    db32 = torch.zeros(n, dtype=torch.float32, device=pipe.dev)
+    dw_b, db_b = torch.empty_like(wd), torch.empty_like(wd)
+    blocks = _row_blocks(m, n * 2, multiple=4)
+    prow = lib.lego_layernorm_bwd_partial_rows(max(r1 - r0 for r0, r1 in blocks), n)
+    partial = torch.empty((2, prow, n), dtype=torch.float32, device=pipe.dev)
+    for r0, r1 in blocks:
+        pipe.feed(xd[r0:r1], xh[r0:r1])
+        pipe.feed(dyd[r0:r1], dyh[r0:r1])
+        pipe.ready()
+        _abi.check(lib.lego_layernorm_bwd_f16(dyd[r0:r1].data_ptr(), xd[r0:r1].data_ptr(), wd.data_ptr(),
+                                              md[r0:r1].data_ptr(), rd[r0:r1].data_ptr(), dx[r0:r1].data_ptr(),
+                                              dw_b.data_ptr(), db_b.data_ptr(), partial.data_ptr(), r1 - r0, n, _stream()),
+                   "lego_layernorm_bwd_f16")
+        dw32 += dw_b
+        db32 += db_b
+        pipe.drain(dx_h[r0:r1], dx[r0:r1])
+    dw, db = dw32.to(torch.float16), db32.to(torch.float16)
+    pipe.finish()
+    return dx_h.reshape(x.shape), _like_input(dw, weight), _like_input(db, weight)
 
 
 lego_layer_norm = LEGOLayerNorm.apply

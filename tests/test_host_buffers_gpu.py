@@ -85,3 +85,22 @@ def test_eval_range_into_host_memory():
     part = ops.eval_range(lay, begin=12345, count=3 * (1 << 20) + 17, host=True)
     assert torch.equal(part, want[12345:12345 + 3 * (1 << 20) + 17])
     assert torch.equal(ops.eval_range(lay, count=1000, host=True), want[:1000])
+
+
+def test_layernorm_backward_host_rows():
+    g = torch.Generator().manual_seed(15)
+    rows, cols = 2500, 4096                                  # 20 MiB each of x and dy: three blocks
+    x = torch.randn(rows, cols, generator=g).half()
+    dy = (0.1 * torch.randn(rows, cols, generator=g)).half()
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).half()
+    b = (0.1 * torch.randn(cols, generator=g)).half()
+    _, mean, rstd = ops.layer_norm_fwd(x.cuda(), w.cuda(), b.cuda(), 1e-5)
+    dx_d, dw_d, db_d = ops.layer_norm_bwd(dy.cuda(), x.cuda(), w.cuda(), mean, rstd)
+    dx, dw, db = ops.layer_norm_bwd(dy.pin_memory(), x.pin_memory(), w, mean.cpu(), rstd.cpu())
+    assert not dx.is_cuda and not dw.is_cuda and not db.is_cuda
+    assert torch.equal(dx, dx_d.cpu())                       # rows are independent: same bits
+    # the column sums are rounded to fp16 per block (at the magnitude of the block's sum) and once more
+    # at the end: a few fp16 ulps of the largest entry, far inside the 1e-2 of the largest entry that
+    # the oracle comparison allows
+    for got, want in ((dw, dw_d.cpu()), (db, db_d.cpu())):
+        assert (got.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
