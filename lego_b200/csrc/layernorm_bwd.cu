@@ -258,13 +258,17 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
       s2 = ptx::add2(s2, w[k]);
     }
     float2 ss = make_float2(s1.x + s1.y, s2.x + s2.y);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
-      ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
-    }
     float2* r = red2 + (n & 1) * NW;
-    if (lane == 0) r[warp] = ss;
+    {
+      // Even lanes fold the first sum, odd lanes the second: one shuffle per level instead of
+      // two (4 900 -> 4 990 GB/s on one box); lanes 0 and 1 end with the warp's two totals.
+      const bool odd = (lane & 1) != 0;
+      float keep = odd ? ss.y : ss.x;
+      keep += __shfl_xor_sync(0xffffffffu, odd ? ss.x : ss.y, 1);
+#pragma unroll
+      for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+      if (lane < 2) reinterpret_cast<float*>(&r[warp])[lane] = keep;
+    }
     ptx::named_barrier<1, kBwd1Consumers>();
     if (*abort_flag) break;  // uniform: every flag write of this row precedes the barrier above
     // Both half-warps fold the same 16 partials, so every lane ends with the total after four
