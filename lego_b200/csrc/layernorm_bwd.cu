@@ -503,14 +503,23 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
       s2 = ptx::add2(s2, w[k]);
     }
     float2 ss = make_float2(s1.x + s1.y, s2.x + s2.y);
+    if (nw == 1) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
-      ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
-    }
-    if (nw > 1) {
+      for (int o = 16; o > 0; o >>= 1) {
+        ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+        ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+      }
+    } else {
       float2* r = red_all[group][parity];
-      if (lane == 0) r[warp_in_group] = ss;
+      {
+        // even lanes fold the first sum, odd lanes the second: one shuffle per level instead of two
+        const bool odd = (lane & 1) != 0;
+        float keep = odd ? ss.y : ss.x;
+        keep += __shfl_xor_sync(0xffffffffu, odd ? ss.x : ss.y, 1);
+#pragma unroll
+        for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+        if (lane < 2) reinterpret_cast<float*>(&r[warp_in_group])[lane] = keep;
+      }
       asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(gsize) : "memory");
       if (nw > 8) {
         // 16 partials: both half-warps fold the same 16 values by shuffles (few registers)
