@@ -713,7 +713,7 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   int32_t st = LEGO_ERR_UNSUPPORTED;
   // Ring-fed kernel: 16-byte aligned rows of 1 Ki .. 8 Ki columns, enough rows to fill the
   // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
-  if (vec && cols > 1024 && cols <= kBwdConsumers * 16 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
+  if (vec && cols >= 1024 && cols <= kBwdConsumers * 16 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
       a16(partial) && rows >= 2 * 148) {
     int32_t err = LEGO_OK;
     DeviceCtx* ctx = device_ctx(&err);
