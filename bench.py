@@ -5,10 +5,24 @@
 
 A step is one pass of one kernel over one batch of seeded synthetic input.  The
 headline workload is the row-wise softmax (fp16, 16384 x 8192); the other four
-configurations (tiled transpose, LayerNorm, GEMM 8192^3, grouped GEMM) are
-measured in the same run and reported under "workloads".  One JSON line is
-printed by rank 0.  With --impl reference the reference's CPU path (index maps
-in numpy as lego_python prints them + torch CPU ops) is timed on the host cores.
+configurations (tiled transpose, LayerNorm, GEMM 8192^3, grouped GEMM), LayerNorm
+backward, the e5m2 GEMM and the index-map evaluator are measured in the same run and
+reported under "workloads".
+
+With N > 1 (one process per GPU, launched by torch.distributed.run) every named shape is
+SPLIT across the ranks -- rows for the row-wise kernels, output-row slabs for the
+transpose, M for the GEMM with B replicated, every group's M for the grouped GEMM, id
+ranges for the index map -- with no data-path collective: "scaling": "strong", value =
+the named shape's work / the slowest rank's device time.  After the timed region the
+shards are gathered over NCCL and rank 0 checks the assembled result against the oracle.
+The replica figure (every rank the full shape, "weak") is reported beside it.
+
+Timing: R replays (default 10) of a CUDA graph of L = max(K, 100) launches, one CUDA-event
+pair per replay on the launching stream, barrier + synchronize before each replay, max
+over ranks per replay, then the median over replays.  Rank 0 prints ONE JSON line on
+stdout; a detailed record per workload goes to stderr.  With --impl reference the
+reference's CPU path (index maps in numpy as lego_python prints them + torch CPU ops) is
+timed on the host cores at the full named shape.
 """
 from __future__ import annotations
 
@@ -27,11 +41,17 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-import inputs  # noqa: E402  (tests/inputs.py: the seeded builders of the five configurations)
+from lego_b200 import configs as inputs  # noqa: E402  (seeded builders of the five configurations)
+from lego_b200 import shard  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+MIN_LAUNCHES = 100
+REPLAYS = 10
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
 
 
 # --------------------------------------------------------------------------------------
@@ -44,21 +64,30 @@ class Workload:
     bound = "hbm"
     dtype = "f16"
     kernels_per_step = 1
-    description = ""
-    graph_ok = False   # the step can be captured in a CUDA graph (no host-to-device copy inside)
+    graph_ok = True    # the step can be captured in a CUDA graph (no host-to-device copy inside)
+    peak_scale = 1.0
 
     def work(self) -> float:
-        """Algorithmic bytes (or flops) of one step."""
+        """Algorithmic bytes (or flops) of one pass over the whole named shape."""
         raise NotImplementedError
 
     def metric(self) -> str:
         kind = "HBM GB/s" if self.unit == "GB/s" else "TFLOP/s"
         return f"{getattr(self, 'short', self.name.split('_f')[0])} {kind}"
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
+        """Create this rank's shard of the inputs (the whole shape when world == 1)."""
         raise NotImplementedError
 
     def step(self, i: int):
+        raise NotImplementedError
+
+    def shard_result(self):
+        """This rank's part of the result as one contiguous tensor (equal sizes on every rank)."""
+        raise NotImplementedError
+
+    def check(self, full):
+        """Rank 0: the assembled result against the oracle -> (ok, text)."""
         raise NotImplementedError
 
     def e2e_setup(self):
@@ -67,271 +96,337 @@ class Workload:
     def e2e_step(self, i: int):
         raise NotImplementedError
 
-    def cpu_sample(self, threads: int, budget: float = 4.0):
-        """(work done, seconds, what was run) for a bounded sample (about `budget` seconds) on the host cores."""
+    def cpu_pass(self):
+        """One pass of the reference's CPU path over the whole named shape: (work, seconds, what)."""
         raise NotImplementedError
+
+    def comparators(self):
+        """name -> callable(i) of same-box library kernels doing the same work (never a product path)."""
+        return {}
+
+    @staticmethod
+    def n_sets(bytes_per_set):
+        """Rotating buffer sets so that consecutive launches never find their data in L2."""
+        return max(1, min(64, math.ceil(3 * L2_BYTES / max(1, bytes_per_set))))
 
 
 def _rate(work: float, seconds: float, unit: str) -> float:
     return work / seconds / (1e9 if unit == "GB/s" else 1e12)
 
 
-class Softmax(Workload):
-    graph_ok = True
-    name = "softmax_f16_16384x8192"
-    description = ("row-wise softmax, fp16 16384 x 8192 ~ N(0, 2^2) seed 1, fp32 arithmetic, rows mapped by "
-                   "OrderBy(Row(16384)).TileBy([4096],[4]); inputs (256 MiB) larger than L2")
+def _timed(fn):
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+class _Rows(Workload):
     rows, cols = 16384, 8192
+
+    def _rows_setup(self, rank, world):
+        self.rank, self.world = rank, world
+        self.r0, self.r1 = shard.shard_rows(self.rows, rank, world)
+        self.sets = self.n_sets(2 * (self.r1 - self.r0) * self.cols * 2)
+        self.keep = [None] * (self.sets + 1)
+
+
+class Softmax(_Rows):
+    name = "softmax_f16_16384x8192"
 
     def work(self):
         return 2.0 * self.rows * self.cols * 2
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
         from lego_b200 import ops
         self.ops = ops
+        self._rows_setup(rank, world)
         self.x_host = inputs.softmax_input(self.rows, self.cols)
-        self.x = self.x_host.to(dev)
-        self.row_map = ops.row_tiling_layout(self.rows, 4)
-        self.y = None
+        xs = self.x_host[self.r0:self.r1]
+        self.x = [xs.to(dev) for _ in range(self.sets)]
+        self.row_map = ops.row_tiling_layout(self.r1 - self.r0, 4)
 
     def step(self, i):
-        self.y = self.ops.softmax(self.x, self.row_map)
+        k = i % self.sets
+        self.keep[i % len(self.keep)] = self.y = self.ops.softmax(self.x[k], self.row_map)
 
-    def check(self):
+    def shard_result(self):
+        return self.y
+
+    def check(self, full):
         from oracle import lego_oracle as O
         sel = torch.arange(0, self.rows, 257)
-        err = (self.y[sel.to(self.y.device)].cpu().float() - O.softmax(self.x_host[sel]).float()).abs().max().item()
+        err = (full[sel.to(full.device)].cpu().float() - O.softmax(self.x_host[sel]).float()).abs().max().item()
         return err <= 1e-3, f"max-abs {err:.2e} on {len(sel)} rows vs oracle (tol 1e-3)"
 
     def e2e_setup(self):
-        self.x_pinned = self.x_host.pin_memory()
+        self.x_pinned = self.x_host[self.r0:self.r1].contiguous().pin_memory()
         return self.x_pinned.numel() * 2, self.x_pinned.numel() * 2
 
     def e2e_step(self, i):
         return self.ops.softmax(self.x_pinned, self.row_map)
 
-    def cpu_sample(self, threads, budget=4.0):
-        rows = 2048
-        x = self.x_host[:rows]
-        t0 = time.perf_counter()
-        n = 0
-        while time.perf_counter() - t0 < budget:
-            torch.softmax(x.float(), dim=-1).half()
-            n += 1
-        dt = time.perf_counter() - t0
-        return 2.0 * rows * self.cols * 2 * n, dt, f"{n} x torch.softmax(x.float(),-1).half() on {rows} of {self.rows} rows"
+    def cpu_pass(self):
+        x = self.x_host
+        dt = _timed(lambda: torch.softmax(x.float(), dim=-1).half())
+        return self.work(), dt, f"torch.softmax(x.float(),-1).half() on all {self.rows} rows"
+
+    def comparators(self):
+        return {"torch.softmax": lambda i: torch.softmax(self.x[i % self.sets], dim=-1),
+                "d2d_copy": _copy_comparator(self.x[0], self.sets)}
 
 
-class LayerNorm(Workload):
-    graph_ok = True
+def _copy_comparator(like, sets):
+    src = [torch.empty_like(like) for _ in range(sets)]
+    dst = [torch.empty_like(like) for _ in range(sets)]
+    return lambda i: dst[i % sets].copy_(src[i % sets])
+
+
+class LayerNorm(_Rows):
     name = "layernorm_fwd_f16_16384x8192"
-    description = ("LayerNorm forward, fp16 16384 x 8192 seed 2, eps 1e-5, fp32 statistics, fp16 y + fp32 mean/rstd; "
-                   "inputs (256 MiB) larger than L2")
-    rows, cols = 16384, 8192
 
     def work(self):
         return 2.0 * self.rows * self.cols * 2
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
         from lego_b200 import ops
         self.ops = ops
+        self._rows_setup(rank, world)
         self.x_host, self.g_host, self.b_host = inputs.layernorm_input(self.rows, self.cols)
-        self.x, self.g, self.b = self.x_host.to(dev), self.g_host.to(dev), self.b_host.to(dev)
-        self.row_map = ops.row_tiling_layout(self.rows, 4)
+        xs = self.x_host[self.r0:self.r1]
+        self.x = [xs.to(dev) for _ in range(self.sets)]
+        self.g, self.b = self.g_host.to(dev), self.b_host.to(dev)
+        self.row_map = ops.row_tiling_layout(self.r1 - self.r0, 4)
 
     def step(self, i):
-        self.out = self.ops.layer_norm_fwd(self.x, self.g, self.b, 1e-5, self.row_map)
+        self.keep[i % len(self.keep)] = self.out = self.ops.layer_norm_fwd(self.x[i % self.sets], self.g, self.b,
+                                                                           1e-5, self.row_map)
 
-    def check(self):
+    def shard_result(self):
+        return self.out[0]
+
+    def check(self, full):
         from oracle import lego_oracle as O
         sel = torch.arange(0, self.rows, 257)
         ref = O.layernorm_fwd(self.x_host[sel], self.g_host, self.b_host, 1e-5, round_output=False)[0]
-        err = (self.out[0][sel.to(self.x.device)].cpu().float() - ref).abs()
+        err = (full[sel.to(full.device)].cpu().float() - ref).abs()
         ok = bool((err <= 1e-3 + ref.abs() * 2.0 ** -11).all())
         small = err[ref.abs() < 2].max().item()
         return ok, (f"max-abs {small:.2e} where |y| < 2 on {len(sel)} rows vs fp32 oracle (tol 1e-3; beyond, "
                     f"1e-3 + half an fp16 ulp of y)")
 
     def e2e_setup(self):
-        self.xp = self.x_host.pin_memory()
-        return self.xp.numel() * 2 + 2 * self.cols * 2, self.xp.numel() * 2 + 2 * self.rows * 4
+        self.xp = self.x_host[self.r0:self.r1].contiguous().pin_memory()
+        return self.xp.numel() * 2 + 2 * self.cols * 2, self.xp.numel() * 2 + 2 * (self.r1 - self.r0) * 4
 
     def e2e_step(self, i):
         return self.ops.layer_norm_fwd(self.xp, self.g_host, self.b_host, 1e-5, self.row_map)
 
-    def cpu_sample(self, threads, budget=4.0):
-        rows = 2048
-        x = self.x_host[:rows]
-        t0 = time.perf_counter()
-        n = 0
-        while time.perf_counter() - t0 < budget:
-            torch.nn.functional.layer_norm(x.float(), (self.cols,), self.g_host.float(), self.b_host.float(), 1e-5).half()
-            n += 1
-        dt = time.perf_counter() - t0
-        return 2.0 * rows * self.cols * 2 * n, dt, f"{n} x F.layer_norm fp32 on {rows} of {self.rows} rows"
+    def cpu_pass(self):
+        x, g, b = self.x_host, self.g_host.float(), self.b_host.float()
+        dt = _timed(lambda: torch.nn.functional.layer_norm(x.float(), (self.cols,), g, b, 1e-5).half())
+        return self.work(), dt, f"F.layer_norm fp32 on all {self.rows} rows"
+
+    def comparators(self):
+        F = torch.nn.functional
+        return {"F.layer_norm": lambda i: F.layer_norm(self.x[i % self.sets], (self.cols,), self.g, self.b, 1e-5),
+                "d2d_copy": _copy_comparator(self.x[0], self.sets)}
 
 
-class LayerNormBwd(Workload):
-    graph_ok = True
+class LayerNormBwd(_Rows):
     name = "layernorm_bwd_f16_16384x8192"
     short = "layernorm_bwd"
     kernels_per_step = 2   # dx + column partials, then the column reduction
-    description = ("LayerNorm backward (dx, dgamma, dbeta), fp16 16384 x 8192 seed 2 with dy ~ N(0, 0.1^2) from the same "
-                   "generator, fp32 arithmetic, fixed-order two-stage column reduction; x and dy (512 MiB) larger than L2")
-    rows, cols = 16384, 8192
 
     def work(self):
         return 3.0 * self.rows * self.cols * 2   # x and dy read, dx written (the reference's formula)
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
         from lego_b200 import ops
-        from oracle import lego_oracle as O
         self.ops = ops
+        self._rows_setup(rank, world)
+        self.sets = self.n_sets(3 * (self.r1 - self.r0) * self.cols * 2)
+        self.keep = [None] * (self.sets + 1)
         self.x_host, self.g_host, self.b_host = inputs.layernorm_input(self.rows, self.cols)
         self.dy_host = (0.1 * torch.randn(self.rows, self.cols, generator=torch.Generator().manual_seed(22))).half()
-        self.x, self.g, self.dy = self.x_host.to(dev), self.g_host.to(dev), self.dy_host.to(dev)
-        _, self.mean, self.rstd = ops.layer_norm_fwd(self.x, self.g, self.b_host.to(dev), 1e-5)
+        xs, dys = self.x_host[self.r0:self.r1], self.dy_host[self.r0:self.r1]
+        self.x = [xs.to(dev) for _ in range(self.sets)]
+        self.dy = [dys.to(dev) for _ in range(self.sets)]
+        self.g = self.g_host.to(dev)
+        self.bdev = self.b_host.to(dev)
+        _, self.mean, self.rstd = ops.layer_norm_fwd(self.x[0], self.g, self.bdev, 1e-5)
 
     def step(self, i):
-        self.out = self.ops.layer_norm_bwd(self.dy, self.x, self.g, self.mean, self.rstd)
+        k = i % self.sets
+        self.keep[i % len(self.keep)] = self.out = self.ops.layer_norm_bwd(self.dy[k], self.x[k], self.g, self.mean,
+                                                                           self.rstd)
 
-    def check(self):
+    def shard_result(self):
+        # dx rows, then this rank's partial dgamma / dbeta as two more rows (summed over ranks by the check)
+        return torch.cat([self.out[0], self.out[1][None], self.out[2][None]])
+
+    def check(self, full):
         from oracle import lego_oracle as O
+        per = (self.r1 - self.r0) + 2
+        parts = full.reshape(self.world, per, self.cols)
+        dx = parts[:, :per - 2].reshape(-1, self.cols)
+        dw = parts[:, per - 2].float().sum(0).cpu().double()
+        db = parts[:, per - 1].float().sum(0).cpu().double()
         sel = torch.arange(0, self.rows, 257)
         _, mean, rstd = O.layernorm_fwd(self.x_host[sel], self.g_host, self.b_host, 1e-5)
         rdx, _, _ = O.layernorm_bwd(self.dy_host[sel], self.x_host[sel], self.g_host, mean, rstd)
-        err = (self.out[0][sel.to(self.x.device)].cpu().float() - rdx.float()).abs().max().item()
+        err = (dx[sel.to(dx.device)].cpu().float() - rdx.float()).abs().max().item()
         # column sums over all rows, against fp64 sums of a strided sample of columns
         cols = torch.arange(0, self.cols, 263)
+        _, mean_all, rstd_all = O.layernorm_fwd(self.x_host, self.g_host, self.b_host, 1e-5)
         xs, dys = self.x_host[:, cols].double(), self.dy_host[:, cols].double()
-        m, r = self.mean.cpu().double()[:, None], self.rstd.cpu().double()[:, None]
+        m, r = mean_all.double()[:, None], rstd_all.double()[:, None]
         dw_ref, db_ref = (dys * (xs - m) * r).sum(0), dys.sum(0)
-        dw, db = self.out[1].cpu().double()[cols], self.out[2].cpu().double()[cols]
-        ew = ((dw - dw_ref).abs().max() / dw_ref.abs().max()).item()
-        eb = ((db - db_ref).abs().max() / db_ref.abs().max()).item()
+        ew = ((dw[cols] - dw_ref).abs().max() / dw_ref.abs().max()).item()
+        eb = ((db[cols] - db_ref).abs().max() / db_ref.abs().max()).item()
         ok = err <= 1e-3 and ew <= 2e-3 and eb <= 2e-3
         return ok, (f"dx max-abs {err:.2e} on {len(sel)} rows vs oracle (tol 1e-3); dgamma / dbeta rel-to-max "
                     f"{ew:.1e} / {eb:.1e} on {len(cols)} columns vs fp64 sums (tol 2e-3)")
 
     def e2e_setup(self):
-        self.xp, self.dyp = self.x_host.pin_memory(), self.dy_host.pin_memory()
+        n = self.r1 - self.r0
+        self.xp = self.x_host[self.r0:self.r1].contiguous().pin_memory()
+        self.dyp = self.dy_host[self.r0:self.r1].contiguous().pin_memory()
         self.mp, self.rp = self.mean.cpu().pin_memory(), self.rstd.cpu().pin_memory()
-        return 2 * self.xp.numel() * 2 + self.cols * 2 + 2 * self.rows * 4, self.xp.numel() * 2 + 2 * self.cols * 2
+        return 2 * self.xp.numel() * 2 + self.cols * 2 + 2 * n * 4, self.xp.numel() * 2 + 2 * self.cols * 2
 
     def e2e_step(self, i):
         return self.ops.layer_norm_bwd(self.dyp, self.xp, self.g_host, self.mp, self.rp)
 
-    def cpu_sample(self, threads, budget=4.0):
+    def cpu_pass(self):
         from oracle import lego_oracle as O
-        rows = 2048
-        x, dy = self.x_host[:rows], self.dy_host[:rows]
-        mean, rstd = self.mean[:rows].cpu(), self.rstd[:rows].cpu()
-        t0 = time.perf_counter()
-        n = 0
-        while time.perf_counter() - t0 < budget:
-            O.layernorm_bwd(dy, x, self.g_host, mean, rstd)
-            n += 1
-        dt = time.perf_counter() - t0
-        return 3.0 * rows * self.cols * 2 * n, dt, f"{n} x oracle layernorm_bwd (torch fp32) on {rows} of {self.rows} rows"
+        _, mean, rstd = O.layernorm_fwd(self.x_host, self.g_host, self.b_host, 1e-5)
+        dt = _timed(lambda: O.layernorm_bwd(self.dy_host, self.x_host, self.g_host, mean, rstd))
+        return self.work(), dt, f"oracle layernorm_bwd (torch fp32) on all {self.rows} rows"
+
+    def comparators(self):
+        def torch_bwd(i):
+            k = i % self.sets
+            return torch.ops.aten.native_layer_norm_backward(self.dy[k], self.x[k], [self.cols], self.mean[:, None],
+                                                             self.rstd[:, None], self.g, self.bdev, [True, True, True])
+        return {"aten.native_layer_norm_backward": torch_bwd}
 
 
 class Transpose(Workload):
-    graph_ok = True
     name = "tiled_transpose_f32_4096"
     dtype = "f32"
-    description = ("LEGO 2-level tiled transpose, fp32 4096 x 4096 uniform[-1,1) seed 0, 32 x 32 tiles, tiles in "
-                   "column-major order; 4 rotating buffer pairs (512 MiB) so no step finds its data in L2")
     n = 4096
-    sets = 4
 
     def work(self):
         return 2.0 * self.n * self.n * 4
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
         import lego_b200 as L
         from lego_b200 import ops
         self.ops = ops
-        n = self.n
+        self.rank, self.world = rank, world
+        n, nt = self.n, self.n // 32
         self.a_host = inputs.transpose_input(n)
-        self.src = L.OrderBy(L.Row(n, n)).TileBy([n // 32, n // 32], [32, 32])
-        self.dst = L.OrderBy(L.Col(n, n)).TileBy([n // 32, n // 32], [32, 32])
-        self.order = L.OrderBy(L.Col(n // 32, n // 32)).TileBy([n // 32, n // 32])
+        self.src = L.OrderBy(L.Row(n, n)).TileBy([nt, nt], [32, 32])
+        self.dst = L.OrderBy(L.Col(n, n)).TileBy([nt, nt], [32, 32])
+        self.order = L.OrderBy(L.Col(nt, nt)).TileBy([nt, nt])
+        # this rank's slab of OUTPUT rows = a range of ids of the column-major tile order
+        self.r0, self.r1 = shard.shard_transpose(n, n, rank, world, 32)
+        self.tiles = (self.r0 // 32 * nt, (self.r1 - self.r0) // 32 * nt)
+        self.sets = self.n_sets(2 * (self.r1 - self.r0) * n * 4)
         self.ins = [self.a_host.to(dev) for _ in range(self.sets)]
         self.outs = [torch.empty_like(self.ins[0]) for _ in range(self.sets)]
 
     def step(self, i):
         k = i % self.sets
-        self.ops.permute(self.ins[k], self.src, self.dst, self.order, out=self.outs[k])
+        self.ops.permute(self.ins[k], self.src, self.dst, self.order, out=self.outs[k],
+                         tiles=None if self.world == 1 else self.tiles)
 
-    def check(self):
-        ok = torch.equal(self.outs[0].cpu().reshape(self.n, self.n), self.a_host.t().contiguous())
+    def shard_result(self):
+        return self.outs[0].reshape(self.n, self.n)[self.r0:self.r1].contiguous()
+
+    def check(self, full):
+        ok = torch.equal(full.cpu().reshape(self.n, self.n), self.a_host.t().contiguous())
         return ok, "bit-exact vs A.T"
 
     def e2e_setup(self):
-        self.ap = self.a_host.pin_memory()
+        if self.world == 1:
+            self.ap = self.a_host.pin_memory()
+            return self.ap.numel() * 4, self.ap.numel() * 4
+        # a rank's slab of output rows is a slab of input columns: a matrix of its own
+        self.ap = self.a_host[:, self.r0:self.r1].contiguous().pin_memory()
         return self.ap.numel() * 4, self.ap.numel() * 4
 
     def e2e_step(self, i):
-        return self.ops.permute(self.ap, self.src, self.dst, self.order)
+        if self.world == 1:
+            return self.ops.permute(self.ap, self.src, self.dst, self.order)
+        return self.ops.transpose(self.ap)
 
-    def cpu_sample(self, threads, budget=4.0):
+    def cpu_pass(self):
         from oracle import lego_oracle as O
-        from helpers import spec_of
         x = self.a_host.reshape(-1).numpy()
-        t0 = time.perf_counter()
-        O.permute(x, spec_of(self.src), spec_of(self.dst))
-        dt = time.perf_counter() - t0
-        return self.work(), dt, "1 x numpy index maps of both layouts over 4096^2 ids + gather/scatter (single thread)"
+        dt = _timed(lambda: O.permute(x, O.spec_of(self.src), O.spec_of(self.dst)))
+        return self.work(), dt, "numpy index maps of both layouts over 4096^2 ids + gather/scatter (single thread)"
+
+    def comparators(self):
+        return {"x.t().contiguous()": lambda i: self.ins[i % self.sets].t().contiguous(),
+                "d2d_copy": _copy_comparator(self.ins[0], self.sets)}
 
 
 class Gemm(Workload):
-    graph_ok = True
     name = "gemm_f16_8192"
     unit = "TFLOP/s"
     bound = "tensor"
-    description = ("C = A.B, fp16 8192^3 ~ N(0, 1/sqrt(8192)) seed 3, fp32 accumulate, fp16 C, 128 x 256 tiles, "
-                   "tile order = LEGO grouped swizzle GROUP_M = 8; operands (384 MiB) larger than L2")
     m = n = k = 8192
 
     def work(self):
         return 2.0 * self.m * self.n * self.k
 
-    def setup(self, dev):
+    def _cast(self, t):
+        return t
+
+    def setup(self, dev, rank, world):
         from lego_b200 import ops
         self.ops = ops
+        self.rank, self.world = rank, world
         self.a_host, self.b_host = inputs.gemm_input(self.m, self.n, self.k)
-        self.a, self.b = self.a_host.to(dev), self.b_host.to(dev)
-        self.order = ops.grouped_swizzle_layout(self.m // 128, self.n // 256, 8)
+        self.a_host, self.b_host = self._cast(self.a_host), self._cast(self.b_host)
+        self.r0, self.r1 = shard.shard_gemm_m(self.m, rank, world)
+        self.a, self.b = self.a_host[self.r0:self.r1].to(dev), self.b_host.to(dev)
+        npm, npn = -(-(self.r1 - self.r0) // 128), -(-self.n // 256)
+        self.order = ops.grouped_swizzle_layout(npm, npn, 8) if (npm % 8 == 0 or npm <= 8) else None
+        self.keep = [None] * 3
 
     def step(self, i):
-        self.c = self.ops.matmul(self.a, self.b, tile_order=self.order)
+        self.keep[i % 3] = self.c = self.ops.matmul(self.a, self.b, tile_order=self.order)
 
-    def check(self):
+    def shard_result(self):
+        return self.c
+
+    def check(self, full):
         self.ops.device_status()
         rows = torch.tensor([0, 129, self.m // 2 + 1, self.m - 1])
         ref = self.a_host[rows].float() @ self.b_host.float()
-        got = self.c[rows.to(self.c.device)].cpu().float()
+        got = full[rows.to(full.device)].cpu().float()
         err = ((got - ref).norm() / ref.norm()).item()
         return err <= 1e-3, f"rel-Frobenius {err:.2e} on 4 rows vs oracle (tol 1e-3)"
 
     def e2e_setup(self):
-        self.ap, self.bp = self.a_host.pin_memory(), self.b_host.pin_memory()
-        return (self.ap.numel() + self.bp.numel()) * 2, self.m * self.n * 2
+        self.ap, self.bp = self.a_host[self.r0:self.r1].contiguous().pin_memory(), self.b_host.pin_memory()
+        eb = self.ap.element_size()
+        return (self.ap.numel() + self.bp.numel()) * eb, (self.r1 - self.r0) * self.n * 2
 
     def e2e_step(self, i):
         return self.ops.matmul(self.ap, self.bp)  # default tile order = the same swizzle, per row block
 
-    def cpu_sample(self, threads, budget=4.0):
-        m = 1024
-        a = self.a_host[:m].float()
-        b = self.b_host.float()
-        t0 = time.perf_counter()
-        n = 0
-        while time.perf_counter() - t0 < budget:
-            a @ b
-            n += 1
-        dt = time.perf_counter() - t0
-        return 2.0 * m * self.n * self.k * n, dt, f"{n} x (A[:{m}].float() @ B.float()) of the 8192^3 problem"
+    def cpu_pass(self):
+        a, b = self.a_host.float(), self.b_host.float()
+        dt = _timed(lambda: a @ b)
+        return self.work(), dt, "A.float() @ B.float() of the whole 8192^3 problem"
+
+    def comparators(self):
+        if self.a.dtype != torch.float16:
+            return {}
+        return {"torch.matmul(fp16)": lambda i: torch.matmul(self.a, self.b)}
 
 
 class GemmE5M2(Gemm):
@@ -339,144 +434,135 @@ class GemmE5M2(Gemm):
     short = "gemm_e5m2"
     dtype = "f8e5m2"
     peak_scale = 2.0   # no measured fp8 peak on file: twice the measured bf16 figure (the tensor cores' nominal ratio)
-    description = ("C = A.B, e5m2 operands 8192^3 (the fp16 inputs of the GEMM workload scaled by 64 and rounded to e5m2), "
-                   "fp32 accumulate (tcgen05 kind::f8f6f4), fp16 C, 128 x 256 tiles, tile order = LEGO grouped swizzle "
-                   "GROUP_M = 8; operands (256 MiB) larger than L2")
 
-    def setup(self, dev):
-        super().setup(dev)
-        self.a_host = (self.a_host * 64).to(torch.float8_e5m2)
-        self.b_host = (self.b_host * 64).to(torch.float8_e5m2)
-        self.a, self.b = self.a_host.to(dev), self.b_host.to(dev)
+    def _cast(self, t):
+        return (t * 64).to(torch.float8_e5m2)
 
-    def check(self):
-        self.ops.device_status()
-        rows = torch.tensor([0, 129, self.m // 2 + 1, self.m - 1])
-        ref = self.a_host[rows].float() @ self.b_host.float()
-        got = self.c[rows.to(self.c.device)].cpu().float()
-        err = ((got - ref).norm() / ref.norm()).item()
-        return err <= 1e-3, f"rel-Frobenius {err:.2e} on 4 rows vs fp32 product of the e5m2 values (tol 1e-3)"
-
-    def e2e_setup(self):
-        self.ap, self.bp = self.a_host.pin_memory(), self.b_host.pin_memory()
-        return self.ap.numel() + self.bp.numel(), self.m * self.n * 2
-
-    def cpu_sample(self, threads, budget=4.0):
-        m = 1024
-        a = self.a_host[:m].float()
-        b = self.b_host.float()
-        t0 = time.perf_counter()
-        n = 0
-        while time.perf_counter() - t0 < budget:
-            a @ b
-            n += 1
-        dt = time.perf_counter() - t0
-        return 2.0 * m * self.n * self.k * n, dt, f"{n} x (e5m2 -> fp32) a @ b on {m} of {self.m} rows of A"
+    def check(self, full):
+        ok, text = super().check(full)
+        return ok, text.replace("vs oracle", "vs fp32 product of the e5m2 values")
 
 
 class GroupedGemm(Workload):
     name = "grouped_gemm_f16_16groups"
     unit = "TFLOP/s"
     bound = "tensor"
-    description = ("16 independent fp16 GEMMs, M,N drawn from {1024,2048,4096} seed 4, K = 4096, inputs ~ N(0,1/64), "
-                   "fp32 accumulate; persistent CTAs walk (group, tile_m, tile_n), per-group order OrderBy(Row(M/128, N/256)) as in the reference; operands larger than L2")
+    graph_ok = False   # the call uploads its problem table from host memory
+    groups, k = 16, 4096
 
     def work(self):
         return float(sum(2 * m * n * k for m, n, k in self.sizes))
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
         import lego_b200 as L
         from lego_b200 import ops
         self.ops = ops
-        self.sizes, _ = inputs.grouped_sizes()
-        self.A_host, self.B_host = inputs.grouped_input()
-        self.A = [t.to(dev) for t in self.A_host]
+        self.rank, self.world = rank, world
+        self.sizes, _ = inputs.grouped_sizes(self.groups, self.k)
+        self.A_host, self.B_host = inputs.grouped_input(self.groups, self.k)
+        self.blocks = shard.shard_grouped_gemm(self.sizes, rank, world)
+        self.A = [t[b:e].to(dev) for t, (b, e) in zip(self.A_host, self.blocks)]
         self.B = [t.to(dev) for t in self.B_host]
-        self.orders = [L.OrderBy(L.Row(m // 128, n // 256)).TileBy([m // 128, n // 256]) for m, n, _ in self.sizes]
+        self.orders = [L.OrderBy(L.Row(-(-(e - b) // 128), n // 256)).TileBy([-(-(e - b) // 128), n // 256])
+                       for (b, e), (_m, n, _k) in zip(self.blocks, self.sizes)]
+        self.keep = [None] * 3
 
     def step(self, i):
-        self.C = self.ops.lego_group_gemm_fn(self.A, self.B, self.orders)
+        self.keep[i % 3] = self.C = self.ops.lego_group_gemm_fn(self.A, self.B, self.orders)
 
-    def check(self):
+    def shard_result(self):
+        return torch.cat([c.reshape(-1) for c in self.C])
+
+    def check(self, full):
         self.ops.device_status()
+        per = full.numel() // self.world
         worst = 0.0
-        for g in (0, 4, 13):
-            ref = self.A_host[g][:64].float() @ self.B_host[g].float()
-            got = self.C[g][:64].cpu().float()
+        # 64 rows of EVERY group, spread over the ranks' row blocks
+        for g, (m, n, _k) in enumerate(self.sizes):
+            rows_per_rank = m // self.world
+            off = sum((mm // self.world) * nn for mm, nn, _ in self.sizes[:g])
+            pick = torch.arange(0, m, max(1, m // 64))[:64]
+            got = torch.stack([full[(int(r) // rows_per_rank) * per + off + (int(r) % rows_per_rank) * n:][:n]
+                               for r in pick]).cpu().float()
+            ref = self.A_host[g][pick].float() @ self.B_host[g].float()
             worst = max(worst, ((got - ref).norm() / ref.norm()).item())
-        return worst <= 1e-3, f"rel-Frobenius {worst:.2e} on 64 rows of 3 groups vs oracle (tol 1e-3)"
+        return worst <= 1e-3, f"rel-Frobenius {worst:.2e} (worst group) on 64 rows of each of the {len(self.sizes)} groups vs oracle (tol 1e-3)"
 
     def e2e_setup(self):
-        self.Ap = [t.pin_memory() for t in self.A_host]
+        self.Ap = [t[b:e].contiguous().pin_memory() for t, (b, e) in zip(self.A_host, self.blocks)]
         self.Bp = [t.pin_memory() for t in self.B_host]
         h2d = sum(t.numel() for t in self.Ap + self.Bp) * 2
-        d2h = sum(m * n for m, n, _ in self.sizes) * 2
+        d2h = sum((e - b) * n for (b, e), (_m, n, _k) in zip(self.blocks, self.sizes)) * 2
         return h2d, d2h
 
     def e2e_step(self, i):
         return self.ops.lego_group_gemm_fn(self.Ap, self.Bp, self.orders)
 
-    def cpu_sample(self, threads, budget=4.0):
-        a = self.A_host[4].float()
-        b = self.B_host[4].float()
-        t0 = time.perf_counter()
-        n = 0
-        while time.perf_counter() - t0 < budget:
-            a @ b
-            n += 1
-        dt = time.perf_counter() - t0
-        m, nn, k = self.sizes[4]
-        return 2.0 * m * nn * k * n, dt, f"{n} x group 4 ({m}x{nn}x{k}) as a.float() @ b.float()"
+    def cpu_pass(self):
+        A = [t.float() for t in self.A_host]
+        B = [t.float() for t in self.B_host]
+        dt = _timed(lambda: [a @ b for a, b in zip(A, B)])
+        return self.work(), dt, "a.float() @ b.float() for each of the 16 groups"
+
+    def comparators(self):
+        return {"torch.matmul loop": lambda i: [torch.matmul(a, b) for a, b in zip(self.A, self.B)]}
 
 
 class IndexMap(Workload):
-    graph_ok = True
     name = "index_map_range_i64_4096x4096"
     short = "index_map"
     dtype = "int64"
-    description = ("index-map evaluator: layout.apply over all 2^24 logical ids of OrderBy(Col(4096,4096))"
-                   ".TileBy([128,128],[32,32]) (the transpose's destination layout), int64 results (128 MiB, larger than L2)")
+    size = 1 << 24
 
     def work(self):
-        return 8.0 * (1 << 24)
+        return 8.0 * self.size
 
-    def setup(self, dev):
+    def setup(self, dev, rank, world):
         import lego_b200 as L
         from lego_b200 import ops
         self.ops = ops
+        self.rank, self.world = rank, world
         self.layout = L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])
+        self.b0, self.b1 = shard.split_range(self.size, rank, world, 1024)
+        self.keep = [None] * (self.n_sets(8 * (self.b1 - self.b0)) + 1)
 
     def step(self, i):
-        self.flat = self.ops.eval_range(self.layout)
+        self.keep[i % len(self.keep)] = self.flat = self.ops.eval_range(self.layout, self.b0, self.b1 - self.b0)
 
-    def check(self):
+    def shard_result(self):
+        return self.flat
+
+    def check(self, full):
         from oracle import lego_oracle as O
-        from helpers import spec_of
-        ids = torch.arange(0, 1 << 24, 4099)
+        ids = torch.arange(0, self.size, 4099)
         idx = [v.numpy() for v in torch.unravel_index(ids, self.layout.dims())]
-        ref = O.groupby_apply(spec_of(self.layout), idx)
-        ok = bool((self.flat[ids.to(self.flat.device)].cpu().numpy() == ref).all())
+        ref = O.groupby_apply(O.spec_of(self.layout), idx)
+        ok = bool((full[ids.to(full.device)].cpu().numpy() == ref).all())
         return ok, f"bit-exact on {len(ids)} sampled ids vs oracle"
 
     def e2e_setup(self):
-        return 0, 8 * (1 << 24)
+        return 0, 8 * (self.b1 - self.b0)
 
     def e2e_step(self, i):
-        return self.ops.eval_range(self.layout, host=True)
+        return self.ops.eval_range(self.layout, self.b0, self.b1 - self.b0, host=True)
 
-    def cpu_sample(self, threads, budget=4.0):
+    def cpu_pass(self):
         from oracle import lego_oracle as O
-        from helpers import spec_of
-        n = 1 << 22
-        t0 = time.perf_counter()
-        ids = np.arange(n, dtype=np.int64)
-        O.groupby_apply(spec_of(self.layout), O.unflatten_index(ids, list(self.layout.dims())))
-        dt = time.perf_counter() - t0
-        return 8.0 * n, dt, "1 x numpy GroupBy.apply over 2^22 of the 2^24 ids (single thread)"
+        spec = O.spec_of(self.layout)
+
+        def run():
+            ids = np.arange(self.size, dtype=np.int64)
+            O.groupby_apply(spec, O.unflatten_index(ids, list(self.layout.dims())))
+        return self.work(), _timed(run), "numpy GroupBy.apply over all 2^24 ids (single thread)"
+
+    def comparators(self):
+        n = self.b1 - self.b0
+        bufs = [torch.empty(n, dtype=torch.int64, device="cuda") for _ in range(len(self.keep))]
+        return {"fill_i64": lambda i: bufs[i % len(bufs)].fill_(i)}
 
 
-WORKLOADS = {"softmax": Softmax, "layernorm": LayerNorm, "layernorm_bwd": LayerNormBwd, "transpose": Transpose, "gemm": Gemm, "gemm_e5m2": GemmE5M2,
-             "grouped_gemm": GroupedGemm, "index_map": IndexMap}
+WORKLOADS = {"softmax": Softmax, "layernorm": LayerNorm, "layernorm_bwd": LayerNormBwd, "transpose": Transpose,
+             "gemm": Gemm, "gemm_e5m2": GemmE5M2, "grouped_gemm": GroupedGemm, "index_map": IndexMap}
 
 
 # --------------------------------------------------------------------------------------
@@ -484,9 +570,9 @@ WORKLOADS = {"softmax": Softmax, "layernorm": LayerNorm, "layernorm_bwd": LayerN
 # --------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks, power and throttle reasons with nvidia-smi while a region runs."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
 
     def __init__(self, index: int):
         self.index = index
@@ -520,7 +606,7 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for s in self.samples:
             try:
@@ -531,10 +617,17 @@ class ClockSampler:
             for name, v in zip(names, s[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
+            if len(s) > 6:
+                try:
+                    power.append(float(s[6]))
+                except ValueError:
+                    pass
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if power:
+            out["power_w_max"] = max(power)
+        return out
 
 
 def measured_peaks():
@@ -556,126 +649,275 @@ def recorded_traffic(name):
     return None
 
 
-def time_steps(fn, steps, warmup, dist_ctx, graph=False):
-    """Device time of `steps` calls of fn(i): CUDA events on the launching stream,
-    barrier + synchronize on both sides, max over ranks.  Returns seconds.  With
-    graph=True the `steps` launches are captured once in a CUDA graph and the
-    timed region is its replay, so host launch overhead is not in the number."""
-    for i in range(warmup):
-        fn(i)
-    torch.cuda.synchronize()
-    g = None
-    if graph:
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for i in range(steps):
-                fn(warmup + i)
-        g.replay()
-        torch.cuda.synchronize()
-    if dist_ctx:
-        torch.distributed.barrier()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    if g is not None:
-        g.replay()
-    else:
-        for i in range(steps):
-            fn(warmup + i)
-    end.record()
-    torch.cuda.synchronize()
-    if dist_ctx:
-        torch.distributed.barrier()
-    ms = start.elapsed_time(end)
-    if dist_ctx:
+class Timer:
+    """Device time of `replays` runs of `launches` calls of fn(i).  The launches are captured
+    once in a CUDA graph (host launch overhead stays out of the number) when the step allows
+    it, else issued on the stream.  Every replay is bracketed by its own CUDA-event pair on
+    the launching stream, preceded by a barrier + synchronize; per replay the MAX over ranks
+    is kept.  Returns the list of replay times in seconds."""
+
+    def __init__(self, dist_ctx):
+        self.dist = dist_ctx
+        self.stream = torch.cuda.Stream()
+
+    def run(self, fn, launches, replays, warmup, graph=True):
+        s = self.stream
+        s.wait_stream(torch.cuda.current_stream())
+        times = []
+        with torch.cuda.stream(s):
+            for i in range(warmup):
+                fn(i)
+            s.synchronize()
+            g = None
+            if graph:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    for i in range(launches):
+                        fn(warmup + i)
+                g.replay()
+                s.synchronize()
+            for _ in range(replays):
+                if self.dist:
+                    torch.distributed.barrier()
+                torch.cuda.synchronize()
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record(s)
+                if g is not None:
+                    g.replay()
+                else:
+                    for i in range(launches):
+                        fn(warmup + i)
+                end.record(s)
+                s.synchronize()
+                times.append(start.elapsed_time(end))
+            del g
+        torch.cuda.current_stream().wait_stream(s)
+        t = torch.tensor(times, dtype=torch.float64, device="cuda")
+        if self.dist:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return [float(v) / 1e3 for v in t.tolist()]
+
+    def sustained(self, fn, launches, seconds, warmup):
+        """One event pair around back-to-back graph replays lasting at least `seconds`."""
+        s = self.stream
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for i in range(warmup):
+                fn(i)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for i in range(launches):
+                    fn(warmup + i)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(s)
+            g.replay()
+            end.record(s)
+            s.synchronize()
+            n = max(2, math.ceil(seconds * 1e3 / max(1e-3, start.elapsed_time(end))))
+            if self.dist:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+            start.record(s)
+            for _ in range(n):
+                g.replay()
+            end.record(s)
+            s.synchronize()
+            ms = start.elapsed_time(end)
+            del g
+        torch.cuda.current_stream().wait_stream(s)
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms / 1e3
+        if self.dist:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item()) / 1e3, n * launches
 
 
-def run_workload(w: Workload, args, dev, n_gpus, rank, dist_ctx, peaks, with_cpu, with_e2e):
-    w.setup(dev)
+def gather(t, world):
+    """All ranks' equal-sized shards, concatenated along the first axis (NCCL over NVLink)."""
+    if world == 1:
+        return t
+    t = t.contiguous()
+    out = torch.empty((world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    if t.dtype in (torch.float8_e5m2,):
+        torch.distributed.all_gather_into_tensor(out.view(torch.uint8), t.view(torch.uint8))
+    else:
+        torch.distributed.all_gather_into_tensor(out, t)
+    return out
+
+
+def run_workload(cls, args, dev, world, rank, timer, peaks, local_rank):
+    w = cls()
+    launches = max(args.steps, MIN_LAUNCHES)
+    w.setup(dev, rank, world)
     w.step(0)
     torch.cuda.synchronize()
-    ok, parity = w.check()
-    sec = time_steps(w.step, args.steps, args.warmup, dist_ctx, graph=(w.graph_ok and not args.no_graph))
-    per_step = sec / args.steps
-    value = _rate(w.work() * n_gpus, per_step, w.unit)
-    # One kernel per step everywhere except LayerNorm backward, whose short column reduction
-    # is charged to the dominant (dx) kernel: the algorithmic bytes over the whole step.
-    achieved = _rate(w.work(), per_step, w.unit)
+    full = gather(w.shard_result(), world)
+    ok, parity = (True, "")
+    if rank == 0:
+        ok, parity = w.check(full)
+    del full
+    graph = w.graph_ok and not args.no_graph
+    with ClockSampler(local_rank) as clocks:
+        times = timer.run(w.step, launches, args.replays, args.warmup, graph=graph)
+    med = statistics.median(times)
+    per_step = med / launches
+    value = _rate(w.work(), per_step, w.unit)            # whole named shape / slowest rank's time
+    per_gpu = value / world                              # what one GPU achieves on its shard
     if w.bound == "hbm":
         peak, which = peaks["hbm"], "copy bandwidth"
     else:
-        peak, which = peaks["tensor_sustained"], "cuBLAS bf16 sustained (kernel timed inside a seconds-long loop)"
-        if getattr(w, "peak_scale", 1.0) != 1.0:
-            peak, which = peak * w.peak_scale, which + f" x {w.peak_scale:g} for 8-bit operands"
+        peak = peaks["tensor_burst"] * w.peak_scale
+        which = "cuBLAS bf16 burst (best single launch); the timed replays are shorter than a second each"
+        if w.peak_scale != 1.0:
+            which += f", x {w.peak_scale:g} for 8-bit operands"
     res = {
-        "workload": w.name, "metric": w.metric(), "value": value, "unit": w.unit,
-        "ms_per_step": per_step * 1e3, "dtype": w.dtype, "parity": parity, "parity_ok": bool(ok),
-        "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": w.unit, "frac": achieved / peak,
-                     "traffic": recorded_traffic(w.name), "peak_source": f"{peaks['source']}: {which}"},
-        "gpu_launches": args.steps * w.kernels_per_step,
-        "timed_as": "cuda graph replay" if (w.graph_ok and not args.no_graph) else "stream launches",
-        "description": w.description,
+        "workload": w.name, "metric": w.metric(), "value": value, "unit": w.unit, "ms_per_step": per_step * 1e3,
+        "dtype": w.dtype, "parity": parity, "parity_ok": bool(ok),
+        "timed": {"launches_per_replay": launches, "replays": len(times), "median_ms": med * 1e3,
+                  "min_ms": min(times) * 1e3, "max_ms": max(times) * 1e3,
+                  "as": "cuda graph replay" if graph else "stream launches"},
+        "roofline": {"bound": w.bound, "achieved": per_gpu, "peak": peak, "unit": w.unit, "frac": per_gpu / peak,
+                     "traffic": recorded_traffic(w.name) if world == 1 else None,
+                     "peak_source": f"{peaks['source']}: {which}"},
+        "gpu_launches": launches * len(times) * w.kernels_per_step,
+        "clocks": clocks.summary(),
     }
-    if w.bound == "tensor":
-        res["roofline"]["frac_of_burst"] = achieved / (peaks["tensor_burst"] * getattr(w, "peak_scale", 1.0))
-    if with_e2e:
+    if w.bound == "tensor" and graph and not args.no_sustained:
+        with ClockSampler(local_rank) as c2:
+            sec, n = timer.sustained(w.step, launches, 2.0, 2)
+        v = _rate(w.work() * n / world, sec, w.unit)     # per GPU
+        res["sustained"] = {"value": v * world, "per_gpu": v, "seconds": sec, "launches": n,
+                            "peak": peaks["tensor_sustained"] * w.peak_scale,
+                            "frac": v / (peaks["tensor_sustained"] * w.peak_scale),
+                            "peak_source": f"{peaks['source']}: cuBLAS bf16 back to back for seconds under the power cap",
+                            "clocks": c2.summary()}
+    if not args.no_e2e:
         h2d, d2h = w.e2e_setup()
-        e_steps = max(3, min(args.steps, 10))
-        sec_e = time_steps(w.e2e_step, e_steps, 3, dist_ctx)
-        res["e2e"] = {"value": _rate(w.work() * n_gpus, sec_e / e_steps, w.unit), "unit": w.unit,
-                      "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                      "ms_per_step": sec_e / e_steps * 1e3}
-    if with_cpu and rank == 0:
+        e_launches = 5
+        te = timer.run(w.e2e_step, e_launches, 3, 3, graph=False)
+        sec_e = statistics.median(te) / e_launches
+        res["e2e"] = {"value": _rate(w.work(), sec_e, w.unit), "unit": w.unit, "h2d_bytes_per_step": int(h2d),
+                      "d2h_bytes_per_step": int(d2h), "ms_per_step": sec_e * 1e3}
+    if world == 1 and not args.no_cmp:
+        cmp_res = {}
+        for name, fn in w.comparators().items():
+            ring = [None] * 4   # results stay alive for a few launches: no output block is rewritten while in L2
+
+            def call(i, fn=fn, ring=ring):
+                ring[i % 4] = fn(i)
+            tc = timer.run(call, launches, max(3, args.replays // 2), args.warmup, graph=True)
+            del ring[:]
+            cmp_res[name] = _rate(w.work(), statistics.median(tc) / launches, w.unit)
+        res["comparators"] = cmp_res
+    if world == 1 and rank == 0 and not args.no_cpu:
         threads = torch.get_num_threads()
-        work, dt, what = w.cpu_sample(threads)
+        work, dt, what = w.cpu_pass()
         res["cpu_baseline"] = {"value": _rate(work, dt, w.unit), "unit": w.unit, "cores": threads, "kind": "port",
-                               "sample": what}
+                               "sample": "1 x " + what}
+    if world > 1 and not args.no_weak:
+        # replicas: every rank the full named shape (per-GPU work fixed as N grows)
+        del w
+        torch.cuda.empty_cache()
+        w = cls()
+        w.setup(dev, 0, 1)
+        tw = timer.run(w.step, launches, max(3, args.replays // 2), args.warmup, graph=graph)
+        res["weak"] = {"value": _rate(w.work() * world, statistics.median(tw) / launches, w.unit), "unit": w.unit,
+                       "scaling": "weak", "what": "every rank runs the full named shape"}
+    del w
+    torch.cuda.empty_cache()
     return res
 
 
+def brief(r):
+    """The few numbers of a workload that go on the one-line record."""
+    out = {"v": round(r["value"], 1), "u": r["unit"], "frac": round(r["roofline"]["frac"], 3),
+           "ms": round(r["ms_per_step"], 5), "ok": r["parity_ok"]}
+    if "sustained" in r:
+        out["sus"] = round(r["sustained"]["value"], 1)
+        out["sus_frac"] = round(r["sustained"]["frac"], 3)
+    if "e2e" in r:
+        out["e2e"] = round(r["e2e"]["value"], 1)
+    if "cpu_baseline" in r:
+        out["cpu"] = round(r["cpu_baseline"]["value"], 2)
+    if "comparators" in r:
+        out["cmp"] = {k: round(v, 1) for k, v in r["comparators"].items()}
+    if "weak" in r:
+        out["weak"] = round(r["weak"]["value"], 1)
+    return out
+
+
 def reference_arm(args, rank):
-    """The reference's CPU path on the host cores, same metric and config."""
+    """The reference's CPU path on the host cores, same metric and config, whole named shape per step."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
     w = WORKLOADS[args.workload]()
-    w.setup(torch.device("cpu"))
+    _cpu_setup(w)
     threads = torch.get_num_threads()
-    rates = []
+    done = []
     what = ""
-    budget = min(4.0, 150.0 / (args.warmup + args.steps))
+    t_begin = time.perf_counter()
+    budget = 150.0
     for i in range(args.warmup + args.steps):
-        work, dt, what = w.cpu_sample(threads, budget)
-        if i >= args.warmup:
-            rates.append((work, dt))
-    work = sum(r[0] for r in rates)
-    dt = sum(r[1] for r in rates)
+        work, dt, what = w.cpu_pass()
+        if i >= args.warmup or not done:
+            done.append((work, dt))
+        if time.perf_counter() - t_begin > budget and done:
+            break
+    timed = done[-args.steps:]
+    work = sum(r[0] for r in timed)
+    dt = sum(r[1] for r in timed)
     value = _rate(work, dt, w.unit)
     line = {"impl": "reference", "metric": w.metric(), "value": value, "unit": w.unit,
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / max(1, args.steps) * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-            "config": {"workload": w.name, "description": w.description},
-            "cpu_baseline": {"value": value, "unit": w.unit, "cores": threads, "kind": "port", "sample": what},
+            "n_gpus": args.gpus, "steps": len(timed), "warmup": args.warmup, "ms_per_step": dt / len(timed) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": w.name},
+            "cpu_baseline": {"value": value, "unit": w.unit, "cores": threads, "kind": "port",
+                             "sample": f"{len(timed)} x " + what},
             "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
+def _cpu_setup(w):
+    """Host inputs of a workload without touching a GPU (the reference arm runs where there may be none)."""
+    import lego_b200 as L
+    if isinstance(w, Softmax):
+        w.x_host = inputs.softmax_input(w.rows, w.cols)
+    elif isinstance(w, LayerNormBwd):
+        w.x_host, w.g_host, w.b_host = inputs.layernorm_input(w.rows, w.cols)
+        w.dy_host = (0.1 * torch.randn(w.rows, w.cols, generator=torch.Generator().manual_seed(22))).half()
+    elif isinstance(w, LayerNorm):
+        w.x_host, w.g_host, w.b_host = inputs.layernorm_input(w.rows, w.cols)
+    elif isinstance(w, Transpose):
+        n, nt = w.n, w.n // 32
+        w.a_host = inputs.transpose_input(n)
+        w.src = L.OrderBy(L.Row(n, n)).TileBy([nt, nt], [32, 32])
+        w.dst = L.OrderBy(L.Col(n, n)).TileBy([nt, nt], [32, 32])
+    elif isinstance(w, Gemm):
+        a, b = inputs.gemm_input(w.m, w.n, w.k)
+        w.a_host, w.b_host = w._cast(a), w._cast(b)
+    elif isinstance(w, GroupedGemm):
+        w.sizes, _ = inputs.grouped_sizes(w.groups, w.k)
+        w.A_host, w.B_host = inputs.grouped_input(w.groups, w.k)
+    elif isinstance(w, IndexMap):
+        w.layout = L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--replays", type=int, default=REPLAYS)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
     ap.add_argument("--only", action="store_true", help="measure the headline workload only")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a graph replay")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cmp", action="store_true", help="skip the same-box library comparators")
+    ap.add_argument("--no-weak", action="store_true", help="skip the replica (weak-scaling) leg at N > 1")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long leg of the GEMMs")
     ap.add_argument("--small", action="store_true",
                     help="halve the row / matrix sizes (for profiler captures; not a bench configuration)")
     args = ap.parse_args()
@@ -697,50 +939,37 @@ def main():
     if dist_ctx:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=dev)
-    n_gpus = world
 
     peaks = measured_peaks()
     if args.small:
-        Softmax.rows = LayerNorm.rows = LayerNormBwd.rows = 8192
+        _Rows.rows = 8192
         Gemm.m = Gemm.n = Gemm.k = 4096
-    head = WORKLOADS[args.workload]()
-    with ClockSampler(local_rank) as clocks:
-        res = run_workload(head, args, dev, n_gpus, rank, dist_ctx, peaks,
-                           with_cpu=(n_gpus == 1 and not args.no_cpu), with_e2e=not args.no_e2e)
-    clock_summary = clocks.summary()
-    others = {}
-    if not args.only:
-        for name, cls in WORKLOADS.items():
-            if name == args.workload:
-                continue
-            del head
-            head = None
-            torch.cuda.empty_cache()
-            w = cls()
-            with ClockSampler(local_rank) as c2:
-                r = run_workload(w, args, dev, n_gpus, rank, dist_ctx, peaks,
-                                 with_cpu=(n_gpus == 1 and not args.no_cpu), with_e2e=not args.no_e2e)
-            r["clocks"] = c2.summary()
-            others[name] = r
-            del w
-
+    timer = Timer(dist_ctx)
+    names = [args.workload] + ([] if args.only else [n for n in WORKLOADS if n != args.workload])
+    results = {}
+    for name in names:
+        r = run_workload(WORKLOADS[name], args, dev, world, rank, timer, peaks, local_rank)
+        results[name] = r
+        if rank == 0:
+            log(json.dumps({"detail": name, **r}))
     if rank == 0:
+        res = results[args.workload]
         line = {
-            "metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": n_gpus,
+            "metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": res["dtype"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": res["dtype"],
             "data": "synthetic",
-            "config": {"workload": res["workload"], "description": res["description"],
-                       "l2_policy": "inputs larger than L2 (transpose rotates 4 buffer pairs)",
-                       "sharding": "each rank runs the full named shape on its own GPU (independent rows / tiles; "
-                                   "no data-path collective)"},
+            "config": {"workload": res["workload"],
+                       "l2_policy": "inputs larger than L2, rotating buffer sets where a shard is smaller",
+                       "sharding": "named shape split across ranks (rows / output slabs / M / every group's M), "
+                                   "no data-path collective; NCCL gathers the result for the parity check"},
             "roofline": res["roofline"], "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"],
-            "timed_as": res["timed_as"],
-            "clocks": clock_summary, "parity": res["parity"], "parity_ok": res["parity_ok"],
-            "workloads": others,
+            "timed": res["timed"], "clocks": res["clocks"], "parity": res["parity"], "parity_ok": res["parity_ok"],
         }
-        if "cpu_baseline" in res:
-            line["cpu_baseline"] = res["cpu_baseline"]
+        for key in ("cpu_baseline", "comparators", "weak"):
+            if key in res:
+                line[key] = res[key]
+        line["workloads"] = {n: brief(r) for n, r in results.items() if n != args.workload}
         print(json.dumps(line), flush=True)
     if dist_ctx:
         torch.distributed.barrier()

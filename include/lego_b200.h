@@ -142,6 +142,18 @@ int32_t lego_eval_range(const lego_layout_t* layout, int64_t begin, int64_t n, i
 int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
                      const lego_layout_t* dst, const lego_layout_t* tile_order, void* stream);
 
+/* The same for a contiguous range of tiles: only the tiles tile_order.inv(t), t in
+ * [tile_begin, tile_begin + tile_count), are moved; the rest of `out` is left as it is.
+ * This is how one GPU of several moves its slab of a reorganisation (the block ids of
+ * benchmarks/mlir/transpose_smem.py:52-55 restricted to a sub-grid): with a column-major
+ * tile order over the source's tile grid a range of ids is a slab of output rows.
+ * tile_order is required, and the two layouts must be a pair the library moves tile by
+ * tile (lego_permute_plan kinds 2 and 3 with a tile order); otherwise
+ * LEGO_ERR_UNSUPPORTED.  A range outside the order's ids is LEGO_ERR_SIZE.        */
+int32_t lego_permute_tiles(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                           const lego_layout_t* dst, const lego_layout_t* tile_order,
+                           int64_t tile_begin, int64_t tile_count, void* stream);
+
 /* ---- row-wise kernels ----------------------------------------------------- */
 
 /* y = softmax(x) along the last axis of a contiguous rows x cols matrix, fp32
@@ -200,12 +212,47 @@ int32_t lego_gemm_e5m2(const void* A, const void* B, void* C, int64_t M, int64_t
                        int32_t trans_a, int32_t trans_b, int32_t activation,
                        const lego_layout_t* tile_order, void* stream);
 
+/* The same two GEMMs with a caller-owned scratch buffer that lets the library split the
+ * partial last wave of tiles along K (a stream-K tail): when the tile count is not a
+ * multiple of what the GPU holds at once -- 8192 x 8192 x 8192 is 13.8 waves, a 1024-row
+ * slab of it 1.7 -- every pair of SMs gets the same number of k-steps, partial fp32
+ * accumulators travel through the buffer and the tile's owner adds them in a fixed order
+ * (same bits on every run).  No counterpart in the reference, whose matmul() launches
+ * one program per tile and leaves the tail to the hardware scheduler
+ * (triton_generated/matmul/matmul_NTA_NTB.py:136-145).
+ *
+ * workspace: device memory, 16-byte aligned, lego_gemm_workspace_bytes() bytes for the
+ * current device (NULL or a smaller buffer: the call runs like lego_gemm_f16).  Its first
+ * 4 KiB are flags: zero them once after allocating; every call that completes leaves
+ * them zero.  After a LEGO_ERR_DEVICE_TIMEOUT zero them again.  Calls that may overlap
+ * on the GPU need a buffer each.                                                 */
+int64_t lego_gemm_workspace_bytes(void);
+int32_t lego_gemm_f16_ws(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                         int32_t trans_a, int32_t trans_b, int32_t activation,
+                         const lego_layout_t* tile_order, void* workspace, int64_t workspace_bytes,
+                         void* stream);
+int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                          int32_t trans_a, int32_t trans_b, int32_t activation,
+                          const lego_layout_t* tile_order, void* workspace, int64_t workspace_bytes,
+                          void* stream);
+
+/* Process-wide tuning knobs of the GEMMs (the reference exposes the same kind of choice
+ * through its @triton.autotune lists, matmul_NTA_NTB.py:17-52).
+ *   LEGO_TUNE_GEMM_BLOCKS   0 = library's choice, 1 = 256 x 256 output per SM pair,
+ *                           2 = 512 x 256 per SM pair when the tile order allows it
+ *   LEGO_TUNE_GEMM_STREAMK  0 = never split along K even when a workspace is given     */
+enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2 };
+int32_t lego_tune(int32_t knob, int32_t value);
+
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by
  * persistent CTAs through the concatenated tile lists; replaces
  * lego_grouped_matmul_kernel / lego_group_gemm_fn, triton_generated/
  * grouped_gemm/grouped_gemm.py:39-162.  A, B, C: host arrays of G device
  * pointers; mnk: host int64 [G,3].  tile_orders (nullable): host array of G
- * layout pointers, entry g with logical dims (M_g/128, N_g/256).               */
+ * layout pointers, entry g with logical dims (M_g/128, N_g/256).  The call uploads
+ * its problem table from host memory that does not outlive it, so it cannot be
+ * part of a stream capture: on a capturing stream it returns
+ * LEGO_ERR_UNSUPPORTED and enqueues nothing.                                    */
 int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* const* C,
                               const int64_t* mnk, int32_t G,
                               const lego_layout_t* const* tile_orders, void* stream);
@@ -227,14 +274,18 @@ int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* 
  *
  * Same arguments and results as lego_grouped_gemm_f16, plus dev_status: a
  * device uint32 owned and zeroed by the caller that receives the code of a
- * bounded wait that ran out, or NULL to use (and clear) a word inside the
- * array.  G > LEGO_STATIC_MAX_GROUPS is rejected with LEGO_ERR_SIZE.
+ * bounded wait that ran out, or NULL to use a word inside the array, which
+ * lego_device_status reads and clears (without allocating anything either).
+ * G > LEGO_STATIC_MAX_GROUPS is rejected with LEGO_ERR_SIZE.
  *
  * The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress, with that device current) and the SM count; make that
- * first call before any stream capture begins.  Every call on a device shares
- * the one array and overwrites what the previous call left there, so two calls
- * whose kernels may overlap on the GPU (different streams) race: order them.  */
+ * (cudaGetSymbolAddress, with that device current) and the SM count.  Like
+ * lego_grouped_gemm_f16, no call of this entry point may be part of a stream
+ * capture (the problem table is uploaded from the caller's stack): on a capturing
+ * stream it returns LEGO_ERR_UNSUPPORTED and enqueues nothing.  Every call on a
+ * device shares the one array and overwrites what the previous call left there,
+ * so two calls whose kernels may overlap on the GPU (different streams) race:
+ * order them.                                                                  */
 #define LEGO_STATIC_MAX_GROUPS     64
 #define LEGO_STATIC_SCRATCH_BYTES  (256 + LEGO_STATIC_MAX_GROUPS * 640)
 int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B, void* const* C,
@@ -245,8 +296,17 @@ int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B,
 /* ---- housekeeping --------------------------------------------------------- */
 
 /* Synchronise `stream` and return (then clear) the current device's status word:
- * LEGO_OK or LEGO_ERR_DEVICE_TIMEOUT; *detail (nullable) receives the raw word. */
+ * LEGO_OK or LEGO_ERR_DEVICE_TIMEOUT; *detail (nullable) receives the raw word.
+ * Covers the workspace's word and the one inside the static array; allocates nothing. */
 int32_t lego_device_status(void* stream, uint32_t* detail);
+
+/* Runs the give-up path of the kernels' bounded waits for real, without a fault: one
+ * CTA waits on a barrier nothing will ever complete, gives up after limit_cycles SM
+ * cycles (1 .. 2e9), records code 0x7e570000 in the status word like a production
+ * kernel does, and returns.  lego_device_status then reports
+ * LEGO_ERR_DEVICE_TIMEOUT once; the device stays usable.  No counterpart in the
+ * reference (its kernels have no waits to bound).                              */
+int32_t lego_selftest_bounded_wait(int64_t limit_cycles, void* stream);
 
 const char* lego_status_string(int32_t status);
 

@@ -23,6 +23,9 @@ BLOCK_REVERSE = 2
 ACT_NONE = 0
 ACT_LEAKY_RELU = 1
 
+TUNE_GEMM_BLOCKS = 1
+TUNE_GEMM_STREAMK = 2
+
 ERR_CUDA_BASE = 1000
 ERR_DEVICE_TIMEOUT = 2001
 
@@ -63,6 +66,8 @@ SIGNATURES = {
     "lego_eval_inv": (C.c_int32, [LayoutP, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lego_eval_range": (C.c_int32, [LayoutP, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "lego_permute": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, LayoutP, LayoutP, LayoutP, C.c_void_p]),
+    "lego_permute_tiles": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, LayoutP, LayoutP, LayoutP, C.c_int64,
+                                       C.c_int64, C.c_void_p]),
     "lego_softmax_f16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, LayoutP, C.c_void_p]),
     "lego_softmax_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, LayoutP, C.c_void_p]),
     "lego_layernorm_fwd_f16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -73,6 +78,13 @@ SIGNATURES = {
                                   C.c_int32, C.c_int32, C.c_int32, LayoutP, C.c_void_p]),
     "lego_gemm_e5m2": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                    C.c_int32, C.c_int32, C.c_int32, LayoutP, C.c_void_p]),
+    "lego_gemm_workspace_bytes": (C.c_int64, []),
+    "lego_gemm_f16_ws": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                     C.c_int32, C.c_int32, C.c_int32, LayoutP, C.c_void_p, C.c_int64, C.c_void_p]),
+    "lego_gemm_e5m2_ws": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                      C.c_int32, C.c_int32, C.c_int32, LayoutP, C.c_void_p, C.c_int64, C.c_void_p]),
+    "lego_tune": (C.c_int32, [C.c_int32, C.c_int32]),
+    "lego_selftest_bounded_wait": (C.c_int32, [C.c_int64, C.c_void_p]),
     "lego_grouped_gemm_f16": (C.c_int32, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                           C.POINTER(C.c_int64), C.c_int32, C.POINTER(LayoutP), C.c_void_p]),
     "lego_grouped_gemm_f16_static": (C.c_int32, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),

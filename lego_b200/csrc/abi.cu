@@ -4,8 +4,11 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace lego {
+
+int32_t static_status_take(cudaStream_t s, uint32_t* word);  // gemm_sm100.cu
 
 namespace {
 std::mutex g_mu;
@@ -39,6 +42,31 @@ DeviceCtx* device_ctx(int32_t* err) {
   g_ctx[dev] = c;
   return c;
 }
+
+DeviceCtx* device_ctx_if_any() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mu);
+  return dev < (int)g_ctx.size() ? g_ctx[dev] : nullptr;
+}
+
+namespace {
+// The give-up path of a bounded wait, run for real: one CTA initialises an mbarrier that
+// nothing ever arrives on, waits on it with the same helper the kernels use, and on expiry
+// records its code in the status word exactly as they do.  It neither faults nor hangs;
+// the context stays usable.
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles, uint32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_barrier_init();
+    if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bar), 0, &abort_flag, limit_cycles))
+      atomicCAS(status, 0u, 0x7e570000u);
+  }
+}
+}  // namespace
 
 void release_all_ctx() {
   std::lock_guard<std::mutex> lock(g_mu);
@@ -89,20 +117,35 @@ int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out) {
 }
 
 int32_t lego_device_status(void* stream, uint32_t* detail) {
+  // Reads what exists and creates nothing: a process that only ever used the non-allocating
+  // entry point must not get a workspace allocated by asking for its status.
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t word = 0;
+  if (DeviceCtx* c = device_ctx_if_any()) {
+    LEGO_CUDA_TRY(cudaMemcpyAsync(&word, c->status_word, sizeof(word), cudaMemcpyDeviceToHost, s));
+    LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+    if (word) {
+      LEGO_CUDA_TRY(cudaMemsetAsync(c->status_word, 0, sizeof(word), s));
+      LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+    }
+  } else {
+    LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+  }
+  uint32_t static_word = 0;
+  const int32_t st = static_status_take(s, &static_word);
+  if (st != LEGO_OK) return st;
+  if (!word) word = static_word;
+  if (detail) *detail = word;
+  return word ? (int32_t)LEGO_ERR_DEVICE_TIMEOUT : (int32_t)LEGO_OK;
+}
+
+int32_t lego_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+  if (limit_cycles < 1 || limit_cycles > 2000000000LL) return LEGO_ERR_SIZE;
   int32_t err = LEGO_OK;
   DeviceCtx* c = device_ctx(&err);
   if (!c) return err;
-  cudaStream_t s = (cudaStream_t)stream;
-  uint32_t word = 0;
-  LEGO_CUDA_TRY(cudaMemcpyAsync(&word, c->status_word, sizeof(word), cudaMemcpyDeviceToHost, s));
-  LEGO_CUDA_TRY(cudaStreamSynchronize(s));
-  if (detail) *detail = word;
-  if (word) {
-    LEGO_CUDA_TRY(cudaMemsetAsync(c->status_word, 0, sizeof(word), s));
-    LEGO_CUDA_TRY(cudaStreamSynchronize(s));
-    return LEGO_ERR_DEVICE_TIMEOUT;
-  }
-  return LEGO_OK;
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)limit_cycles, c->status_word);
+  return cuda_status(cudaGetLastError());
 }
 
 const char* lego_status_string(int32_t status) {

@@ -1,6 +1,7 @@
 // Shared helpers of the CUDA translation units.
 #pragma once
 
+#include <atomic>
 #include <utility>
 
 #include <cuda_runtime.h>
@@ -45,6 +46,20 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// Which devices a kernel has been set up on.  cudaFuncSetAttribute (the opt-in to more
+// than 48 KiB of dynamic shared memory) and occupancy answers hold for the device that was
+// current when they were made, so every launcher keeps one of these per kernel instead of a
+// process-wide flag.  Two host threads that race both do the (idempotent) set-up.
+struct PerDeviceFlag {
+  std::atomic<uint64_t> mask{0};
+  bool test(int dev) const {
+    return dev >= 0 && dev < 64 && ((mask.load(std::memory_order_acquire) >> dev) & 1u) != 0;
+  }
+  void set(int dev) {
+    if (dev >= 0 && dev < 64) mask.fetch_or(1ull << dev, std::memory_order_release);
+  }
+};
+
 // Per-device facts and the lazily created workspace.
 struct DeviceCtx {
   int device;
@@ -56,6 +71,8 @@ struct DeviceCtx {
 };
 // Context of the current device (created on first use); nullptr + *err on failure.
 DeviceCtx* device_ctx(int32_t* err);
+// Context of the current device if one exists; never creates (or allocates) anything.
+DeviceCtx* device_ctx_if_any();
 void release_all_ctx();
 
 __device__ __forceinline__ uint32_t fd_div(uint32_t n, const FastDiv& f) {

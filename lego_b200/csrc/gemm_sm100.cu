@@ -16,6 +16,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -54,6 +55,10 @@ constexpr int TMEM_COLS = 512;
 constexpr int EPI_STAGE_TOTAL = 4 * 2 * 32 * 64 * 2;  // epilogue staging, see EPI_BYTES
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_TOTAL + 1024 + 256;
 constexpr long long WAIT_LIMIT = 2000000000LL;  // SM cycles, about a second
+// A wait that spans a whole k-loop (accumulator full / empty) gets this much more per k-step,
+// about a hundred times what a step takes, so that a very deep K cannot trip a false timeout.
+constexpr long long WAIT_PER_KSTEP = 65536LL;
+__device__ __forceinline__ long long loop_wait_limit(int kblocks) { return WAIT_LIMIT + WAIT_PER_KSTEP * kblocks; }
 
 constexpr int kMaxOrderTerms = 8;
 struct TileTerm { uint32_t a, m, b, dst; };  // coord[dst] += ((t / a) % m) * b; m == 0: no wrap
@@ -294,7 +299,8 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
         const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
         const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
         const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
-        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
+        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag,
+                                          loop_wait_limit(kblocks))) {
           fail(status, abort_flag, 0x20000u | 0x100u | acc);
           break;
         }
@@ -341,7 +347,8 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
       const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
       bool ok = true;
       if (lane == 0)
-        ok = ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
+        ok = ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag,
+                                          loop_wait_limit((p->k + geometry_of(p->elem8).bk - 1) / geometry_of(p->elem8).bk));
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) {
         if (lane == 0) fail(status, abort_flag, 0x30000u | acc);
@@ -366,51 +373,229 @@ gemm_kernel(const __grid_constant__ Problem single, const Problem* __restrict__ 
 
 // ---- CTA-pair kernel ---------------------------------------------------------------------
 //
-// Two CTAs on neighbouring SMs (a cluster of two) compute a 256 x 256 block of C with
-// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own 128
-// columns of B, so an SM pulls 32 KiB per 64-deep k-step from L2 instead of 48 KiB
-// and the ring holds 5 stages next to the epilogue staging.  CTA r of pair p works on flat tile id 2p + r; the host
-// only selects this kernel when the tile order puts ids 2p and 2p + 1 on vertically
-// adjacent tiles of the same tile column.  The leader (rank 0) issues the MMAs; TMA
-// loads of both CTAs complete on the leader's "full" barrier, MMA completion is
-// committed to the "empty" / "accumulator full" barriers of both CTAs, and both
-// epilogues report to the leader's "accumulator empty" barrier.  No load is multicast.
+// Two CTAs on neighbouring SMs (a cluster of two) compute MT blocks of 256 x 256 of C with
+// tcgen05.mma.cta_group::2.  A "pair tile" is 2 * MT consecutive flat tile ids that share a
+// tile column: id 2 * MT * t + 2 * j + r is the 128 x 256 tile whose rows CTA r contributes
+// to block j.  Each CTA stages its own MT x 128 rows of A and its own 128 columns of B per
+// 64-deep k-step, so an SM pulls 32 KiB (MT = 1) or 48 KiB for twice the flops (MT = 2) from
+// L2 where one CTA per tile pulls 48 KiB.  MT = 1 alternates two 256-column accumulators so
+// the epilogue of one pair tile overlaps the main loop of the next; MT = 2 fills all 512
+// TMEM columns with one pair tile (block 0 is drained while block 1's last MMAs retire).
+// The leader (rank 0) issues the MMAs; TMA loads of both CTAs complete on the leader's
+// "full" barrier, MMA completion is committed to the "empty" / "accumulator full" barriers
+// of both CTAs, and both epilogues report to the leader's "accumulator empty" barrier.  No
+// load is multicast.
+//
+// Work split (single problem only): pair tiles [0, dp_tiles) are walked data-parallel,
+// worker w taking w, w + W, ...; the remaining sk_tiles -- the partial last wave -- are cut
+// along K into W equal runs of k-steps (stream-K), so every pair of SMs gets the same number
+// of k-steps.  A run may start inside a tile: that worker is not the tile's owner and writes
+// its fp32 accumulator to its slot of the workspace; the owner (the worker whose run holds
+// k-step 0 of the tile) adds the slots of the workers that follow it and stores C.  Runs are
+// processed before the data-parallel tiles and in increasing k order, so an owner's own part
+// finishes after its peers' parts: the flag waits are there for correctness and are bounded
+// like every other wait.
 
-constexpr int P_STAGES = 5;
 constexpr int P_BN_HALF = BN / 2;                    // B columns staged per CTA
-constexpr int P_A_BYTES = BM * BK * 2;
+constexpr int P_A_BYTES = BM * BK * 2;               // one 128-row block of A
 constexpr int P_B_BYTES = P_BN_HALF * BK * 2;
-constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + EPI_STAGE_TOTAL + 1024 + 256;
+__host__ __device__ constexpr int pair_stage_bytes(int mt) { return mt * P_A_BYTES + P_B_BYTES; }
+__host__ __device__ constexpr int pair_stages(int mt) { return mt == 1 ? 5 : 4; }
+__host__ __device__ constexpr int pair_smem_bytes(int mt) {
+  return pair_stages(mt) * pair_stage_bytes(mt) + EPI_STAGE_TOTAL + 1024 + 256;
+}
+constexpr int P_MAX_STAGES = 5;
 
 struct PairBarriers {
-  uint64_t full[P_STAGES];
-  uint64_t empty[P_STAGES];
+  uint64_t full[P_MAX_STAGES];
+  uint64_t empty[P_MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
 
-template <bool GROUPED>
+// Stream-K workspace: kSkFlagBytes of flags (one word per worker, CTA rank and epilogue warp;
+// zero before the first call, every call that completes leaves them zero) followed by one
+// fp32 accumulator slot per worker: [rank][block j][column 0..255][row 0..127].
+constexpr int kSkFlagBytes = 4096;
+constexpr int kSkMaxWorkers = kSkFlagBytes / (2 * 4 * 4);
+constexpr int kSkBlockFloats = BM * BN;  // one CTA's 128 x 256 accumulator
+
+struct Sched {
+  int32_t total_tiles;  // pair tiles
+  int32_t dp_tiles;     // walked whole, round-robin
+  int32_t sk_tiles;     // cut along K (ids dp_tiles .. total_tiles - 1)
+  int32_t sk_run;       // k-steps per worker in the stream-K part
+  int32_t kblocks;      // k-steps per tile (uniform: the stream-K part exists for one problem only)
+  int32_t reserved;
+  float* workspace;     // nullable when sk_tiles == 0
+};
+
+struct WorkItem {
+  int tile;       // pair tile
+  int kb0, kb1;   // k-steps [kb0, kb1); kb1 < 0: all of the tile's
+  int n_peers;    // > 0: add the slots of workers w + 1 .. w + n_peers before storing C
+  bool partial;   // true: write the accumulator to this worker's slot instead of C
+};
+
+struct WorkIter {
+  int u, u_end;  // stream-K k-steps left, as offsets into the stream-K part
+  int tile;      // next data-parallel pair tile
+};
+
+__device__ __forceinline__ WorkIter work_begin(const Sched& sc, int w) {
+  WorkIter it;
+  const long long total = (long long)sc.sk_tiles * sc.kblocks;
+  const long long u0 = (long long)w * sc.sk_run;
+  it.u = (int)(u0 < total ? u0 : total);
+  it.u_end = (int)(u0 + sc.sk_run < total ? u0 + sc.sk_run : total);
+  it.tile = w;
+  return it;
+}
+
+__device__ __forceinline__ bool work_next(WorkIter& it, const Sched& sc, int w, int n_workers, WorkItem* out) {
+  if (it.u < it.u_end) {
+    const int j = it.u / sc.kblocks;
+    const int kb0 = it.u - j * sc.kblocks;
+    const int tile_end = (j + 1) * sc.kblocks;
+    const int seg_end = it.u_end < tile_end ? it.u_end : tile_end;
+    out->tile = sc.dp_tiles + j;
+    out->kb0 = kb0;
+    out->kb1 = kb0 + (seg_end - it.u);
+    out->partial = kb0 > 0;
+    out->n_peers = (kb0 == 0 && seg_end < tile_end) ? (tile_end - 1) / sc.sk_run - w : 0;
+    it.u = seg_end;
+    return true;
+  }
+  if (it.tile < sc.dp_tiles) {
+    out->tile = it.tile;
+    out->kb0 = 0;
+    out->kb1 = -1;
+    out->partial = false;
+    out->n_peers = 0;
+    it.tile += n_workers;
+    return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// What the pair kernel's epilogue does besides storing C.
+struct EpiSplit {
+  float* partial_out;       // non-null: dump this warp's accumulator rows here, store no C
+  const float* partial_in;  // first peer's block (same rank and j); further peers follow at `stride`
+  int n_in;
+  size_t stride;
+};
+
+// One accumulator block (this warp's 32 rows x 256 columns) -> [+ peers' partial sums] ->
+// activation -> fp16 -> swizzled shared memory -> TMA store; or -> fp32 partial slot.
+__device__ __forceinline__ void epilogue_pair_block(const Problem* p, int tm, int tn, int q, int lane,
+                                                    uint32_t tmem_tile, uint8_t* warp_stage, int activation,
+                                                    uint32_t* chunk_no, const Problem** fenced, const EpiSplit& sp) {
+  const int row0 = tm * BM + q * 32;
+  const int row = q * 32 + lane;
+  if (sp.partial_out) {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      ptx::tmem_ld_32x32(tmem_tile + c * 32, r);
+      ptx::tmem_ld_wait();
+      float* dst = sp.partial_out + (size_t)(c * 32) * BM + row;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) __stcg(dst + (size_t)i * BM, __uint_as_float(r[i]));
+    }
+    return;
+  }
+  if (row0 >= p->m && sp.n_in == 0) return;  // nothing of this warp's rows exists (warp-uniform)
+  if (fenced && *fenced != p) {  // table-resident map: acquire once per problem
+    if (lane == 0) ptx::tensormap_acquire(&p->tma_c);
+    *fenced = p;
+  }
+#pragma unroll 1
+  for (int c = 0; c < BN / EPI_CHUNK_COLS; ++c) {
+    // Chunks past the last column are not staged at all: every staged chunk commits
+    // exactly one bulk group, which is what the "at most one pending" wait below counts.
+    const int col0 = tn * BN + c * EPI_CHUNK_COLS;
+    if (col0 >= p->n || row0 >= p->m) break;
+    uint32_t r[64];
+    ptx::tmem_ld_32x32(tmem_tile + c * EPI_CHUNK_COLS, r);
+    ptx::tmem_ld_32x32(tmem_tile + c * EPI_CHUNK_COLS + 32, r + 32);
+    uint8_t* buf = warp_stage + ((*chunk_no) & 1u) * EPI_BUF_BYTES;
+    if (lane == 0) ptx::bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
+    __syncwarp();
+    ptx::tmem_ld_wait();
+    for (int peer = 0; peer < sp.n_in; ++peer) {
+      const float* src = sp.partial_in + peer * sp.stride + (size_t)(c * EPI_CHUNK_COLS) * BM + row;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldcg(src + (size_t)i * BM));
+    }
+    uint4* dst = reinterpret_cast<uint4*>(buf + lane * 128);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t h[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float x0 = __uint_as_float(r[j * 8 + 2 * e]);
+        float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
+        if (activation == LEGO_ACT_LEAKY_RELU) {
+          x0 = x0 >= 0.f ? x0 : 0.01f * x0;
+          x1 = x1 >= 0.f ? x1 : 0.01f * x1;
+        }
+        const __half2 hh = __floats2half2_rn(x0, x1);
+        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+      }
+      dst[j ^ (lane & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+    ptx::fence_proxy_async();  // generic-proxy writes above -> visible to the TMA engine
+    __syncwarp();
+    if (lane == 0) {
+      ptx::tma_store_2d(&p->tma_c, col0, row0, ptx::smem_u32(buf));
+      ptx::bulk_commit_group();
+    }
+    ++(*chunk_no);
+  }
+}
+
+// Raise the abort flag of this CTA and of its peer: the peer's waits then give up at their
+// next check instead of running out one after another.
+__device__ __forceinline__ void fail_pair(uint32_t* status, volatile uint32_t* abort_flag, uint32_t peer_rank,
+                                          uint32_t code) {
+  *abort_flag = 1;
+  ptx::st_cluster_u32(ptx::mapa(ptx::smem_u32(const_cast<uint32_t*>(abort_flag)), peer_rank), 1u);
+  atomicCAS(status, 0u, code);
+}
+
+template <bool GROUPED, int MT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict__ table, int n_problems,
-                 int total_pairs, int activation, uint32_t* status) {
+                 const __grid_constant__ Sched sched, int activation, uint32_t* status) {
+  constexpr int NSTAGE = pair_stages(MT);
+  constexpr int STAGE = pair_stage_bytes(MT);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint8_t* epi_stage = smem + P_STAGES * P_STAGE_BYTES;
+  uint8_t* epi_stage = smem + NSTAGE * STAGE;
   PairBarriers* bars = reinterpret_cast<PairBarriers*>(epi_stage + EPI_BYTES);
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
-  const int n_pairs_grid = gridDim.x >> 1;
-  const int first_pair = blockIdx.x >> 1;
+  const int n_workers = gridDim.x >> 1;
+  const int worker = blockIdx.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < P_STAGES; ++s) {
+    for (int s = 0; s < NSTAGE; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
     }
@@ -422,9 +607,9 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
   }
-  if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), TMEM_COLS);
-    ptx::tmem_relinquish();
+  if (warp == 1) {  // warp 1 of both CTAs: the pair's allocation is collective
+    ptx::tmem_alloc_pair(ptx::smem_u32(&bars->tmem_base), TMEM_COLS);
+    ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -432,89 +617,80 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  // problem owning flat tile id `tile` (ids of one pair always belong to one problem)
+  // problem owning pair tile `tile` (the ids of one pair tile always belong to one problem)
   auto problem_of = [&](int tile, int* cursor) -> const Problem* {
     if (!GROUPED) return &prob;
     int g = *cursor;
-    while (g + 1 < n_problems && tile >= table[g + 1].tile_start) ++g;
+    while (g + 1 < n_problems && 2 * MT * tile >= table[g + 1].tile_start) ++g;
     *cursor = g;
     return &table[g];
+  };
+  auto kblocks_of = [](const Problem* pr) {
+    const int bk = geometry_of(pr->elem8).bk;
+    return (pr->k + bk - 1) / bk;
   };
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      uint32_t issued[P_STAGES] = {};
-      bool ok = true;
+      uint32_t issued[NSTAGE] = {};
       const Problem* fenced = nullptr;
-      // One k-step of this CTA's share of the pair's tile: the boxes of A and B to fetch.
-      struct Step {
-        int pair, kb, kblocks, cursor, tm, n0;
-        const Problem* pr;
-      };
-      auto enter = [&](Step& st) {  // position `st` on the first k-step of st.pair
-        if (st.pair >= total_pairs) return;
-        st.pr = problem_of(2 * st.pair, &st.cursor);
-        st.kblocks = (st.pr->k + geometry_of(st.pr->elem8).bk - 1) / geometry_of(st.pr->elem8).bk;
-        st.kb = 0;
-        int tn;
-        tile_coords(*st.pr, 2 * st.pair + (int)rank - st.pr->tile_start, &st.tm, &tn);
-        st.n0 = tn * BN + (int)rank * P_BN_HALF;
-      };
-      auto advance = [&](Step& st) {
-        if (++st.kb == st.kblocks) {
-          st.pair += n_pairs_grid;
-          enter(st);
-        }
-      };
-      auto acquire = [&](const Problem* pr) {  // once per problem this CTA meets, not per tile
-        if (GROUPED && pr != fenced) {
+      int cursor = 0;
+      WorkIter iter = work_begin(sched, worker);
+      WorkItem item;
+      bool ok = true;
+      while (ok && work_next(iter, sched, worker, n_workers, &item)) {
+        const Problem* pr = problem_of(item.tile, &cursor);
+        if (GROUPED && pr != fenced) {  // once per problem this CTA meets, not per tile
           ptx::tensormap_acquire(&pr->tma_a);
           ptx::tensormap_acquire(&pr->tma_b);
           fenced = pr;
         }
-      };
-      Step ld = {first_pair, 0, 0, 0, 0, 0, nullptr};
-      enter(ld);
-      while (ld.pair < total_pairs) {
-        const Problem* pr = ld.pr;
-        acquire(pr);
-        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
-          fail(status, abort_flag, 0x110000u | stage);
-          ok = false;
-          break;
-        }
-        const uint32_t full_local = ptx::smem_u32(&bars->full[stage]);
-        const uint32_t full_leader = ptx::mapa(full_local, 0);
-        const uint32_t a_dst = ptx::smem_u32(smem + stage * P_STAGE_BYTES);
-        const uint32_t b_dst = a_dst + P_A_BYTES;
-        if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * P_STAGE_BYTES);  // both CTAs' bytes
         const Geometry geo = geometry_of(pr->elem8);
-        if (pr->a_mn_major) {
-          for (int j = 0; j < BM / geo.mn_box; ++j)
-            ptx::tma_load_2d_pair(a_dst + j * geo.sub_bytes, &pr->tma_a, ld.tm * BM + j * geo.mn_box, ld.kb * geo.bk,
-                                  full_leader);
-        } else {
-          ptx::tma_load_2d_pair(a_dst, &pr->tma_a, ld.kb * geo.bk, ld.tm * BM, full_leader);
+        const int kb1 = item.kb1 < 0 ? kblocks_of(pr) : item.kb1;
+        int tm[MT], tn = 0;
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+          tile_coords(*pr, 2 * MT * item.tile + 2 * j + (int)rank - pr->tile_start, &tm[j], &tn);
+        const int n0 = tn * BN + (int)rank * P_BN_HALF;
+        for (int kb = item.kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, WAIT_LIMIT)) {
+            fail_pair(status, abort_flag, rank ^ 1u, 0x110000u | stage);
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = ptx::smem_u32(&bars->full[stage]);
+          const uint32_t full_leader = ptx::mapa(full_local, 0);
+          const uint32_t a_dst = ptx::smem_u32(smem + stage * STAGE);
+          const uint32_t b_dst = a_dst + MT * P_A_BYTES;
+          if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * STAGE);  // both CTAs' bytes
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            if (pr->a_mn_major) {
+              for (int b = 0; b < BM / geo.mn_box; ++b)
+                ptx::tma_load_2d_pair(a_dst + j * P_A_BYTES + b * geo.sub_bytes, &pr->tma_a,
+                                      tm[j] * BM + b * geo.mn_box, kb * geo.bk, full_leader);
+            } else {
+              ptx::tma_load_2d_pair(a_dst + j * P_A_BYTES, &pr->tma_a, kb * geo.bk, tm[j] * BM, full_leader);
+            }
+          }
+          if (pr->b_mn_major) {
+            for (int b = 0; b < P_BN_HALF / geo.mn_box; ++b)
+              ptx::tma_load_2d_pair(b_dst + b * geo.sub_bytes, &pr->tma_b, n0 + b * geo.mn_box, kb * geo.bk,
+                                    full_leader);
+          } else {
+            ptx::tma_load_2d_pair(b_dst, &pr->tma_b, kb * geo.bk, n0, full_leader);
+          }
+          ++issued[stage];
+          if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
         }
-        if (pr->b_mn_major) {
-          for (int j = 0; j < P_BN_HALF / geo.mn_box; ++j)
-            ptx::tma_load_2d_pair(b_dst + j * geo.sub_bytes, &pr->tma_b, ld.n0 + j * geo.mn_box, ld.kb * geo.bk,
-                                  full_leader);
-        } else {
-          ptx::tma_load_2d_pair(b_dst, &pr->tma_b, ld.kb * geo.bk, ld.n0, full_leader);
-        }
-        ++issued[stage];
-        if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
-        advance(ld);
       }
-      (void)ok;
       if (*abort_flag && rank == 0) {
         // Leave no copy in flight on the barrier we own: wait (bounded) for each stage's last load.
         uint32_t never = 0;
 #pragma unroll
-        for (int s = 0; s < P_STAGES; ++s)
+        for (int s = 0; s < NSTAGE; ++s)
           if (issued[s])
             ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[s]), (issued[s] - 1) & 1, &never, WAIT_LIMIT);
       }
@@ -523,15 +699,18 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0;
-      uint32_t it = 0;
+      uint32_t acc_it = 0;
       bool ok = true;
       int cursor = 0;
       const uint32_t smem_enc = ptx::smem_u32(smem) >> 4;
-      for (int pair = first_pair; ok && pair < total_pairs; pair += n_pairs_grid, ++it) {
-        const Problem* pr = problem_of(2 * pair, &cursor);
+      WorkIter iter = work_begin(sched, worker);
+      WorkItem item;
+      while (ok && work_next(iter, sched, worker, n_workers, &item)) {
+        const Problem* pr = problem_of(item.tile, &cursor);
         const Geometry geo = geometry_of(pr->elem8);
         const bool f8 = pr->elem8 != 0;
-        const int kblocks = (pr->k + geo.bk - 1) / geo.bk;
+        const int kblocks = kblocks_of(pr);
+        const int kb1 = item.kb1 < 0 ? kblocks : item.kb1;
         const bool a_mn = pr->a_mn_major != 0, b_mn = pr->b_mn_major != 0;
         const uint32_t idesc = f8 ? ptx::idesc_f8(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u, 1u)
                                   : ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
@@ -539,64 +718,128 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? geo.sub_bytes : 16, 1024);
         const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? geo.sub_bytes : 16, 1024);
         const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
-        const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
-        if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag, WAIT_LIMIT)) {
-          fail(status, abort_flag, 0x120000u | 0x100u | acc);
-          break;
+        uint32_t d_tmem[MT];
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          const uint32_t acc = (acc_it + j) & 1, aphase = ((acc_it + j) >> 1) & 1;
+          if (ok && !ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag,
+                                                  loop_wait_limit(kblocks))) {
+            fail_pair(status, abort_flag, 1u, 0x120000u | 0x100u | acc);
+            ok = false;
+          }
+          d_tmem[j] = tmem_base + acc * BN;
         }
+        if (!ok) break;
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = item.kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
-            fail(status, abort_flag, 0x120000u | stage);
+            fail_pair(status, abort_flag, 1u, 0x120000u | stage);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t a_enc = smem_enc + stage * (P_STAGE_BYTES >> 4);
-          const uint32_t b_enc = a_enc + (P_A_BYTES >> 4);
-          if (f8) {
+          const uint32_t a_enc = smem_enc + stage * (STAGE >> 4);
+          const uint32_t b_enc = a_enc + MT * (P_A_BYTES >> 4);
+          const bool last = kb + 1 == kb1;
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk)
-              ptx::mma_f8_ss_pair(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
-                                  db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (kb | kk) != 0 ? 1u : 0u);
-          } else {
+          for (int j = 0; j < MT; ++j) {
+            const uint32_t aj = a_enc + j * (P_A_BYTES >> 4);
+            if (f8) {
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk)
-              ptx::mma_f16_ss_pair(d_tmem, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
-                                   db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (kb | kk) != 0 ? 1u : 0u);
+              for (int kk = 0; kk < BK / 16; ++kk)
+                ptx::mma_f8_ss_pair(d_tmem[j], da_fixed | (uint64_t)(aj + kk * a_kstep),
+                                    db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc,
+                                    (kb > item.kb0 || kk != 0) ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                ptx::mma_f16_ss_pair(d_tmem[j], da_fixed | (uint64_t)(aj + kk * a_kstep),
+                                     db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc,
+                                     (kb > item.kb0 || kk != 0) ? 1u : 0u);
+            }
+            // block j is complete with the last k-step: let its epilogue start while the next block's MMAs retire
+            if (last) ptx::mma_commit_pair(ptx::smem_u32(&bars->tmem_full[(acc_it + j) & 1]), 3);
           }
           ptx::mma_commit_pair(ptx::smem_u32(&bars->empty[stage]), 3);  // frees the slot in both CTAs
-          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
         }
-        if (ok) ptx::mma_commit_pair(ptx::smem_u32(&bars->tmem_full[acc]), 3);
+        acc_it += MT;
       }
     }
   } else {
-    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    // ---------------- epilogue (both CTAs, own rows) ----------------
     const int q = warp & 3;
     uint32_t chunk_no = 0;
     const Problem* epi_fenced = nullptr;
-    uint32_t it = 0;
+    uint32_t acc_it = 0;
     int cursor = 0;
-    for (int pair = first_pair; pair < total_pairs; pair += n_pairs_grid, ++it) {
-      const Problem* pr = problem_of(2 * pair, &cursor);
-      int tm, tn;
-      tile_coords(*pr, 2 * pair + (int)rank - pr->tile_start, &tm, &tn);
-      const uint32_t acc = it & 1, aphase = (it >> 1) & 1;
-      bool ok = true;
-      if (lane == 0)
-        ok = ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag, WAIT_LIMIT);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) {
-        if (lane == 0) fail(status, abort_flag, 0x130000u | acc);
-        break;
+    uint32_t* flags = reinterpret_cast<uint32_t*>(sched.workspace);
+    float* slots = sched.workspace ? sched.workspace + kSkFlagBytes / 4 : nullptr;
+    const size_t worker_stride = (size_t)2 * MT * kSkBlockFloats;
+    WorkIter iter = work_begin(sched, worker);
+    WorkItem item;
+    bool ok = true;
+    while (ok && work_next(iter, sched, worker, n_workers, &item)) {
+      const Problem* pr = problem_of(item.tile, &cursor);
+      const int kblocks = kblocks_of(pr);
+      if (item.n_peers > 0) {
+        // the peers' parts were computed before ours; make sure their slots are complete
+        if (lane == 0) {
+          const long long t0 = clock64();
+          for (int peer = 1; ok && peer <= item.n_peers; ++peer) {
+            const uint32_t* f = flags + ((worker + peer) * 2 + (int)rank) * 4 + q;
+            while (ld_acquire_gpu(f) == 0u) {
+              if (*abort_flag || clock64() - t0 > loop_wait_limit(kblocks)) { ok = false; break; }
+              __nanosleep(200);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) {
+          if (lane == 0) fail_pair(status, abort_flag, rank ^ 1u, 0x140000u | (uint32_t)q);
+          break;
+        }
       }
-      ptx::tc_fence_after();
-      epilogue_store_tile(pr, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
-                          epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no, GROUPED ? &epi_fenced : nullptr);
-      ptx::tc_fence_before();
-      ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0));
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        int tm, tn;
+        tile_coords(*pr, 2 * MT * item.tile + 2 * j + (int)rank - pr->tile_start, &tm, &tn);
+        const uint32_t acc = (acc_it + j) & 1, aphase = ((acc_it + j) >> 1) & 1;
+        if (lane == 0)
+          ok = ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_full[acc]), aphase, abort_flag,
+                                            loop_wait_limit(kblocks));
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) {
+          if (lane == 0) fail_pair(status, abort_flag, rank ^ 1u, 0x130000u | acc);
+          break;
+        }
+        ptx::tc_fence_after();
+        EpiSplit sp;
+        sp.partial_out = item.partial ? slots + (size_t)worker * worker_stride + ((size_t)rank * MT + j) * kSkBlockFloats
+                                      : nullptr;
+        sp.n_in = item.n_peers;
+        sp.partial_in = item.n_peers > 0
+                            ? slots + (size_t)(worker + 1) * worker_stride + ((size_t)rank * MT + j) * kSkBlockFloats
+                            : nullptr;
+        sp.stride = worker_stride;
+        epilogue_pair_block(pr, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
+                            epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no,
+                            GROUPED ? &epi_fenced : nullptr, sp);
+        ptx::tc_fence_before();
+        ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0));
+      }
+      if (!ok) break;
+      if (item.partial) {
+        // publish this warp's rows of the slot: every lane's stores, then the flag
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(flags + (worker * 2 + (int)rank) * 4 + q, 1u);
+      } else if (item.n_peers > 0) {
+        __syncwarp();  // every lane has read the peers' slots
+        if (lane == 0)
+          for (int peer = 1; peer <= item.n_peers; ++peer) flags[((worker + peer) * 2 + (int)rank) * 4 + q] = 0u;
+      }
+      acc_it += MT;
     }
     if (lane == 0) ptx::bulk_wait_group_read<0>();  // staging must outlive the stores that read it
   }
@@ -606,7 +849,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
   ptx::cluster_sync();  // neither CTA leaves while the other may still touch its shared memory
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -687,10 +930,10 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 struct StaticScratch {
   unsigned char* dev;  // device address of g_static_scratch on this device
   int sm_count;
+  int device;
   bool ready;
 };
-constexpr int kMaxDevices = 64;
-StaticScratch g_static[kMaxDevices];
+StaticScratch g_static[64];
 std::mutex g_static_mu;
 
 // In host code `g_static_scratch` is only a stand-in for the symbol; the address a
@@ -699,7 +942,7 @@ std::mutex g_static_mu;
 int32_t static_scratch(StaticScratch** out) {
   int dev = 0;
   LEGO_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return LEGO_ERR_UNSUPPORTED;
+  if (dev < 0 || dev >= 64) return LEGO_ERR_UNSUPPORTED;
   std::lock_guard<std::mutex> lock(g_static_mu);
   StaticScratch& sc = g_static[dev];
   if (!sc.ready) {
@@ -707,6 +950,7 @@ int32_t static_scratch(StaticScratch** out) {
     LEGO_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
     LEGO_CUDA_TRY(cudaDeviceGetAttribute(&sc.sm_count, cudaDevAttrMultiProcessorCount, dev));
     sc.dev = (unsigned char*)p;
+    sc.device = dev;
     sc.ready = true;
   }
   *out = &sc;
@@ -714,29 +958,33 @@ int32_t static_scratch(StaticScratch** out) {
 }
 
 template <bool GROUPED>
-int32_t configure() {
-  static std::once_flag once;
-  static cudaError_t result = cudaSuccess;
-  std::call_once(once, [] {
-    result = cudaFuncSetAttribute(gemm_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  });
-  return cuda_status(result);
+int32_t configure(int dev) {
+  static PerDeviceFlag done;
+  if (done.test(dev)) return LEGO_OK;
+  LEGO_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  done.set(dev);
+  return LEGO_OK;
 }
 
-// One-time set-up of the CTA-pair kernel: shared-memory limit and how many pairs
-// the device can hold at once.
-template <bool GROUPED>
-int32_t configure_pair(int* max_clusters) {
-  static std::once_flag once;
-  static int32_t result = LEGO_OK;
-  static int clusters = 0;
-  std::call_once(once, [] {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
-    if (e == cudaSuccess) {
+// Set-up of one CTA-pair kernel on the current device: shared-memory limit and how many
+// pairs the device can hold at once.  Both belong to the device, so they are kept per
+// device ordinal.
+constexpr int kMaxDevices = 64;
+template <bool GROUPED, int MT>
+int32_t configure_pair(int dev, int* max_clusters) {
+  static PerDeviceFlag done;
+  static int clusters[kMaxDevices];
+  static std::mutex mu;
+  if (dev < 0 || dev >= kMaxDevices) return LEGO_ERR_UNSUPPORTED;
+  if (!done.test(dev)) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done.test(dev)) {
+      LEGO_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<GROUPED, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         pair_smem_bytes(MT)));
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2, 1, 1);
       cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-      cfg.dynamicSmemBytes = P_SMEM_BYTES;
+      cfg.dynamicSmemBytes = pair_smem_bytes(MT);
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 2;
@@ -744,25 +992,73 @@ int32_t configure_pair(int* max_clusters) {
       attr.val.clusterDim.z = 1;
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
-      e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<GROUPED>, &cfg);
+      int n = 0;
+      LEGO_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<GROUPED, MT>, &cfg));
+      clusters[dev] = n;
+      done.set(dev);
     }
-    if (e != cudaSuccess) { (void)cudaGetLastError(); result = cuda_status(e); }
-  });
-  *max_clusters = clusters;
-  return result;
+  }
+  *max_clusters = clusters[dev];
+  return LEGO_OK;
 }
 
-// Do tile ids 2p and 2p + 1 of this problem share a tile column (they would share B)?
-bool pairs_share_columns(const Problem& p) {
+// Do the flat tile ids g * n .. g * n + n - 1 of this problem share a tile column (they
+// would share B) for every g?
+bool ids_share_columns(const Problem& p, int n) {
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
-  if (total % 2 || total > (1 << 22)) return false;
-  for (int64_t t = 0; t < total; t += 2) {
-    int m0, n0, m1, n1;
+  if (total < n || total % n || total > (1 << 22)) return false;
+  for (int64_t t = 0; t < total; t += n) {
+    int m0, n0;
     tile_coords(p, (int)t, &m0, &n0);
-    tile_coords(p, (int)t + 1, &m1, &n1);
-    if (n0 != n1) return false;
+    for (int i = 1; i < n; ++i) {
+      int m1, n1;
+      tile_coords(p, (int)t + i, &m1, &n1);
+      if (n1 != n0) return false;
+    }
   }
   return true;
+}
+
+// Tuning knobs (lego_tune), process-wide.
+std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
+std::atomic<int> g_tune_streamk{1};  // 1: split the partial last wave along K when a workspace is given
+
+// Data-parallel over `tiles` pair tiles, or with the partial last wave cut along K.
+Sched make_sched(int64_t tiles, int workers, int kblocks, int mt, void* workspace, int64_t workspace_bytes) {
+  Sched sc = {};
+  sc.total_tiles = (int32_t)tiles;
+  sc.dp_tiles = (int32_t)tiles;
+  sc.kblocks = kblocks;
+  const int64_t need = kSkFlagBytes + (int64_t)workers * 2 * mt * kSkBlockFloats * 4;
+  const int64_t rest = tiles % workers;
+  if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) || workers > kSkMaxWorkers ||
+      g_tune_streamk.load() == 0 || rest == 0 || kblocks > (1 << 20))
+    return sc;
+  const int64_t units = rest * kblocks;
+  const int64_t run = (units + workers - 1) / workers;
+  if (run < 4) return sc;  // a handful of k-steps per worker is not worth a fix-up
+  sc.dp_tiles = (int32_t)(tiles - rest);
+  sc.sk_tiles = (int32_t)rest;
+  sc.sk_run = (int32_t)run;
+  sc.workspace = reinterpret_cast<float*>(workspace);
+  return sc;
+}
+
+template <bool GROUPED, int MT>
+int32_t launch_pair(const Problem& p, const Problem* dev_table, int n_problems, int64_t tiles, int kblocks,
+                    int activation, void* workspace, int64_t workspace_bytes, int dev, uint32_t* status,
+                    cudaStream_t s, bool* launched) {
+  *launched = false;
+  int max_clusters = 0;
+  const int32_t st = configure_pair<GROUPED, MT>(dev, &max_clusters);
+  if (st != LEGO_OK || max_clusters < 1) return LEGO_OK;  // the caller falls back to one CTA per tile
+  const int64_t n_pair_tiles = tiles / (2 * MT);
+  Sched sc = make_sched(n_pair_tiles, max_clusters, kblocks, MT, GROUPED ? nullptr : workspace, workspace_bytes);
+  const int workers = sc.sk_tiles ? max_clusters : (int)(n_pair_tiles < max_clusters ? n_pair_tiles : max_clusters);
+  gemm_pair_kernel<GROUPED, MT><<<2 * workers, NUM_THREADS, pair_smem_bytes(MT), s>>>(p, dev_table, n_problems, sc,
+                                                                                     activation, status);
+  *launched = true;
+  return cuda_status(cudaGetLastError());
 }
 
 // Build the problem records of a grouped GEMM into `table` (host), copy them to
@@ -771,33 +1067,41 @@ bool pairs_share_columns(const Problem& p) {
 // single-CTA kernel runs; CTA pairs are used when every group's order puts tiles 2p and
 // 2p + 1 in one tile column.  (Sustained A/B on one box, 16 groups: row-major / single CTA
 // 1 050-1 090 TFLOP/s, column-major / pairs 1 010-1 050; isolated launches tie.)  Allocates nothing.
+// The host table dies with the caller's frame, so the upload cannot be part of a stream
+// capture: a captured copy node would read a dead frame on every replay.
 int32_t run_grouped(EncodeFn enc, Problem* table, const void* const* A, const void* const* B, void* const* C,
                     const int64_t* mnk, int32_t G, const lego_layout_t* const* tile_orders, Problem* dev_table,
-                    uint32_t* status, int sm_count, cudaStream_t s) {
+                    uint32_t* status, int sm_count, int dev, cudaStream_t s) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  LEGO_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
+  if (cap != cudaStreamCaptureStatusNone) return LEGO_ERR_UNSUPPORTED;
   int64_t total = 0;
-  bool pairs = true;
+  bool pairs = true, quads = true;
   for (int g = 0; g < G; ++g) {
     const lego_layout_t* order = tile_orders ? tile_orders[g] : nullptr;
     const int32_t st = fill_problem(enc, &table[g], A[g], B[g], C[g], mnk[3 * g], mnk[3 * g + 1], mnk[3 * g + 2],
                                     0, 0, order, (int)total);
     if (st != LEGO_OK) return st;
     Problem& p = table[g];
-    pairs = pairs && pairs_share_columns(p);
+    pairs = pairs && ids_share_columns(p, 2);
+    quads = quads && pairs && ids_share_columns(p, 4);
     total += (int64_t)p.tiles_m * p.tiles_n;
     if (total > 0x7fffffff) return LEGO_ERR_SIZE;
   }
   LEGO_CUDA_TRY(cudaMemcpyAsync(dev_table, table, (size_t)G * sizeof(Problem), cudaMemcpyHostToDevice, s));
-  if (pairs) {
-    int max_clusters = 0;
-    if (configure_pair<true>(&max_clusters) == LEGO_OK && max_clusters >= 1) {
-      const int64_t n_pairs = total / 2;
-      const int clusters = (int)(n_pairs < max_clusters ? n_pairs : max_clusters);
-      gemm_pair_kernel<true><<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, s>>>(table[0], dev_table, G, (int)n_pairs,
-                                                                            LEGO_ACT_NONE, status);
-      return cuda_status(cudaGetLastError());
-    }
+  bool launched = false;
+  const int blocks = g_tune_blocks.load();
+  if (quads && blocks == 2) {
+    const int32_t st = launch_pair<true, 2>(table[0], dev_table, G, total, 0, LEGO_ACT_NONE, nullptr, 0, dev, status, s,
+                                            &launched);
+    if (launched) return st;
   }
-  const int32_t st = configure<true>();
+  if (pairs) {
+    const int32_t st = launch_pair<true, 1>(table[0], dev_table, G, total, 0, LEGO_ACT_NONE, nullptr, 0, dev, status, s,
+                                            &launched);
+    if (launched) return st;
+  }
+  const int32_t st = configure<true>(dev);
   if (st != LEGO_OK) return st;
   const int grid = (int)(total < sm_count ? total : sm_count);
   gemm_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(table[0], dev_table, G, (int)total, LEGO_ACT_NONE, status);
@@ -809,13 +1113,38 @@ int32_t run_grouped(EncodeFn enc, Problem* table, const void* const* A, const vo
 
 using namespace lego;
 
+// Read (and clear, when set) the status word inside the static scratch of the current
+// device, if lego_grouped_gemm_f16_static has been used there.  Allocates nothing.
+namespace lego {
+int32_t static_status_take(cudaStream_t s, uint32_t* word) {
+  *word = 0;
+  int dev = 0;
+  LEGO_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return LEGO_OK;
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static[dev].ready) return LEGO_OK;
+    base = g_static[dev].dev;
+  }
+  LEGO_CUDA_TRY(cudaMemcpyAsync(word, base, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+  LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+  if (*word) {
+    LEGO_CUDA_TRY(cudaMemsetAsync(base, 0, sizeof(uint32_t), s));
+    LEGO_CUDA_TRY(cudaStreamSynchronize(s));
+  }
+  return LEGO_OK;
+}
+}  // namespace lego
+
 extern "C" {
 
 // One GEMM, fp16 or e5m2 operands: CTA pairs when the tile order allows, else one CTA per tile.
 static int32_t run_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int32_t trans_a,
                         int32_t trans_b, int32_t activation, const lego_layout_t* tile_order, int elem8,
-                        void* stream) {
+                        void* workspace, int64_t workspace_bytes, void* stream) {
   if (activation != LEGO_ACT_NONE && activation != LEGO_ACT_LEAKY_RELU) return LEGO_ERR_UNSUPPORTED;
+  if (workspace_bytes < 0) return LEGO_ERR_SIZE;
   int32_t err = LEGO_OK;
   DeviceCtx* ctx = device_ctx(&err);
   if (!ctx) return err;
@@ -826,47 +1155,78 @@ static int32_t run_gemm(const void* A, const void* B, void* C, int64_t M, int64_
   if (st != LEGO_OK) return st;
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n;
   if (total > 0x7fffffff) return LEGO_ERR_SIZE;
-  // CTA pairs: tile ids 2p and 2p + 1 must share their tile column (they share B).
-  bool pairs = total >= 2 && total % 2 == 0 && total <= (1 << 22);
-  for (int64_t t = 0; pairs && t < total; t += 2) {
-    int m0, n0, m1, n1;
-    tile_coords(p, (int)t, &m0, &n0);
-    tile_coords(p, (int)t + 1, &m1, &n1);
-    pairs = (n0 == n1);
-  }
+  const Geometry geo = geometry_of(p.elem8);
+  const int kblocks = (int)((K + geo.bk - 1) / geo.bk);
+  cudaStream_t s = (cudaStream_t)stream;
+  // CTA pairs: the tile ids of a pair tile must share their tile column (they share B).
+  const bool pairs = ids_share_columns(p, 2);
   if (pairs) {
     st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF, elem8);
     if (st != LEGO_OK) return st;
-    int max_clusters = 0;
-    st = configure_pair<false>(&max_clusters);
-    if (st == LEGO_OK && max_clusters >= 1) {
-      const int64_t n_pairs = total / 2;
-      const int clusters = (int)(n_pairs < max_clusters ? n_pairs : max_clusters);
-      gemm_pair_kernel<false><<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, (cudaStream_t)stream>>>(p, nullptr, 1, (int)n_pairs, activation,
-                                                                                   ctx->status_word);
-      return cuda_status(cudaGetLastError());
+    bool launched = false;
+    const int blocks = g_tune_blocks.load();
+    if (blocks == 2 && ids_share_columns(p, 4)) {
+      st = launch_pair<false, 2>(p, nullptr, 1, total, kblocks, activation, workspace, workspace_bytes, ctx->device,
+                                 ctx->status_word, s, &launched);
+      if (launched) return st;
     }
+    st = launch_pair<false, 1>(p, nullptr, 1, total, kblocks, activation, workspace, workspace_bytes, ctx->device,
+                               ctx->status_word, s, &launched);
+    if (launched) return st;
     st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, BN, elem8);
     if (st != LEGO_OK) return st;
   }
-  st = configure<false>();
+  st = configure<false>(ctx->device);
   if (st != LEGO_OK) return st;
   const int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
-  gemm_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(p, nullptr, 1, (int)total, activation,
-                                                                         ctx->status_word);
+  gemm_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(p, nullptr, 1, (int)total, activation, ctx->status_word);
   return cuda_status(cudaGetLastError());
 }
 
 int32_t lego_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                       int32_t trans_a, int32_t trans_b, int32_t activation,
                       const lego_layout_t* tile_order, void* stream) {
-  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 0, stream);
+  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 0, nullptr, 0, stream);
 }
 
 int32_t lego_gemm_e5m2(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                        int32_t trans_a, int32_t trans_b, int32_t activation,
                        const lego_layout_t* tile_order, void* stream) {
-  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 1, stream);
+  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 1, nullptr, 0, stream);
+}
+
+int64_t lego_gemm_workspace_bytes(void) {
+  int32_t err = LEGO_OK;
+  DeviceCtx* ctx = device_ctx(&err);
+  if (!ctx) return 0;
+  const int64_t workers = ctx->sm_count / 2;
+  return kSkFlagBytes + workers * 2 * 2 * (int64_t)kSkBlockFloats * 4;
+}
+
+int32_t lego_gemm_f16_ws(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                         int32_t trans_a, int32_t trans_b, int32_t activation,
+                         const lego_layout_t* tile_order, void* workspace, int64_t workspace_bytes, void* stream) {
+  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 0, workspace, workspace_bytes, stream);
+}
+
+int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                          int32_t trans_a, int32_t trans_b, int32_t activation,
+                          const lego_layout_t* tile_order, void* workspace, int64_t workspace_bytes, void* stream) {
+  return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 1, workspace, workspace_bytes, stream);
+}
+
+int32_t lego_tune(int32_t knob, int32_t value) {
+  switch (knob) {
+    case LEGO_TUNE_GEMM_BLOCKS:
+      if (value < 0 || value > 2) return LEGO_ERR_SIZE;
+      g_tune_blocks.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_GEMM_STREAMK:
+      g_tune_streamk.store(value ? 1 : 0);
+      return LEGO_OK;
+    default:
+      return LEGO_ERR_UNSUPPORTED;
+  }
 }
 
 int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* const* C,
@@ -885,7 +1245,7 @@ int32_t lego_grouped_gemm_f16(const void* const* A, const void* const* B, void* 
   // The device table is per device and reused by every call: calls on one stream are
   // ordered; callers overlapping grouped GEMMs on different streams must serialise.
   return run_grouped(enc, table.data(), A, B, C, mnk, G, tile_orders, (Problem*)ctx->tmap_table, ctx->status_word,
-                     ctx->sm_count, (cudaStream_t)stream);
+                     ctx->sm_count, ctx->device, (cudaStream_t)stream);
 }
 
 int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B, void* const* C,
@@ -902,16 +1262,19 @@ int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B,
   if (err != LEGO_OK) return err;
   EncodeFn enc = encode_fn(&err);
   if (!enc) return err;
-  Problem table[kStaticGroups];  // host stack: no heap, no device allocation anywhere in this call
   cudaStream_t s = (cudaStream_t)stream;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  LEGO_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
+  if (cap != cudaStreamCaptureStatusNone) return LEGO_ERR_UNSUPPORTED;  // before anything is enqueued
+  Problem table[kStaticGroups];  // host stack: no heap, no device allocation anywhere in this call
   uint32_t* status = dev_status;
   if (!status) {
-    // the array keeps whatever the previous call left: the status word must start at zero
+    // The word inside the array is read and cleared by lego_device_status; a code a previous
+    // call left there stays until then (a kernel only records the first failure).
     status = reinterpret_cast<uint32_t*>(sc->dev);
-    LEGO_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(uint32_t), s));
   }
   Problem* dev_table = reinterpret_cast<Problem*>(sc->dev + kStaticStatusBytes);
-  return run_grouped(enc, table, A, B, C, mnk, G, tile_orders, dev_table, status, sc->sm_count, s);
+  return run_grouped(enc, table, A, B, C, mnk, G, tile_orders, dev_table, status, sc->sm_count, sc->device, s);
 }
 
 }  // extern "C"

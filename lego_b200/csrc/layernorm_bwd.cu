@@ -320,10 +320,10 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   auto kern = ln_bwd_ring1_kernel<EPT>;
   const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceFlag configured;
+  if (!configured.test(ctx->device)) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
-    configured = true;
+    configured.set(ctx->device);
   }
   const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128;
   int stages = (int)(budget / slot);
@@ -579,10 +579,10 @@ template <int EPT, int G>
 int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int grid, int stages, int groups, int gsize,
                          size_t smem) {
   auto kern = ln_bwd_ring_kernel<EPT, G>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceFlag configured;
+  if (!configured.test(ctx->device)) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 2048));
-    configured = true;
+    configured.set(ctx->device);
   }
   const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32), smem, s, P, stages, groups, gsize,
                                           ctx->status_word);
@@ -711,13 +711,13 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   auto a16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   const bool vec = cols % 8 == 0 && a16(dy) && a16(x) && a16(gamma) && a16(dx);
   int32_t st = LEGO_ERR_UNSUPPORTED;
+  int32_t err = LEGO_OK;
+  DeviceCtx* ctx = device_ctx(&err);
+  if (!ctx) return err;
   // Ring-fed kernel: 16-byte aligned rows of 1 Ki .. 8 Ki columns, enough rows to fill the
   // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
   if (vec && cols >= 1024 && cols <= kBwdConsumers * 16 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
-      a16(partial) && rows >= 2 * 148) {
-    int32_t err = LEGO_OK;
-    DeviceCtx* ctx = device_ctx(&err);
-    if (!ctx) return err;
+      a16(partial) && rows >= 2 * (int64_t)ctx->sm_count) {
     // Same box, GB/s, 16384 rows: one group of 512 threads / groups of cols/16 threads:
     // N = 2048: 2440 / 3890, N = 4096: 4430 / 4260, N = 8192: 4730 / 4490.
     if (cols > 3072) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);

@@ -31,7 +31,8 @@ constexpr int kMaxTilesPerCta = 16;
 struct TiledParams {
   DigitProgram p1;  // tile id -> tile coordinates
   DigitProgram p2;  // tile coordinates -> (input base, output base), in elements
-  int64_t n_tiles;
+  int64_t n_tiles;  // tiles this launch moves: ids tile_begin .. tile_begin + n_tiles - 1
+  int64_t tile_begin;
   int64_t s_in_o;   // input stride of the output-fast digit (elements)
   int64_t s_out_i;  // output stride of the input-fast digit (elements)
   int32_t tiles_per_cta;
@@ -50,7 +51,8 @@ struct GatherParams {
 struct TmaParams {
   DigitProgram p1;  // tile id -> tile coordinates
   DigitProgram p2;  // tile coordinates -> (input base, output base), in elements
-  int64_t n_tiles;
+  int64_t n_tiles;  // tiles this launch moves: ids tile_begin .. tile_begin + n_tiles - 1
+  int64_t tile_begin;
   int64_t pitch;    // elements between consecutive rows of the input tensor map
   int64_t s_out_i;  // output stride of the input-contiguous digit (elements)
   int32_t stages;   // ring slots per CTA
@@ -59,6 +61,7 @@ struct TmaParams {
 
 struct Plan {
   int kind;
+  bool by_order;  // tile ids are the ids of the caller's tile_order layout
   int elem_bytes;
   int vec_bytes;
   int64_t size;
@@ -158,7 +161,8 @@ tiled_transpose_kernel(const __grid_constant__ TiledParams P, const uint8_t* __r
     if (t < P.n_tiles) {
       uint64_t coord[LEGO_MAX_RANK];
       for (int k = 0; k < LEGO_MAX_RANK; ++k) coord[k] = 0;
-      for (int j = 0; j < P.p1.n_terms; ++j) coord[P.p1.t[j].dst] += term_eval<WIDE>(P.p1.t[j], (uint64_t)t);
+      for (int j = 0; j < P.p1.n_terms; ++j)
+        coord[P.p1.t[j].dst] += term_eval<WIDE>(P.p1.t[j], (uint64_t)(t + P.tile_begin));
       uint64_t b0 = 0, b1 = 0;
       for (int j = 0; j < P.p2.n_terms; ++j) {
         const uint64_t v = term_eval<WIDE>(P.p2.t[j], coord[P.p2.t[j].src]);
@@ -328,7 +332,7 @@ tma_transpose_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_cons
 #pragma unroll
         for (int c = 0; c < LEGO_MAX_RANK; ++c) coord[c] = 0;
         for (int j = 0; j < P.p1.n_terms; ++j) {
-          const uint64_t v = term_eval<WIDE>(P.p1.t[j], (uint64_t)t);
+          const uint64_t v = term_eval<WIDE>(P.p1.t[j], (uint64_t)(t + P.tile_begin));
           const int dst = P.p1.t[j].dst;
 #pragma unroll
           for (int c = 0; c < LEGO_MAX_RANK; ++c)
@@ -551,6 +555,7 @@ bool finish_tiled(int64_t ti, int64_t to, int64_t s_out_i, int64_t s_in_o, int e
     pl->tma.p1 = tp.p1;
     pl->tma.p2 = tp.p2;
     pl->tma.n_tiles = tp.n_tiles;
+    pl->tma.tile_begin = 0;
     pl->tma.pitch = s_in_o;
     pl->tma.s_out_i = s_out_i;
   }
@@ -578,6 +583,7 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
   pl->elem_bytes = eb;
   pl->size = size;
   pl->tile_in = pl->tile_out = 1;
+  pl->by_order = false;
 
   std::vector<Digit> ds, dd, dor;
   const int32_t fs = fold_layout(src, &ds);
@@ -615,8 +621,10 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
       for (const Digit& d : dd)
         if (d.src < order->rank) set_term(&tp.p2.t[tp.p2.n_terms++], d.src, 1, d.div, d.mod, d.stride);
       tp.n_tiles = osize;
-      if (finish_tiled(inner[0].radix, inner[1].radix, inner[0].sb, inner[1].sa, eb, in, out, pl))
+      if (finish_tiled(inner[0].radix, inner[1].radix, inner[0].sb, inner[1].sa, eb, in, out, pl)) {
+        pl->by_order = true;
         return LEGO_OK;
+      }
     }
   }
 
@@ -731,14 +739,14 @@ int32_t launch_tma(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cu
     err = make_tmap_row_groups(enc, &tmap, dt, in, (uint64_t)tp.pitch, (uint64_t)(pl.size / tp.pitch),
                                (uint64_t)tp.pitch * EB, 16 / EB, 128 / EB, 8);
   if (err != LEGO_OK) return err;
-  static size_t configured[2] = {0, 0};  // dynamic shared memory each instantiation is set up for
+  static PerDeviceFlag configured[2];  // one per instantiation (SMEM is a constant of EB)
   const int wide = tp.p1.wide ? 1 : 0;
-  if (configured[wide] < SMEM) {
+  if (!configured[wide].test(ctx->device)) {
     if (wide) LEGO_CUDA_TRY(cudaFuncSetAttribute(tma_transpose_kernel<EB, true>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     else LEGO_CUDA_TRY(cudaFuncSetAttribute(tma_transpose_kernel<EB, false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
-    configured[wide] = SMEM;
+    configured[wide].set(ctx->device);
   }
   int64_t grid = (int64_t)ctx->sm_count * ctas_per_sm;
   if (grid > tp.n_tiles) grid = tp.n_tiles;
@@ -789,14 +797,28 @@ int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const le
   return st;
 }
 
-int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
-                     const lego_layout_t* dst, const lego_layout_t* tile_order, void* stream) {
+// tile_count < 0: every tile.  Otherwise only the tiles tile_begin .. tile_begin +
+// tile_count - 1 of tile_order are moved, which needs a plan whose tiles are tile_order's.
+static int32_t run_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                           const lego_layout_t* dst, const lego_layout_t* tile_order, int64_t tile_begin,
+                           int64_t tile_count, void* stream) {
   if (!in || !out) return LEGO_ERR_NULL;
   if (in == out) return LEGO_ERR_UNSUPPORTED;  // in-place reorganisation is not defined
   if (!aligned(in, elem_bytes > 0 ? elem_bytes : 1) || !aligned(out, elem_bytes > 0 ? elem_bytes : 1))
     return LEGO_ERR_ALIGN;
   Plan* pl = new Plan();
   int32_t st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl);
+  if (st == LEGO_OK && tile_count >= 0) {
+    if (!tile_order) st = LEGO_ERR_NULL;
+    else if (!pl->by_order) st = LEGO_ERR_UNSUPPORTED;  // this pair of layouts is not moved tile_order-tile by tile
+    else if (tile_begin < 0 || tile_begin + tile_count > pl->tiled.n_tiles) st = LEGO_ERR_SIZE;
+    else {
+      pl->tiled.tile_begin = pl->tma.tile_begin = tile_begin;
+      pl->tiled.n_tiles = pl->tma.n_tiles = tile_count;
+      if (pl->tiled.tiles_per_cta > tile_count) pl->tiled.tiles_per_cta = (int32_t)(tile_count > 0 ? tile_count : 1);
+      if (tile_count == 0) pl->size = 0;
+    }
+  }
   if (st == LEGO_OK && pl->size > 0) {
     int32_t err = LEGO_OK;
     DeviceCtx* ctx = device_ctx(&err);
@@ -829,6 +851,18 @@ int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_l
   }
   delete pl;
   return st;
+}
+
+int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                     const lego_layout_t* dst, const lego_layout_t* tile_order, void* stream) {
+  return run_permute(in, out, elem_bytes, src, dst, tile_order, 0, -1, stream);
+}
+
+int32_t lego_permute_tiles(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                           const lego_layout_t* dst, const lego_layout_t* tile_order, int64_t tile_begin,
+                           int64_t tile_count, void* stream) {
+  if (tile_count < 0) return LEGO_ERR_SIZE;
+  return run_permute(in, out, elem_bytes, src, dst, tile_order, tile_begin, tile_count, stream);
 }
 
 }  // extern "C"

@@ -420,10 +420,10 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
 template <int OP, typename T, int G>
 int32_t launch_ring_g(const RowParams& P, DeviceCtx* ctx, cudaStream_t s, int stages, int groups, int gsize, size_t smem) {
   auto kern = row_ring_kernel<OP, T, G>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceFlag configured;
+  if (!configured.test(ctx->device)) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 4096));  // static part: reduction slots
-    configured = true;
+    configured.set(ctx->device);
   }
   int64_t grid = ctx->sm_count;
   if (grid > P.rows) grid = P.rows;

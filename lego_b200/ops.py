@@ -29,7 +29,7 @@ from .lowering import lower, lower_optional
 __all__ = [
     "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "transpose", "softmax",
     "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "layer_norm_bwd", "matmul", "lego_group_gemm_fn",
-    "grouped_swizzle_layout", "row_tiling_layout", "device_status",
+    "grouped_swizzle_layout", "row_tiling_layout", "device_status", "tune", "selftest_bounded_wait",
 ]
 
 
@@ -130,8 +130,50 @@ def device_status() -> int:
     detail = C.c_uint32(0)
     st = _abi.lib().lego_device_status(_stream(), C.byref(detail))
     if st != 0:
+        for ws in _gemm_workspaces.values():   # a kernel that gave up may have left split-K flags set
+            ws[:4096].zero_()
         raise _abi.LegoError(st, f"device status word 0x{detail.value:x}")
     return 0
+
+
+def selftest_bounded_wait(limit_cycles: int = 1_000_000) -> None:
+    """Launch the one-CTA kernel whose wait nothing completes: it gives up after
+    ``limit_cycles`` SM cycles and records its code; ``device_status()`` then raises once."""
+    _device()
+    _abi.check(_abi.lib().lego_selftest_bounded_wait(int(limit_cycles), _stream()), "lego_selftest_bounded_wait")
+
+
+def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None) -> None:
+    """Process-wide GEMM knobs: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
+    pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` False keeps every tile whole."""
+    lib = _abi.lib()
+    if gemm_blocks is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_GEMM_BLOCKS, int(gemm_blocks)), "lego_tune")
+    if gemm_streamk is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_GEMM_STREAMK, int(bool(gemm_streamk))), "lego_tune")
+
+
+# One split-K scratch buffer per (device, stream): calls on one stream are ordered, calls on
+# different streams must not share a buffer.  Flags (first 4 KiB) start at zero and every
+# completed call leaves them zero.
+_gemm_workspaces = {}
+
+
+def _gemm_workspace(dev: torch.device) -> torch.Tensor:
+    key = (dev.index, torch.cuda.current_stream().cuda_stream)
+    ws = _gemm_workspaces.get(key)
+    if ws is None:
+        nbytes = _abi.lib().lego_gemm_workspace_bytes()
+        if nbytes <= 0:
+            raise RuntimeError("lego_gemm_workspace_bytes failed")
+        if torch.cuda.is_current_stream_capturing():
+            # memory allocated while capturing belongs to the graph: use it for this call only
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            ws[:4096].zero_()
+            return ws
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        _gemm_workspaces[key] = ws
+    return ws
 
 
 # ---- layouts used by the ops --------------------------------------------------------
@@ -219,15 +261,23 @@ def permute_plan(elem_bytes: int, src: GroupBy, dst: GroupBy, tile_order: Option
 
 
 def permute(x: torch.Tensor, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+            out: Optional[torch.Tensor] = None, tiles: Optional[Sequence[int]] = None) -> torch.Tensor:
     """``out_flat[dst(idx)] = x_flat[src(idx)]`` over the layouts' common logical
-    domain.  ``x`` is read as a flat contiguous buffer; the result has x's shape."""
+    domain.  ``x`` is read as a flat contiguous buffer; the result has x's shape.
+    ``tiles=(begin, count)`` moves only that range of ``tile_order`` ids (one GPU's
+    slab of a reorganisation split across several) and leaves the rest of ``out`` alone."""
     if src.size() != x.numel():
         raise ValueError(f"layout covers {src.size()} elements, tensor has {x.numel()}")
     d = _to_device(x).contiguous()
     res = out if out is not None else torch.empty_like(d)
     if not res.is_cuda or not res.is_contiguous() or res.numel() != d.numel() or res.dtype != d.dtype:
         raise ValueError("out must be a contiguous CUDA tensor of x's size and dtype")
+    if tiles is not None:
+        begin, count = tiles
+        _abi.check(_abi.lib().lego_permute_tiles(d.data_ptr(), res.data_ptr(), d.element_size(), C.byref(lower(src)),
+                                                 C.byref(lower(dst)), lower_optional(tile_order), int(begin),
+                                                 int(count), _stream()), "lego_permute_tiles")
+        return _like_input(res, x)
     _abi.check(_abi.lib().lego_permute(d.data_ptr(), res.data_ptr(), d.element_size(), C.byref(lower(src)),
                                        C.byref(lower(dst)), lower_optional(tile_order), _stream()),
                "lego_permute")
@@ -466,14 +516,15 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         ad = torch.empty(a.shape, dtype=a.dtype, device=pipe.dev)
         c = torch.empty((m, n), dtype=torch.float16, device=pipe.dev)
         c_h = _pinned_like((m, n), torch.float16)
-        call = getattr(lib, fn)
+        call = getattr(lib, fn + "_ws")
+        ws = _gemm_workspace(pipe.dev)
         for r0, r1 in _row_blocks(m, max(k * a.element_size(), n * 2), multiple=256):
             pipe.feed(ad[r0:r1], a[r0:r1])
             pipe.ready()
             npm, npn = -(-(r1 - r0) // 128), -(-n // 256)
             order = grouped_swizzle_layout(npm, npn, group_m) if (npm % group_m == 0 or npm <= group_m) else None
             _abi.check(call(ad[r0:r1].data_ptr(), b_st.data_ptr(), c[r0:r1].data_ptr(), r1 - r0, n, k,
-                            0, tb, act, lower_optional(order), _stream()), fn)
+                            0, tb, act, lower_optional(order), ws.data_ptr(), ws.numel(), _stream()), fn)
             pipe.drain(c_h[r0:r1], c[r0:r1])
         pipe.finish()
         return c_h
@@ -485,8 +536,9 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         npm, npn = -(-m // 128), -(-n // 256)
         if npm % group_m == 0 or npm <= group_m:
             tile_order = grouped_swizzle_layout(npm, npn, group_m)
-    _abi.check(getattr(lib, fn)(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
-                                lower_optional(tile_order), _stream()), fn)
+    ws = _gemm_workspace(ad.device)
+    _abi.check(getattr(lib, fn + "_ws")(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
+                                        lower_optional(tile_order), ws.data_ptr(), ws.numel(), _stream()), fn)
     return _like_input(c, a)
 
 

@@ -28,6 +28,25 @@ from __future__ import annotations
 import numpy as np
 
 
+def spec_of(layout) -> dict:
+    """Plain spec of a layout object that exposes the reference's attributes
+    (``.objects`` -> OrderBy with ``.perms``; a perm has ``.dims()`` and either
+    ``.permutation`` (RegP / Row / Col) or ``.kind`` (a named GenP body or ``"lut"``
+    with its tables).  Structure only: no arithmetic of the object is used."""
+    objects = []
+    for o in layout.objects:
+        stage = []
+        for p in o.perms:
+            if hasattr(p, "permutation"):
+                stage.append({"kind": "regp", "dims": list(p.dims()), "perm": list(p.permutation)})
+            elif getattr(p, "kind", None) == "lut":
+                stage.append({"kind": "lut", "dims": list(p.dims()), "table": list(p.table)})
+            else:
+                stage.append({"kind": p.kind, "dims": list(p.dims())})
+        objects.append(stage)
+    return {"dims": list(layout.dims()), "objects": objects}
+
+
 # --------------------------------------------------------------------------
 # index maps
 # --------------------------------------------------------------------------

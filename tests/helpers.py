@@ -15,18 +15,7 @@ def build_layout(src: str, env=None):
     return eval(src, ns)
 
 
-def spec_of(layout) -> dict:
-    """Oracle spec of a lego_b200 layout (structure only; no product arithmetic)."""
-    objects = []
-    for o in layout.objects:
-        stage = []
-        for p in o.perms:
-            if isinstance(p, L.RegP):
-                stage.append({"kind": "regp", "dims": list(p.dims()), "perm": list(p.permutation)})
-            else:
-                stage.append({"kind": p.kind, "dims": list(p.dims())})
-        objects.append(stage)
-    return {"dims": list(layout.dims()), "objects": objects}
+from oracle.lego_oracle import spec_of  # noqa: E402,F401  (structure-only bridge from a layout object to an oracle spec)
 
 
 def unravel(ids, dims):

@@ -1,50 +1,5 @@
-"""Seeded synthetic inputs of the five benchmark configurations (shapes, dtypes
-and value distributions as the benchmark description names them), shared by the
-tests and bench.py.  All generation happens on the CPU generator so the values
-do not depend on the GPU."""
-import math
-
-import torch
-
-GROUPED_CHOICES = (1024, 2048, 4096)
-
-
-def transpose_input(n=4096, seed=0):
-    g = torch.Generator().manual_seed(seed)
-    return torch.rand(n, n, generator=g, dtype=torch.float32) * 2 - 1
-
-
-def softmax_input(rows=16384, cols=8192, seed=1):
-    g = torch.Generator().manual_seed(seed)
-    return (torch.randn(rows, cols, generator=g) * 2).half()
-
-
-def layernorm_input(rows=16384, cols=8192, seed=2):
-    g = torch.Generator().manual_seed(seed)
-    x = torch.randn(rows, cols, generator=g).half()
-    gamma = (1 + 0.1 * torch.randn(cols, generator=g)).half()
-    beta = (0.1 * torch.randn(cols, generator=g)).half()
-    return x, gamma, beta
-
-
-def gemm_input(m=8192, n=8192, k=8192, seed=3):
-    g = torch.Generator().manual_seed(seed)
-    a = (torch.randn(m, k, generator=g) / math.sqrt(k)).half()
-    b = (torch.randn(k, n, generator=g) / math.sqrt(k)).half()
-    return a, b
-
-
-def grouped_sizes(groups=16, k=4096, seed=4):
-    g = torch.Generator().manual_seed(seed)
-    idx = torch.randint(0, 3, (groups, 2), generator=g)
-    return [(GROUPED_CHOICES[int(i)], GROUPED_CHOICES[int(j)], k) for i, j in idx], g
-
-
-def grouped_input(groups=16, k=4096, seed=4, scale_rows=1):
-    """A_g [M_g / scale_rows, K], B_g [K, N_g]; scale_rows shrinks M for quick tests."""
-    sizes, g = grouped_sizes(groups, k, seed)
-    A, B = [], []
-    for m, n, kk in sizes:
-        A.append((torch.randn(m // scale_rows, kk, generator=g) / 64).half())
-        B.append((torch.randn(kk, n, generator=g) / 64).half())
-    return A, B
+"""The seeded inputs of the benchmark configurations live in the package
+(``lego_b200/configs.py``) so that bench.py runs without the test tree; the tests
+import them under this name."""
+from lego_b200.configs import *  # noqa: F401,F403
+from lego_b200.configs import GROUPED_CHOICES  # noqa: F401

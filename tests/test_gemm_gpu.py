@@ -176,3 +176,81 @@ def test_e5m2_operand_layouts_edges_and_both_kernels(ta, tb):
         ops.matmul(a.cuda(), b.cuda().half())                      # mixed operand types
     with pytest.raises(ValueError):
         ops.matmul(a.cuda()[:, :200].contiguous(), b.cuda()[:200])  # K = 200 is not a multiple of 16
+
+
+def test_stream_k_tail_matches_the_oracle_and_is_deterministic():
+    """Shapes whose tile count is not a multiple of the SM pairs: the partial last wave is
+    cut along K, partial accumulators go through the workspace and the owner adds them.
+    256 x 1536 x 4096 is six pair tiles on 74 pairs, so every tile is shared by about a
+    dozen workers (an owner adds up to eleven peers); 1024 x 8192 x 2048 is the M/8 slab of
+    the benchmark GEMM's shape with a shorter K (128 pair tiles = 1.73 waves)."""
+    g = torch.Generator().manual_seed(41)
+    for m, n, k in [(256, 1536, 4096), (1024, 8192, 2048), (2304, 2304, 1024), (200, 520, 1096)]:
+        a = (torch.randn(m, k, generator=g) / math.sqrt(k)).half()
+        b = (torch.randn(k, n, generator=g) / math.sqrt(k)).half()
+        ref = O.matmul(a, b)
+        ad, bd = a.cuda(), b.cuda()
+        first = ops.matmul(ad, bd)
+        ops.device_status()
+        assert rel_fro(first.cpu(), ref) <= REL_FRO, (m, n, k)
+        for _ in range(3):                       # flags are left clean, results repeat bit for bit
+            assert torch.equal(ops.matmul(ad, bd), first), (m, n, k)
+        ops.device_status()
+        ops.tune(gemm_streamk=False)
+        try:
+            whole = ops.matmul(ad, bd)
+        finally:
+            ops.tune(gemm_streamk=True)
+        ops.device_status()
+        assert rel_fro(whole.cpu(), ref) <= REL_FRO
+        # fp32 partial sums added in another order: equal up to the last fp16 bit
+        assert (first.float() - whole.float()).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("streamk", [False, True])
+def test_tall_pair_tiles_512x256(streamk):
+    """The 512 x 256 pair tile (two 256-row accumulator blocks sharing one B tile), with and
+    without the stream-K tail, fp16 and e5m2, all operand layouts of one shape."""
+    ops.tune(gemm_blocks=2, gemm_streamk=streamk)
+    try:
+        g = torch.Generator().manual_seed(43)
+        for m, n, k in [(512, 256, 64), (1024, 768, 320), (1536, 2304, 1024), (1000, 520, 136)]:
+            a = (torch.randn(m, k, generator=g) / math.sqrt(k)).half()
+            b = (torch.randn(k, n, generator=g) / math.sqrt(k)).half()
+            order = L.OrderBy(L.Col(-(-m // 128), -(-n // 256))).TileBy([-(-m // 128), -(-n // 256)])
+            c = ops.matmul(a.cuda(), b.cuda(), tile_order=order)
+            ops.device_status()
+            assert rel_fro(c.cpu(), O.matmul(a, b)) <= REL_FRO, (m, n, k)
+        for ta, tb in [(0, 1), (1, 0), (1, 1)]:
+            a = (torch.randn(1024, 320, generator=g) / 16).half()
+            b = (torch.randn(320, 768, generator=g) / 16).half()
+            ad = a.t().contiguous().cuda().t() if ta else a.cuda()
+            bd = b.t().contiguous().cuda().t() if tb else b.cuda()
+            assert rel_fro(ops.matmul(ad, bd).cpu(), O.matmul(a, b)) <= REL_FRO, (ta, tb)
+        a8, b8 = _e5m2_pair(1024, 512, 384, 5)
+        assert rel_fro(ops.matmul(a8.cuda(), b8.cuda()).cpu(), O.matmul(a8.float(), b8.float())) <= REL_FRO
+        a, b = gemm_input(4096, 4096, 4096)
+        c = ops.matmul(a.cuda(), b.cuda())
+        ops.device_status()
+        rows = torch.tensor([0, 127, 128, 383, 511, 512, 2049, 4095])
+        assert rel_fro(c[rows.cuda()].cpu(), a[rows].float() @ b.float()) <= REL_FRO
+    finally:
+        ops.tune(gemm_blocks=0, gemm_streamk=True)
+
+
+def test_grouped_gemm_refuses_stream_capture():
+    """The grouped entry points upload their problem table from host memory that dies with
+    the call: inside a stream capture they return LEGO_ERR_UNSUPPORTED and enqueue nothing."""
+    a = torch.zeros(128, 64, dtype=torch.float16, device="cuda")
+    b = torch.zeros(64, 256, dtype=torch.float16, device="cuda")
+    ops.lego_group_gemm_fn([a], [b])            # set-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        with pytest.raises(ValueError, match="no kernel"):
+            ops.lego_group_gemm_fn([a], [b])
+        c = ops.matmul(a, b)                     # a plain GEMM is capturable
+    graph.replay()
+    torch.cuda.synchronize()
+    assert c.abs().max().item() == 0
+    ops.device_status()

@@ -113,3 +113,33 @@ def test_argument_errors():
         ops.permute(x[:32], a, a)
     with pytest.raises(ValueError):
         ops.permute(x, a, a, out=x)        # in place is refused
+
+
+@pytest.mark.parametrize("dtype,n,t", [(torch.float32, 1024, 32), (torch.float16, 512, 64), (torch.float64, 256, 16)])
+def test_tile_ranges_assemble_the_whole_reorganisation(dtype, n, t):
+    """One GPU of several moves a contiguous range of tile_order ids.  With the column-major
+    tile order a range is a slab of output rows: four ragged ranges written into one buffer
+    give the whole transpose, and a single range touches nothing outside its slab."""
+    from lego_b200 import shard
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(n, n, generator=g).to(dtype)
+    nt = n // t
+    src = L.OrderBy(L.Row(n, n)).TileBy([nt, nt], [t, t])
+    dst = L.OrderBy(L.Col(n, n)).TileBy([nt, nt], [t, t])
+    order = L.OrderBy(L.Col(nt, nt)).TileBy([nt, nt])
+    xd = x.cuda()
+    out = torch.full_like(xd, 7.0)
+    for rank in range(3):
+        r0, r1 = shard.shard_transpose(n, n, rank, 3, t)          # output rows of this rank
+        ops.permute(xd, src, dst, order, out=out, tiles=(r0 // t * nt, (r1 - r0) // t * nt))
+        done = out.reshape(n, n)[:r1].cpu()
+        assert torch.equal(done, x.t().contiguous()[:r1])
+        assert bool((out.reshape(n, n)[r1:] == 7.0).all())
+    ops.device_status()
+    empty = torch.full_like(xd, 7.0)
+    ops.permute(xd, src, dst, order, out=empty, tiles=(5, 0))
+    assert bool((empty == 7.0).all())
+    with pytest.raises(ValueError):
+        ops.permute(xd, src, dst, order, out=out, tiles=(nt * nt - 1, 2))     # past the last tile
+    with pytest.raises(ValueError):
+        ops.permute(xd, src, dst, None, out=out, tiles=(0, 1))                # a range needs a tile order

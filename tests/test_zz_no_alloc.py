@@ -53,6 +53,31 @@ def test_static_scratch_matches_allocating_entry_point_twice():
             assert torch.equal(w, g)
 
 
+def test_static_entry_point_allocates_no_device_memory():
+    """Free device memory as the driver reports it is the same before and after a run of
+    calls (the first call, made above or here, has already loaded the kernels)."""
+    gen = torch.Generator().manual_seed(22)
+    A = [(torch.randn(256, 128, generator=gen) / 16).half().cuda() for _ in range(3)]
+    B = [(torch.randn(128, 512, generator=gen) / 16).half().cuda() for _ in range(3)]
+    outs = [torch.empty((256, 512), dtype=torch.float16, device="cuda") for _ in range(3)]
+    Ptr = C.c_void_p * 3
+    args = (Ptr(*[t.data_ptr() for t in A]), Ptr(*[t.data_ptr() for t in B]), Ptr(*[t.data_ptr() for t in outs]),
+            (C.c_int64 * 9)(*([256, 512, 128] * 3)), 3, None, None, torch.cuda.current_stream().cuda_stream)
+    lib = _abi.lib()
+    assert lib.lego_grouped_gemm_f16_static(*args) == 0      # loads the module if nothing has yet
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(20):
+        assert lib.lego_grouped_gemm_f16_static(*args) == 0
+    torch.cuda.synchronize()
+    assert lib.lego_device_status(torch.cuda.current_stream().cuda_stream, None) == 0   # reads the in-array word
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    for o, a, b in zip(outs, A, B):
+        ref = a.float() @ b.float()
+        assert ((o.float() - ref).norm() / ref.norm()).item() <= 1e-3
+
+
 def test_static_scratch_rejects_more_groups_than_it_holds():
     a = torch.zeros(128, 64, dtype=torch.float16, device="cuda")
     b = torch.zeros(64, 256, dtype=torch.float16, device="cuda")
