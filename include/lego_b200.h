@@ -240,8 +240,12 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  * through its @triton.autotune lists, matmul_NTA_NTB.py:17-52).
  *   LEGO_TUNE_GEMM_BLOCKS   0 = library's choice, 1 = 256 x 256 output per SM pair,
  *                           2 = 512 x 256 per SM pair when the tile order allows it
- *   LEGO_TUNE_GEMM_STREAMK  0 = never split along K even when a workspace is given     */
-enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2 };
+ *   LEGO_TUNE_GEMM_STREAMK  0 = never split along K even when a workspace is given, 1 = when the
+ *                           last wave of tiles would leave SMs idle (default), 2 = whenever
+ *                           the tile count is not a multiple of the resident SM pairs
+ *   LEGO_TUNE_GEMM_LAG      0..4 k-steps by which the first accumulator block of a 512 x 256
+ *                           tile leads the second at both ends of the tile (epilogue overlap) */
+enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

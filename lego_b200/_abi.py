@@ -25,6 +25,7 @@ ACT_LEAKY_RELU = 1
 
 TUNE_GEMM_BLOCKS = 1
 TUNE_GEMM_STREAMK = 2
+TUNE_GEMM_LAG = 3
 
 ERR_CUDA_BASE = 1000
 ERR_DEVICE_TIMEOUT = 2001

@@ -428,7 +428,7 @@ struct Sched {
   int32_t sk_tiles;     // cut along K (ids dp_tiles .. total_tiles - 1)
   int32_t sk_run;       // k-steps per worker in the stream-K part
   int32_t kblocks;      // k-steps per tile (uniform: the stream-K part exists for one problem only)
-  int32_t reserved;
+  int32_t lag;          // MT = 2: k-steps block 0 runs ahead of block 1 at both ends of a tile
   float* workspace;     // nullable when sk_tiles == 0
 };
 
@@ -698,7 +698,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (lane == 0 && rank == 0) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t kcount = 0;  // k-steps consumed so far: ring slot kcount % NSTAGE, parity (kcount / NSTAGE) & 1
       uint32_t acc_it = 0;
       bool ok = true;
       int cursor = 0;
@@ -710,7 +710,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         const Geometry geo = geometry_of(pr->elem8);
         const bool f8 = pr->elem8 != 0;
         const int kblocks = kblocks_of(pr);
-        const int kb1 = item.kb1 < 0 ? kblocks : item.kb1;
+        const int n_steps = (item.kb1 < 0 ? kblocks : item.kb1) - item.kb0;
         const bool a_mn = pr->a_mn_major != 0, b_mn = pr->b_mn_major != 0;
         const uint32_t idesc = f8 ? ptx::idesc_f8(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u, 1u)
                                   : ptx::idesc_f16(2 * BM, BN, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
@@ -718,51 +718,96 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         const uint64_t da_fixed = ptx::smem_desc_sw128(0, a_mn ? geo.sub_bytes : 16, 1024);
         const uint64_t db_fixed = ptx::smem_desc_sw128(0, b_mn ? geo.sub_bytes : 16, 1024);
         const uint32_t a_kstep = a_mn ? geo.mn_kstep : (32 >> 4), b_kstep = b_mn ? geo.mn_kstep : (32 >> 4);
-        uint32_t d_tmem[MT];
+
+        // the MMAs of k-step t (relative to the item) into accumulator block j
+        auto issue = [&](int j, int t) {
+          const uint32_t slot = (kcount + (uint32_t)t) % NSTAGE;
+          const uint32_t a_enc = smem_enc + slot * (STAGE >> 4) + j * (P_A_BYTES >> 4);
+          const uint32_t b_enc = smem_enc + slot * (STAGE >> 4) + MT * (P_A_BYTES >> 4);
+          const uint32_t d = tmem_base + ((acc_it + j) & 1) * BN;
+          if (f8) {
 #pragma unroll
-        for (int j = 0; j < MT; ++j) {
-          const uint32_t acc = (acc_it + j) & 1, aphase = ((acc_it + j) >> 1) & 1;
-          if (ok && !ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag,
-                                                  loop_wait_limit(kblocks))) {
-            fail_pair(status, abort_flag, 1u, 0x120000u | 0x100u | acc);
-            ok = false;
+            for (int kk = 0; kk < BK / 16; ++kk)
+              ptx::mma_f8_ss_pair(d, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
+                                  db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (t > 0 || kk != 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+              ptx::mma_f16_ss_pair(d, da_fixed | (uint64_t)(a_enc + kk * a_kstep),
+                                   db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc, (t > 0 || kk != 0) ? 1u : 0u);
           }
-          d_tmem[j] = tmem_base + acc * BN;
-        }
-        if (!ok) break;
-        ptx::tc_fence_after();
-        for (int kb = item.kb0; kb < kb1; ++kb) {
-          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[stage]), phase, abort_flag, WAIT_LIMIT)) {
-            fail_pair(status, abort_flag, 1u, 0x120000u | stage);
+        };
+        auto wait_loaded = [&](int t) {
+          const uint32_t c = kcount + (uint32_t)t;
+          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->full[c % NSTAGE]), (c / NSTAGE) & 1u, abort_flag,
+                                            WAIT_LIMIT)) {
+            fail_pair(status, abort_flag, 1u, 0x120000u | (c % NSTAGE));
             ok = false;
-            break;
+            return false;
           }
           ptx::tc_fence_after();
-          const uint32_t a_enc = smem_enc + stage * (STAGE >> 4);
-          const uint32_t b_enc = a_enc + MT * (P_A_BYTES >> 4);
-          const bool last = kb + 1 == kb1;
-#pragma unroll
-          for (int j = 0; j < MT; ++j) {
-            const uint32_t aj = a_enc + j * (P_A_BYTES >> 4);
-            if (f8) {
-#pragma unroll
-              for (int kk = 0; kk < BK / 16; ++kk)
-                ptx::mma_f8_ss_pair(d_tmem[j], da_fixed | (uint64_t)(aj + kk * a_kstep),
-                                    db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc,
-                                    (kb > item.kb0 || kk != 0) ? 1u : 0u);
-            } else {
-#pragma unroll
-              for (int kk = 0; kk < BK / 16; ++kk)
-                ptx::mma_f16_ss_pair(d_tmem[j], da_fixed | (uint64_t)(aj + kk * a_kstep),
-                                     db_fixed | (uint64_t)(b_enc + kk * b_kstep), idesc,
-                                     (kb > item.kb0 || kk != 0) ? 1u : 0u);
-            }
-            // block j is complete with the last k-step: let its epilogue start while the next block's MMAs retire
-            if (last) ptx::mma_commit_pair(ptx::smem_u32(&bars->tmem_full[(acc_it + j) & 1]), 3);
+          return true;
+        };
+        auto release = [&](int t) {  // frees the ring slot of k-step t in both CTAs once the MMAs so far are done
+          ptx::mma_commit_pair(ptx::smem_u32(&bars->empty[(kcount + (uint32_t)t) % NSTAGE]), 3);
+        };
+        auto wait_drained = [&](int j) {
+          const uint32_t acc = (acc_it + j) & 1, aphase = ((acc_it + j) >> 1) & 1;
+          if (!ptx::mbar_wait_bounded<true>(ptx::smem_u32(&bars->tmem_empty[acc]), aphase ^ 1, abort_flag,
+                                            loop_wait_limit(kblocks))) {
+            fail_pair(status, abort_flag, 1u, 0x120000u | 0x100u | acc);
+            ok = false;
+            return false;
           }
-          ptx::mma_commit_pair(ptx::smem_u32(&bars->empty[stage]), 3);  // frees the slot in both CTAs
-          if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
+          ptx::tc_fence_after();
+          return true;
+        };
+        auto publish = [&](int j) {
+          ptx::mma_commit_pair(ptx::smem_u32(&bars->tmem_full[(acc_it + j) & 1]), 3);
+        };
+
+        if (MT == 1) {
+          if (!wait_drained(0)) break;
+          for (int t = 0; t < n_steps; ++t) {
+            if (!wait_loaded(t)) break;
+            issue(0, t);
+            release(t);
+          }
+          if (ok) publish(0);
+        } else {
+          // Two accumulator blocks fill all of TMEM, so there is no spare buffer to hide the
+          // epilogue behind.  Instead block 0 runs `lag` k-steps ahead of block 1 at both ends
+          // of the tile: at the end block 0 completes while block 1 still has `lag` steps of
+          // MMAs to go (its drain overlaps them), and at the start of the next tile block 0's
+          // first `lag` steps run while block 1 is being drained.  In between the two blocks
+          // alternate on every k-step and a ring slot is released as soon as both have read it.
+          int lag = sched.lag < n_steps / 2 ? sched.lag : n_steps / 2;
+          if (lag > NSTAGE) lag = NSTAGE;
+          if (!wait_drained(0)) break;
+          for (int t = 0; ok && t < lag; ++t)
+            if (wait_loaded(t)) issue(0, t);
+          if (!ok || !wait_drained(1)) break;
+          for (int t = 0; t < lag; ++t) {
+            issue(1, t);
+            release(t);
+          }
+          for (int t = lag; ok && t < n_steps - lag; ++t) {
+            if (!wait_loaded(t)) break;
+            issue(0, t);
+            issue(1, t);
+            release(t);
+          }
+          for (int t = n_steps - lag; ok && t < n_steps; ++t)
+            if (wait_loaded(t)) issue(0, t);
+          if (!ok) break;
+          publish(0);
+          for (int t = n_steps - lag; t < n_steps; ++t) {
+            issue(1, t);
+            release(t);
+          }
+          publish(1);
         }
+        kcount += (uint32_t)n_steps;
         acc_it += MT;
       }
     }
@@ -1022,6 +1067,7 @@ bool ids_share_columns(const Problem& p, int n) {
 // Tuning knobs (lego_tune), process-wide.
 std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
 std::atomic<int> g_tune_streamk{1};  // 1: split the partial last wave along K when a workspace is given
+std::atomic<int> g_tune_lag{3};      // see Sched::lag
 
 // Data-parallel over `tiles` pair tiles, or with the partial last wave cut along K.
 Sched make_sched(int64_t tiles, int workers, int kblocks, int mt, void* workspace, int64_t workspace_bytes) {
@@ -1029,11 +1075,18 @@ Sched make_sched(int64_t tiles, int workers, int kblocks, int mt, void* workspac
   sc.total_tiles = (int32_t)tiles;
   sc.dp_tiles = (int32_t)tiles;
   sc.kblocks = kblocks;
+  sc.lag = g_tune_lag.load();
   const int64_t need = kSkFlagBytes + (int64_t)workers * 2 * mt * kSkBlockFloats * 4;
   const int64_t rest = tiles % workers;
   if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) || workers > kSkMaxWorkers ||
       g_tune_streamk.load() == 0 || rest == 0 || kblocks > (1 << 20))
     return sc;
+  // Worth it only when the last wave leaves a fair share of the SMs idle: the fix-up costs an
+  // fp32 round trip through L2 per shared tile.  (8192^3: 512 tall tiles on 74 pairs, last wave
+  // 92 % full, 1 176 with the split against 1 208 TFLOP/s without; a 1024-row slab of it,
+  // 1.73 waves, is the case the split is for.)
+  const int64_t waves = (tiles + workers - 1) / workers;
+  if (g_tune_streamk.load() == 1 && (waves * workers - tiles) * 25 < waves * workers) return sc;
   const int64_t units = rest * kblocks;
   const int64_t run = (units + workers - 1) / workers;
   if (run < 4) return sc;  // a handful of k-steps per worker is not worth a fix-up
@@ -1164,8 +1217,14 @@ static int32_t run_gemm(const void* A, const void* B, void* C, int64_t M, int64_
     st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF, elem8);
     if (st != LEGO_OK) return st;
     bool launched = false;
+    // 512 x 256 per SM pair moves a quarter less operand data per flop (sustained 8192^3 on one
+    // box: 1 208 against 1 109 TFLOP/s) but halves the number of work items: it is the choice
+    // once there is at least a full wave of them.
+    int max_tall = 0;
     const int blocks = g_tune_blocks.load();
-    if (blocks == 2 && ids_share_columns(p, 4)) {
+    const bool tall_ok = blocks != 1 && ids_share_columns(p, 4) &&
+                         configure_pair<false, 2>(ctx->device, &max_tall) == LEGO_OK && max_tall >= 1;
+    if (tall_ok && (blocks == 2 || total / 4 >= max_tall)) {
       st = launch_pair<false, 2>(p, nullptr, 1, total, kblocks, activation, workspace, workspace_bytes, ctx->device,
                                  ctx->status_word, s, &launched);
       if (launched) return st;
@@ -1222,7 +1281,12 @@ int32_t lego_tune(int32_t knob, int32_t value) {
       g_tune_blocks.store(value);
       return LEGO_OK;
     case LEGO_TUNE_GEMM_STREAMK:
-      g_tune_streamk.store(value ? 1 : 0);
+      if (value < 0 || value > 2) return LEGO_ERR_SIZE;
+      g_tune_streamk.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_GEMM_LAG:
+      if (value < 0 || value > 4) return LEGO_ERR_SIZE;
+      g_tune_lag.store(value);
       return LEGO_OK;
     default:
       return LEGO_ERR_UNSUPPORTED;

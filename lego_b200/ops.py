@@ -143,14 +143,19 @@ def selftest_bounded_wait(limit_cycles: int = 1_000_000) -> None:
     _abi.check(_abi.lib().lego_selftest_bounded_wait(int(limit_cycles), _stream()), "lego_selftest_bounded_wait")
 
 
-def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None) -> None:
+def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
+         gemm_lag: Optional[int] = None) -> None:
     """Process-wide GEMM knobs: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
-    pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` False keeps every tile whole."""
+    pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` 0 / False keeps every tile whole,
+    1 / True splits a poorly filled last wave along K, 2 splits any partial wave;
+    ``gemm_lag`` 0..4, the lead of the first accumulator block of a 512 x 256 tile."""
     lib = _abi.lib()
     if gemm_blocks is not None:
         _abi.check(lib.lego_tune(_abi.TUNE_GEMM_BLOCKS, int(gemm_blocks)), "lego_tune")
     if gemm_streamk is not None:
-        _abi.check(lib.lego_tune(_abi.TUNE_GEMM_STREAMK, int(bool(gemm_streamk))), "lego_tune")
+        _abi.check(lib.lego_tune(_abi.TUNE_GEMM_STREAMK, int(gemm_streamk)), "lego_tune")
+    if gemm_lag is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_GEMM_LAG, int(gemm_lag)), "lego_tune")
 
 
 # One split-K scratch buffer per (device, stream): calls on one stream are ordered, calls on

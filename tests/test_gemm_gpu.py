@@ -185,6 +185,7 @@ def test_stream_k_tail_matches_the_oracle_and_is_deterministic():
     dozen workers (an owner adds up to eleven peers); 1024 x 8192 x 2048 is the M/8 slab of
     the benchmark GEMM's shape with a shorter K (128 pair tiles = 1.73 waves)."""
     g = torch.Generator().manual_seed(41)
+    ops.tune(gemm_streamk=2)                      # split whenever a partial wave exists
     for m, n, k in [(256, 1536, 4096), (1024, 8192, 2048), (2304, 2304, 1024), (200, 520, 1096)]:
         a = (torch.randn(m, k, generator=g) / math.sqrt(k)).half()
         b = (torch.randn(k, n, generator=g) / math.sqrt(k)).half()
@@ -196,22 +197,24 @@ def test_stream_k_tail_matches_the_oracle_and_is_deterministic():
         for _ in range(3):                       # flags are left clean, results repeat bit for bit
             assert torch.equal(ops.matmul(ad, bd), first), (m, n, k)
         ops.device_status()
-        ops.tune(gemm_streamk=False)
+        ops.tune(gemm_streamk=0)
         try:
             whole = ops.matmul(ad, bd)
         finally:
-            ops.tune(gemm_streamk=True)
+            ops.tune(gemm_streamk=2)
         ops.device_status()
         assert rel_fro(whole.cpu(), ref) <= REL_FRO
         # fp32 partial sums added in another order: equal up to the last fp16 bit
         assert (first.float() - whole.float()).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
+    ops.tune(gemm_streamk=1)
 
 
-@pytest.mark.parametrize("streamk", [False, True])
-def test_tall_pair_tiles_512x256(streamk):
+@pytest.mark.parametrize("streamk,lag", [(0, 0), (0, 3), (2, 4), (2, 1)])
+def test_tall_pair_tiles_512x256(streamk, lag):
     """The 512 x 256 pair tile (two 256-row accumulator blocks sharing one B tile), with and
-    without the stream-K tail, fp16 and e5m2, all operand layouts of one shape."""
-    ops.tune(gemm_blocks=2, gemm_streamk=streamk)
+    without the stream-K tail and with several leads of block 0 over block 1 (including k
+    loops shorter than twice the lead), fp16 and e5m2, all operand layouts of one shape."""
+    ops.tune(gemm_blocks=2, gemm_streamk=streamk, gemm_lag=lag)
     try:
         g = torch.Generator().manual_seed(43)
         for m, n, k in [(512, 256, 64), (1024, 768, 320), (1536, 2304, 1024), (1000, 520, 136)]:
@@ -235,7 +238,7 @@ def test_tall_pair_tiles_512x256(streamk):
         rows = torch.tensor([0, 127, 128, 383, 511, 512, 2049, 4095])
         assert rel_fro(c[rows.cuda()].cpu(), a[rows].float() @ b.float()) <= REL_FRO
     finally:
-        ops.tune(gemm_blocks=0, gemm_streamk=True)
+        ops.tune(gemm_blocks=0, gemm_streamk=1, gemm_lag=3)
 
 
 def test_grouped_gemm_refuses_stream_capture():
