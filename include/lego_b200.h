@@ -29,6 +29,7 @@ extern "C" {
 #define LEGO_MAX_STAGES   8   /* OrderBy stages in one GroupBy                          */
 #define LEGO_MAX_TERMS   32   /* digits of a folded layout                              */
 #define LEGO_MAX_GROUPS 256   /* problems in one grouped GEMM call                      */
+#define LEGO_MAX_LUT (1 << 24) /* entries of one table-driven (LUT) permutation block   */
 
 /* status codes */
 enum {
@@ -51,16 +52,27 @@ enum {
 enum {
   LEGO_BLOCK_REGP     = 0,  /* regular permutation: flatten(sigma(idx), sigma(dims))    */
   LEGO_BLOCK_ANTIDIAG = 1,  /* GenP: anti-diagonal enumeration of a square, dims = (n,n)*/
-  LEGO_BLOCK_REVERSE  = 2   /* GenP: (n1-1-i)*n2 + (n2-1-j), dims = (n1,n2)             */
+  LEGO_BLOCK_REVERSE  = 2,  /* GenP: (n1-1-i)*n2 + (n2-1-j), dims = (n1,n2)             */
+  LEGO_BLOCK_LUT      = 3   /* GenP with arbitrary callables, tabulated over its domain */
 };
 
-/* One permutation block: RegP / Row / Col of lego/lego.py:197-240, or one of
- * the GenP bodies of lego/lego.py:490-535.  sigma(v)[i] = v[perm[i]].          */
+/* One permutation block: RegP / Row / Col of lego/lego.py:197-240, one of the
+ * GenP bodies of lego/lego.py:490-535, or any GenP (lego/lego.py:150-178) given
+ * by its tables.  sigma(v)[i] = v[perm[i]].
+ * LEGO_BLOCK_LUT: the binding evaluates the block's f_apply once over the whole
+ * domain (at most LEGO_MAX_LUT entries) and passes two device tables of
+ * prod(dims) int64 each, owned by the caller and alive while the layout is used:
+ * lut_apply[row-major id of idx over dims] = f_apply(idx), a permutation of
+ * 0 .. prod(dims)-1, and lut_inv its inverse (row-major id of f_inv(flat)).
+ * The host services cannot read device memory: the binding vouches that the
+ * tables are permutations.  Other kinds leave both pointers NULL.               */
 typedef struct lego_block {
   int32_t rank;
   int32_t kind;
   int64_t dims[LEGO_MAX_RANK];
   int32_t perm[LEGO_MAX_RANK];
+  const int64_t* lut_apply;
+  const int64_t* lut_inv;
 } lego_block_t;
 
 /* One OrderBy (lego/lego.py:243-362): blocks concatenated big-endian.          */
@@ -213,9 +225,9 @@ int32_t lego_gemm_e5m2(const void* A, const void* B, void* C, int64_t M, int64_t
                        const lego_layout_t* tile_order, void* stream);
 
 /* The same two GEMMs with a caller-owned scratch buffer that lets the library split the
- * partial last wave of tiles along K (a stream-K tail): when the tile count is not a
- * multiple of what the GPU holds at once -- 8192 x 8192 x 8192 is 13.8 waves, a 1024-row
- * slab of it 1.7 -- every pair of SMs gets the same number of k-steps, partial fp32
+ * partial last wave of tiles along K (a stream-K tail; opt-in through lego_tune): when
+ * the tile count is not a multiple of what the GPU holds at once -- 8192 x 8192 x 8192 is
+ * 13.8 waves, a 1024-row slab of it 1.7 -- every pair of SMs gets the same number of k-steps, partial fp32
  * accumulators travel through the buffer and the tile's owner adds them in a fixed order
  * (same bits on every run).  No counterpart in the reference, whose matmul() launches
  * one program per tile and leaves the tail to the hardware scheduler
@@ -240,9 +252,10 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  * through its @triton.autotune lists, matmul_NTA_NTB.py:17-52).
  *   LEGO_TUNE_GEMM_BLOCKS   0 = library's choice, 1 = 256 x 256 output per SM pair,
  *                           2 = 512 x 256 per SM pair when the tile order allows it
- *   LEGO_TUNE_GEMM_STREAMK  0 = never split along K even when a workspace is given, 1 = when the
- *                           last wave of tiles would leave SMs idle (default), 2 = whenever
- *                           the tile count is not a multiple of the resident SM pairs
+ *   LEGO_TUNE_GEMM_STREAMK  0 = never split along K (default), 1 = when a workspace is given and
+ *                           the last wave of tiles would leave SMs idle, 2 = whenever a
+ *                           workspace is given and the tile count is not a multiple of the
+ *                           resident SM pairs
  *   LEGO_TUNE_GEMM_LAG      0..4 k-steps by which the first accumulator block of a 512 x 256
  *                           tile leads the second at both ends of the tile (epilogue overlap) */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3 };

@@ -19,6 +19,8 @@ MAX_GROUPS = 256
 BLOCK_REGP = 0
 BLOCK_ANTIDIAG = 1
 BLOCK_REVERSE = 2
+BLOCK_LUT = 3
+MAX_LUT = 1 << 24
 
 ACT_NONE = 0
 ACT_LEAKY_RELU = 1
@@ -33,7 +35,8 @@ ERR_DEVICE_TIMEOUT = 2001
 
 class Block(C.Structure):
     _fields_ = [("rank", C.c_int32), ("kind", C.c_int32),
-                ("dims", C.c_int64 * MAX_RANK), ("perm", C.c_int32 * MAX_RANK)]
+                ("dims", C.c_int64 * MAX_RANK), ("perm", C.c_int32 * MAX_RANK),
+                ("lut_apply", C.c_void_p), ("lut_inv", C.c_void_p)]
 
 
 class Stage(C.Structure):

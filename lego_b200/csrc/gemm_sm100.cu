@@ -1066,8 +1066,8 @@ bool ids_share_columns(const Problem& p, int n) {
 
 // Tuning knobs (lego_tune), process-wide.
 std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
-std::atomic<int> g_tune_streamk{1};  // 1: split the partial last wave along K when a workspace is given
-std::atomic<int> g_tune_lag{3};      // see Sched::lag
+std::atomic<int> g_tune_streamk{0};  // see make_sched
+std::atomic<int> g_tune_lag{4};      // see Sched::lag
 
 // Data-parallel over `tiles` pair tiles, or with the partial last wave cut along K.
 Sched make_sched(int64_t tiles, int workers, int kblocks, int mt, void* workspace, int64_t workspace_bytes) {
@@ -1081,10 +1081,12 @@ Sched make_sched(int64_t tiles, int workers, int kblocks, int mt, void* workspac
   if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) || workers > kSkMaxWorkers ||
       g_tune_streamk.load() == 0 || rest == 0 || kblocks > (1 << 20))
     return sc;
-  // Worth it only when the last wave leaves a fair share of the SMs idle: the fix-up costs an
-  // fp32 round trip through L2 per shared tile.  (8192^3: 512 tall tiles on 74 pairs, last wave
-  // 92 % full, 1 176 with the split against 1 208 TFLOP/s without; a 1024-row slab of it,
-  // 1.73 waves, is the case the split is for.)
+  // Off unless asked for (LEGO_TUNE_GEMM_STREAMK).  The split balances the k-steps exactly but
+  // it also takes the workers out of step: CTAs that share a B column block no longer walk K
+  // together, so B is fetched from DRAM once per worker instead of once per wave.  Measured
+  // on one box, sustained TFLOP/s with / without: 8192^3 1 175 / 1 200; 1024 x 8192 x 8192 (1.73
+  // waves of 256 x 256 tiles, the case it was built for) 1 030 / 1 051, and 982 against 1 134
+  // for 512 x 256 tiles that fit one wave.  Mode 1 splits only a poorly filled last wave.
   const int64_t waves = (tiles + workers - 1) / workers;
   if (g_tune_streamk.load() == 1 && (waves * workers - tiles) * 25 < waves * workers) return sc;
   const int64_t units = rest * kblocks;
@@ -1217,14 +1219,15 @@ static int32_t run_gemm(const void* A, const void* B, void* C, int64_t M, int64_
     st = fill_problem(enc, &p, A, B, C, M, N, K, trans_a, trans_b, tile_order, 0, P_BN_HALF, elem8);
     if (st != LEGO_OK) return st;
     bool launched = false;
-    // 512 x 256 per SM pair moves a quarter less operand data per flop (sustained 8192^3 on one
-    // box: 1 208 against 1 109 TFLOP/s) but halves the number of work items: it is the choice
-    // once there is at least a full wave of them.
+    // 512 x 256 per SM pair moves a quarter less operand data per flop (sustained on one box,
+    // TFLOP/s: 8192^3 1 200 against 1 100; a 1024-row slab of it, 64 tall tiles on 74 pairs,
+    // 1 134 against 1 051) but halves the number of work items: it is the choice from half a
+    // wave of them.
     int max_tall = 0;
     const int blocks = g_tune_blocks.load();
     const bool tall_ok = blocks != 1 && ids_share_columns(p, 4) &&
                          configure_pair<false, 2>(ctx->device, &max_tall) == LEGO_OK && max_tall >= 1;
-    if (tall_ok && (blocks == 2 || total / 4 >= max_tall)) {
+    if (tall_ok && (blocks == 2 || total / 4 >= max_tall / 2)) {
       st = launch_pair<false, 2>(p, nullptr, 1, total, kblocks, activation, workspace, workspace_bytes, ctx->device,
                                  ctx->status_word, s, &launched);
       if (launched) return st;

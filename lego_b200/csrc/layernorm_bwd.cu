@@ -118,16 +118,17 @@ ln_bwd_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dga
 // copies; 512 consumer threads own 8 or 16 fixed columns each: gamma and the two
 // column accumulators of those columns stay in registers for the whole kernel, a row
 // costs one two-value reduction over the CTA, and dx leaves in 128-bit streaming
-// stores.  Memory-level parallelism comes from the ring (up to 6 rows of x and dy in
-// flight per SM), not from occupancy.
+// stores.  Memory-level parallelism comes from the ring (as many rows of x and dy in
+// flight per SM as fit, up to 12), not from occupancy.
 
 constexpr int kBwd1Consumers = 512;
-constexpr int kBwd1Ring = 6;
+constexpr int kBwd1Ring = 12;  // two slots are held by the rows in phase 1 and phase 2, the rest are loads in flight
 constexpr long long kBwd1WaitLimit = 2000000000LL;  // SM cycles, about a second
 
 struct BwdRing1Ctl {
   uint64_t full[kBwd1Ring];
   uint64_t empty[kBwd1Ring];
+  uint64_t rowbar[2];  // row n's warp totals are all in red[]: 16 arrivals (one per consumer warp)
   int64_t row[kBwd1Ring];
   uint32_t abort_flag;
 };
@@ -138,7 +139,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   constexpr int NV = EPT / 8;
   constexpr int NW = kBwd1Consumers / 32;
   extern __shared__ __align__(128) uint8_t bwd1_smem[];
-  __shared__ __align__(16) float red[2][NW][2];  // [row parity][warp] -> (s1, s2)
+  __shared__ __align__(16) float red[4][NW][2];  // [row & 3][warp] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
   const uint32_t half_slot = (row_bytes + 127u) & ~127u;
@@ -153,6 +154,8 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
       ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), NW);
     }
+    ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[0]), NW);
+    ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[1]), NW);
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -198,7 +201,17 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   }
 
   // ---------------- consumers ----------------
-  // All element-wise fp32 work runs as packed pairs (f32x2): P = EPT / 2 pairs per thread.
+  // All element-wise fp32 work runs as packed pairs (f32x2).  A row is handled in two
+  // phases with the next row's first phase in between, so that the CTA-wide reduction of a
+  // row (shuffles, a hop through shared memory, an mbarrier) is in flight while the thread
+  // does useful work instead of waiting at a barrier:
+  //   phase 1 (row n)  column accumulators, the row's two sums -> warp totals -> red[n & 3],
+  //                    arrive on rowbar[n & 1];
+  //   phase 2 (row n)  wait for rowbar, fold the 16 warp totals, re-read x and dy from the
+  //                    ring slot, recompute xhat and dy * gamma (cheaper than keeping 32
+  //                    registers alive across phase 1 of the next row), write dx, free the slot.
+  // Four red[] buffers: a warp in phase 1 of row n + 2 has passed the barrier of row n, so
+  // every warp has finished phase 1 of row n, which follows its phase 2 of row n - 2.
   constexpr int P2 = EPT / 2;
   const int lane = tid & 31, warp = tid >> 5;
   float2 g[P2], acc_w[P2], acc_b[P2];
@@ -214,88 +227,120 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 #pragma unroll
   for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
   const float inv_cols = 1.0f / (float)cols;
-  float2* red2 = reinterpret_cast<float2*>(&red[0][0][0]);  // [row parity][warp] -> (s1, s2)
 
-  int s = 0;
-  uint32_t use = 0;
-  for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
-    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwd1WaitLimit);
-    if (!ok) {
+  bool alive = true;
+  auto phase1 = [&](int64_t n, int s, uint32_t use) {
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwd1WaitLimit)) {
       *abort_flag = 1;
       atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
+      alive = false;
+      return;
     }
     const uint8_t* slot = bwd1_smem + (size_t)s * slot_bytes;
-    const int64_t row = ok ? ctl->row[s] : 0;
-    const float mean = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3] : 0.f;
-    const float rstd = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3] : 0.f;
-    uint4 xr[NV], dr[NV];
+    const int64_t row = ctl->row[s];
+    const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
+    const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3];
+    // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
+    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int v = k * kBwd1Consumers + tid;
-      xr[k] = dr[k] = make_uint4(0u, 0u, 0u, 0u);
-      if (ok && v * 8 < cols) {
-        xr[k] = reinterpret_cast<const uint4*>(slot)[v];
-        dr[k] = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
+      if (v * 8 < cols) {
+        xr = reinterpret_cast<const uint4*>(slot)[v];
+        dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
+        const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
+        acc_w[k * 4 + e] = ptx::fma2(d, h, acc_w[k * 4 + e]);
+        acc_b[k * 4 + e] = ptx::add2(acc_b[k * 4 + e], d);
+        const float2 w = ptx::mul2(d, g[k * 4 + e]);
+        s1 = ptx::fma2(h, w, s1);
+        s2 = ptx::add2(s2, w);
       }
     }
+    // Even lanes fold the first sum, odd lanes the second: one shuffle per level instead of
+    // two; lanes 0 and 1 end with the warp's two totals.
+    const bool odd = (lane & 1) != 0;
+    const float a = s1.x + s1.y, bsum = s2.x + s2.y;
+    float keep = odd ? bsum : a;
+    keep += __shfl_xor_sync(0xffffffffu, odd ? a : bsum, 1);
+#pragma unroll
+    for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+    if (lane < 2) red[n & 3][warp][lane] = keep;
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
-
-    // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
-    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
-    float2 h[P2], w[P2];
-    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
-#pragma unroll
-    for (int k = 0; k < P2; ++k) {
-      const __half2 xh2 = reinterpret_cast<const __half2*>(&xr[k / 4])[k % 4];
-      const __half2 dh2 = reinterpret_cast<const __half2*>(&dr[k / 4])[k % 4];
-      const float2 d = __half22float2(dh2);
-      h[k] = ptx::fma2(__half22float2(xh2), rstd2, shift2);
-      acc_w[k] = ptx::fma2(d, h[k], acc_w[k]);
-      acc_b[k] = ptx::add2(acc_b[k], d);
-      w[k] = ptx::mul2(d, g[k]);
-      s1 = ptx::fma2(h[k], w[k], s1);
-      s2 = ptx::add2(s2, w[k]);
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->rowbar[n & 1]));
+  };
+  auto phase2 = [&](int64_t n, int s) {
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
+                                kBwd1WaitLimit)) {
+      *abort_flag = 1;
+      atomicCAS(status, 0u, 0x78000u | (uint32_t)s);
+      alive = false;
+      return;
     }
-    float2 ss = make_float2(s1.x + s1.y, s2.x + s2.y);
-    float2* r = red2 + (n & 1) * NW;
-    {
-      // Even lanes fold the first sum, odd lanes the second: one shuffle per level instead of
-      // two (4 900 -> 4 990 GB/s on one box); lanes 0 and 1 end with the warp's two totals.
-      const bool odd = (lane & 1) != 0;
-      float keep = odd ? ss.y : ss.x;
-      keep += __shfl_xor_sync(0xffffffffu, odd ? ss.x : ss.y, 1);
-#pragma unroll
-      for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-      if (lane < 2) reinterpret_cast<float*>(&r[warp])[lane] = keep;
-    }
-    ptx::named_barrier<1, kBwd1Consumers>();
-    if (*abort_flag) break;  // uniform: every flag write of this row precedes the barrier above
-    // Both half-warps fold the same 16 partials, so every lane ends with the total after four
-    // shuffle levels.  (Same box: five levels from 16 active lanes 4 730 GB/s, this 4 900; folding
-    // more per lane with 128-bit loads before 3 / 2 / 1 levels 4 850 / 4 830 / 4 770.)
-    ss = r[lane & (NW - 1)];
+    // Both half-warps fold the same 16 warp totals, so every lane ends with the row's totals
+    // after four shuffle levels.
+    float2 ss = *reinterpret_cast<const float2*>(&red[n & 3][lane & (NW - 1)][0]);
 #pragma unroll
     for (int o = NW / 2; o > 0; o >>= 1) {
       ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
       ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
     }
+    const uint8_t* slot = bwd1_smem + (size_t)s * slot_bytes;
+    const int64_t row = ctl->row[s];
+    const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
+    const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3];
+    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
     // dx = (wdy - (xhat * c1 + c2)) * rstd, as two fused steps per pair
     const float c1r = ss.x * inv_cols * rstd, c2r = ss.y * inv_cols * rstd;
     const float2 nc1 = make_float2(-c1r, -c1r), nc2 = make_float2(-c2r, -c2r);
     __half* __restrict__ dx = P.dx + row * cols;
+    uint4 outv[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int v = k * kBwd1Consumers + tid;
+      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
+      if (v * 8 < cols) {
+        xr = reinterpret_cast<const uint4*>(slot)[v];
+        dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      }
+      __half2* o2 = reinterpret_cast<__half2*>(&outv[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
+        const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
+        const float2 w = ptx::mul2(d, g[k * 4 + e]);
+        const float2 t = ptx::fma2(h, nc1, ptx::fma2(w, rstd2, nc2));
+        o2[e] = __floats2half2_rn(t.x, t.y);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int c = (k * kBwd1Consumers + tid) * 8;
-      uint4 outv;
-      __half2* o2 = reinterpret_cast<__half2*>(&outv);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 t = ptx::fma2(h[k * 4 + e], nc1, ptx::fma2(w[k * 4 + e], rstd2, nc2));
-        o2[e] = __floats2half2_rn(t.x, t.y);
-      }
-      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv);
+      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
     }
+  };
+
+  // ring cursors of the row in phase 1 (s1, use1) and of the row in phase 2 (s2)
+  int s1 = 0, s2 = 0;
+  uint32_t use1 = 0;
+  auto advance = [&](int& s) { s = (s + 1 == stages) ? 0 : s + 1; };
+  if (my_rows > 0) phase1(0, s1, use1);
+  for (int64_t n = 0; alive && n < my_rows; ++n) {
+    if (n + 1 < my_rows) {
+      advance(s1);
+      use1 += (s1 == 0);
+      phase1(n + 1, s1, use1);
+      if (!alive) break;
+    }
+    phase2(n, s2);
+    advance(s2);
   }
   if (*abort_flag) return;
   float* pw = P.partial + (size_t)blockIdx.x * cols;

@@ -110,6 +110,12 @@ int32_t check_layout(const lego_layout_t* L, int64_t* size_out) {
         if (bl.rank != 2 || bl.dims[0] != bl.dims[1]) return LEGO_ERR_DIM;
       } else if (bl.kind == LEGO_BLOCK_REVERSE) {
         if (bl.rank != 2) return LEGO_ERR_DIM;
+      } else if (bl.kind == LEGO_BLOCK_LUT) {
+        if (!bl.lut_apply || !bl.lut_inv) return LEGO_ERR_NULL;
+        int64_t bsz = 1;
+        for (int i = 0; i < bl.rank; ++i)
+          if (!mul_ok(bsz, bl.dims[i], &bsz)) return LEGO_ERR_OVERFLOW;
+        if (bsz > LEGO_MAX_LUT) return LEGO_ERR_SIZE;
       } else {
         return LEGO_ERR_UNSUPPORTED;
       }
@@ -203,6 +209,8 @@ int32_t build_staged(const lego_layout_t* L, StagedProgram* out) {
       d.blk_start[b] = (int8_t)at;
       d.blk_rank[b] = (int8_t)bl.rank;
       d.blk_kind[b] = (int8_t)bl.kind;
+      d.lut_apply[b] = bl.kind == LEGO_BLOCK_LUT ? bl.lut_apply : nullptr;
+      d.lut_inv[b] = bl.kind == LEGO_BLOCK_LUT ? bl.lut_inv : nullptr;
       for (int i = 0; i < bl.rank; ++i) {
         d.dims[at + i] = bl.dims[i];
         const int p = (bl.kind == LEGO_BLOCK_REGP) ? bl.perm[i] : i;

@@ -53,6 +53,8 @@ struct DevStage {
   int8_t blk_start[LEGO_MAX_BLOCKS];
   int8_t blk_rank[LEGO_MAX_BLOCKS];
   int8_t blk_kind[LEGO_MAX_BLOCKS];
+  const int64_t* lut_apply[LEGO_MAX_BLOCKS];  // device tables of LEGO_BLOCK_LUT blocks, else null
+  const int64_t* lut_inv[LEGO_MAX_BLOCKS];
 };
 
 struct StagedProgram {

@@ -55,6 +55,13 @@ __device__ inline int64_t staged_apply(const StagedProgram& sp, int64_t flat) {
         for (int i = 0; i < st.blk_rank[b]; ++i) acc = acc * st.pdims[at + i] + idx[st.gperm[at + i]];
       } else if (st.blk_kind[b] == LEGO_BLOCK_ANTIDIAG) {
         acc = acc * (st.dims[at] * st.dims[at]) + antidiag_apply(st.dims[at], idx[at], idx[at + 1]);
+      } else if (st.blk_kind[b] == LEGO_BLOCK_LUT) {
+        int64_t r = 0, bsz = 1;
+        for (int i = 0; i < st.blk_rank[b]; ++i) {
+          r = r * st.dims[at + i] + idx[at + i];
+          bsz *= st.dims[at + i];
+        }
+        acc = acc * bsz + __ldg(st.lut_apply[b] + r);
       } else {
         acc = acc * (st.dims[at] * st.dims[at + 1]) +
               ((st.dims[at] - 1 - idx[at]) * st.dims[at + 1] + st.dims[at + 1] - 1 - idx[at + 1]);
@@ -85,6 +92,13 @@ __device__ inline int64_t staged_inv(const StagedProgram& sp, int64_t flat) {
       } else {
         if (st.blk_kind[b] == LEGO_BLOCK_ANTIDIAG) {
           antidiag_inv(st.dims[at], v, &idx[at], &idx[at + 1]);
+        } else if (st.blk_kind[b] == LEGO_BLOCK_LUT) {
+          int64_t w = __ldg(st.lut_inv[b] + v);
+          for (int i = r - 1; i > 0; --i) {
+            idx[at + i] = w % st.dims[at + i];
+            w /= st.dims[at + i];
+          }
+          idx[at] = w;
         } else {
           const int64_t w = bsz - 1 - v;
           idx[at] = w / st.dims[at + 1];

@@ -20,8 +20,72 @@ import numpy as np
 __all__ = [
     "Row", "Col", "RegP", "GenP", "OrderBy", "GroupBy",
     "flatten_index", "unflatten_index", "get_sigma_perm", "inverse_permutation",
-    "antidiag", "antidiag_inv",
+    "antidiag", "antidiag_inv", "new_antidiag", "new_antidiag_inv",
+    "get_arange", "divisibility_constraint", "le_constraint", "equal_constraint",
 ]
+
+
+# -- constraint helpers (``lego/lego.py:67-85``) -------------------------------
+#
+# The reference hands these to its simplifier as facts about symbolic sizes.  Sizes here
+# are concrete, so a constraint is a fact that can be checked on the spot: the helpers
+# return a small record, and ``TileBy`` / ``GroupBy`` raise ``ValueError`` when a
+# ``user_constraints`` entry does not hold.
+
+class Constraint:
+    def __init__(self, kind: str, lhs, rhs):
+        self.kind, self.lhs, self.rhs = kind, lhs, rhs
+
+    def holds(self) -> bool:
+        lhs, rhs = int(self.lhs), int(self.rhs)
+        if self.kind == "divisible":
+            return rhs != 0 and lhs % rhs == 0
+        if self.kind == "less":
+            return lhs < rhs
+        return lhs == rhs
+
+    def __repr__(self):
+        op = {"divisible": "%% %s == 0", "less": "< %s", "equal": "== %s"}[self.kind] % (self.rhs,)
+        return f"Constraint({self.lhs} {op})"
+
+
+def divisibility_constraint(lhs, rhs) -> Constraint:
+    """``lhs % rhs == 0`` (``lego/lego.py:76-77``)."""
+    return Constraint("divisible", lhs, rhs)
+
+
+def le_constraint(lhs, rhs) -> Constraint:
+    """``lhs < rhs`` -- strict, like the reference's helper of this name (``lego/lego.py:80-81``)."""
+    return Constraint("less", lhs, rhs)
+
+
+def equal_constraint(lhs, rhs) -> Constraint:
+    """``lhs == rhs`` (``lego/lego.py:84-85``)."""
+    return Constraint("equal", lhs, rhs)
+
+
+def _check_constraints(constraints) -> list:
+    out = list(constraints or ())
+    for c in out:
+        if isinstance(c, Constraint) and not c.holds():
+            raise ValueError(f"user constraint does not hold: {c!r}")
+    return out
+
+
+class Arange:
+    """Placeholder for ``tl.arange(start, stop)`` as a key item of ``layout[...]``
+    (``get_arange``, ``lego/lego.py:67-69``): numerically it is that range of integers,
+    broadcast like a slice at the same key position."""
+
+    def __init__(self, start: int, stop: int):
+        self.start, self.stop = int(start), int(stop)
+
+    def __repr__(self):
+        return f"tl.arange({self.start}, {self.stop})"
+
+
+def get_arange(start, stop) -> Arange:
+    return Arange(start, stop)
 
 
 def _prod(xs: Iterable[int]) -> int:
@@ -143,9 +207,9 @@ class GenP(_Block):
     """General permutation block given by a pair of callables
     (``lego/lego.py:150-178``).  ``f_apply`` takes the index tuple and returns
     the flat id; ``f_inv`` takes a flat id and returns the index tuple.  A
-    ``kind`` tag names the bodies the device evaluator knows (``"antidiag"``,
-    ``"reverse"``); untagged blocks evaluate on the host only and lowering
-    refuses them."""
+    ``kind`` tag names the bodies the device evaluator computes in closed form
+    (``"antidiag"``, ``"reverse"``); any other block is tabulated over its domain when
+    it is lowered and evaluated on the device by table look-up."""
 
     def __init__(self, dims: Sequence[int], f_apply: Callable, f_inv: Callable, kind: str | None = None):
         self._dims = tuple(int(d) for d in dims)
@@ -253,7 +317,7 @@ class GroupBy(_Block):
         self._dims = tuple(int(d) for g in group_dims for d in g)
         self.objects = list(objects)
         self.d = len(group_dims[0])
-        self.user_constraints = list(user_constraints)
+        self.user_constraints = _check_constraints(user_constraints)
 
     def dims(self) -> tuple:
         return self._dims
@@ -301,17 +365,66 @@ class GroupBy(_Block):
         nd = len(self.objects[0].dims()) if self.objects else len(self._dims)
         idx = []
         for pos, item in enumerate(key):
-            if isinstance(item, slice):
+            if isinstance(item, (slice, Arange)):
                 start = 0 if item.start is None else int(item.start)
                 stop = self._dims[pos] if item.stop is None else int(item.stop)
                 shape = [1] * nd
                 shape[pos % nd] = stop - start
                 idx.append(np.arange(start, stop, dtype=np.int64).reshape(shape))
-            elif isinstance(item, str):
-                raise TypeError("symbolic (string) coordinates are not supported: pass integers or arrays")
+            elif isinstance(item, str) or type(item).__module__.startswith("sympy"):
+                return self._symbolic_getitem(key)
             else:
                 idx.append(_as_index(item))
         return self.apply(*idx)
+
+    def _symbolic_getitem(self, key):
+        """The offset as a SymPy expression in the named coordinates, the form the
+        reference returns for printing into kernel text (``lego/lego.py:443-487``).  The
+        dims are concrete, so the closed form comes from the library's constant folding
+        (one ``stride * ((c // div) % mod)`` term per digit, the div / mod dropped where the
+        coordinate's range makes them the identity) instead of a rewrite-rule search.  A
+        string names an integer symbol in ``[0, dim)``; a slice or ``get_arange`` becomes a
+        ``tl.arange(start, stop)`` function term.  Needs SymPy and a layout that folds."""
+        import sympy as sp
+        from .lowering import fold
+        folded = fold(self)
+        if not folded.foldable:
+            raise ValueError("this layout does not reduce to digit strides: no closed-form offset expression")
+        nd = len(self.objects[0].dims()) if self.objects else len(self._dims)
+
+        class TritonRange(sp.Function):
+            """``tl.arange(start, stop)`` laid on broadcast axis ``axis`` of ``nd`` (the
+            reference's placeholder of the same name, ``lego/lego.py:10-64``)."""
+            is_integer = True
+
+            @classmethod
+            def eval(cls, *args):
+                return None
+
+            def _sympystr(self, printer):
+                a, b, axis, total = (int(v) for v in self.args)
+                where = ", ".join(":" if i == axis else "None" for i in range(total))
+                return f"((tl.arange({a}, {b}))[{where}])"
+
+        coords = []
+        for pos, item in enumerate(key):
+            if isinstance(item, str):
+                coords.append(sp.Symbol(item, integer=True, nonnegative=True))
+            elif isinstance(item, (slice, Arange)):
+                start = 0 if item.start is None else int(item.start)
+                stop = self._dims[pos] if item.stop is None else int(item.stop)
+                coords.append(TritonRange(start, stop, pos % nd, nd))
+            else:
+                coords.append(sp.sympify(item))
+        expr = sp.Integer(0)
+        for t in folded.terms:
+            c = coords[t.src]
+            if t.div != 1:
+                c = sp.floor(c / t.div)
+            if t.div * t.mod != self._dims[t.src]:
+                c = sp.Mod(c, t.mod)
+            expr += t.stride * c
+        return expr
 
     def __repr__(self):
         return f"GroupBy(dims={list(self._dims)}, objects={self.objects})"
@@ -330,6 +443,20 @@ def antidiag(n: int, args):
     if isinstance(k, int):
         return upper if k <= n else lower
     return np.where(k <= n, upper, lower)
+
+
+def new_antidiag(n1: int, n2: int, args):
+    """Point reflection of an ``n1 x n2`` grid, ``(n1-1-i) * n2 + (n2-1-j)``
+    (``lego/lego.py:534-535``)."""
+    i, j = (_as_index(a) for a in args)
+    return (n1 - 1 - i) * n2 + (n2 - 1 - j)
+
+
+def new_antidiag_inv(n1: int, n2: int, flat):
+    """Inverse of :func:`new_antidiag` (the reference gives none; the map is an involution
+    on flat ids: ``flat -> n1 * n2 - 1 - flat`` in row-major coordinates)."""
+    w = n1 * n2 - 1 - _as_index(flat)
+    return w // n2, w % n2
 
 
 def antidiag_inv(n: int, flat):

@@ -13,18 +13,87 @@ import ctypes as C
 from dataclasses import dataclass
 from typing import List, Optional
 
+import numpy as np
+
 from . import _abi
-from .layout import GenP, GroupBy, OrderBy, RegP
+from .layout import GenP, GroupBy, OrderBy, RegP, unflatten_index
 
 _GENP_KINDS = {"antidiag": _abi.BLOCK_ANTIDIAG, "reverse": _abi.BLOCK_REVERSE}
 
 
-def lower(layout: GroupBy) -> _abi.Layout:
-    """Serialise a layout.  Raises ValueError for shapes beyond the ABI limits
-    and for GenP blocks whose body the device evaluator does not know."""
+def genp_tables(blk: GenP):
+    """Tabulate a GenP block over its whole domain: ``(apply_table, inv_table)`` as int64
+    arrays of ``prod(dims)`` entries.  ``apply_table[r]`` is ``f_apply`` at the index whose
+    row-major id over ``dims`` is ``r``; it must be a permutation of ``0 .. size-1`` (that is
+    what makes the block a bijection, and what the reference silently assumes,
+    ``lego/lego.py:150-178``).  ``inv_table`` is its inverse; when the block carries an
+    ``f_inv`` it is checked against the table on a sample."""
+    dims = blk.dims()
+    size = 1
+    for d in dims:
+        size *= int(d)
+    if size > _abi.MAX_LUT:
+        raise ValueError(f"GenP block of {size} entries is beyond the table limit of {_abi.MAX_LUT}; "
+                         "give it a `kind` the device evaluator computes in closed form")
+    ids = np.arange(size, dtype=np.int64)
+    idx = unflatten_index(ids, dims)
+    try:
+        table = np.asarray(blk.f_apply(tuple(idx)), dtype=np.int64)
+        if table.shape != (size,):
+            raise TypeError
+    except Exception:  # the callable is scalar-only (SymPy Piecewise, Python branches): one id at a time
+        table = np.fromiter((int(blk.f_apply(tuple(int(c[i]) for c in idx))) for i in range(size)),
+                            dtype=np.int64, count=size)
+    inv = np.full(size, -1, dtype=np.int64)
+    ok = (table >= 0) & (table < size)
+    if not ok.all():
+        raise ValueError("GenP f_apply leaves the block's index range: not a permutation")
+    inv[table] = ids
+    if (inv < 0).any():
+        raise ValueError("GenP f_apply is not a bijection over the block's dims")
+    if blk.f_inv is not None:
+        probe = np.unique(np.linspace(0, size - 1, num=min(size, 257)).astype(np.int64))
+        for f in probe:
+            got = tuple(int(v) for v in blk.f_inv(int(f)))
+            want = tuple(int(c[inv[f]]) for c in idx)
+            if got != want:
+                raise ValueError(f"GenP f_inv({int(f)}) = {got} disagrees with f_apply, whose inverse there is {want}")
+    return table, inv
+
+
+def _device_tables(blk: GenP):
+    """The block's tables on the current CUDA device (kept on the block, per device)."""
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("lego_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+    dev = torch.cuda.current_device()
+    cache = blk.__dict__.setdefault("_tables", {})
+    if dev not in cache:
+        host = blk.__dict__.get("_host_tables")
+        if host is None:
+            host = blk.__dict__["_host_tables"] = genp_tables(blk)
+        cache[dev] = tuple(torch.from_numpy(t).to(torch.device("cuda", dev)) for t in host)
+    return cache[dev]
+
+
+def lower(layout: GroupBy, host_only: bool = False) -> _abi.Layout:
+    """Serialise a layout.  Raises ValueError for shapes beyond the ABI limits.  A GenP block
+    with a known ``kind`` lowers to its closed form; any other GenP is tabulated on the host
+    once and lowers to a pair of device tables (``LEGO_BLOCK_LUT``).  ``host_only`` is for the
+    host services (validation, folding), which never read a table: the descriptor then points
+    at the host copies and must not reach a kernel."""
     if not isinstance(layout, GroupBy):
         raise TypeError(f"expected a GroupBy layout (from .TileBy/.GroupBy), got {type(layout).__name__}")
-    cached = getattr(layout, "_lowered", None)
+    uses_tables = any(isinstance(b, GenP) and b.kind not in _GENP_KINDS for o in layout.objects for b in o.perms)
+    key = "_lowered"
+    if uses_tables and host_only:
+        key = "_lowered_host"
+    elif uses_tables:
+        import torch
+        if not torch.cuda.is_available():
+            raise RuntimeError("lego_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+        key = f"_lowered_dev{torch.cuda.current_device()}"
+    cached = layout.__dict__.get(key)
     if cached is not None:
         return cached
     dims = layout.dims()
@@ -58,17 +127,24 @@ def lower(layout: GroupBy) -> _abi.Layout:
                 for i, p in enumerate(blk.permutation):
                     dst.perm[i] = int(p)
             elif isinstance(blk, GenP):
-                if blk.kind not in _GENP_KINDS:
-                    raise ValueError(
-                        "GenP block without a known `kind` cannot be lowered: the device evaluator "
-                        f"knows {sorted(_GENP_KINDS)}")
-                dst.kind = _GENP_KINDS[blk.kind]
                 for i in range(len(bd)):
                     dst.perm[i] = i
+                if blk.kind in _GENP_KINDS:
+                    dst.kind = _GENP_KINDS[blk.kind]
+                else:
+                    dst.kind = _abi.BLOCK_LUT
+                    if host_only:
+                        host = blk.__dict__.get("_host_tables")
+                        if host is None:
+                            host = blk.__dict__["_host_tables"] = genp_tables(blk)
+                        dst.lut_apply, dst.lut_inv = host[0].ctypes.data, host[1].ctypes.data
+                    else:
+                        t_apply, t_inv = _device_tables(blk)
+                        dst.lut_apply, dst.lut_inv = t_apply.data_ptr(), t_inv.data_ptr()
             else:
                 raise TypeError(f"unknown permutation block {type(blk).__name__}")
     _abi.check(_abi.lib().lego_layout_check(C.byref(out)), "lego_layout_check")
-    layout._lowered = out
+    layout.__dict__[key] = out
     return out
 
 
@@ -94,7 +170,7 @@ class FoldedLayout:
 def fold(layout: GroupBy) -> FoldedLayout:
     """The library's constant-folded form of a layout:
     ``flat = sum_j ((idx[src_j] // div_j) % mod_j) * stride_j``."""
-    desc = lower(layout)
+    desc = lower(layout, host_only=True)
     raw = _abi.Folded()
     _abi.check(_abi.lib().lego_layout_fold(C.byref(desc), C.byref(raw)), "lego_layout_fold")
     terms = [FoldedTerm(t.src, t.div, t.mod, t.stride) for t in raw.terms[:raw.n_terms]]

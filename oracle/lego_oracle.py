@@ -31,16 +31,18 @@ import numpy as np
 def spec_of(layout) -> dict:
     """Plain spec of a layout object that exposes the reference's attributes
     (``.objects`` -> OrderBy with ``.perms``; a perm has ``.dims()`` and either
-    ``.permutation`` (RegP / Row / Col) or ``.kind`` (a named GenP body or ``"lut"``
-    with its tables).  Structure only: no arithmetic of the object is used."""
+    ``.permutation`` (RegP / Row / Col), ``.kind`` (a named GenP body) or, for a GenP
+    given only by callables, the user's ``f_apply`` itself.  Structure only: no arithmetic
+    of the layout object is used."""
     objects = []
     for o in layout.objects:
         stage = []
         for p in o.perms:
             if hasattr(p, "permutation"):
                 stage.append({"kind": "regp", "dims": list(p.dims()), "perm": list(p.permutation)})
-            elif getattr(p, "kind", None) == "lut":
-                stage.append({"kind": "lut", "dims": list(p.dims()), "table": list(p.table)})
+            elif getattr(p, "kind", None) is None and hasattr(p, "f_apply"):
+                # a GenP given only by the user's callables: the oracle calls them itself
+                stage.append({"kind": "callable", "dims": list(p.dims()), "f_apply": p.f_apply})
             else:
                 stage.append({"kind": p.kind, "dims": list(p.dims())})
         objects.append(stage)
@@ -110,6 +112,25 @@ def _reverse(n1, n2, idx):
     return (n1 - 1 - i) * n2 + n2 - 1 - j
 
 
+def _callable_table(block):
+    """GenP.apply, lego/lego.py:168-171, for an arbitrary user callable: f_apply at every
+    index of the block, one scalar call at a time, in row-major order of the block's dims."""
+    if "_table" not in block:
+        dims = [int(d) for d in block["dims"]]
+        size = 1
+        for d in dims:
+            size *= d
+        table = np.empty(size, dtype=np.int64)
+        for r in range(size):
+            idx, rest = [], r
+            for d in reversed(dims):
+                idx.append(rest % d)
+                rest //= d
+            table[r] = int(block["f_apply"](tuple(reversed(idx))))
+        block["_table"] = table
+    return block["_table"]
+
+
 def block_apply(block, idx):
     """RegP.apply, lego/lego.py:215-218 (GenP.apply :168-171 for the two bodies
     the reference ships)."""
@@ -123,6 +144,8 @@ def block_apply(block, idx):
         return _antidiag(dims[0], idx)
     if kind == "reverse":
         return _reverse(dims[0], dims[1], idx)
+    if kind == "callable":
+        return _callable_table(block)[flatten_index(list(idx), dims)]
     raise ValueError(kind)
 
 
@@ -144,6 +167,13 @@ def block_inv(block, flat):
         table[_antidiag(n, (ii.ravel(), jj.ravel()))] = np.arange(n * n)
         cell = table[np.asarray(flat, dtype=np.int64)]
         return (cell // n, cell % n)
+    if kind == "callable":
+        # GenP.inv, lego/lego.py:173-174, is the user's f_inv; the oracle inverts f_apply by
+        # brute force instead, which also holds a wrong f_inv to account
+        fwd = _callable_table(block)
+        back = np.empty_like(fwd)
+        back[fwd] = np.arange(fwd.size)
+        return unflatten_index(back[np.asarray(flat, dtype=np.int64)], dims)
     raise ValueError(kind)
 
 

@@ -14,9 +14,13 @@ run on, so its outputs are frozen here:
   kernels (the same text as ``triton_generated/**``), generated symbolically,
   with concrete values at which the tests evaluate them.
 
+* ``c_strings``: the expressions ``LEGOCCodePrinter`` prints into the CUDA benchmark
+  programs (brick offsets, the anti-diagonal GenP with symbolic n).
+
 The layout source strings use only names that exist both in the reference's
-``lego.lego`` and in ``lego_b200`` (Row, Col, RegP, OrderBy), so the tests
-rebuild the same layout with the product's classes.
+``lego.lego`` and in ``lego_b200`` (Row, Col, RegP, GenP, OrderBy, antidiag,
+antidiag_inv, new_antidiag), so the tests rebuild the same layout with the
+product's classes.
 """
 from __future__ import annotations
 
@@ -77,24 +81,48 @@ LAYOUTS = {
     "regp_3": "OrderBy(RegP([3,4,5],[1,2,0])).GroupBy([(3,4,5)])",
     "two_blocks_regp": "OrderBy(RegP([3,4],[1,0]),RegP([5,2],[0,1])).GroupBy([(12,10)])",
     "single": "OrderBy(Row(1)).TileBy([1])",
+    # --- 3-D bricks (benchmarks/cuda/bricks_f3d.py:10-13; bricks_laplasian.py uses the same two)
+    "bricks_normal_384": "OrderBy(Row(384,384,384)).TileBy([48,48,48],[8,8,8])",
+    "bricks_384": "OrderBy(Row(48,48,48),Row(8,8,8)).TileBy([48,48,48],[8,8,8])",
+    # --- GenP blocks (lego/lego.py:150-178 with the bodies of :490-535; benchmarks/cuda/nw_sympy.py:9-11)
+    "genp_antidiag_8": "OrderBy(GenP([8,8], lambda x: antidiag(8,x), lambda f: antidiag_inv(8,f))).TileBy((8,8))",
+    "genp_antidiag_33": "OrderBy(GenP([33,33], lambda x: antidiag(33,x), lambda f: antidiag_inv(33,f))).TileBy((33,33))",
+    "genp_reverse_6x10": ("OrderBy(GenP([6,10], lambda x: new_antidiag(6,10,x), "
+                          "lambda f: ((59-f)//10, (59-f)%10))).TileBy((6,10))"),
+    "genp_mixed_3x5x5": ("OrderBy(Row(3), GenP([5,5], lambda x: antidiag(5,x), lambda f: antidiag_inv(5,f)))"
+                         ".GroupBy([(3,5,5)])"),
+    "genp_tiled_antidiag": ("OrderBy(Row(2,3), GenP([4,4], lambda x: antidiag(4,x), lambda f: antidiag_inv(4,f)))"
+                            ".TileBy([2,3],[4,4])"),
+    "genp_xor_4x8": ("OrderBy(GenP([4,8], lambda x: (x[0]*8 + x[1]) ^ 5, lambda f: ((f ^ 5)//8, (f ^ 5)%8)))"
+                     ".TileBy((4,8))"),
 }
+
+# which closed form a GenP layout's block is (for the spec the oracle reads); anything else
+# is recorded by the source of its f_apply
+GENP_KIND = {"genp_antidiag_8": "antidiag", "genp_antidiag_33": "antidiag", "genp_reverse_6x10": "reverse",
+             "genp_mixed_3x5x5": "antidiag", "genp_tiled_antidiag": "antidiag"}
+GENP_SRC = {"genp_xor_4x8": "lambda x: (x[0]*8 + x[1]) ^ 5"}
 
 MAX_FULL = 4096
 N_APPLY = 1536
 N_INV = 192
 
 
-def block_spec(p):
+def block_spec(p, name):
     dims = [int(d) for d in p.dims()]
+    if isinstance(p, R.GenP):
+        if name in GENP_KIND:
+            return {"kind": GENP_KIND[name], "dims": dims}
+        return {"kind": "callable", "dims": dims, "f_apply_src": GENP_SRC[name]}
     if not isinstance(p, R.RegP):
-        raise TypeError("only RegP blocks are serialised here")
+        raise TypeError("unknown permutation block")
     perm = [int(v) for v in p.perm(list(range(len(dims))))]  # the permutation lives in a closure
     return {"kind": "regp", "dims": dims, "perm": perm}
 
 
-def layout_spec(layout):
+def layout_spec(layout, name):
     return {"dims": [int(d) for d in layout.dims()],
-            "objects": [[block_spec(p) for p in o.perms] for o in layout.objects]}
+            "objects": [[block_spec(p, name) for p in o.perms] for o in layout.objects]}
 
 
 def unravel(flat, dims):
@@ -106,7 +134,8 @@ def unravel(flat, dims):
 
 
 def sample_layout(name, src, rng):
-    layout = eval(src, {k: getattr(R, k) for k in ("Row", "Col", "RegP", "OrderBy")})
+    layout = eval(src, {k: getattr(R, k) for k in ("Row", "Col", "RegP", "GenP", "OrderBy", "antidiag",
+                                                   "antidiag_inv", "new_antidiag")})
     dims = [int(d) for d in layout.dims()]
     size = 1
     for d in dims:
@@ -119,7 +148,7 @@ def sample_layout(name, src, rng):
     inv_flat = ids if size <= N_INV else sorted(set([0, size - 1] + [rng.randrange(size) for _ in range(N_INV)]))
     inv = [[int(v) for v in layout.inv(f)] for f in inv_flat]
     print(f"  {name}: dims={dims} apply@{len(ids)} inv@{len(inv_flat)}", flush=True)
-    return {"src": src, "dims": dims, "spec": layout_spec(layout), "ids": ids, "apply": applied,
+    return {"src": src, "dims": dims, "spec": layout_spec(layout, name), "ids": ids, "apply": applied,
             "inv_flat": inv_flat, "inv": inv}
 
 
@@ -202,6 +231,35 @@ def golden_strings():
     return out
 
 
+def golden_c_strings():
+    """Index expressions as LEGOCCodePrinter (lego/lego_c.py:9-38) prints them into the CUDA
+    benchmark programs: the brick offsets of benchmarks/cuda/bricks_f3d.py:10-21 (the text of
+    benchmarks/cuda/bricks/main.cu:48,56-57,91,99-100) and the anti-diagonal GenP of
+    benchmarks/cuda/nw_sympy.py:9-11 with a symbolic n."""
+    from lego.lego_c import LEGOCCodePrinter
+    pr = LEGOCCodePrinter()
+    out = {}
+    i, j, k, i_diff, j_diff, k_diff, bx, by, bz = sp.symbols("i j k i_diff j_diff k_diff bx by bz",
+                                                             integer=True, positive=True)
+    N, B = 384, 8
+    normal = R.OrderBy(R.Row(N, N, N)).TileBy([N // B] * 3, [B] * 3)
+    bricks = R.OrderBy(R.Row(N // B, N // B, N // B), R.Row(B, B, B)).TileBy([N // B] * 3, [B] * 3)
+    out["bricks_normal_out"] = {"text": pr.doprint(sp.simplify(normal[bx, by, bz, i, j, k])),
+                                "layout": "bricks_normal_384", "key": ["bx", "by", "bz", "i", "j", "k"]}
+    out["bricks_out"] = {"text": pr.doprint(sp.simplify(bricks[bx, by, bz, i, j, k])),
+                         "layout": "bricks_384", "key": ["bx", "by", "bz", "i", "j", "k"]}
+    out["bricks_normal_in"] = {
+        "text": pr.doprint(sp.simplify(normal[bx, by, bz, i + i_diff, j + j_diff, k + k_diff])),
+        "layout": "bricks_normal_384", "key": ["bx", "by", "bz", "i+i_diff", "j+j_diff", "k+k_diff"]}
+    out["bricks_in"] = {
+        "text": pr.doprint(sp.simplify(bricks[bx, by, bz, i + i_diff, j + j_diff, k + k_diff])),
+        "layout": "bricks_384", "key": ["bx", "by", "bz", "i+i_diff", "j+j_diff", "k+k_diff"]}
+    n, ii, jj = sp.symbols("n i j", integer=True, postive=True)
+    anti = R.OrderBy(R.GenP([n, n], lambda x: R.antidiag(n, x), None)).TileBy((n, n))
+    out["nw_antidiag"] = {"text": pr.doprint(sp.simplify(anti[ii, jj])), "genp": "antidiag", "key": ["i", "j"]}
+    return out
+
+
 def main():
     rng = random.Random(20240607)
     print("sampling layouts through the reference ...", flush=True)
@@ -210,10 +268,13 @@ def main():
     strings = golden_strings()
     for k_, v in strings.items():
         print(f"  {k_}: {v['text']}")
+    c_strings = golden_c_strings()
+    for k_, v in c_strings.items():
+        print(f"  {k_}: {v['text']}")
     path = os.path.join(HERE, "layouts.json")
     with open(path, "w") as f:
         json.dump({"reference": "tavakkoliamirmohammad/LEGO", "sympy": sp.__version__,
-                   "layouts": layouts, "strings": strings}, f, separators=(",", ":"))
+                   "layouts": layouts, "strings": strings, "c_strings": c_strings}, f, separators=(",", ":"))
     print("wrote", path, os.path.getsize(path), "bytes")
 
 

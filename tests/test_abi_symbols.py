@@ -29,7 +29,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 def test_struct_sizes_match_the_header():
     # lego_block_t: 2 x int32 + 12 x int64 + 12 x int32
-    assert ctypes.sizeof(_abi.Block) == 8 + 96 + 48
+    assert ctypes.sizeof(_abi.Block) == 8 + 96 + 48 + 16
     assert ctypes.sizeof(_abi.Stage) == 8 + 4 * ctypes.sizeof(_abi.Block)
     assert ctypes.sizeof(_abi.Layout) == 8 + 96 + 8 * ctypes.sizeof(_abi.Stage)
     assert ctypes.sizeof(_abi.Term) == 32

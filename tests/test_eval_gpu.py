@@ -5,17 +5,21 @@ import torch
 
 import lego_b200 as L
 from lego_b200 import ops
-from helpers import build_layout, spec_of, unravel
+from helpers import build_layout, genp_kind_of, golden_spec, spec_of, unravel
 from oracle import lego_oracle as O
 
 pytestmark = pytest.mark.gpu
 
 
 def test_range_apply_inv_for_every_golden_layout(golden):
+    cases = []
     for name, g in golden["layouts"].items():
-        lay = build_layout(g["src"])
+        cases.append((name, g, build_layout(g["src"])))                 # GenP blocks as look-up tables
+        if genp_kind_of(g):
+            cases.append((name + " (closed form)", g, build_layout(g["src"], genp_kind=genp_kind_of(g))))
+    for name, g, lay in cases:
         size = lay.size()
-        spec = g["spec"]
+        spec = golden_spec(g)
         # golden vectors of the reference itself
         ids = torch.tensor(g["ids"], dtype=torch.int64)
         idx = torch.stack([torch.from_numpy(v) for v in unravel(g["ids"], g["dims"])], dim=1).contiguous()

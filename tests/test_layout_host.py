@@ -7,7 +7,8 @@ import pytest
 import lego_b200 as L
 from lego_b200 import ops
 from lego_b200.lowering import fold, lower
-from helpers import build_layout, eval_reference_string, spec_of, unravel
+from helpers import (build_layout, eval_c_string, eval_reference_string, genp_kind_of, golden_spec, same_structure,
+                     spec_of, unravel)
 from oracle import lego_oracle as O
 
 
@@ -15,7 +16,7 @@ def test_apply_and_inv_match_reference(golden):
     for name, g in golden["layouts"].items():
         lay = build_layout(g["src"])
         assert list(lay.dims()) == g["dims"], name
-        assert spec_of(lay) == g["spec"], name
+        assert same_structure(spec_of(lay), g["spec"]), name
         got = lay.apply(*unravel(g["ids"], g["dims"]))
         assert np.array_equal(np.broadcast_to(got, (len(g["ids"]),)), np.asarray(g["apply"])), name
         inv = lay.inv(np.asarray(g["inv_flat"], dtype=np.int64))
@@ -45,8 +46,9 @@ def test_fold_matches_reference(golden):
         for k in range(len(g["dims"])):
             back = sum(((flat // t.stride) % t.mod) * t.div for t in f.terms if t.src == k)
             assert np.array_equal(np.broadcast_to(back, idx[k].shape), idx[k]), (name, k)
-    # cuts that no digit split can realise stay on the staged interpreter
-    assert staged == {"misaligned_col", "misaligned_row", "misaligned_two"}
+    # cuts that no digit split can realise, and GenP blocks, stay on the staged interpreter
+    assert staged == {"misaligned_col", "misaligned_row", "misaligned_two"} | {n for n in golden["layouts"]
+                                                                             if n.startswith("genp_")}
 
 
 def test_fold_examples():
@@ -115,10 +117,66 @@ def test_errors_follow_the_reference():
     # the grouped swizzle for 10 tile rows in groups of 8 is not a bijection: rejected at lowering
     with pytest.raises(ValueError, match="bijection"):
         lower(ops.grouped_swizzle_layout(10, 4, 8))
-    with pytest.raises(ValueError):
-        lower(L.OrderBy(L.GenP((4, 4), lambda i: i[0] * 4 + i[1], lambda f: (f // 4, f % 4))).GroupBy([(4, 4)]))
-    with pytest.raises(TypeError):
-        lay["bi", 0, 0, 0]
+
+
+def test_genp_tables_constraints_and_symbolic_offsets(golden):
+    from lego_b200.lowering import genp_tables
+    # an arbitrary callable is tabulated over its domain; the table must be a permutation
+    xor = L.GenP((4, 8), lambda x: (x[0] * 8 + x[1]) ^ 5, lambda f: ((f ^ 5) // 8, (f ^ 5) % 8))
+    fwd, back = genp_tables(xor)
+    assert np.array_equal(fwd, np.arange(32) ^ 5) and np.array_equal(fwd[back], np.arange(32))
+    g = golden["layouts"]["genp_xor_4x8"]
+    assert np.array_equal(fwd[np.asarray(g["ids"])], np.asarray(g["apply"]))     # the reference ran the same callable
+    scalar_only = L.GenP((3, 3), lambda x: int(x[0]) * 3 + (int(x[1]) + 1) % 3, None)   # int() refuses arrays
+    assert sorted(genp_tables(scalar_only)[0].tolist()) == list(range(9))
+    with pytest.raises(ValueError, match="bijection"):
+        genp_tables(L.GenP((4, 4), lambda x: x[0] * 4, None))
+    with pytest.raises(ValueError, match="index range"):
+        genp_tables(L.GenP((4, 4), lambda x: x[0] * 4 + x[1] + 1, None))
+    with pytest.raises(ValueError, match="disagrees"):
+        genp_tables(L.GenP((4, 4), lambda x: x[0] * 4 + x[1], lambda f: (f % 4, f // 4)))
+    with pytest.raises(ValueError, match="table limit"):
+        genp_tables(L.GenP((1 << 13, 1 << 12), lambda x: x[0], None))
+    # user constraints on concrete sizes are facts to check (lego/lego.py:76-85)
+    lay = L.OrderBy(L.Row(24, 512)).TileBy([24, 4], [1, 128], user_constraints=[L.divisibility_constraint(512, 128),
+                                                                              L.le_constraint(1, 24),
+                                                                              L.equal_constraint(4 * 128, 512)])
+    assert len(lay.user_constraints) == 3
+    for bad in (L.divisibility_constraint(500, 128), L.le_constraint(24, 24), L.equal_constraint(3, 4)):
+        with pytest.raises(ValueError, match="constraint"):
+            L.OrderBy(L.Row(24, 512)).TileBy([24, 4], [1, 128], user_constraints=[bad])
+    # get_arange is a slice with explicit bounds
+    assert np.array_equal(lay[3, 1, 0, L.get_arange(0, 128)], lay[3, 1, 0, :])
+    # string coordinates give the closed-form expression the reference prints
+    sp = pytest.importorskip("sympy")
+    t = L.OrderBy(L.Row(4096, 4096)).TileBy([128, 128], [32, 32])
+    e = t["bi", "bj", :, :]
+    assert str(e) == "131072*bi + 32*bj + 4096*((tl.arange(0, 32))[:, None]) + ((tl.arange(0, 32))[None, :])"
+    sw = ops.grouped_swizzle_layout(64, 32, 8)
+    pm, pn = sp.symbols("pm pn", integer=True, nonnegative=True)
+    f = sp.lambdify((pm, pn), sw["pm", "pn"], "numpy")
+    a, b = np.indices((64, 32))
+    assert np.array_equal(f(a, b), sw.apply(a, b))
+    br = golden["c_strings"]["bricks_out"]
+    bl = build_layout(golden["layouts"]["bricks_384"]["src"])
+    assert str(bl["bx", "by", "bz", "i", "j", "k"]).replace(" ", "") == br["text"].replace(" ", "")
+    with pytest.raises(ValueError, match="closed-form"):
+        L.OrderBy(L.Col(3, 2)).GroupBy([(2, 3)])["a", "b"]
+
+
+def test_c_printer_strings_match_the_layouts(golden):
+    cs = golden["c_strings"]
+    rng = np.random.default_rng(4)
+    bx, by, bz = (rng.integers(0, 48, 512) for _ in range(3))
+    i, j, k = (rng.integers(0, 8, 512) for _ in range(3))
+    env = dict(bx=bx, by=by, bz=bz, i=i, j=j, k=k)
+    for name in ("bricks_normal_out", "bricks_out"):
+        lay = build_layout(golden["layouts"][cs[name]["layout"]]["src"])
+        assert np.array_equal(eval_c_string(cs[name]["text"], env), lay.apply(bx, by, bz, i, j, k)), name
+    n = 11
+    ii, jj = np.indices((n, n))
+    got = eval_c_string(cs["nw_antidiag"]["text"], dict(n=n, i=ii.ravel(), j=jj.ravel()))
+    assert np.array_equal(got, L.antidiag(n, (ii.ravel(), jj.ravel())))
 
 
 def test_genp_bodies_round_trip():

@@ -3,7 +3,7 @@ reference itself (tests/golden/layouts.json, made by tests/golden/make_golden.py
 import numpy as np
 import pytest
 
-from helpers import eval_reference_string, unravel
+from helpers import eval_c_string, eval_reference_string, golden_spec, unravel
 from oracle import lego_oracle as O
 
 
@@ -16,13 +16,13 @@ def test_golden_file_is_complete(golden):
 def test_apply_matches_reference(golden):
     for name, g in golden["layouts"].items():
         idx = unravel(g["ids"], g["dims"])
-        got = O.groupby_apply(g["spec"], idx)
+        got = O.groupby_apply(golden_spec(g), idx)
         assert np.array_equal(got, np.asarray(g["apply"], dtype=np.int64)), name
 
 
 def test_inv_matches_reference(golden):
     for name, g in golden["layouts"].items():
-        got = O.groupby_inv(g["spec"], np.asarray(g["inv_flat"], dtype=np.int64))
+        got = O.groupby_inv(golden_spec(g), np.asarray(g["inv_flat"], dtype=np.int64))
         exp = np.asarray(g["inv"], dtype=np.int64).reshape(len(g["inv_flat"]), len(g["dims"]))
         for k in range(len(g["dims"])):
             assert np.array_equal(np.broadcast_to(got[k], exp[:, k].shape), exp[:, k]), (name, k)
@@ -33,12 +33,47 @@ def test_apply_is_a_bijection_where_the_reference_is(golden):
         size = int(np.prod(g["dims"]))
         if size > 1 << 16:
             continue
-        full = O.groupby_apply_all(g["spec"])
+        full = O.groupby_apply_all(golden_spec(g))
         assert np.array_equal(np.sort(full), np.arange(size)), name
-        back = O.groupby_inv(g["spec"], full)
+        back = O.groupby_inv(golden_spec(g), full)
         idx = unravel(np.arange(size), g["dims"])
         for k in range(len(g["dims"])):
             assert np.array_equal(back[k], idx[k]), (name, k)
+
+
+def test_genp_and_brick_layouts_are_pinned(golden):
+    names = set(golden["layouts"])
+    assert {"genp_antidiag_8", "genp_antidiag_33", "genp_reverse_6x10", "genp_mixed_3x5x5", "genp_tiled_antidiag",
+            "genp_xor_4x8", "bricks_normal_384", "bricks_384"} <= names
+    # the whole domain of the small GenP layouts was recorded, so the oracle's bodies are pinned everywhere
+    for name in ("genp_antidiag_8", "genp_antidiag_33", "genp_reverse_6x10", "genp_xor_4x8"):
+        g = golden["layouts"][name]
+        assert g["ids"] == list(range(int(np.prod(g["dims"])))), name
+
+
+def test_c_printer_strings(golden):
+    """The expressions LEGOCCodePrinter prints into the CUDA programs, evaluated as C would,
+    against the oracle: brick offsets (with and without the stencil displacement) and the
+    anti-diagonal GenP with a symbolic n."""
+    cs = golden["c_strings"]
+    rng = np.random.default_rng(3)
+    m = 4096
+    bx, by, bz = (rng.integers(0, 48, m) for _ in range(3))
+    i, j, k = (rng.integers(2, 6, m) for _ in range(3))
+    di, dj, dk = (rng.integers(-2, 3, m) for _ in range(3))
+    env = dict(bx=bx, by=by, bz=bz, i=i, j=j, k=k, i_diff=di, j_diff=dj, k_diff=dk)
+    for name, shifted in (("bricks_normal_out", False), ("bricks_out", False), ("bricks_normal_in", True),
+                          ("bricks_in", True)):
+        spec = golden_spec(golden["layouts"][cs[name]["layout"]])
+        idx = [bx, by, bz, i + di, j + dj, k + dk] if shifted else [bx, by, bz, i, j, k]
+        assert np.array_equal(eval_c_string(cs[name]["text"], env), O.groupby_apply(spec, idx)), name
+    for n in (1, 2, 7, 64):
+        ii, jj = np.indices((n, n))
+        got = eval_c_string(cs["nw_antidiag"]["text"], dict(n=n, i=ii.ravel(), j=jj.ravel()))
+        spec = {"dims": [n, n], "objects": [[{"kind": "antidiag", "dims": [n, n]}],
+                                            [{"kind": "regp", "dims": [n, n], "perm": [0, 1]}],
+                                            [{"kind": "regp", "dims": [n, n], "perm": [0, 1]}]]}
+        assert np.array_equal(got, O.groupby_apply(spec, [ii.ravel(), jj.ravel()])), n
 
 
 def test_swizzle_string(golden):
