@@ -372,6 +372,70 @@ class Transpose(Workload):
                 "d2d_copy": _copy_comparator(self.ins[0], self.sets)}
 
 
+class Bricks(Workload):
+    """The reference's brick re-layout (benchmarks/cuda/bricks_f3d.py:10-13): a 384^3 fp32 volume from
+    row-major order into 8^3 bricks, one permute call.  Ranks split the slowest axis."""
+    name = "bricks_relayout_f32_384"
+    short = "bricks"
+    dtype = "f32"
+    n, b = 384, 8
+
+    def work(self):
+        return 2.0 * self.n ** 3 * 4
+
+    def setup(self, dev, rank, world):
+        import lego_b200 as L
+        from lego_b200 import ops
+        self.ops = ops
+        self.rank, self.world = rank, world
+        n, b = self.n, self.b
+        self.r0, self.r1 = shard.split_range(n, rank, world, b)
+        m = self.r1 - self.r0                                  # this rank's slab of planes is a volume of its own
+        self.x_host = torch.rand(n, n, n, generator=torch.Generator().manual_seed(8))
+        self.src = L.OrderBy(L.Row(m, n, n)).TileBy([m // b, n // b, n // b], [b, b, b])
+        self.dst = L.OrderBy(L.Row(m // b, n // b, n // b), L.Row(b, b, b)).TileBy([m // b, n // b, n // b], [b, b, b])
+        self.sets = self.n_sets(2 * m * n * n * 4)
+        self.ins = [self.x_host[self.r0:self.r1].to(dev) for _ in range(self.sets)]
+        self.outs = [torch.empty_like(self.ins[0]) for _ in range(self.sets)]
+
+    def step(self, i):
+        k = i % self.sets
+        self.ops.permute(self.ins[k], self.src, self.dst, out=self.outs[k])
+
+    def shard_result(self):
+        return self.outs[0]
+
+    def check(self, full):
+        n, b = self.n, self.b
+        want = self.x_host.reshape(n // b, b, n // b, b, n // b, b).permute(0, 2, 4, 1, 3, 5).contiguous()
+        ok = torch.equal(full.cpu().reshape(-1), want.reshape(-1))
+        return ok, "bit-exact vs reshape(48,8,48,8,48,8).permute(0,2,4,1,3,5)"
+
+    def e2e_setup(self):
+        self.xp = self.x_host[self.r0:self.r1].contiguous().pin_memory()
+        return self.xp.numel() * 4, self.xp.numel() * 4
+
+    def e2e_step(self, i):
+        return self.ops.permute(self.xp, self.src, self.dst)
+
+    def cpu_pass(self):
+        from oracle import lego_oracle as O
+        import lego_b200 as L
+        n, b = self.n, self.b
+        src = L.OrderBy(L.Row(n, n, n)).TileBy([n // b] * 3, [b] * 3)
+        dst = L.OrderBy(L.Row(n // b, n // b, n // b), L.Row(b, b, b)).TileBy([n // b] * 3, [b] * 3)
+        x = self.x_host.reshape(-1).numpy()
+        dt = _timed(lambda: O.permute(x, O.spec_of(src), O.spec_of(dst)))
+        return self.work(), dt, "numpy index maps of both layouts over 384^3 ids + gather/scatter (single thread)"
+
+    def comparators(self):
+        n, b = self.n, self.b
+
+        def torch_relayout(i):
+            return self.ins[i % self.sets].reshape(n // b, b, n // b, b, n // b, b).permute(0, 2, 4, 1, 3, 5).contiguous()
+        return {"reshape.permute.contiguous": torch_relayout, "d2d_copy": _copy_comparator(self.ins[0], self.sets)}
+
+
 class Gemm(Workload):
     name = "gemm_f16_8192"
     unit = "TFLOP/s"
@@ -562,7 +626,7 @@ class IndexMap(Workload):
 
 
 WORKLOADS = {"softmax": Softmax, "layernorm": LayerNorm, "layernorm_bwd": LayerNormBwd, "transpose": Transpose,
-             "gemm": Gemm, "gemm_e5m2": GemmE5M2, "grouped_gemm": GroupedGemm, "index_map": IndexMap}
+             "gemm": Gemm, "gemm_e5m2": GemmE5M2, "grouped_gemm": GroupedGemm, "index_map": IndexMap, "bricks": Bricks}
 
 
 # --------------------------------------------------------------------------------------
@@ -888,6 +952,8 @@ def _cpu_setup(w):
         w.dy_host = (0.1 * torch.randn(w.rows, w.cols, generator=torch.Generator().manual_seed(22))).half()
     elif isinstance(w, LayerNorm):
         w.x_host, w.g_host, w.b_host = inputs.layernorm_input(w.rows, w.cols)
+    elif isinstance(w, Bricks):
+        w.x_host = torch.rand(w.n, w.n, w.n, generator=torch.Generator().manual_seed(8))
     elif isinstance(w, Transpose):
         n, nt = w.n, w.n // 32
         w.a_host = inputs.transpose_input(n)

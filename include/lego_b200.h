@@ -121,7 +121,9 @@ int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out);
 
 /* Plan of a permute call, for inspection: which kernel lego_permute would pick
  * (0 staged interpreter, 1 output-order gather, 2 shared-memory tiled transpose,
- * 3 TMA-fed tiled transpose) and its tile extents.             */
+ * 3 TMA-fed tiled transpose, 4 chunk-tiled permute for layouts that share a
+ * contiguous run, e.g. a volume into bricks) and the contiguous extents it reads
+ * and writes, in elements.                                                     */
 int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
                           const lego_layout_t* tile_order, int32_t* kernel_kind, int64_t* tile_in,
                           int64_t* tile_out);
@@ -257,8 +259,10 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *                           workspace is given and the tile count is not a multiple of the
  *                           resident SM pairs
  *   LEGO_TUNE_GEMM_LAG      0..4 k-steps by which the first accumulator block of a 512 x 256
- *                           tile leads the second at both ends of the tile (epilogue overlap) */
-enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3 };
+ *                           tile leads the second at both ends of the tile (epilogue overlap)
+ *   LEGO_TUNE_LNBWD_SPLIT   LayerNorm backward: rows wider than this many columns are taken by
+ *                           one group of 512 threads, narrower ones by several groups          */
+enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

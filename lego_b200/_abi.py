@@ -94,6 +94,7 @@ SIGNATURES = {
     "lego_grouped_gemm_f16_static": (C.c_int32, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                                  C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int32,
                                                  C.POINTER(LayoutP), C.c_void_p, C.c_void_p]),
+    "lego_copy_2d": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "lego_device_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "lego_status_string": (C.c_char_p, [C.c_int32]),
     "lego_shutdown": (C.c_int32, []),

@@ -139,6 +139,16 @@ int32_t lego_device_status(void* stream, uint32_t* detail) {
   return word ? (int32_t)LEGO_ERR_DEVICE_TIMEOUT : (int32_t)LEGO_OK;
 }
 
+int32_t lego_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes,
+                     int64_t height, void* stream) {
+  if (!dst || !src) return LEGO_ERR_NULL;
+  if (width_bytes < 0 || height < 0 || dst_pitch < width_bytes || src_pitch < width_bytes) return LEGO_ERR_SIZE;
+  if (width_bytes == 0 || height == 0) return LEGO_OK;
+  LEGO_CUDA_TRY(cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width_bytes, (size_t)height,
+                                  cudaMemcpyDefault, (cudaStream_t)stream));
+  return LEGO_OK;
+}
+
 int32_t lego_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
   if (limit_cycles < 1 || limit_cycles > 2000000000LL) return LEGO_ERR_SIZE;
   int32_t err = LEGO_OK;

@@ -1064,6 +1064,9 @@ bool ids_share_columns(const Problem& p, int n) {
   return true;
 }
 
+}  // namespace
+extern std::atomic<int> g_lnbwd_split;  // layernorm_bwd.cu
+namespace {
 // Tuning knobs (lego_tune), process-wide.
 std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
 std::atomic<int> g_tune_streamk{0};  // see make_sched
@@ -1286,6 +1289,10 @@ int32_t lego_tune(int32_t knob, int32_t value) {
     case LEGO_TUNE_GEMM_STREAMK:
       if (value < 0 || value > 2) return LEGO_ERR_SIZE;
       g_tune_streamk.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_LNBWD_SPLIT:
+      if (value < 0) return LEGO_ERR_SIZE;
+      g_lnbwd_split.store(value);
       return LEGO_OK;
     case LEGO_TUNE_GEMM_LAG:
       if (value < 0 || value > 4) return LEGO_ERR_SIZE;

@@ -16,7 +16,7 @@
 namespace lego {
 namespace {
 
-constexpr int kMaxPartialRows = 592;  // 4 CTAs on each of 148 SMs
+constexpr int kMaxPartialRows = 1184;  // 8 partial rows (one per consumer group) on each of 148 SMs
 
 struct BwdParams {
   const __half* dy;
@@ -395,7 +395,7 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
 // packed (f32x2).  Memory-level parallelism comes from the ring, not from occupancy.
 
 constexpr int kBwdConsumers = 512;
-constexpr int kBwdMaxGroups = 4;   // partial rows: 4 per SM (kMaxPartialRows)
+constexpr int kBwdMaxGroups = 8;   // partial rows: 8 per SM (kMaxPartialRows)
 constexpr int kBwdRing = 16;
 constexpr long long kBwdWaitLimit = 2000000000LL;  // SM cycles, about a second
 
@@ -403,8 +403,9 @@ struct BwdRingCtl {
   uint64_t full[kBwdRing];
   uint64_t empty[kBwdRing];
   int64_t row[kBwdRing];
+  uint64_t rowbar[kBwdMaxGroups][2];    // [group][row & 1]: the row's warp totals are all in red_all
   uint32_t abort_flag;                  // any role gave up: polled inside every bounded wait
-  uint32_t group_abort[kBwdMaxGroups];  // written only by the group's own threads, read after its barrier
+  uint32_t group_abort[kBwdMaxGroups];  // set by a thread of the group that gave up
 };
 
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
@@ -416,7 +417,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   const int groups = G == kBwdConsumers ? 1 : groups_rt;
   constexpr int P2 = EPT / 2;  // packed pairs per thread and row
   extern __shared__ __align__(128) uint8_t bwd_smem[];
-  __shared__ __align__(16) float2 red_all[kBwdMaxGroups][2][16];  // [group][row parity][warp] -> (s1, s2)
+  __shared__ __align__(16) float2 red_all[kBwdMaxGroups][4][16];  // [group][row & 3][warp] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
   const uint32_t half_slot = (row_bytes + 127u) & ~127u;
@@ -434,12 +435,16 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
       ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), nw);
     }
     ctl->abort_flag = 0;
-    for (int g = 0; g < kBwdMaxGroups; ++g) ctl->group_abort[g] = 0;
+    for (int g = 0; g < kBwdMaxGroups; ++g) {
+      ctl->group_abort[g] = 0;
+      ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[g][0]), nw);
+      ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[g][1]), nw);
+    }
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
   }
   // partials of warps a group does not have: zero, so the fold below is a fixed tree
-  for (int i = tid; i < kBwdMaxGroups * 2 * 16; i += blockDim.x) (&red_all[0][0][0])[i] = make_float2(0.f, 0.f);
+  for (int i = tid; i < kBwdMaxGroups * 4 * 16; i += blockDim.x) (&red_all[0][0][0])[i] = make_float2(0.f, 0.f);
   __syncthreads();
   ptx::launch_dependents();     // the column reduction (or the next op) may set itself up now
   ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
@@ -484,7 +489,6 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   const int group = tid / gsize;
   const int gtid = tid - group * gsize;
   const int lane = tid & 31, warp_in_group = gtid >> 5;
-  const int bar = 1 + group;
   volatile uint32_t* group_abort = &ctl->group_abort[group];
   float2 g[P2], acc_w[P2], acc_b[P2];
 #pragma unroll
@@ -500,106 +504,135 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
   const float inv_cols = 1.0f / (float)cols;
 
-  int s = group;
-  uint32_t use = 0;
-  uint32_t parity = 0;
-  for (int64_t n = group; n < my_rows; n += groups, s += groups, parity ^= 1u) {
-    if (s >= stages) {
-      s -= stages;
-      ++use;
-    }
-    const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwdWaitLimit);
-    if (!ok) {
+  // A row is handled in two phases with the group's next row's first phase in between (see
+  // ln_bwd_ring1_kernel): the group-wide reduction of a row is in flight while its threads work
+  // on the next row, and x and dy are read from the ring slot again for phase 2.
+  float2 (*red)[16] = red_all[group];           // [row & 3][warp]
+  uint64_t* rowbar = ctl->rowbar[group];        // [row & 1], nw arrivals
+  bool alive = true;
+  auto phase1 = [&](int64_t j, int s, uint32_t use) {   // j: this group's j-th row
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwdWaitLimit)) {
       *abort_flag = 1;
-      *group_abort = 1;
       atomicCAS(status, 0u, 0x70000u | (uint32_t)s);
+      alive = false;
+      return;
     }
     const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
-    const int64_t row = ok ? ctl->row[s] : 0;
-    const float mean = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3] : 0.f;
-    const float rstd = ok ? reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3] : 0.f;
-    uint4 xr[NV], dr[NV];
+    const int64_t row = ctl->row[s];
+    const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
+    const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3];
+    // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
+    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int v = k * gsize + gtid;
-      xr[k] = dr[k] = make_uint4(0u, 0u, 0u, 0u);
-      if (ok && v * 8 < cols) {
-        xr[k] = reinterpret_cast<const uint4*>(slot)[v];
-        dr[k] = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
+      if (v * 8 < cols) {
+        xr = reinterpret_cast<const uint4*>(slot)[v];
+        dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
+        const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
+        acc_w[k * 4 + e] = ptx::fma2(d, h, acc_w[k * 4 + e]);
+        acc_b[k * 4 + e] = ptx::add2(acc_b[k * 4 + e], d);
+        const float2 w = ptx::mul2(d, g[k * 4 + e]);
+        s1 = ptx::fma2(h, w, s1);
+        s2 = ptx::add2(s2, w);
       }
     }
+    // even lanes fold the first sum, odd lanes the second: one shuffle per level instead of two
+    const bool odd = (lane & 1) != 0;
+    const float a = s1.x + s1.y, bsum = s2.x + s2.y;
+    float keep = odd ? bsum : a;
+    keep += __shfl_xor_sync(0xffffffffu, odd ? a : bsum, 1);
+#pragma unroll
+    for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+    if (lane < 2) reinterpret_cast<float*>(&red[j & 3][warp_in_group])[lane] = keep;
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
-
-    // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
-    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
-    float2 h[P2], w[P2];
-    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
-#pragma unroll
-    for (int k = 0; k < P2; ++k) {
-      const __half2 xh2 = reinterpret_cast<const __half2*>(&xr[k / 4])[k % 4];
-      const __half2 dh2 = reinterpret_cast<const __half2*>(&dr[k / 4])[k % 4];
-      const float2 d = __half22float2(dh2);
-      h[k] = ptx::fma2(__half22float2(xh2), rstd2, shift2);
-      acc_w[k] = ptx::fma2(d, h[k], acc_w[k]);
-      acc_b[k] = ptx::add2(acc_b[k], d);
-      w[k] = ptx::mul2(d, g[k]);
-      s1 = ptx::fma2(h[k], w[k], s1);
-      s2 = ptx::add2(s2, w[k]);
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&rowbar[j & 1]));
+  };
+  auto phase2 = [&](int64_t j, int s) {
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&rowbar[j & 1]), (uint32_t)((j >> 1) & 1), abort_flag, kBwdWaitLimit)) {
+      *abort_flag = 1;
+      atomicCAS(status, 0u, 0x78000u | (uint32_t)s);
+      alive = false;
+      return;
     }
-    float2 ss = make_float2(s1.x + s1.y, s2.x + s2.y);
-    if (nw == 1) {
+    float2 ss;
+    const float2* r = red[j & 3];
+    if (nw > 8) {
+      // 16 partials: both half-warps fold the same 16 values by shuffles (few registers)
+      ss = r[lane & 15];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
+      for (int o = 8; o > 0; o >>= 1) {
         ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
         ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
       }
     } else {
-      float2* r = red_all[group][parity];
-      {
-        // even lanes fold the first sum, odd lanes the second: one shuffle per level instead of two
-        const bool odd = (lane & 1) != 0;
-        float keep = odd ? ss.y : ss.x;
-        keep += __shfl_xor_sync(0xffffffffu, odd ? ss.x : ss.y, 1);
-#pragma unroll
-        for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-        if (lane < 2) reinterpret_cast<float*>(&r[warp_in_group])[lane] = keep;
-      }
-      asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(gsize) : "memory");
-      if (nw > 8) {
-        // 16 partials: both half-warps fold the same 16 values by shuffles (few registers)
-        ss = r[lane & 15];
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
-          ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
-          ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
-        }
-      } else {
-        // up to 8 partials (absent warps hold zeros): a fixed tree over four 128-bit loads
-        const float4* q = reinterpret_cast<const float4*>(r);
-        const float4 a0 = q[0], a1 = q[1], a2 = q[2], a3 = q[3];
-        ss.x = ((a0.x + a0.z) + (a1.x + a1.z)) + ((a2.x + a2.z) + (a3.x + a3.z));
-        ss.y = ((a0.y + a0.w) + (a1.y + a1.w)) + ((a2.y + a2.w) + (a3.y + a3.w));
-      }
+      // up to 8 partials (absent warps hold zeros): a fixed tree over four 128-bit loads
+      const float4* q = reinterpret_cast<const float4*>(r);
+      const float4 a0 = q[0], a1 = q[1], a2 = q[2], a3 = q[3];
+      ss.x = ((a0.x + a0.z) + (a1.x + a1.z)) + ((a2.x + a2.z) + (a3.x + a3.z));
+      ss.y = ((a0.y + a0.w) + (a1.y + a1.w)) + ((a2.y + a2.w) + (a3.y + a3.w));
     }
-    if (*group_abort) break;  // uniform: the group's own flag writes of this row precede the barrier / __syncwarp above
+    const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
+    const int64_t row = ctl->row[s];
+    const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
+    const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3];
+    const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
     // dx = (wdy - (xhat * c1 + c2)) * rstd, as two fused steps per pair
     const float c1r = ss.x * inv_cols * rstd, c2r = ss.y * inv_cols * rstd;
     const float2 nc1 = make_float2(-c1r, -c1r), nc2 = make_float2(-c2r, -c2r);
     __half* __restrict__ dx = P.dx + row * cols;
+    uint4 outv[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int v = k * gsize + gtid;
+      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
+      if (v * 8 < cols) {
+        xr = reinterpret_cast<const uint4*>(slot)[v];
+        dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      }
+      __half2* o2 = reinterpret_cast<__half2*>(&outv[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
+        const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
+        const float2 w = ptx::mul2(d, g[k * 4 + e]);
+        const float2 t = ptx::fma2(h, nc1, ptx::fma2(w, rstd2, nc2));
+        o2[e] = __floats2half2_rn(t.x, t.y);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int c = (k * gsize + gtid) * 8;
-      uint4 outv;
-      __half2* o2 = reinterpret_cast<__half2*>(&outv);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 t = ptx::fma2(h[k * 4 + e], nc1, ptx::fma2(w[k * 4 + e], rstd2, nc2));
-        o2[e] = __floats2half2_rn(t.x, t.y);
-      }
-      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv);
+      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
     }
+  };
+
+  // ring cursors of the group's row in phase 1 (s1, use1) and in phase 2 (s2); the slot count is a
+  // multiple of the group count and at least twice it, so the two rows sit in different slots
+  const int64_t group_rows = my_rows > group ? (my_rows - group + groups - 1) / groups : 0;
+  int s1 = group, s2 = group;
+  uint32_t use1 = 0;
+  if (group_rows > 0) phase1(0, s1, use1);
+  for (int64_t j = 0; alive && j < group_rows; ++j) {
+    if (j + 1 < group_rows) {
+      s1 += groups;
+      if (s1 >= stages) { s1 -= stages; ++use1; }
+      phase1(j + 1, s1, use1);
+      if (!alive) break;
+    }
+    phase2(j, s2);
+    s2 += groups;
+    if (s2 >= stages) s2 -= stages;
   }
+  if (!alive) *group_abort = 1;
   if (*group_abort) return;
   // this group's partial row of column sums
   const size_t prow = (size_t)blockIdx.x * groups + group;
@@ -655,7 +688,7 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   if (stages > kBwdRing) stages = kBwdRing;
   if ((size_t)stages > budget / slot) stages = (int)(budget / slot);
   stages -= stages % groups;
-  if (stages < 2 || stages < groups) return LEGO_ERR_UNSUPPORTED;
+  if (stages < 2 * groups) return LEGO_ERR_UNSUPPORTED;  // a group holds two slots: its rows in phase 1 and phase 2
   const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
   P.partial_rows = grid * groups;  // every group writes its row, all zeros if it saw no row of x
   return launch_ring_dx_g<EPT, 0>(P, ctx, s, grid, stages, groups, gsize, smem);
@@ -731,7 +764,15 @@ int32_t launch_dx_by_cols(const BwdParams& P, cudaStream_t s) {
 int64_t partial_rows_for(int64_t rows) { return rows < kMaxPartialRows ? rows : kMaxPartialRows; }
 
 }  // namespace
+extern std::atomic<int> g_lnbwd_split;
+namespace {
+
+}  // namespace
 }  // namespace lego
+
+namespace lego {
+std::atomic<int> g_lnbwd_split{6144};  // rows wider than this take the one-group kernel
+}
 
 using namespace lego;
 
@@ -763,10 +804,11 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
   if (vec && cols >= 1024 && cols <= kBwdConsumers * 16 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
       a16(partial) && rows >= 2 * (int64_t)ctx->sm_count) {
-    // Same box, GB/s, 16384 rows: one group of 512 threads / groups of cols/16 threads:
-    // N = 2048: 2440 / 3890, N = 4096: 4430 / 4260, N = 8192: 4730 / 4490.
-    if (cols > 3072) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
-    else st = cols <= 1536 ? launch_ring_dx<8>(P, ctx, s) : launch_ring_dx<16>(P, ctx, s);
+    // Same box, GB/s, 16384 rows, both kernels with rows in two phases: one group of 512 threads /
+    // groups of cols/16 threads: N = 2048: 2010 / 4180, N = 4096: 3850 / 5350, N = 6144: 4160 / 4670,
+    // N = 8192: 5500 / 5250.
+    if (cols > g_lnbwd_split.load()) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
+    else st = launch_ring_dx<16>(P, ctx, s);
   }
   if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
   if (st != LEGO_OK) return st;

@@ -10,6 +10,7 @@
 //            allows (also the fallback for digit sets the tiled kernel rejects);
 //   staged : any layout pair, element by element through the staged interpreter.
 // The tile a CTA moves is named by tile_order.inv(cta) when that layout is given.
+#include <algorithm>
 #include <cstring>
 
 #include "common.cuh"
@@ -21,7 +22,7 @@ namespace lego {
 
 namespace {
 
-enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2, KIND_TMA = 3 };
+enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2, KIND_TMA = 3, KIND_CHUNK = 4 };
 
 constexpr int kThreads = 256;
 constexpr int kVecPerThread = 4;
@@ -59,6 +60,37 @@ struct TmaParams {
   int32_t one_load; // 1: the tensor map is group-major, one TMA load fetches a whole tile
 };
 
+// Chunk-tiled permute: both sides share a contiguous run of rv 16-byte vectors (the
+// innermost digit is the same on both sides), and a tile is made of the digits that
+// continue that run on the input side plus the digits that continue it on the output
+// side, so that a tile is read in long contiguous pieces, parked in shared memory, and
+// written in long contiguous pieces.  Example: a 384^3 volume from row-major order into
+// 8^3 bricks (benchmarks/cuda/bricks_f3d.py:10-13) -- the run is a brick row of 8 floats,
+// the input continues with the brick index along z (48 bricks = 1536 contiguous bytes),
+// the output with the rows and planes of the brick (2 KiB contiguous).
+constexpr int kChunkMaxInner = 4;
+constexpr int kChunkMaxVecs = 6144;  // 96 KiB of shared memory per tile, two tiles per SM
+struct ChunkDigit {
+  uint32_t radix;
+  uint32_t w_smem;   // weight in the tile's input-order run index (position in shared memory / rv)
+  uint32_t w_out;    // weight in the tile's output-order run index
+  uint32_t reserved;
+  FastDiv fd;
+  int64_t s_in;      // strides in 16-byte vectors
+  int64_t s_out;
+};
+struct ChunkParams {
+  DigitProgram p1;  // tile id -> outer coordinates
+  DigitProgram p2;  // outer coordinates -> (input base, output base), in 16-byte vectors
+  int64_t n_tiles;
+  int32_t n_inner;
+  int32_t rv;         // vectors per run
+  int32_t tile_runs;  // runs per tile
+  int32_t swizzle;    // 1: XOR the low bits of the shared-memory position with the output-order run index
+  ChunkDigit by_in[kChunkMaxInner];   // inner digits, input-fastest first
+  ChunkDigit by_out[kChunkMaxInner];  // the same digits, output-fastest first
+};
+
 struct Plan {
   int kind;
   bool by_order;  // tile ids are the ids of the caller's tile_order layout
@@ -69,6 +101,7 @@ struct Plan {
   TiledParams tiled;
   TmaParams tma;
   GatherParams gather;
+  ChunkParams chunk;
   StagedProgram staged_src, staged_dst;
 };
 
@@ -91,6 +124,99 @@ template <> struct VecT<2> { using type = uint16_t; };
 template <> struct VecT<4> { using type = uint32_t; };
 template <> struct VecT<8> { using type = uint2; };
 template <> struct VecT<16> { using type = uint4; };
+
+// ---- chunk-tiled permute ---------------------------------------------------------
+
+template <bool WIDE>
+__global__ void __launch_bounds__(kThreads, 2)
+chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restrict__ in, uint4* __restrict__ out) {
+  extern __shared__ uint4 chunk_tile[];
+  __shared__ int64_t base[2];
+  if (threadIdx.x == 0) {
+    const uint64_t t = blockIdx.x;
+    uint64_t coord[LEGO_MAX_RANK];
+    for (int k = 0; k < LEGO_MAX_RANK; ++k) coord[k] = 0;
+    for (int j = 0; j < P.p1.n_terms; ++j) coord[P.p1.t[j].dst] += term_eval<WIDE>(P.p1.t[j], t);
+    uint64_t b0 = 0, b1 = 0;
+    for (int j = 0; j < P.p2.n_terms; ++j) {
+      const uint64_t v = term_eval<WIDE>(P.p2.t[j], coord[P.p2.t[j].src]);
+      if (P.p2.t[j].dst == 0) b0 += v; else b1 += v;
+    }
+    base[0] = (int64_t)b0;
+    base[1] = (int64_t)b1;
+  }
+  __syncthreads();
+  const uint4* src = in + base[0];
+  uint4* dst = out + base[1];
+  const int rv = P.rv, n = P.n_inner;
+  const uint32_t mask = P.swizzle ? 7u : 0u;
+  // phase 1: runs in input order (contiguous global reads); position in shared memory = run index * rv.
+  // Four runs per thread and step: all their loads are issued before the first is parked.
+  constexpr int UNROLL = 4;
+  for (uint32_t r0 = threadIdx.x; r0 < (uint32_t)P.tile_runs; r0 += UNROLL * kThreads) {
+    int64_t off[UNROLL];
+    uint32_t tw[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      uint32_t rest = r0 + u * kThreads, w = 0;
+      off[u] = 0;
+#pragma unroll
+      for (int k = 0; k < kChunkMaxInner; ++k) {
+        if (k < n) {
+          const ChunkDigit& d = P.by_in[k];
+          const uint32_t q = (k + 1 < n) ? fd_div(rest, d.fd) : 0u;
+          const uint32_t v = (k + 1 < n) ? rest - q * d.radix : rest;
+          rest = q;
+          off[u] += (int64_t)v * d.s_in;
+          w += v * d.w_out;
+        }
+      }
+      tw[u] = (w * (uint32_t)rv) & mask;
+    }
+    if (rv == 2) {
+      uint4 v[UNROLL][2];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (r0 + u * kThreads < (uint32_t)P.tile_runs) {
+          v[u][0] = __ldcs(src + off[u]);
+          v[u][1] = __ldcs(src + off[u] + 1);
+        }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (r0 + u * kThreads < (uint32_t)P.tile_runs) {
+          const uint32_t pos = (r0 + u * kThreads) * 2u;
+          chunk_tile[pos ^ tw[u]] = v[u][0];
+          chunk_tile[(pos + 1) ^ tw[u]] = v[u][1];
+        }
+    } else {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (r0 + u * kThreads < (uint32_t)P.tile_runs) {
+          const uint32_t pos = (r0 + u * kThreads) * (uint32_t)rv;
+          for (int x = 0; x < rv; ++x) chunk_tile[(pos + x) ^ tw[u]] = __ldcs(src + off[u] + x);
+        }
+    }
+  }
+  __syncthreads();
+  // phase 2: runs in output order (contiguous global writes)
+  for (uint32_t q0 = threadIdx.x; q0 < (uint32_t)P.tile_runs; q0 += kThreads) {
+    uint32_t rest = q0, r = 0;
+    int64_t off = 0;
+#pragma unroll
+    for (int k = 0; k < kChunkMaxInner; ++k) {
+      if (k < n) {
+        const ChunkDigit& d = P.by_out[k];
+        const uint32_t q = (k + 1 < n) ? fd_div(rest, d.fd) : 0u;
+        const uint32_t v = (k + 1 < n) ? rest - q * d.radix : rest;
+        rest = q;
+        off += (int64_t)v * d.s_out;
+        r += v * d.w_smem;
+      }
+    }
+    const uint32_t pos = r * (uint32_t)rv, tw = (q0 * (uint32_t)rv) & mask;
+    for (int x = 0; x < rv; ++x) __stcs(dst + off + x, chunk_tile[(pos + x) ^ tw]);
+  }
+}
 
 // ---- gather: thread per output vector ------------------------------------------
 
@@ -562,6 +688,148 @@ bool finish_tiled(int64_t ti, int64_t to, int64_t s_out_i, int64_t s_in_o, int e
   return true;
 }
 
+// Chunk-tiled plan (see ChunkParams); false when the pair of layouts has no common run of
+// whole 16-byte vectors, or nothing continues it on one of the sides.
+bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, const void* in, const void* out,
+                Plan* pl) {
+  if (eb > 16 || !aligned(in, 16) || !aligned(out, 16) || size >= ((int64_t)1 << 40)) return false;
+  const int64_t ev = 16 / eb;  // elements per vector
+  int c = -1;
+  for (size_t j = 0; j < merged.size(); ++j)
+    if (merged[j].sa == 1 && merged[j].sb == 1) c = (int)j;
+  if (c < 0 || (merged[c].radix * eb) % 16) return false;
+  const int64_t rv = merged[c].radix * eb / 16;
+  if (rv < 1 || rv >= 8) return false;  // runs of a whole 128-byte line: the plain vector copy is already coalesced
+  struct D { int64_t radix, sa, sb; bool in_tile; };
+  std::vector<D> ds;
+  for (size_t j = 0; j < merged.size(); ++j) {
+    if ((int)j == c || merged[j].radix == 1) continue;
+    if (merged[j].sa % ev || merged[j].sb % ev) return false;
+    ds.push_back({merged[j].radix, merged[j].sa / ev, merged[j].sb / ev, false});
+  }
+  // the digits continuing the run on either side, up to two per side and about a KiB per piece
+  // (the two sides take turns, so that a digit both could use goes to the side that is shorter)
+  std::vector<int> chain_in, chain_out;
+  int64_t len_i = rv, len_o = rv;
+  bool open_i = true, open_o = true;
+  while (open_i || open_o) {
+    const bool turn_in = open_i && (!open_o || len_i <= len_o);
+    std::vector<int>& ch = turn_in ? chain_in : chain_out;
+    int64_t& len = turn_in ? len_i : len_o;
+    bool& open = turn_in ? open_i : open_o;
+    int f = -1;
+    if (ch.size() < 2 && len * 16 < 1024)
+      for (size_t j = 0; j < ds.size(); ++j)
+        if (!ds[j].in_tile && (turn_in ? ds[j].sa : ds[j].sb) == len) f = (int)j;
+    if (f < 0) { open = false; continue; }
+    ds[f].in_tile = true;
+    ch.push_back(f);
+    len *= ds[f].radix;
+  }
+  if (chain_in.empty() || chain_out.empty()) return false;
+  // fit the tile into shared memory: cut the slowest digit of the longer side
+  auto tile_vecs = [&]() {
+    int64_t v = rv;
+    for (const D& d : ds)
+      if (d.in_tile) v *= d.radix;
+    return v;
+  };
+  for (int guard = 0; tile_vecs() > kChunkMaxVecs && guard < 16; ++guard) {
+    int64_t len_in = rv, len_out = rv;
+    for (int j : chain_in) len_in *= ds[j].radix;
+    for (int j : chain_out) len_out *= ds[j].radix;
+    std::vector<int>& ch = len_in >= len_out ? chain_in : chain_out;
+    D& d = ds[ch.back()];
+    const int64_t over = (tile_vecs() + kChunkMaxVecs - 1) / kChunkMaxVecs;
+    int64_t part = 0;
+    for (int64_t p = d.radix / over; p >= 2; --p)
+      if (d.radix % p == 0) { part = p; break; }
+    if (part < 2) {
+      if (ch.size() == 1) return false;
+      d.in_tile = false;
+      ch.pop_back();
+      continue;
+    }
+    ds.push_back({d.radix / part, d.sa * part, d.sb * part, false});  // the rest of the digit stays outside
+    ds[ch.back()].radix = part;
+  }
+  if (tile_vecs() > kChunkMaxVecs) return false;
+
+  ChunkParams& cp = pl->chunk;
+  std::memset(&cp, 0, sizeof(cp));
+  std::vector<int> inner;
+  for (size_t j = 0; j < ds.size(); ++j)
+    if (ds[j].in_tile) inner.push_back((int)j);
+  if ((int)inner.size() > kChunkMaxInner) return false;
+  std::vector<int> by_in = inner, by_out = inner;
+  std::sort(by_in.begin(), by_in.end(), [&](int a, int b) { return ds[a].sa < ds[b].sa; });
+  std::sort(by_out.begin(), by_out.end(), [&](int a, int b) { return ds[a].sb < ds[b].sb; });
+  std::vector<int64_t> w_smem(ds.size(), 0), w_out(ds.size(), 0);
+  int64_t acc = 1;
+  for (int j : by_in) { w_smem[j] = acc; acc *= ds[j].radix; }
+  cp.tile_runs = (int32_t)acc;
+  acc = 1;
+  for (int j : by_out) { w_out[j] = acc; acc *= ds[j].radix; }
+  auto fill = [&](ChunkDigit* dst, const std::vector<int>& order) {
+    for (size_t k = 0; k < order.size(); ++k) {
+      const D& d = ds[order[k]];
+      dst[k].radix = (uint32_t)d.radix;
+      dst[k].w_smem = (uint32_t)w_smem[order[k]];
+      dst[k].w_out = (uint32_t)w_out[order[k]];
+      dst[k].fd = make_fastdiv((uint64_t)d.radix);
+      dst[k].s_in = d.sa;
+      dst[k].s_out = d.sb;
+    }
+  };
+  fill(cp.by_in, by_in);
+  fill(cp.by_out, by_out);
+  cp.n_inner = (int32_t)inner.size();
+  cp.rv = (int32_t)rv;
+  // The XOR on the low three position bits must be one value per aligned group of eight
+  // vectors in shared memory: the input-chain digits (which vary inside such a group) must
+  // not reach the low bits of rv * output-order index, and the input pieces must be whole groups.
+  int64_t piece_in = rv;
+  bool swz = (rv == 1 || rv == 2 || rv == 4 || rv == 8);
+  for (int j : chain_in) {
+    piece_in *= ds[j].radix;
+    if ((w_out[j] * rv) % 8) swz = false;
+  }
+  if (piece_in % 8) swz = false;
+  cp.swizzle = swz ? 1 : 0;
+
+  // outer digits: everything not in the tile
+  const int32_t wide = size > ((int64_t)1 << 31) ? 1 : 0;
+  cp.p1.n_src = 1;
+  cp.p2.n_dst = 2;
+  cp.p1.wide = cp.p2.wide = wide;
+  int64_t before = 1;
+  int n_outer = 0;
+  std::vector<int> outer;
+  for (size_t j = 0; j < ds.size(); ++j)
+    if (!ds[j].in_tile) outer.push_back((int)j);
+  if ((int)outer.size() > LEGO_MAX_RANK || 2 * (int)outer.size() > LEGO_MAX_TERMS) return false;
+  // neighbouring tile ids walk the digit that is contiguous on the output side first
+  std::sort(outer.begin(), outer.end(), [&](int a, int b) { return ds[a].sb < ds[b].sb; });
+  for (int j : outer) {
+    const bool last = (j == outer.back());
+    set_term(&cp.p1.t[cp.p1.n_terms++], 0, n_outer, before, last ? 0 : ds[j].radix, 1);
+    set_term(&cp.p2.t[cp.p2.n_terms++], n_outer, 0, 1, 0, ds[j].sa);
+    set_term(&cp.p2.t[cp.p2.n_terms++], n_outer, 1, 1, 0, ds[j].sb);
+    before *= ds[j].radix;
+    ++n_outer;
+  }
+  cp.p1.n_dst = cp.p2.n_src = n_outer;
+  cp.n_tiles = before;
+  if (cp.n_tiles >= ((int64_t)1 << 31)) return false;
+  pl->kind = KIND_CHUNK;
+  pl->vec_bytes = 16;
+  pl->tile_in = piece_in * ev;
+  int64_t piece_out = rv;
+  for (int j : chain_out) piece_out *= ds[j].radix;
+  pl->tile_out = piece_out * ev;
+  return true;
+}
+
 int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
                   const lego_layout_t* order, const void* in, const void* out, Plan* pl) {
   if (!src || !dst) return LEGO_ERR_NULL;
@@ -680,6 +948,7 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
       if (finish_tiled(ti, to, merged[ii].sb, merged[oo].sa, eb, in, out, pl)) return LEGO_OK;
     }
   }
+  if (plan_chunk(merged, size, eb, in, out, pl)) return LEGO_OK;
   plan_gather(merged, size, eb, in, out, pl);
   return LEGO_OK;
 }
@@ -762,6 +1031,26 @@ int32_t launch_tma(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cu
   return cuda_status(e);
 }
 
+int32_t launch_chunk(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
+  const ChunkParams& cp = pl.chunk;
+  const size_t vecs = ((size_t)cp.tile_runs * cp.rv + 7) & ~(size_t)7;
+  const size_t smem = vecs * 16;
+  static PerDeviceFlag configured[2];
+  const int wide = cp.p1.wide ? 1 : 0;
+  if (!configured[wide].test(ctx->device)) {
+    if (wide) LEGO_CUDA_TRY(cudaFuncSetAttribute(chunk_permute_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kChunkMaxVecs * 16));
+    else LEGO_CUDA_TRY(cudaFuncSetAttribute(chunk_permute_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kChunkMaxVecs * 16));
+    configured[wide].set(ctx->device);
+  }
+  if (wide)
+    chunk_permute_kernel<true><<<(unsigned)cp.n_tiles, kThreads, smem, s>>>(cp, (const uint4*)in, (uint4*)out);
+  else
+    chunk_permute_kernel<false><<<(unsigned)cp.n_tiles, kThreads, smem, s>>>(cp, (const uint4*)in, (uint4*)out);
+  return cuda_status(cudaGetLastError());
+}
+
 template <int VB>
 int32_t launch_gather(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
   const GatherParams& gp = pl.gather;
@@ -833,6 +1122,8 @@ static int32_t run_permute(const void* in, void* out, int32_t elem_bytes, const 
         case 8: st = launch_gather<8>(*pl, in, out, ctx, s); break;
         default: st = launch_gather<16>(*pl, in, out, ctx, s); break;
       }
+    } else if (pl->kind == KIND_CHUNK) {
+      st = launch_chunk(*pl, in, out, ctx, s);
     } else if (pl->kind == KIND_TMA) {
       switch (elem_bytes) {
         case 2: st = launch_tma<2>(*pl, in, out, ctx, s); break;

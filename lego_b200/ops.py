@@ -301,9 +301,40 @@ def transpose(x: torch.Tensor, tile: int = 32, tile_order: Optional[GroupBy] = N
         raise ValueError(f"matrix {r}x{c} is not a multiple of the {tile}x{tile} tile")
     src = OrderBy(Row(r, c)).TileBy([r // tile, c // tile], [tile, tile])
     dst = OrderBy(Col(r, c)).TileBy([r // tile, c // tile], [tile, tile])
-    if tile_order is None:
+    default_order = tile_order is None
+    if default_order:
         tile_order = OrderBy(Col(r // tile, c // tile)).TileBy([r // tile, c // tile])
+    nbytes = x.numel() * x.element_size()
+    if (not x.is_cuda and x.is_contiguous() and default_order and nbytes > 2 * _HOST_BLOCK_BYTES
+            and permute_plan(x.element_size(), src, dst, tile_order)[0] in (2, 3)):
+        return _transpose_from_host(x, tile, src, dst, tile_order)
     return permute(x, src, dst, tile_order).reshape(c, r)
+
+
+def _transpose_from_host(x, tile, src, dst, tile_order):
+    """Host matrix: slabs of output rows.  A slab's input is a band of columns, copied in with
+    one strided copy; its tiles are a contiguous range of the column-major tile order; its
+    output rows are contiguous.  Slab i + 1 arrives while slab i is transposed and slab i - 1
+    leaves, so the call costs about one PCIe direction instead of copy-in + kernel + copy-out."""
+    r, c = x.shape
+    eb = x.element_size()
+    pipe = _HostPipeline()
+    lib = _abi.lib()
+    d_in = torch.empty((r, c), dtype=x.dtype, device=pipe.dev)
+    d_out = torch.empty((c, r), dtype=x.dtype, device=pipe.dev)
+    out = _pinned_like((c, r), x.dtype)
+    band = max(tile, (_HOST_BLOCK_BYTES // (r * eb)) // tile * tile)        # columns per slab
+    tiles_down = r // tile
+    for c0 in range(0, c, band):
+        c1 = min(c, c0 + band)
+        _abi.check(lib.lego_copy_2d(d_in.data_ptr() + c0 * eb, c * eb, x.data_ptr() + c0 * eb, c * eb,
+                                    (c1 - c0) * eb, r, pipe.inbound.cuda_stream), "lego_copy_2d")
+        pipe.ready()
+        permute(d_in, src, dst, tile_order, out=d_out.reshape(r, c),
+                tiles=(c0 // tile * tiles_down, (c1 - c0) // tile * tiles_down))
+        pipe.drain(out[c0:c1], d_out[c0:c1])
+    pipe.finish()
+    return out
 
 
 # ---- row-wise kernels ---------------------------------------------------------------

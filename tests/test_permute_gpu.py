@@ -143,3 +143,36 @@ def test_tile_ranges_assemble_the_whole_reorganisation(dtype, n, t):
         ops.permute(xd, src, dst, order, out=out, tiles=(nt * nt - 1, 2))     # past the last tile
     with pytest.raises(ValueError):
         ops.permute(xd, src, dst, None, out=out, tiles=(0, 1))                # a range needs a tile order
+
+
+def test_brick_relayout_384_cubed(golden):
+    """The reference's brick layouts (benchmarks/cuda/bricks_f3d.py:10-13): a 384^3 fp32
+    volume from row-major order into 8^3 bricks and back, each as ONE permute call on the
+    chunk-tiled kernel.  Checked three ways: against the reference's own index vectors for
+    both layouts (golden file), against the oracle on a 96^3 volume, and at full size against
+    the same re-layout written as reshape + transpose."""
+    n, b = 384, 8
+    normal = L.OrderBy(L.Row(n, n, n)).TileBy([n // b] * 3, [b] * 3)
+    bricks = L.OrderBy(L.Row(n // b, n // b, n // b), L.Row(b, b, b)).TileBy([n // b] * 3, [b] * 3)
+    assert ops.permute_plan(4, normal, bricks)[0] == 4 and ops.permute_plan(4, bricks, normal)[0] == 4
+    x = torch.rand(n, n, n, generator=torch.Generator().manual_seed(8))
+    xd = x.cuda()
+    out = ops.permute(xd, normal, bricks)
+    ops.device_status()
+    want = x.reshape(n // b, b, n // b, b, n // b, b).permute(0, 2, 4, 1, 3, 5).contiguous()
+    assert torch.equal(out.cpu().reshape(-1), want.reshape(-1))
+    assert torch.equal(ops.permute(out, bricks, normal).cpu(), x)          # and back
+    # the reference's vectors: element idx sits at normal(idx) before and at bricks(idx) after
+    gn, gb = golden["layouts"]["bricks_normal_384"], golden["layouts"]["bricks_384"]
+    assert gn["ids"] == gb["ids"]
+    src_pos = torch.tensor(gn["apply"])
+    dst_pos = torch.tensor(gb["apply"])
+    assert torch.equal(out.cpu().reshape(-1)[dst_pos], x.reshape(-1)[src_pos])
+    # oracle on a volume it handles in seconds, several element sizes
+    m = 96
+    sn = L.OrderBy(L.Row(m, m, m)).TileBy([m // b] * 3, [b] * 3)
+    sb = L.OrderBy(L.Row(m // b, m // b, m // b), L.Row(b, b, b)).TileBy([m // b] * 3, [b] * 3)
+    for dtype in (torch.float16, torch.float32, torch.float64):
+        y = torch.rand(m, m, m, generator=torch.Generator().manual_seed(9)).to(dtype)
+        _check(y, sn, sb, kind=4)
+        _check(y, sb, sn, kind=4)
