@@ -316,6 +316,16 @@ int32_t lego_grouped_gemm_f16_static(const void* const* A, const void* const* B,
 
 /* ---- housekeeping --------------------------------------------------------- */
 
+/* Strided copy of `height` rows of `width_bytes` between any two of host (pinned for a
+ * copy that overlaps) and device memory, enqueued on `stream` (cudaMemcpy2DAsync,
+ * direction inferred).  It lets a binding stage a column slab of a host matrix without
+ * packing it first, which is how the host-buffer transpose overlaps copy-in, kernel and
+ * copy-out.  No counterpart in the reference (its harnesses keep everything on the
+ * device, lego/lego_mlir.py:114-165).                                               */
+int32_t lego_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
+                     int64_t width_bytes, int64_t height, void* stream);
+
+
 /* Synchronise `stream` and return (then clear) the current device's status word:
  * LEGO_OK or LEGO_ERR_DEVICE_TIMEOUT; *detail (nullable) receives the raw word.
  * Covers the workspace's word and the one inside the static array; allocates nothing. */
