@@ -42,7 +42,7 @@ def test_status_strings_and_host_only_calls():
     assert b"bijection" in lib.lego_status_string(-5)
     assert lib.lego_layout_check(None) == -1
     assert lib.lego_layernorm_bwd_partial_rows(10, 64) == 10
-    assert lib.lego_layernorm_bwd_partial_rows(100000, 64) == 592
+    assert lib.lego_layernorm_bwd_partial_rows(100000, 64) == 1184
 
 
 def test_device_timeout_status_maps_to_lego_error():
