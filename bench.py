@@ -11,8 +11,8 @@ reported under "workloads".
 
 With N > 1 (one process per GPU, launched by torch.distributed.run) every named shape is
 SPLIT across the ranks -- rows for the row-wise kernels, output-row slabs for the
-transpose, M for the GEMM with B replicated, every group's M for the grouped GEMM, id
-ranges for the index map -- with no data-path collective: "scaling": "strong", value =
+transpose, M for the GEMM with B replicated, 512-row blocks of the groups packed by weight
+for the grouped GEMM, id ranges for the index map -- with no data-path collective: "scaling": "strong", value =
 the named shape's work / the slowest rank's device time.  After the timed region the
 shards are gathered over NCCL and rank 0 checks the assembled result against the oracle.
 The replica figure (every rank the full shape, "weak") is reported beside it.
@@ -357,9 +357,7 @@ class Transpose(Workload):
         return self.ap.numel() * 4, self.ap.numel() * 4
 
     def e2e_step(self, i):
-        if self.world == 1:
-            return self.ops.permute(self.ap, self.src, self.dst, self.order)
-        return self.ops.transpose(self.ap)
+        return self.ops.transpose(self.ap)      # the same layouts and tile order, built by the op from the shape
 
     def cpu_pass(self):
         from oracle import lego_oracle as O
@@ -524,39 +522,56 @@ class GroupedGemm(Workload):
         self.rank, self.world = rank, world
         self.sizes, _ = inputs.grouped_sizes(self.groups, self.k)
         self.A_host, self.B_host = inputs.grouped_input(self.groups, self.k)
-        self.blocks = shard.shard_grouped_gemm(self.sizes, rank, world)
-        self.A = [t[b:e].to(dev) for t, (b, e) in zip(self.A_host, self.blocks)]
-        self.B = [t.to(dev) for t in self.B_host]
-        self.orders = [L.OrderBy(L.Row(-(-(e - b) // 128), n // 256)).TileBy([-(-(e - b) // 128), n // 256])
-                       for (b, e), (_m, n, _k) in zip(self.blocks, self.sizes)]
+        # one rank: the 16 groups as they are.  Several: 512-row blocks of the groups, packed by weight.
+        self.packing = ([[(g, 0, m) for g, (m, _n, _k) in enumerate(self.sizes)]] if world == 1
+                        else shard.pack_grouped_gemm_blocks(self.sizes, world, 512))
+        self.mine = self.packing[rank]
+        self.A = [self.A_host[g][b:e].to(dev) for g, b, e in self.mine]
+        b_dev = {g: self.B_host[g].to(dev) for g in sorted({g for g, _, _ in self.mine})}
+        self.B = [b_dev[g] for g, _, _ in self.mine]
+        # in-group tile order: column-major LEGO layout over the (M/128, N/256) tile grid
+        self.orders = [L.OrderBy(L.Col(-(-(e - b) // 128), self.sizes[g][1] // 256)).TileBy(
+            [-(-(e - b) // 128), self.sizes[g][1] // 256]) for g, b, e in self.mine]
+        self.slot = max(sum((e - b) * self.sizes[g][1] for g, b, e in p) for p in self.packing)
         self.keep = [None] * 3
 
     def step(self, i):
         self.keep[i % 3] = self.C = self.ops.lego_group_gemm_fn(self.A, self.B, self.orders)
 
     def shard_result(self):
-        return torch.cat([c.reshape(-1) for c in self.C])
+        flat = torch.cat([c.reshape(-1) for c in self.C])
+        out = torch.zeros(self.slot, dtype=flat.dtype, device=flat.device)   # ranks' results differ in size
+        out[:flat.numel()] = flat
+        return out
 
     def check(self, full):
         self.ops.device_status()
-        per = full.numel() // self.world
+        where = {}                                   # (group, row_begin) -> offset of that block in `full`
+        for r, blocks in enumerate(self.packing):
+            off = r * self.slot
+            for g, b, e in blocks:
+                where[(g, b)] = (off, e)
+                off += (e - b) * self.sizes[g][1]
         worst = 0.0
-        # 64 rows of EVERY group, spread over the ranks' row blocks
-        for g, (m, n, _k) in enumerate(self.sizes):
-            rows_per_rank = m // self.world
-            off = sum((mm // self.world) * nn for mm, nn, _ in self.sizes[:g])
+        for g, (m, n, _k) in enumerate(self.sizes):  # 64 rows of EVERY group
             pick = torch.arange(0, m, max(1, m // 64))[:64]
-            got = torch.stack([full[(int(r) // rows_per_rank) * per + off + (int(r) % rows_per_rank) * n:][:n]
-                               for r in pick]).cpu().float()
+            rows = []
+            for r in pick.tolist():
+                b0 = max(b for (gg, b) in where if gg == g and b <= r)
+                off, _e = where[(g, b0)]
+                rows.append(full[off + (r - b0) * n: off + (r - b0 + 1) * n])
+            got = torch.stack(rows).cpu().float()
             ref = self.A_host[g][pick].float() @ self.B_host[g].float()
             worst = max(worst, ((got - ref).norm() / ref.norm()).item())
-        return worst <= 1e-3, f"rel-Frobenius {worst:.2e} (worst group) on 64 rows of each of the {len(self.sizes)} groups vs oracle (tol 1e-3)"
+        return worst <= 1e-3, (f"rel-Frobenius {worst:.2e} (worst group) on 64 rows of each of the "
+                               f"{len(self.sizes)} groups vs oracle (tol 1e-3)")
 
     def e2e_setup(self):
-        self.Ap = [t[b:e].contiguous().pin_memory() for t, (b, e) in zip(self.A_host, self.blocks)]
-        self.Bp = [t.pin_memory() for t in self.B_host]
+        self.Ap = [self.A_host[g][b:e].contiguous().pin_memory() for g, b, e in self.mine]
+        b_pin = {g: self.B_host[g].pin_memory() for g in sorted({g for g, _, _ in self.mine})}
+        self.Bp = [b_pin[g] for g, _, _ in self.mine]
         h2d = sum(t.numel() for t in self.Ap + self.Bp) * 2
-        d2h = sum((e - b) * n for (b, e), (_m, n, _k) in zip(self.blocks, self.sizes)) * 2
+        d2h = sum((e - b) * self.sizes[g][1] for g, b, e in self.mine) * 2
         return h2d, d2h
 
     def e2e_step(self, i):
@@ -810,7 +825,7 @@ def gather(t, world):
 
 def run_workload(cls, args, dev, world, rank, timer, peaks, local_rank):
     w = cls()
-    launches = max(args.steps, MIN_LAUNCHES)
+    launches = args.steps if args.profile else max(args.steps, MIN_LAUNCHES)
     w.setup(dev, rank, world)
     w.step(0)
     torch.cuda.synchronize()
@@ -984,10 +999,15 @@ def main():
     ap.add_argument("--no-cmp", action="store_true", help="skip the same-box library comparators")
     ap.add_argument("--no-weak", action="store_true", help="skip the replica (weak-scaling) leg at N > 1")
     ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long leg of the GEMMs")
+    ap.add_argument("--profile", action="store_true",
+                    help="for profiler captures: exactly --steps launches in one replay, kernel legs only")
     ap.add_argument("--small", action="store_true",
                     help="halve the row / matrix sizes (for profiler captures; not a bench configuration)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.profile:
+        args.replays = 1
+        args.no_e2e = args.no_cpu = args.no_cmp = args.no_weak = args.no_sustained = True
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -1010,6 +1030,7 @@ def main():
     if args.small:
         _Rows.rows = 8192
         Gemm.m = Gemm.n = Gemm.k = 4096
+        Bricks.n = 192
     timer = Timer(dist_ctx)
     names = [args.workload] + ([] if args.only else [n for n in WORKLOADS if n != args.workload])
     results = {}
@@ -1027,7 +1048,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": res["workload"],
                        "l2_policy": "inputs larger than L2, rotating buffer sets where a shard is smaller",
-                       "sharding": "named shape split across ranks (rows / output slabs / M / every group's M), "
+                       "sharding": "named shape split across ranks (rows / output slabs / M / 512-row blocks of the groups), "
                                    "no data-path collective; NCCL gathers the result for the parity check"},
             "roofline": res["roofline"], "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"],
             "timed": res["timed"], "clocks": res["clocks"], "parity": res["parity"], "parity_ok": res["parity_ok"],

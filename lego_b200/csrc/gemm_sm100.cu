@@ -1123,8 +1123,8 @@ int32_t launch_pair(const Problem& p, const Problem* dev_table, int n_problems, 
 // `dev_table` and launch on `s`.  A group without a tile order gets the reference's
 // in-group order, row-major tiles (tile_m = t / tiles_n, tile_n = t % tiles_n), which the
 // single-CTA kernel runs; CTA pairs are used when every group's order puts tiles 2p and
-// 2p + 1 in one tile column.  (Sustained A/B on one box, 16 groups: row-major / single CTA
-// 1 050-1 090 TFLOP/s, column-major / pairs 1 010-1 050; isolated launches tie.)  Allocates nothing.
+// 2p + 1 in one tile column, with 512 x 256 per pair when that holds for 4p .. 4p + 3
+// (column-major in-group orders over a multiple of four tile rows).  Allocates nothing.
 // The host table dies with the caller's frame, so the upload cannot be part of a stream
 // capture: a captured copy node would read a dead frame on every replay.
 int32_t run_grouped(EncodeFn enc, Problem* table, const void* const* A, const void* const* B, void* const* C,
@@ -1149,7 +1149,7 @@ int32_t run_grouped(EncodeFn enc, Problem* table, const void* const* A, const vo
   LEGO_CUDA_TRY(cudaMemcpyAsync(dev_table, table, (size_t)G * sizeof(Problem), cudaMemcpyHostToDevice, s));
   bool launched = false;
   const int blocks = g_tune_blocks.load();
-  if (quads && blocks == 2) {
+  if (quads && blocks != 1) {  // 512 x 256 per SM pair whenever every group's order allows it
     const int32_t st = launch_pair<true, 2>(table[0], dev_table, G, total, 0, LEGO_ACT_NONE, nullptr, 0, dev, status, s,
                                             &launched);
     if (launched) return st;

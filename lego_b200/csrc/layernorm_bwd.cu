@@ -659,7 +659,7 @@ int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int
   auto kern = ln_bwd_ring_kernel<EPT, G>;
   static PerDeviceFlag configured;
   if (!configured.test(ctx->device)) {
-    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 2048));
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 8192));  // static part: 4 KiB of reduction slots
     configured.set(ctx->device);
   }
   const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32), smem, s, P, stages, groups, gsize,
@@ -682,7 +682,7 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const int64_t room = (P.rows < kMaxPartialRows ? P.rows : kMaxPartialRows) / grid;
   if (groups > room) groups = (int)room;
   if (groups < 1) return LEGO_ERR_UNSUPPORTED;
-  const size_t budget = (size_t)ctx->smem_optin - 2048 - sizeof(BwdRingCtl) - 128;
+  const size_t budget = (size_t)ctx->smem_optin - 8192 - sizeof(BwdRingCtl) - 128;
   int stages = (int)((192 * 1024 + slot / 2) / slot);  // about 192 KiB of x and dy in flight
   if (stages < 2 * groups) stages = 2 * groups;
   if (stages > kBwdRing) stages = kBwdRing;

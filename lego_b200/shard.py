@@ -50,3 +50,31 @@ def shard_grouped_gemm(mnk: Sequence[Tuple[int, int, int]], rank: int, world: in
     """Every group's M is split across the ranks (whole-group assignment cannot
     balance ragged groups); returns one ``[begin, end)`` row block per group."""
     return [split_range(m, rank, world, tile_m) for m, _n, _k in mnk]
+
+
+def pack_grouped_gemm_blocks(mnk: Sequence[Tuple[int, int, int]], world: int,
+                             block_m: int = 512) -> List[List[Tuple[int, int, int]]]:
+    """Every group's M is cut into blocks of ``block_m`` rows (the last one of a group may be
+    shorter) and the blocks are packed onto the ranks, heaviest first onto the least loaded
+    rank (weight = rows x N x K).  Returns, per rank, its ``(group, row_begin, row_end)`` list
+    in group order.  Blocks of 512 rows keep every rank's problems on the GEMM's 512 x 256
+    tiles, where an even split of every group's M (128 rows per rank for M = 1024 on eight
+    ranks) would fall back to one 128-row tile per SM; ragged groups still balance to within
+    one block.  Deterministic: every rank computes the same packing."""
+    if world < 1 or block_m < 1:
+        raise ValueError("world and block_m must be >= 1")
+    blocks = []
+    for g, (m, n, k) in enumerate(mnk):
+        for b in range(0, m, block_m):
+            e = min(m, b + block_m)
+            blocks.append(((e - b) * n * k, g, b, e))
+    blocks.sort(key=lambda t: (-t[0], t[1], t[2]))
+    load = [0] * world
+    out: List[List[Tuple[int, int, int]]] = [[] for _ in range(world)]
+    for w, g, b, e in blocks:
+        r = min(range(world), key=lambda i: (load[i], i))
+        load[r] += w
+        out[r].append((g, b, e))
+    for lst in out:
+        lst.sort()
+    return out

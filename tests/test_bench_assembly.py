@@ -30,17 +30,31 @@ def test_grouped_gemm_shards_assemble_for_the_check():
     w.groups, w.k = 5, 64
     bench._cpu_setup(w)
     w.world, w.ops = world, _NoOps
+    w.packing = shard.pack_grouped_gemm_blocks(w.sizes, world, 512)
+    w.slot = max(sum((e - b) * w.sizes[g][1] for g, b, e in p) for p in w.packing)
     per_rank = []
     for rank in range(world):
-        blocks = shard.shard_grouped_gemm(w.sizes, rank, world)
-        cs = [(a[b:e].float() @ bm.float()).half() for a, bm, (b, e) in zip(w.A_host, w.B_host, blocks)]
-        per_rank.append(torch.cat([c.reshape(-1) for c in cs]))
-    assert len({t.numel() for t in per_rank}) == 1
+        cs = [(w.A_host[g][b:e].float() @ w.B_host[g].float()).half().reshape(-1) for g, b, e in w.packing[rank]]
+        slot = torch.zeros(w.slot, dtype=torch.float16)
+        flat = torch.cat(cs)
+        slot[:flat.numel()] = flat
+        per_rank.append(slot)
     ok, text = w.check(torch.cat(per_rank))
     assert ok, text
     per_rank[1][:] = 0                                        # one rank's result lost: must be noticed
     ok, _ = w.check(torch.cat(per_rank))
     assert not ok
+
+
+def test_grouped_gemm_blocks_pack_evenly():
+    from lego_b200 import configs
+    sizes, _ = configs.grouped_sizes()
+    for world in (2, 4, 8):
+        packing = shard.pack_grouped_gemm_blocks(sizes, world, 512)
+        seen = sorted((g, b, e) for p in packing for g, b, e in p)
+        assert seen == sorted((g, b, min(m, b + 512)) for g, (m, _n, _k) in enumerate(sizes) for b in range(0, m, 512))
+        loads = [sum((e - b) * sizes[g][1] for g, b, e in p) for p in packing]
+        assert max(loads) <= 1.03 * sum(loads) / world, (world, loads)
 
 
 def test_layernorm_backward_partial_column_sums_assemble():

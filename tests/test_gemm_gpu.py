@@ -257,3 +257,38 @@ def test_grouped_gemm_refuses_stream_capture():
     torch.cuda.synchronize()
     assert c.abs().max().item() == 0
     ops.device_status()
+
+
+def test_grouped_column_major_orders_take_pair_and_tall_tiles():
+    """Per-group column-major tile orders: with a multiple of four tile rows in every group
+    the persistent CTA pairs work on 512 x 256 tiles, with a multiple of two on 256 x 256,
+    and one group with an odd tile count sends the whole call to one CTA per tile.  Same
+    bits in all three (every output element is one k-ordered accumulation)."""
+    g = torch.Generator().manual_seed(47)
+    for shapes in ([(512, 512, 320), (1024, 256, 192), (512, 768, 64)],       # 4 | tile rows everywhere
+                   [(512, 512, 320), (256, 256, 192), (768, 512, 64)],       # 2 | tile rows
+                   [(512, 512, 320), (384, 256, 192)]):                      # three tile rows in a group
+        A = [(torch.randn(m, k, generator=g) / 16).half() for m, n, k in shapes]
+        B = [(torch.randn(k, n, generator=g) / 16).half() for m, n, k in shapes]
+        orders = [L.OrderBy(L.Col(m // 128, -(-n // 256))).TileBy([m // 128, -(-n // 256)]) for m, n, k in shapes]
+        Ad, Bd = [t.cuda() for t in A], [t.cuda() for t in B]
+        out = ops.lego_group_gemm_fn(Ad, Bd, orders)
+        ops.device_status()
+        plain = ops.lego_group_gemm_fn(Ad, Bd)
+        for c, p, r in zip(out, plain, O.grouped_matmul(A, B)):
+            assert rel_fro(c.cpu(), r) <= REL_FRO, shapes
+            assert torch.equal(c, p), shapes
+    # the blocks one rank of eight gets from the 16-group configuration (512-row blocks of several groups)
+    from lego_b200 import shard
+    sizes, _ = grouped_sizes()
+    A, B = grouped_input()
+    mine = shard.pack_grouped_gemm_blocks(sizes, 8, 512)[3]
+    Ad = [A[gi][b:e].cuda() for gi, b, e in mine]
+    Bd = [B[gi].cuda() for gi, b, e in mine]
+    orders = [L.OrderBy(L.Col((e - b) // 128, sizes[gi][1] // 256)).TileBy([(e - b) // 128, sizes[gi][1] // 256])
+              for gi, b, e in mine]
+    out = ops.lego_group_gemm_fn(Ad, Bd, orders)
+    ops.device_status()
+    for c, (gi, b, e) in zip(out, mine):
+        ref = A[gi][b:b + 64].float() @ B[gi].float()
+        assert rel_fro(c[:64].cpu(), ref) <= REL_FRO
