@@ -640,8 +640,64 @@ class IndexMap(Workload):
         return {"fill_i64": lambda i: bufs[i % len(bufs)].fill_(i)}
 
 
+class IndexInv(Workload):
+    """layout.inv over flat positions: the multi-index of every element (lego_eval_inv)."""
+    name = "index_inv_i64_4096x4096"
+    short = "index_inv"
+    dtype = "int64"
+    size = 1 << 24
+
+    def work(self):
+        return 8.0 * (1 + 4) * self.size        # one int64 read, rank (4) int64 written per id
+
+    def setup(self, dev, rank, world):
+        import lego_b200 as L
+        from lego_b200 import ops
+        self.ops = ops
+        self.rank, self.world = rank, world
+        self.layout = L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])
+        self.b0, self.b1 = shard.split_range(self.size, rank, world, 1024)
+        n = self.b1 - self.b0
+        self.sets = self.n_sets(40 * n)
+        g = torch.Generator().manual_seed(6)
+        self.flat_host = torch.randperm(self.size, generator=g)[self.b0:self.b1].contiguous()
+        self.flat = [self.flat_host.to(dev) for _ in range(self.sets)]
+        self.keep = [None] * (self.sets + 1)
+
+    def step(self, i):
+        self.keep[i % len(self.keep)] = self.idx = self.ops.eval_inv(self.layout, self.flat[i % self.sets])
+
+    def shard_result(self):
+        return self.idx
+
+    def check(self, full):
+        from oracle import lego_oracle as O
+        g = torch.Generator().manual_seed(6)
+        flat = torch.randperm(self.size, generator=g)
+        pick = torch.arange(0, self.size, 4099)
+        ref = O.groupby_inv(O.spec_of(self.layout), flat[pick].numpy())
+        got = full[pick.to(full.device)].cpu().numpy()
+        ok = all(bool((got[:, k] == ref[k]).all()) for k in range(4))
+        return ok, f"bit-exact on {len(pick)} sampled positions vs oracle"
+
+    def e2e_setup(self):
+        self.fp = self.flat_host.pin_memory()
+        n = self.b1 - self.b0
+        return 8 * n, 32 * n
+
+    def e2e_step(self, i):
+        return self.ops.eval_inv(self.layout, self.fp)
+
+    def cpu_pass(self):
+        from oracle import lego_oracle as O
+        spec = O.spec_of(self.layout)
+        flat = torch.randperm(self.size, generator=torch.Generator().manual_seed(6)).numpy()
+        return self.work(), _timed(lambda: O.groupby_inv(spec, flat)), "numpy GroupBy.inv over all 2^24 positions (single thread)"
+
+
 WORKLOADS = {"softmax": Softmax, "layernorm": LayerNorm, "layernorm_bwd": LayerNormBwd, "transpose": Transpose,
-             "gemm": Gemm, "gemm_e5m2": GemmE5M2, "grouped_gemm": GroupedGemm, "index_map": IndexMap, "bricks": Bricks}
+             "gemm": Gemm, "gemm_e5m2": GemmE5M2, "grouped_gemm": GroupedGemm, "index_map": IndexMap, "index_inv": IndexInv,
+             "bricks": Bricks}
 
 
 # --------------------------------------------------------------------------------------
@@ -980,7 +1036,7 @@ def _cpu_setup(w):
     elif isinstance(w, GroupedGemm):
         w.sizes, _ = inputs.grouped_sizes(w.groups, w.k)
         w.A_host, w.B_host = inputs.grouped_input(w.groups, w.k)
-    elif isinstance(w, IndexMap):
+    elif isinstance(w, (IndexMap, IndexInv)):
         w.layout = L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])
 
 

@@ -162,12 +162,13 @@ def test_brick_relayout_384_cubed(golden):
     want = x.reshape(n // b, b, n // b, b, n // b, b).permute(0, 2, 4, 1, 3, 5).contiguous()
     assert torch.equal(out.cpu().reshape(-1), want.reshape(-1))
     assert torch.equal(ops.permute(out, bricks, normal).cpu(), x)          # and back
-    # the reference's vectors: element idx sits at normal(idx) before and at bricks(idx) after
-    gn, gb = golden["layouts"]["bricks_normal_384"], golden["layouts"]["bricks_384"]
-    assert gn["ids"] == gb["ids"]
-    src_pos = torch.tensor(gn["apply"])
-    dst_pos = torch.tensor(gb["apply"])
-    assert torch.equal(out.cpu().reshape(-1)[dst_pos], x.reshape(-1)[src_pos])
+    # the reference's vectors: the element with logical index (bx, by, bz, i, j, k), i.e. voxel
+    # (8 bx + i, 8 by + j, 8 bz + k), sits at normal(idx) before the call and at bricks(idx) after
+    for name, buf in (("bricks_normal_384", x), ("bricks_384", out.cpu())):
+        gl = golden["layouts"][name]
+        bx, by, bz, i, j, k = (torch.from_numpy(v) for v in np.unravel_index(np.asarray(gl["ids"]), gl["dims"]))
+        voxel = x[bx * b + i, by * b + j, bz * b + k]
+        assert torch.equal(buf.reshape(-1)[torch.tensor(gl["apply"])], voxel), name
     # oracle on a volume it handles in seconds, several element sizes
     m = 96
     sn = L.OrderBy(L.Row(m, m, m)).TileBy([m // b] * 3, [b] * 3)
