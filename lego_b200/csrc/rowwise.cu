@@ -205,10 +205,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // G: threads per consumer group when it is one of the common sizes (constants for the
 // address arithmetic and the barrier), 0 = taken from `gsize_rt`.
-template <int OP, typename T, int G>
-__global__ void __launch_bounds__(kMaxConsumers + 32, 1)
+// EPT: values per consumer thread, 32, or 64 for rows beyond 8 Ki values so that such a row is
+// still handled by a group of 256 and a CTA keeps two rows in flight.
+template <int OP, typename T, int G, int EPT = kRingEpt>
+__global__ void __launch_bounds__(EPT > kRingEpt ? 512 + 32 : kMaxConsumers + 32, 1)
 row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int gsize_rt, uint32_t* status) {
-  constexpr int EPT = kRingEpt;
   const int gsize = G > 0 ? G : gsize_rt;
   constexpr int VEC = Elem<T>::VEC;
   constexpr int NV = EPT / VEC;
@@ -417,9 +418,9 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
   }
 }
 
-template <int OP, typename T, int G>
+template <int OP, typename T, int G, int EPT = kRingEpt>
 int32_t launch_ring_g(const RowParams& P, DeviceCtx* ctx, cudaStream_t s, int stages, int groups, int gsize, size_t smem) {
-  auto kern = row_ring_kernel<OP, T, G>;
+  auto kern = row_ring_kernel<OP, T, G, EPT>;
   static PerDeviceFlag configured;
   if (!configured.test(ctx->device)) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 4096));  // static part: reduction slots
@@ -439,10 +440,16 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const size_t row_bytes = (size_t)P.cols * sizeof(T);
   const size_t slot = (row_bytes + 127) & ~(size_t)127;
   const size_t fixed = (OP == OP_LAYERNORM ? 2 * slot : 0) + sizeof(RingCtl) + 128;
-  // threads per row: 32 values each, whole warps
-  const int per_thread = kRingEpt / VEC;  // vectors per thread
+  // threads per row: 32 values each, whole warps; 64 each once that would need more than 256 threads
+  // (one group of 512 turns one row around at a time: 16384-wide fp16 rows ran at 0.76 of the copy peak)
+  int per_thread = kRingEpt / VEC;  // vectors per thread
   const int vectors = P.cols / VEC;
   int gsize = ((vectors + per_thread - 1) / per_thread + 31) & ~31;
+  const bool wide = gsize > 256;
+  if (wide) {
+    per_thread *= 2;
+    gsize = ((vectors + per_thread - 1) / per_thread + 31) & ~31;
+  }
   if (gsize > 512) return LEGO_ERR_UNSUPPORTED;
   // Measured on B200 (16384 x 8192 fp16, 256 threads per row), same box, GB/s: one group turns
   // a row around in about 2500 cycles, so two groups (softmax: 6260; three: 5580, they fight
@@ -450,7 +457,7 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   // other widths keep the same number of consumer threads (512 / 768).  About 96 KiB of rows in
   // flight is the sweet spot (softmax 64 / 96 / 128 KiB: 6170 / 6260 / 6260; LayerNorm 48 / 96 /
   // 144 / 192 KiB: 5930 / 6390 / 6060 / 5930).
-  int groups = (OP == OP_SOFTMAX ? 512 : kMaxConsumers) / gsize;
+  int groups = (OP == OP_SOFTMAX || wide ? 512 : kMaxConsumers) / gsize;
   if (groups < 1) groups = 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
   const size_t budget = (size_t)ctx->smem_optin - 4096 - fixed;
@@ -461,6 +468,10 @@ int32_t launch_ring(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   stages -= stages % groups;  // a slot always belongs to one group
   if (stages < groups) return LEGO_ERR_UNSUPPORTED;
   const size_t smem = (size_t)stages * slot + fixed;
+  if (wide) {
+    if (gsize == 256) return launch_ring_g<OP, T, 256, 2 * kRingEpt>(P, ctx, s, stages, groups, gsize, smem);
+    return launch_ring_g<OP, T, 0, 2 * kRingEpt>(P, ctx, s, stages, groups, gsize, smem);
+  }
   switch (gsize) {
     case 64: return launch_ring_g<OP, T, 64>(P, ctx, s, stages, groups, gsize, smem);
     case 128: return launch_ring_g<OP, T, 128>(P, ctx, s, stages, groups, gsize, smem);
