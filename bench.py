@@ -866,6 +866,39 @@ class Timer:
         return float(t.item()) / 1e3, n * launches
 
 
+def host_ceiling(world, dist_ctx, seconds=0.5):
+    """What the host side allows: every rank copies pinned memory to its GPU and back on two
+    streams at once, no kernel in between.  Returns the whole-box rate in GB/s counted like the
+    bandwidth workloads' e2e figure (bytes in + bytes out over the slowest rank's time)."""
+    n = 64 << 20
+    h_in = torch.empty(n, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(n, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(n, dtype=torch.uint8, device="cuda")
+    d_out = torch.empty(n, dtype=torch.uint8, device="cuda")
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def burst(reps):
+        for _ in range(reps):
+            with torch.cuda.stream(up):
+                d_in.copy_(h_in, non_blocking=True)
+            with torch.cuda.stream(down):
+                h_out.copy_(d_out, non_blocking=True)
+    burst(2)
+    torch.cuda.synchronize()
+    reps = 8
+    if dist_ctx:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    burst(reps)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    t = torch.tensor([dt], dtype=torch.float64, device="cuda")
+    if dist_ctx:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return 2.0 * n * reps * world / float(t.item()) / 1e9
+
+
 def gather(t, world):
     """All ranks' equal-sized shards, concatenated along the first axis (NCCL over NVLink)."""
     if world == 1:
@@ -1099,6 +1132,7 @@ def main():
         results[name] = r
         if rank == 0:
             log(json.dumps({"detail": name, **r}))
+    ceiling = None if args.no_e2e else host_ceiling(world, dist_ctx)
     if rank == 0:
         res = results[args.workload]
         line = {
@@ -1116,6 +1150,11 @@ def main():
         for key in ("cpu_baseline", "comparators", "weak"):
             if key in res:
                 line[key] = res[key]
+        if ceiling is not None:
+            line["host_ceiling"] = {"value": ceiling, "unit": "GB/s",
+                                    "what": "all ranks: pinned H2D + D2H at once, no kernel; bytes in + bytes out"}
+            if res.get("e2e") and res["unit"] == "GB/s":
+                line["e2e"]["frac_of_host_ceiling"] = res["e2e"]["value"] / ceiling
         line["workloads"] = {n: brief(r) for n, r in results.items() if n != args.workload}
         print(json.dumps(line), flush=True)
     if dist_ctx:

@@ -237,7 +237,7 @@ int32_t lego_gemm_e5m2(const void* A, const void* B, void* C, int64_t M, int64_t
  *
  * workspace: device memory, 16-byte aligned, lego_gemm_workspace_bytes() bytes for the
  * current device (NULL or a smaller buffer: the call runs like lego_gemm_f16).  Its first
- * 4 KiB are flags: zero them once after allocating; every call that completes leaves
+ * 8 KiB are flags: zero them once after allocating; every call that completes leaves
  * them zero.  After a LEGO_ERR_DEVICE_TIMEOUT zero them again.  Calls that may overlap
  * on the GPU need a buffer each.                                                 */
 int64_t lego_gemm_workspace_bytes(void);
@@ -261,8 +261,10 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *   LEGO_TUNE_GEMM_LAG      0..4 k-steps by which the first accumulator block of a 512 x 256
  *                           tile leads the second at both ends of the tile (epilogue overlap)
  *   LEGO_TUNE_LNBWD_SPLIT   LayerNorm backward: rows wider than this many columns are taken by
- *                           one group of 512 threads, narrower ones by several groups          */
-enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4 };
+ *                           one group of 512 threads, narrower ones by several groups
+ *   LEGO_TUNE_PERMUTE_TILE_VECS  most 16-byte vectors per tile of the chunk-tiled permute (64 .. 6144) */
+enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
+       LEGO_TUNE_PERMUTE_TILE_VECS = 5 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

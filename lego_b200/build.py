@@ -44,7 +44,8 @@ def _headers_mtime() -> float:
 
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
-    cmd = [_nvcc(), *ARCH, *CFLAGS, "-x", "cu", "-c", os.path.join(CSRC, src), "-o", obj]
+    extra = os.environ.get("LEGO_B200_NVCC_FLAGS", "").split()   # e.g. -DNAME for an instrumented build
+    cmd = [_nvcc(), *ARCH, *CFLAGS, *extra, "-x", "cu", "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -212,25 +212,38 @@ digit_inv_flat_kernel(const __grid_constant__ DigitProgram p, FastDiv rank_div, 
   ptx::grid_dependency_wait();
   const int64_t pairs = (n_out + 1) >> 1;
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < pairs; j += step) {
-    const uint32_t e = (uint32_t)(2 * j);
-    const uint32_t i0 = fd_div(e, rank_div);
-    const uint32_t k0 = e - i0 * rank;
-    const bool wrap = k0 + 1 == rank;
-    const uint32_t i1 = wrap ? i0 + 1 : i0, k1 = wrap ? 0u : k0 + 1;
-    const uint32_t x0 = (uint32_t)in[i0];
-    const int64_t v0 = coord(k0, x0);
-    if ((int64_t)e + 1 < n_out) {
-      const uint32_t x1 = wrap ? (uint32_t)in[i1] : x0;
-      const int64_t v1 = coord(k1, x1);
-      if (vec) {
-        *reinterpret_cast<longlong2*>(out + e) = make_longlong2(v0, v1);
+  // Four pairs per thread and step: their flat ids are loaded before the first is decoded, so a
+  // thread has four independent chains in flight (one pair at a time ran at 0.62 of the copy peak).
+  constexpr int U = 4;
+  for (int64_t j0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j0 < pairs; j0 += U * step) {
+    uint32_t e[U], i0[U], k0[U], x0[U], x1[U];
+    bool wrap[U], live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t j = j0 + u * step;
+      live[u] = j < pairs;
+      e[u] = (uint32_t)(2 * (live[u] ? j : 0));
+      i0[u] = fd_div(e[u], rank_div);
+      k0[u] = e[u] - i0[u] * rank;
+      wrap[u] = k0[u] + 1 == rank;
+      x0[u] = live[u] ? (uint32_t)in[i0[u]] : 0u;
+      x1[u] = (live[u] && wrap[u] && (int64_t)e[u] + 1 < n_out) ? (uint32_t)in[i0[u] + 1] : x0[u];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      const int64_t v0 = coord(k0[u], x0[u]);
+      if ((int64_t)e[u] + 1 < n_out) {
+        const int64_t v1 = coord(wrap[u] ? 0u : k0[u] + 1, x1[u]);
+        if (vec) {
+          *reinterpret_cast<longlong2*>(out + e[u]) = make_longlong2(v0, v1);
+        } else {
+          out[e[u]] = v0;
+          out[e[u] + 1] = v1;
+        }
       } else {
-        out[e] = v0;
-        out[e + 1] = v1;
+        out[e[u]] = v0;
       }
-    } else {
-      out[e] = v0;
     }
   }
 }

@@ -418,8 +418,14 @@ struct PairBarriers {
 // Stream-K workspace: kSkFlagBytes of flags (one word per worker, CTA rank and epilogue warp;
 // zero before the first call, every call that completes leaves them zero) followed by one
 // fp32 accumulator slot per worker: [rank][block j][column 0..255][row 0..127].
-constexpr int kSkFlagBytes = 4096;
-constexpr int kSkMaxWorkers = kSkFlagBytes / (2 * 4 * 4);
+constexpr int kSkFlagBytes = 8192;
+constexpr int kSkMaxWorkers = kSkFlagBytes / (2 * 8 * 4);  // a word per CTA rank and epilogue warp
+// The pair kernel has eight epilogue warps: two per TMEM lane quarter, each taking half of
+// the 256 columns of an accumulator block.  One warp per quarter (four in all) needed about
+// 3 300 cycles per block, more than the 2 048 the MMA schedule hides, and ran a 74-tile wave
+// of one-k-step tiles in 6.7 us where the output stream alone takes 3 us.
+constexpr int P_EPI_WARPS = 8;
+constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;
 constexpr int kSkBlockFloats = BM * BN;  // one CTA's 128 x 256 accumulator
 
 struct Sched {
@@ -497,16 +503,30 @@ struct EpiSplit {
   size_t stride;
 };
 
-// One accumulator block (this warp's 32 rows x 256 columns) -> [+ peers' partial sums] ->
-// activation -> fp16 -> swizzled shared memory -> TMA store; or -> fp32 partial slot.
-__device__ __forceinline__ void epilogue_pair_block(const Problem* p, int tm, int tn, int q, int lane,
-                                                    uint32_t tmem_tile, uint8_t* warp_stage, int activation,
-                                                    uint32_t* chunk_no, const Problem** fenced, const EpiSplit& sp) {
+// One accumulator block, this warp's share (32 rows x the 128 columns of half `half`) ->
+// [+ peers' partial sums] -> activation -> fp16 -> swizzled shared memory -> TMA store; or ->
+// fp32 partial slot.  A warp has one 4 KiB staging buffer: the wait for the previous store to
+// have read it sits after the TMEM load and the conversion of the next chunk.  (Reading the
+// staged chunk back and writing it with plain 128-bit stores, whole lines per instruction, was
+// slower: 8192^3 1 130 against 1 210 TFLOP/s sustained.)
+// This warp is done reading its rows of an accumulator block: every lane's tcgen05.ld has
+// completed (wait::ld before the call); one arrival per warp on the leader CTA's barrier.
+__device__ __forceinline__ void release_accumulator(uint32_t empty_bar, int lane) {
+  ptx::tc_fence_before();
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive_cluster(empty_bar);
+}
+
+template <int ACT>
+__device__ __forceinline__ void epilogue_pair_block(const Problem* p, int tm, int tn, int q, int half, int lane,
+                                                    uint32_t tmem_tile, uint8_t* buf,
+                                                    const Problem** fenced, const EpiSplit& sp,
+                                                    uint32_t empty_bar) {
   const int row0 = tm * BM + q * 32;
   const int row = q * 32 + lane;
   if (sp.partial_out) {
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
       uint32_t r[32];
       ptx::tmem_ld_32x32(tmem_tile + c * 32, r);
       ptx::tmem_ld_wait();
@@ -514,55 +534,63 @@ __device__ __forceinline__ void epilogue_pair_block(const Problem* p, int tm, in
 #pragma unroll
       for (int i = 0; i < 32; ++i) __stcg(dst + (size_t)i * BM, __uint_as_float(r[i]));
     }
+    release_accumulator(empty_bar, lane);
     return;
   }
-  if (row0 >= p->m && sp.n_in == 0) return;  // nothing of this warp's rows exists (warp-uniform)
+  if (row0 >= p->m) {  // nothing of this warp's rows exists (warp-uniform)
+    release_accumulator(empty_bar, lane);
+    return;
+  }
   if (fenced && *fenced != p) {  // table-resident map: acquire once per problem
     if (lane == 0) ptx::tensormap_acquire(&p->tma_c);
     *fenced = p;
   }
-#pragma unroll 1
-  for (int c = 0; c < BN / EPI_CHUNK_COLS; ++c) {
-    // Chunks past the last column are not staged at all: every staged chunk commits
-    // exactly one bulk group, which is what the "at most one pending" wait below counts.
+  constexpr int CHUNKS = BN / EPI_CHUNK_COLS / 2;  // per warp: two chunks of 64 columns
+  static_assert(CHUNKS == 2, "the loads of both chunks are issued up front");
+  // TMEM -> registers takes about a thousand cycles for 64 columns (measured), whatever follows:
+  // both chunks' loads are issued before the first is converted, so the second one's latency
+  // is hidden behind the first one's conversion, staging and store.
+  uint32_t r[2][64];
+  const int c_first = half * CHUNKS;
+  ptx::tmem_ld_32x32(tmem_tile + c_first * EPI_CHUNK_COLS, r[0]);
+  ptx::tmem_ld_32x32(tmem_tile + c_first * EPI_CHUNK_COLS + 32, r[0] + 32);
+  ptx::tmem_ld_32x32(tmem_tile + (c_first + 1) * EPI_CHUNK_COLS, r[1]);
+  ptx::tmem_ld_32x32(tmem_tile + (c_first + 1) * EPI_CHUNK_COLS + 32, r[1] + 32);
+  ptx::tmem_ld_wait();
+  release_accumulator(empty_bar, lane);  // the block is in registers: the next tile's MMAs may overwrite it
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int c = c_first + k;
     const int col0 = tn * BN + c * EPI_CHUNK_COLS;
-    if (col0 >= p->n || row0 >= p->m) break;
-    uint32_t r[64];
-    ptx::tmem_ld_32x32(tmem_tile + c * EPI_CHUNK_COLS, r);
-    ptx::tmem_ld_32x32(tmem_tile + c * EPI_CHUNK_COLS + 32, r + 32);
-    uint8_t* buf = warp_stage + ((*chunk_no) & 1u) * EPI_BUF_BYTES;
-    if (lane == 0) ptx::bulk_wait_group_read<1>();  // the store that last read this buffer is done with it
-    __syncwarp();
-    ptx::tmem_ld_wait();
+    if (col0 >= p->n) break;  // chunks past the last column are not staged at all
     for (int peer = 0; peer < sp.n_in; ++peer) {
       const float* src = sp.partial_in + peer * sp.stride + (size_t)(c * EPI_CHUNK_COLS) * BM + row;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldcg(src + (size_t)i * BM));
+      for (int i = 0; i < 64; ++i) r[k][i] = __float_as_uint(__uint_as_float(r[k][i]) + __ldcg(src + (size_t)i * BM));
     }
+    uint32_t h[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      float x0 = __uint_as_float(r[k][2 * e]);
+      float x1 = __uint_as_float(r[k][2 * e + 1]);
+      if (ACT == LEGO_ACT_LEAKY_RELU) {
+        x0 = x0 >= 0.f ? x0 : 0.01f * x0;
+        x1 = x1 >= 0.f ? x1 : 0.01f * x1;
+      }
+      const __half2 hh = __floats2half2_rn(x0, x1);
+      h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+    if (lane == 0) ptx::bulk_wait_group_read<0>();  // the store that last read this buffer is done with it
+    __syncwarp();
     uint4* dst = reinterpret_cast<uint4*>(buf + lane * 128);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      uint32_t h[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float x0 = __uint_as_float(r[j * 8 + 2 * e]);
-        float x1 = __uint_as_float(r[j * 8 + 2 * e + 1]);
-        if (activation == LEGO_ACT_LEAKY_RELU) {
-          x0 = x0 >= 0.f ? x0 : 0.01f * x0;
-          x1 = x1 >= 0.f ? x1 : 0.01f * x1;
-        }
-        const __half2 hh = __floats2half2_rn(x0, x1);
-        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-      }
-      dst[j ^ (lane & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
-    }
+    for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
     ptx::fence_proxy_async();  // generic-proxy writes above -> visible to the TMA engine
     __syncwarp();
     if (lane == 0) {
       ptx::tma_store_2d(&p->tma_c, col0, row0, ptx::smem_u32(buf));
       ptx::bulk_commit_group();
     }
-    ++(*chunk_no);
   }
 }
 
@@ -576,7 +604,7 @@ __device__ __forceinline__ void fail_pair(uint32_t* status, volatile uint32_t* a
 }
 
 template <bool GROUPED, int MT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict__ table, int n_problems,
                  const __grid_constant__ Sched sched, int activation, uint32_t* status) {
   constexpr int NSTAGE = pair_stages(MT);
@@ -601,7 +629,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(ptx::smem_u32(&bars->tmem_full[a]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->tmem_empty[a]), 256);  // 128 epilogue threads of each CTA
+      ptx::mbar_init(ptx::smem_u32(&bars->tmem_empty[a]), 2 * P_EPI_WARPS);  // one arrival per epilogue warp of both CTAs
     }
     bars->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -813,8 +841,10 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
     }
   } else {
     // ---------------- epilogue (both CTAs, own rows) ----------------
-    const int q = warp & 3;
-    uint32_t chunk_no = 0;
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;    // which 128 of the 256 columns it drains
+    const int fslot = q * 2 + half;      // its flag word within a (worker, rank)
+    uint8_t* stage_buf = epi_stage + (warp - 2) * EPI_BUF_BYTES;
     const Problem* epi_fenced = nullptr;
     uint32_t acc_it = 0;
     int cursor = 0;
@@ -832,7 +862,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         if (lane == 0) {
           const long long t0 = clock64();
           for (int peer = 1; ok && peer <= item.n_peers; ++peer) {
-            const uint32_t* f = flags + ((worker + peer) * 2 + (int)rank) * 4 + q;
+            const uint32_t* f = flags + ((worker + peer) * 2 + (int)rank) * 8 + fslot;
             while (ld_acquire_gpu(f) == 0u) {
               if (*abort_flag || clock64() - t0 > loop_wait_limit(kblocks)) { ok = false; break; }
               __nanosleep(200);
@@ -841,7 +871,7 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) {
-          if (lane == 0) fail_pair(status, abort_flag, rank ^ 1u, 0x140000u | (uint32_t)q);
+          if (lane == 0) fail_pair(status, abort_flag, rank ^ 1u, 0x140000u | (uint32_t)fslot);
           break;
         }
       }
@@ -867,22 +897,26 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
                             ? slots + (size_t)(worker + 1) * worker_stride + ((size_t)rank * MT + j) * kSkBlockFloats
                             : nullptr;
         sp.stride = worker_stride;
-        epilogue_pair_block(pr, tm, tn, q, lane, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN,
-                            epi_stage + q * 2 * EPI_BUF_BYTES, activation, &chunk_no,
-                            GROUPED ? &epi_fenced : nullptr, sp);
-        ptx::tc_fence_before();
-        ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0));
+        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+        // the function arrives on this barrier as soon as the block has left TMEM
+        const uint32_t empty_bar = ptx::mapa(ptx::smem_u32(&bars->tmem_empty[acc]), 0);
+        if (activation == LEGO_ACT_LEAKY_RELU)
+          epilogue_pair_block<LEGO_ACT_LEAKY_RELU>(pr, tm, tn, q, half, lane, t_acc, stage_buf,
+                                                   GROUPED ? &epi_fenced : nullptr, sp, empty_bar);
+        else
+          epilogue_pair_block<LEGO_ACT_NONE>(pr, tm, tn, q, half, lane, t_acc, stage_buf,
+                                             GROUPED ? &epi_fenced : nullptr, sp, empty_bar);
       }
       if (!ok) break;
       if (item.partial) {
         // publish this warp's rows of the slot: every lane's stores, then the flag
         __threadfence();
         __syncwarp();
-        if (lane == 0) st_release_gpu(flags + (worker * 2 + (int)rank) * 4 + q, 1u);
+        if (lane == 0) st_release_gpu(flags + (worker * 2 + (int)rank) * 8 + fslot, 1u);
       } else if (item.n_peers > 0) {
         __syncwarp();  // every lane has read the peers' slots
         if (lane == 0)
-          for (int peer = 1; peer <= item.n_peers; ++peer) flags[((worker + peer) * 2 + (int)rank) * 4 + q] = 0u;
+          for (int peer = 1; peer <= item.n_peers; ++peer) flags[((worker + peer) * 2 + (int)rank) * 8 + fslot] = 0u;
       }
       acc_it += MT;
     }
@@ -1028,7 +1062,7 @@ int32_t configure_pair(int dev, int* max_clusters) {
                                          pair_smem_bytes(MT)));
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2, 1, 1);
-      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.blockDim = dim3(P_THREADS, 1, 1);
       cfg.dynamicSmemBytes = pair_smem_bytes(MT);
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
@@ -1065,7 +1099,8 @@ bool ids_share_columns(const Problem& p, int n) {
 }
 
 }  // namespace
-extern std::atomic<int> g_lnbwd_split;  // layernorm_bwd.cu
+extern std::atomic<int> g_lnbwd_split;      // layernorm_bwd.cu
+extern std::atomic<int> g_chunk_tile_vecs;  // permute.cu
 namespace {
 // Tuning knobs (lego_tune), process-wide.
 std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
@@ -1113,7 +1148,7 @@ int32_t launch_pair(const Problem& p, const Problem* dev_table, int n_problems, 
   const int64_t n_pair_tiles = tiles / (2 * MT);
   Sched sc = make_sched(n_pair_tiles, max_clusters, kblocks, MT, GROUPED ? nullptr : workspace, workspace_bytes);
   const int workers = sc.sk_tiles ? max_clusters : (int)(n_pair_tiles < max_clusters ? n_pair_tiles : max_clusters);
-  gemm_pair_kernel<GROUPED, MT><<<2 * workers, NUM_THREADS, pair_smem_bytes(MT), s>>>(p, dev_table, n_problems, sc,
+  gemm_pair_kernel<GROUPED, MT><<<2 * workers, P_THREADS, pair_smem_bytes(MT), s>>>(p, dev_table, n_problems, sc,
                                                                                      activation, status);
   *launched = true;
   return cuda_status(cudaGetLastError());
@@ -1280,6 +1315,7 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
   return run_gemm(A, B, C, M, N, K, trans_a, trans_b, activation, tile_order, 1, workspace, workspace_bytes, stream);
 }
 
+
 int32_t lego_tune(int32_t knob, int32_t value) {
   switch (knob) {
     case LEGO_TUNE_GEMM_BLOCKS:
@@ -1289,6 +1325,10 @@ int32_t lego_tune(int32_t knob, int32_t value) {
     case LEGO_TUNE_GEMM_STREAMK:
       if (value < 0 || value > 2) return LEGO_ERR_SIZE;
       g_tune_streamk.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_PERMUTE_TILE_VECS:
+      if (value < 64 || value > 6144) return LEGO_ERR_SIZE;
+      g_chunk_tile_vecs.store(value);
       return LEGO_OK;
     case LEGO_TUNE_LNBWD_SPLIT:
       if (value < 0) return LEGO_ERR_SIZE;

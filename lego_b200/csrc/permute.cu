@@ -69,15 +69,15 @@ struct TmaParams {
 // the input continues with the brick index along z (48 bricks = 1536 contiguous bytes),
 // the output with the rows and planes of the brick (2 KiB contiguous).
 constexpr int kChunkMaxInner = 4;
-constexpr int kChunkMaxVecs = 6144;  // 96 KiB of shared memory per tile, two tiles per SM
+constexpr int kChunkMaxVecs = 6144;  // most 16-byte vectors per tile (96 KiB of shared memory)
 struct ChunkDigit {
   uint32_t radix;
   uint32_t w_smem;   // weight in the tile's input-order run index (position in shared memory / rv)
   uint32_t w_out;    // weight in the tile's output-order run index
   uint32_t reserved;
   FastDiv fd;
-  int64_t s_in;      // strides in 16-byte vectors
-  int64_t s_out;
+  uint32_t s_in;     // strides in 16-byte vectors (a tile spans less than 2^31 of them on either side)
+  uint32_t s_out;
 };
 struct ChunkParams {
   DigitProgram p1;  // tile id -> outer coordinates
@@ -128,7 +128,7 @@ template <> struct VecT<16> { using type = uint4; };
 // ---- chunk-tiled permute ---------------------------------------------------------
 
 template <bool WIDE>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restrict__ in, uint4* __restrict__ out) {
   extern __shared__ uint4 chunk_tile[];
   __shared__ int64_t base[2];
@@ -154,7 +154,7 @@ chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restr
   // Four runs per thread and step: all their loads are issued before the first is parked.
   constexpr int UNROLL = 4;
   for (uint32_t r0 = threadIdx.x; r0 < (uint32_t)P.tile_runs; r0 += UNROLL * kThreads) {
-    int64_t off[UNROLL];
+    uint32_t off[UNROLL];
     uint32_t tw[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -167,7 +167,7 @@ chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restr
           const uint32_t q = (k + 1 < n) ? fd_div(rest, d.fd) : 0u;
           const uint32_t v = (k + 1 < n) ? rest - q * d.radix : rest;
           rest = q;
-          off[u] += (int64_t)v * d.s_in;
+          off[u] += v * d.s_in;
           w += v * d.w_out;
         }
       }
@@ -200,8 +200,7 @@ chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restr
   __syncthreads();
   // phase 2: runs in output order (contiguous global writes)
   for (uint32_t q0 = threadIdx.x; q0 < (uint32_t)P.tile_runs; q0 += kThreads) {
-    uint32_t rest = q0, r = 0;
-    int64_t off = 0;
+    uint32_t rest = q0, r = 0, off = 0;
 #pragma unroll
     for (int k = 0; k < kChunkMaxInner; ++k) {
       if (k < n) {
@@ -209,7 +208,7 @@ chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restr
         const uint32_t q = (k + 1 < n) ? fd_div(rest, d.fd) : 0u;
         const uint32_t v = (k + 1 < n) ? rest - q * d.radix : rest;
         rest = q;
-        off += (int64_t)v * d.s_out;
+        off += v * d.s_out;
         r += v * d.w_smem;
       }
     }
@@ -688,6 +687,12 @@ bool finish_tiled(int64_t ti, int64_t to, int64_t s_out_i, int64_t s_in_o, int e
   return true;
 }
 
+}  // namespace
+// Most vectors per tile of the chunk-tiled permute (lego_tune): 3072 = 48 KiB lets three or four
+// CTAs share an SM, so that some load while others store.
+std::atomic<int> g_chunk_tile_vecs{3072};
+namespace {
+
 // Chunk-tiled plan (see ChunkParams); false when the pair of layouts has no common run of
 // whole 16-byte vectors, or nothing continues it on one of the sides.
 bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, const void* in, const void* out,
@@ -734,13 +739,14 @@ bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, cons
       if (d.in_tile) v *= d.radix;
     return v;
   };
-  for (int guard = 0; tile_vecs() > kChunkMaxVecs && guard < 16; ++guard) {
+  const int64_t max_vecs = g_chunk_tile_vecs.load();
+  for (int guard = 0; tile_vecs() > max_vecs && guard < 16; ++guard) {
     int64_t len_in = rv, len_out = rv;
     for (int j : chain_in) len_in *= ds[j].radix;
     for (int j : chain_out) len_out *= ds[j].radix;
     std::vector<int>& ch = len_in >= len_out ? chain_in : chain_out;
     D& d = ds[ch.back()];
-    const int64_t over = (tile_vecs() + kChunkMaxVecs - 1) / kChunkMaxVecs;
+    const int64_t over = (tile_vecs() + max_vecs - 1) / max_vecs;
     int64_t part = 0;
     for (int64_t p = d.radix / over; p >= 2; --p)
       if (d.radix % p == 0) { part = p; break; }
@@ -753,7 +759,14 @@ bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, cons
     ds.push_back({d.radix / part, d.sa * part, d.sb * part, false});  // the rest of the digit stays outside
     ds[ch.back()].radix = part;
   }
-  if (tile_vecs() > kChunkMaxVecs) return false;
+  if (tile_vecs() > max_vecs) return false;
+  int64_t span_in = rv, span_out = rv;  // vectors from a tile's first to its last, on either side
+  for (const D& d : ds)
+    if (d.in_tile) {
+      span_in += (d.radix - 1) * d.sa;
+      span_out += (d.radix - 1) * d.sb;
+    }
+  if (span_in >= ((int64_t)1 << 31) || span_out >= ((int64_t)1 << 31)) return false;
 
   ChunkParams& cp = pl->chunk;
   std::memset(&cp, 0, sizeof(cp));
@@ -777,8 +790,8 @@ bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, cons
       dst[k].w_smem = (uint32_t)w_smem[order[k]];
       dst[k].w_out = (uint32_t)w_out[order[k]];
       dst[k].fd = make_fastdiv((uint64_t)d.radix);
-      dst[k].s_in = d.sa;
-      dst[k].s_out = d.sb;
+      dst[k].s_in = (uint32_t)d.sa;
+      dst[k].s_out = (uint32_t)d.sb;
     }
   };
   fill(cp.by_in, by_in);

@@ -70,6 +70,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // 8192^3 GEMM, +5 % on the grouped GEMM; -1 % on the bandwidth-bound row kernels, whose
 // waits are short, so those keep the plain form.
 constexpr uint32_t kSuspendNs = 20000;
+constexpr int kShortTries = 16;
 __device__ __forceinline__ bool mbar_try_wait_long(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -89,7 +90,14 @@ __device__ __forceinline__ bool mbar_try_wait_long(uint32_t bar, uint32_t parity
 template <bool LONG = false>
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag, long long limit_cycles) {
-  if (LONG ? mbar_try_wait_long(bar, parity) : mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  if (LONG) {
+    // A wait that is about to end should not pay the wake-up of a long suspend: a few plain
+    // tries first (each may itself be suspended for a short, system-defined time), the
+    // power-saving form only for waits that really are long.
+    for (int i = 0; i < kShortTries; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+  }
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (LONG ? mbar_try_wait_long(bar, parity) : mbar_try_wait(bar, parity)) return true;

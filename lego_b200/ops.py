@@ -131,7 +131,7 @@ def device_status() -> int:
     st = _abi.lib().lego_device_status(_stream(), C.byref(detail))
     if st != 0:
         for ws in _gemm_workspaces.values():   # a kernel that gave up may have left split-K flags set
-            ws[:4096].zero_()
+            ws[:8192].zero_()
         raise _abi.LegoError(st, f"device status word 0x{detail.value:x}")
     return 0
 
@@ -159,7 +159,7 @@ def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
 
 
 # One split-K scratch buffer per (device, stream): calls on one stream are ordered, calls on
-# different streams must not share a buffer.  Flags (first 4 KiB) start at zero and every
+# different streams must not share a buffer.  Flags (first 8 KiB) start at zero and every
 # completed call leaves them zero.
 _gemm_workspaces = {}
 
@@ -174,7 +174,7 @@ def _gemm_workspace(dev: torch.device) -> torch.Tensor:
         if torch.cuda.is_current_stream_capturing():
             # memory allocated while capturing belongs to the graph: use it for this call only
             ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-            ws[:4096].zero_()
+            ws[:8192].zero_()
             return ws
         ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         _gemm_workspaces[key] = ws
