@@ -454,8 +454,7 @@ class Gemm(Workload):
         self.a_host, self.b_host = self._cast(self.a_host), self._cast(self.b_host)
         self.r0, self.r1 = shard.shard_gemm_m(self.m, rank, world)
         self.a, self.b = self.a_host[self.r0:self.r1].to(dev), self.b_host.to(dev)
-        npm, npn = -(-(self.r1 - self.r0) // 128), -(-self.n // 256)
-        self.order = ops.grouped_swizzle_layout(npm, npn, 8) if (npm % 8 == 0 or npm <= 8) else None
+        self.order = ops.default_tile_order(self.r1 - self.r0, self.n, self.k, self.a.element_size())
         self.keep = [None] * 3
 
     def step(self, i):

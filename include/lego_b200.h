@@ -259,7 +259,8 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *                           workspace is given and the tile count is not a multiple of the
  *                           resident SM pairs
  *   LEGO_TUNE_GEMM_LAG      0..4 k-steps by which the first accumulator block of a 512 x 256
- *                           tile leads the second at both ends of the tile (epilogue overlap)
+ *                           tile leads the second at the start of a tile (the second block of the
+ *                           previous tile is still being read out of tensor memory meanwhile)
  *   LEGO_TUNE_LNBWD_SPLIT   LayerNorm backward: rows wider than this many columns are taken by
  *                           one group of 512 threads, narrower ones by several groups
  *   LEGO_TUNE_PERMUTE_TILE_VECS  most 16-byte vectors per tile of the chunk-tiled permute (64 .. 6144) */

@@ -503,12 +503,6 @@ struct EpiSplit {
   size_t stride;
 };
 
-// One accumulator block, this warp's share (32 rows x the 128 columns of half `half`) ->
-// [+ peers' partial sums] -> activation -> fp16 -> swizzled shared memory -> TMA store; or ->
-// fp32 partial slot.  A warp has one 4 KiB staging buffer: the wait for the previous store to
-// have read it sits after the TMEM load and the conversion of the next chunk.  (Reading the
-// staged chunk back and writing it with plain 128-bit stores, whole lines per instruction, was
-// slower: 8192^3 1 130 against 1 210 TFLOP/s sustained.)
 // This warp is done reading its rows of an accumulator block: every lane's tcgen05.ld has
 // completed (wait::ld before the call); one arrival per warp on the leader CTA's barrier.
 __device__ __forceinline__ void release_accumulator(uint32_t empty_bar, int lane) {
@@ -517,6 +511,49 @@ __device__ __forceinline__ void release_accumulator(uint32_t empty_bar, int lane
   if (lane == 0) ptx::mbar_arrive_cluster(empty_bar);
 }
 
+// 64 fp32 accumulator columns of one row -> activation -> 32 packed fp16 pairs.
+template <int ACT>
+__device__ __forceinline__ void convert_chunk(const uint32_t* r, uint32_t* h) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    float x0 = __uint_as_float(r[2 * e]);
+    float x1 = __uint_as_float(r[2 * e + 1]);
+    if (ACT == LEGO_ACT_LEAKY_RELU) {
+      x0 = x0 >= 0.f ? x0 : 0.01f * x0;
+      x1 = x1 >= 0.f ? x1 : 0.01f * x1;
+    }
+    const __half2 hh = __floats2half2_rn(x0, x1);
+    h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+  }
+}
+
+// This warp's 32 rows x 64 fp16 columns -> its 4 KiB staging buffer (128-byte swizzle) -> TMA
+// store at (row0, col0) of C.  The buffer is reused: first wait until the store that last read
+// it has done so.
+__device__ __forceinline__ void stage_and_store(const Problem* p, uint8_t* buf, int lane, const uint32_t* h,
+                                                int col0, int row0) {
+  if (lane == 0) ptx::bulk_wait_group_read<0>();
+  __syncwarp();
+  uint4* dst = reinterpret_cast<uint4*>(buf + lane * 128);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+  ptx::fence_proxy_async();  // generic-proxy writes above -> visible to the TMA engine
+  __syncwarp();
+  if (lane == 0) {
+    ptx::tma_store_2d(&p->tma_c, col0, row0, ptx::smem_u32(buf));
+    ptx::bulk_commit_group();
+  }
+}
+
+// One accumulator block, this warp's share (32 rows x the 128 columns of half `half`) ->
+// [+ peers' partial sums] -> activation -> fp16 -> swizzled shared memory -> TMA store; or ->
+// fp32 partial slot.  A warp has one 4 KiB staging buffer: the wait for the previous store to
+// have read it sits after the TMEM load and the conversion of the next chunk.  (Reading the
+// staged chunk back and writing it with plain 128-bit stores, whole lines per instruction, was
+// slower: 8192^3 1 130 against 1 210 TFLOP/s sustained.  Reading block 1 into registers before
+// block 0's second half is stored, so that both blocks leave TMEM within a few hundred cycles
+// of each other, needs 128 + 32 live registers per thread; ten warps leave 168 and the spills
+// cost more than the earlier release gains: 1 229 against 1 291.)
 template <int ACT>
 __device__ __forceinline__ void epilogue_pair_block(const Problem* p, int tm, int tn, int q, int half, int lane,
                                                     uint32_t tmem_tile, uint8_t* buf,
@@ -569,28 +606,8 @@ __device__ __forceinline__ void epilogue_pair_block(const Problem* p, int tm, in
       for (int i = 0; i < 64; ++i) r[k][i] = __float_as_uint(__uint_as_float(r[k][i]) + __ldcg(src + (size_t)i * BM));
     }
     uint32_t h[32];
-#pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      float x0 = __uint_as_float(r[k][2 * e]);
-      float x1 = __uint_as_float(r[k][2 * e + 1]);
-      if (ACT == LEGO_ACT_LEAKY_RELU) {
-        x0 = x0 >= 0.f ? x0 : 0.01f * x0;
-        x1 = x1 >= 0.f ? x1 : 0.01f * x1;
-      }
-      const __half2 hh = __floats2half2_rn(x0, x1);
-      h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-    }
-    if (lane == 0) ptx::bulk_wait_group_read<0>();  // the store that last read this buffer is done with it
-    __syncwarp();
-    uint4* dst = reinterpret_cast<uint4*>(buf + lane * 128);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-    ptx::fence_proxy_async();  // generic-proxy writes above -> visible to the TMA engine
-    __syncwarp();
-    if (lane == 0) {
-      ptx::tma_store_2d(&p->tma_c, col0, row0, ptx::smem_u32(buf));
-      ptx::bulk_commit_group();
-    }
+    convert_chunk<ACT>(r[k], h);
+    stage_and_store(p, buf, lane, h, col0, row0);
   }
 }
 
@@ -804,11 +821,14 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
           if (ok) publish(0);
         } else {
           // Two accumulator blocks fill all of TMEM, so there is no spare buffer to hide the
-          // epilogue behind.  Instead block 0 runs `lag` k-steps ahead of block 1 at both ends
-          // of the tile: at the end block 0 completes while block 1 still has `lag` steps of
-          // MMAs to go (its drain overlaps them), and at the start of the next tile block 0's
-          // first `lag` steps run while block 1 is being drained.  In between the two blocks
-          // alternate on every k-step and a ring slot is released as soon as both have read it.
+          // epilogue behind: when a tile's MMAs end, both blocks are read out of TMEM at once
+          // (the epilogue warps hold them in registers and store afterwards).  Block 0 of the
+          // next tile starts as soon as block 0 has left TMEM and runs `lag` k-steps on its own
+          // while block 1 is still being read; block 1 then catches up on the same ring slots
+          // and from there the two alternate on every k-step, ending together.  (Staggering the
+          // end of the tile as well starves the tensor pipe: the ring has four slots, block 0's
+          // last steps would need all four, and they are released only every two blocks' worth
+          // of MMA time.)
           int lag = sched.lag < n_steps / 2 ? sched.lag : n_steps / 2;
           if (lag > NSTAGE) lag = NSTAGE;
           if (!wait_drained(0)) break;
@@ -819,20 +839,14 @@ gemm_pair_kernel(const __grid_constant__ Problem prob, const Problem* __restrict
             issue(1, t);
             release(t);
           }
-          for (int t = lag; ok && t < n_steps - lag; ++t) {
+          for (int t = lag; ok && t < n_steps; ++t) {
             if (!wait_loaded(t)) break;
             issue(0, t);
             issue(1, t);
             release(t);
           }
-          for (int t = n_steps - lag; ok && t < n_steps; ++t)
-            if (wait_loaded(t)) issue(0, t);
           if (!ok) break;
           publish(0);
-          for (int t = n_steps - lag; t < n_steps; ++t) {
-            issue(1, t);
-            release(t);
-          }
           publish(1);
         }
         kcount += (uint32_t)n_steps;

@@ -29,7 +29,7 @@ from .lowering import lower, lower_optional
 __all__ = [
     "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "transpose", "softmax",
     "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "layer_norm_bwd", "matmul", "lego_group_gemm_fn",
-    "grouped_swizzle_layout", "row_tiling_layout", "device_status", "tune", "selftest_bounded_wait",
+    "grouped_swizzle_layout", "default_group_m", "default_tile_order", "row_tiling_layout", "device_status", "tune", "selftest_bounded_wait",
 ]
 
 
@@ -519,11 +519,41 @@ def _operand(t: torch.Tensor):
     return t.contiguous(), 0
 
 
+# Rows of 128 x 256 tiles walked together by the default tile order.  One wave of the
+# persistent kernel covers 74 tiles of 512 x 256: with GROUP_M tile rows per group it reads a
+# GROUP_M * 128-row panel of A and 74 * 512 / (GROUP_M * 128) tile columns of B.  GROUP_M = 8
+# (the value the reference tunes for its own kernel) makes a wave read every column of an
+# 8192-wide B; 32 makes the wave nearly square (A panel 64 MiB + B 36 MiB for K = 8192 in
+# fp16) and the A panel stays in the 126 MB L2 from wave to wave: 8192^3 fp16 sustained
+# 1 224 -> 1 271 TFLOP/s on one box, DRAM reads per launch 1.17 GB -> about a third.
+_A_PANEL_BYTES = 72 << 20
+
+
+def default_group_m(num_pid_m: int, k: int, elem_bytes: int) -> int:
+    """GROUP_M of the default tile order: the largest of 32, 16, 8 that tiles ``num_pid_m``
+    and whose A panel (GROUP_M * 128 rows x K) stays within about half of L2."""
+    for gm in (32, 16, 8):
+        if (num_pid_m % gm == 0 or num_pid_m <= gm) and (gm == 8 or min(gm, num_pid_m) * 128 * k * elem_bytes <= _A_PANEL_BYTES):
+            return gm
+    return 8
+
+
+def default_tile_order(m: int, n: int, k: int, elem_bytes: int = 2, group_m: Optional[int] = None) -> Optional[GroupBy]:
+    """The tile order ``matmul`` uses when the caller passes none: the reference's grouped
+    swizzle over the grid of 128 x 256 tiles, or None (row-major) when GROUP_M does not tile it."""
+    npm, npn = -(-m // 128), -(-n // 256)
+    gm = default_group_m(npm, k, elem_bytes) if group_m is None else group_m
+    if npm % gm == 0 or npm <= gm:
+        return grouped_swizzle_layout(npm, npn, gm)
+    return None
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: Optional[GroupBy] = None,
-           group_m: int = 8) -> torch.Tensor:
+           group_m: Optional[int] = None) -> torch.Tensor:
     """``C = act(A @ B)``: fp16 in, fp32 accumulate, fp16 out.  Either operand may
     be a ``.T`` view.  Tile order defaults to the reference's grouped swizzle with
-    ``GROUP_M = group_m`` when it is a bijection for the tile grid, row-major otherwise."""
+    ``GROUP_M = group_m`` (chosen by ``default_group_m`` when None) when it is a bijection
+    for the tile grid, row-major otherwise."""
     if a.dtype != b.dtype or a.dtype not in (torch.float16, torch.float8_e5m2):
         raise ValueError("matmul supports float16 operands, or float8_e5m2 operands (fp16 result)")
     fn = "lego_gemm_f16" if a.dtype == torch.float16 else "lego_gemm_e5m2"
@@ -557,8 +587,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
         for r0, r1 in _row_blocks(m, max(k * a.element_size(), n * 2), multiple=256):
             pipe.feed(ad[r0:r1], a[r0:r1])
             pipe.ready()
-            npm, npn = -(-(r1 - r0) // 128), -(-n // 256)
-            order = grouped_swizzle_layout(npm, npn, group_m) if (npm % group_m == 0 or npm <= group_m) else None
+            order = default_tile_order(r1 - r0, n, k, a.element_size(), group_m)
             _abi.check(call(ad[r0:r1].data_ptr(), b_st.data_ptr(), c[r0:r1].data_ptr(), r1 - r0, n, k,
                             0, tb, act, lower_optional(order), ws.data_ptr(), ws.numel(), _stream()), fn)
             pipe.drain(c_h[r0:r1], c[r0:r1])
@@ -569,9 +598,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", tile_order: O
     b_st, tb = _operand(bd)
     c = torch.empty((m, n), dtype=torch.float16, device=ad.device)
     if tile_order is None:
-        npm, npn = -(-m // 128), -(-n // 256)
-        if npm % group_m == 0 or npm <= group_m:
-            tile_order = grouped_swizzle_layout(npm, npn, group_m)
+        tile_order = default_tile_order(m, n, k, a.element_size(), group_m)
     ws = _gemm_workspace(ad.device)
     _abi.check(getattr(lib, fn + "_ws")(a_st.data_ptr(), b_st.data_ptr(), c.data_ptr(), m, n, k, ta, tb, act,
                                         lower_optional(tile_order), ws.data_ptr(), ws.numel(), _stream()), fn)

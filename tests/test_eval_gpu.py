@@ -58,6 +58,30 @@ def test_full_size_domains_are_bijections():
         assert np.array_equal(flat.cpu().numpy()[sel], ref)
 
 
+def test_inv_ragged_counts_ranks_and_unaligned_output():
+    """inv on position counts that are no multiple of a warp, for ranks 2, 3 and 4, into an output
+    that starts 16-byte aligned (thread-per-position kernel) and 8 bytes off (per-word kernel)."""
+    import ctypes
+    from lego_b200 import _abi
+    from lego_b200.lowering import lower
+    lays = (L.OrderBy(L.Col(96, 80)).TileBy([96, 80]), L.OrderBy(L.Row(24, 20, 18)).TileBy([24, 20, 18]),
+            L.OrderBy(L.Col(64, 96)).TileBy([8, 6], [8, 16]))
+    for lay in lays:
+        size, rank = lay.size(), len(lay.dims())
+        for n in (4096, 4097, 4127, 7001):
+            sel = torch.randint(0, size, (n,), generator=torch.Generator().manual_seed(n)).numpy()
+            flat = O.groupby_apply(spec_of(lay), unravel(sel, lay.dims()))
+            exp = np.stack(unravel(sel, lay.dims()), axis=1)
+            dev = torch.from_numpy(flat).cuda()
+            assert np.array_equal(ops.eval_inv(lay, dev).cpu().numpy(), exp), (rank, n)
+            room = torch.zeros(n * rank + 1, dtype=torch.int64, device="cuda")
+            off = room[1:].view(n, rank)                       # 8 bytes past a 16-byte boundary
+            desc = lower(lay)
+            _abi.check(_abi.lib().lego_eval_inv(ctypes.byref(desc), dev.data_ptr(), off.data_ptr(), n, None),
+                       "lego_eval_inv")
+            assert np.array_equal(off.cpu().numpy(), exp), (rank, n)
+
+
 def test_wide_index_space_uses_64_bit_arithmetic():
     lay = L.OrderBy(L.Col(1 << 17, 1 << 16)).TileBy([1 << 10, 1 << 9], [128, 128])   # 2^33 elements
     begin = (1 << 32) + 12345
