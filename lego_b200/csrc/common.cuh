@@ -42,7 +42,11 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
+#ifdef LEGO_NO_PDL
+  cfg.numAttrs = 0;
+#else
   cfg.numAttrs = 1;
+#endif
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 

@@ -739,6 +739,8 @@ bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, cons
       if (d.in_tile) v *= d.radix;
     return v;
   };
+  // (Smaller tiles for small inputs, to fill the last wave, were slower: an eighth of the 384^3
+  // bricks in 768-vector tiles 23.0 us against 19.8 us in 3072-vector tiles.)
   const int64_t max_vecs = g_chunk_tile_vecs.load();
   for (int guard = 0; tile_vecs() > max_vecs && guard < 16; ++guard) {
     int64_t len_in = rv, len_out = rv;
