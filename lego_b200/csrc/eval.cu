@@ -198,27 +198,27 @@ template <int RANK>
 __global__ void __launch_bounds__(256)
 digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __restrict__ in,
                       int64_t* __restrict__ out, int64_t n) {
-  __shared__ TermRegs st[LEGO_MAX_TERMS];
-  __shared__ int first[LEGO_MAX_RANK + 1];
   __shared__ __align__(16) int64_t turn[8][32 * RANK];
-  if (threadIdx.x < p.n_terms) st[threadIdx.x] = load_term(p, threadIdx.x, true);
-  if (threadIdx.x == 0) {
+  // Term ranges per coordinate; the terms themselves are read from the parameter bank at
+  // warp-uniform indices (no shared-memory or L1 traffic for them).
+  int lo[RANK + 1];
+  {
     int t = 0;
+#pragma unroll
     for (int k = 0; k <= RANK; ++k) {
       while (t < p.n_terms && p.t[t].dst < k) ++t;
-      first[k] = t;
+      lo[k] = t;
     }
   }
-  __syncthreads();
-  int lo[RANK + 1];
-#pragma unroll
-  for (int k = 0; k <= RANK; ++k) lo[k] = first[k];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   int64_t* mine = turn[wib];
   ptx::grid_dependency_wait();
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t runs = (n + 31) >> 5;
   constexpr int CHUNKS = RANK * 16;  // 16-byte words a full warp's coordinates make
+  // Even ranks park whole 16-byte words; word w sits at w ^ ((w >> 3) & 1), which spreads a
+  // quarter-warp's words (32 bytes apart for rank 4) over all eight 16-byte bank groups.
+  constexpr bool PAIRS = RANK % 2 == 0;
   int64_t run = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   uint32_t x_next = 0;
   if (run < runs && run * 32 + lane < n) x_next = (uint32_t)in[run * 32 + lane];
@@ -226,21 +226,33 @@ digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __r
     const uint32_t x = x_next;
     const int64_t nxt = (run + n_warps) * 32 + lane;
     if (nxt < n) x_next = (uint32_t)in[nxt];  // the next run's position is in flight while this one is decoded
+    int64_t c[RANK];
 #pragma unroll
     for (int k = 0; k < RANK; ++k) {
       uint32_t acc = 0;
-      for (int t = lo[k]; t < lo[k + 1]; ++t) acc += eval_term(st[t], x);
-      mine[lane * RANK + k] = (int64_t)acc;
+      for (int t = lo[k]; t < lo[k + 1]; ++t) acc += eval_term(load_term(p, t, true), x);
+      c[k] = (int64_t)acc;
+    }
+    if (PAIRS) {
+#pragma unroll
+      for (int h = 0; h < RANK / 2; ++h) {
+        const int w = lane * (RANK / 2) + h;
+        *reinterpret_cast<longlong2*>(mine + 2 * (w ^ ((w >> 3) & 1))) = make_longlong2(c[2 * h], c[2 * h + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < RANK; ++k) mine[lane * RANK + k] = c[k];
     }
     __syncwarp();
     const int64_t word0 = run * 32 * RANK;             // first output word of this run
     const int64_t words = (n - run * 32 < 32 ? n - run * 32 : 32) * RANK;
 #pragma unroll
-    for (int c = lane; c < CHUNKS; c += 32) {
-      if (2 * c + 1 < words) {
-        *reinterpret_cast<longlong2*>(out + word0 + 2 * c) = *reinterpret_cast<const longlong2*>(mine + 2 * c);
-      } else if (2 * c < words) {
-        out[word0 + 2 * c] = mine[2 * c];
+    for (int w = lane; w < CHUNKS; w += 32) {
+      const int at = PAIRS ? 2 * (w ^ ((w >> 3) & 1)) : 2 * w;
+      if (2 * w + 1 < words) {
+        *reinterpret_cast<longlong2*>(out + word0 + 2 * w) = *reinterpret_cast<const longlong2*>(mine + at);
+      } else if (2 * w < words) {
+        out[word0 + 2 * w] = mine[at];
       }
     }
     __syncwarp();
