@@ -122,11 +122,48 @@ int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out);
 /* Plan of a permute call, for inspection: which kernel lego_permute would pick
  * (0 staged interpreter, 1 output-order gather, 2 shared-memory tiled transpose,
  * 3 TMA-fed tiled transpose, 4 chunk-tiled permute for layouts that share a
- * contiguous run, e.g. a volume into bricks) and the contiguous extents it reads
- * and writes, in elements.                                                     */
+ * contiguous run, e.g. a volume into bricks, 5 the same pairs moved by the copy
+ * engine alone: one tiled TMA load and one tiled TMA store per box of digits; if
+ * the driver refuses a tensor map at call time, kernel 4 runs instead) and the
+ * contiguous extents it reads and writes, in elements.                         */
 int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
                           const lego_layout_t* tile_order, int32_t* kernel_kind, int64_t* tile_in,
                           int64_t* tile_out);
+
+/* The DMA plan of a pair of layouts (kernel 5 of lego_permute_plan), for inspection and
+ * for checking the planner on a host without a GPU: the two tensor maps as the encoder
+ * receives them (dimension 0 innermost; strides and sizes in elements of elem_bytes,
+ * which is 8 for 16-byte data) and the digits of the tile id with the tensor-map
+ * coordinate each one moves on either side.  Tile t = sum_j d_j * prod_{i<j} radix_i is
+ * the box at load coordinates  c[outer[j].ld_dim] += d_j * outer[j].ld_mul  and store
+ * coordinates  c[outer[j].st_dim] += d_j * outer[j].st_mul;  both boxes hold the same
+ * bytes in the same order.  LEGO_ERR_UNSUPPORTED when the pair is not moved this way.
+ * No counterpart in the reference.                                              */
+typedef struct lego_dma_side {
+  int32_t rank;
+  int32_t reserved;
+  int64_t size[5];
+  int64_t stride[5];
+  int64_t box[5];
+} lego_dma_side_t;
+
+typedef struct lego_dma_outer {
+  int64_t radix;
+  int32_t ld_dim, ld_mul, st_dim, st_mul;
+  int32_t reserved;
+} lego_dma_outer_t;
+
+typedef struct lego_dma_plan {
+  int32_t elem_bytes;
+  int32_t n_outer;
+  int64_t n_tiles;
+  int64_t tile_bytes;
+  lego_dma_side_t load, store;
+  lego_dma_outer_t outer[8];
+} lego_dma_plan_t;
+
+int32_t lego_permute_dma_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
+                              lego_dma_plan_t* plan);
 
 /* ---- index-map evaluator -------------------------------------------------- */
 
@@ -263,9 +300,12 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *                           previous tile is still being read out of tensor memory meanwhile)
  *   LEGO_TUNE_LNBWD_SPLIT   LayerNorm backward: rows wider than this many columns are taken by
  *                           one group of 512 threads, narrower ones by several groups
- *   LEGO_TUNE_PERMUTE_TILE_VECS  most 16-byte vectors per tile of the chunk-tiled permute (64 .. 6144) */
+ *   LEGO_TUNE_PERMUTE_TILE_VECS  most 16-byte vectors per tile of the chunk-tiled permute (64 .. 6144)
+ *   LEGO_TUNE_PERMUTE_DMA_TILE   most bytes per box of the DMA permute (2048 .. 49152); 0 = the
+ *                           chunk-tiled kernel takes those pairs of layouts instead
+ *   LEGO_TUNE_PERMUTE_DMA_CTAS   CTAs per SM of the DMA permute (1 .. 4) */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
-       LEGO_TUNE_PERMUTE_TILE_VECS = 5 };
+       LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

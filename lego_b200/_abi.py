@@ -28,6 +28,10 @@ ACT_LEAKY_RELU = 1
 TUNE_GEMM_BLOCKS = 1
 TUNE_GEMM_STREAMK = 2
 TUNE_GEMM_LAG = 3
+TUNE_LNBWD_SPLIT = 4
+TUNE_PERMUTE_TILE_VECS = 5
+TUNE_PERMUTE_DMA_TILE = 6
+TUNE_PERMUTE_DMA_CTAS = 7
 
 ERR_CUDA_BASE = 1000
 ERR_DEVICE_TIMEOUT = 2001
@@ -58,6 +62,21 @@ class Folded(C.Structure):
                 ("terms", Term * MAX_TERMS)]
 
 
+class DmaSide(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("reserved", C.c_int32),
+                ("size", C.c_int64 * 5), ("stride", C.c_int64 * 5), ("box", C.c_int64 * 5)]
+
+
+class DmaOuter(C.Structure):
+    _fields_ = [("radix", C.c_int64), ("ld_dim", C.c_int32), ("ld_mul", C.c_int32),
+                ("st_dim", C.c_int32), ("st_mul", C.c_int32), ("reserved", C.c_int32)]
+
+
+class DmaPlan(C.Structure):
+    _fields_ = [("elem_bytes", C.c_int32), ("n_outer", C.c_int32), ("n_tiles", C.c_int64),
+                ("tile_bytes", C.c_int64), ("load", DmaSide), ("store", DmaSide), ("outer", DmaOuter * 8)]
+
+
 LayoutP = C.POINTER(Layout)
 
 # name -> (restype, argtypes); must list every function include/lego_b200.h declares.
@@ -66,6 +85,7 @@ SIGNATURES = {
     "lego_layout_fold": (C.c_int32, [LayoutP, C.POINTER(Folded)]),
     "lego_permute_plan": (C.c_int32, [C.c_int32, LayoutP, LayoutP, LayoutP, C.POINTER(C.c_int32),
                                       C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "lego_permute_dma_plan": (C.c_int32, [C.c_int32, LayoutP, LayoutP, C.POINTER(DmaPlan)]),
     "lego_eval_apply": (C.c_int32, [LayoutP, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lego_eval_inv": (C.c_int32, [LayoutP, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lego_eval_range": (C.c_int32, [LayoutP, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),

@@ -1115,6 +1115,8 @@ bool ids_share_columns(const Problem& p, int n) {
 }  // namespace
 extern std::atomic<int> g_lnbwd_split;      // layernorm_bwd.cu
 extern std::atomic<int> g_chunk_tile_vecs;  // permute.cu
+extern std::atomic<int> g_dma_tile_bytes;   // permute.cu
+extern std::atomic<int> g_dma_ctas_per_sm;  // permute.cu
 namespace {
 // Tuning knobs (lego_tune), process-wide.
 std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
@@ -1343,6 +1345,14 @@ int32_t lego_tune(int32_t knob, int32_t value) {
     case LEGO_TUNE_PERMUTE_TILE_VECS:
       if (value < 64 || value > 6144) return LEGO_ERR_SIZE;
       g_chunk_tile_vecs.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_PERMUTE_DMA_TILE:
+      if (value != 0 && (value < 2048 || value > 49152)) return LEGO_ERR_SIZE;
+      g_dma_tile_bytes.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_PERMUTE_DMA_CTAS:
+      if (value < 1 || value > 4) return LEGO_ERR_SIZE;
+      g_dma_ctas_per_sm.store(value);
       return LEGO_OK;
     case LEGO_TUNE_LNBWD_SPLIT:
       if (value < 0) return LEGO_ERR_SIZE;

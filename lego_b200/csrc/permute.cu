@@ -22,7 +22,7 @@ namespace lego {
 
 namespace {
 
-enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2, KIND_TMA = 3, KIND_CHUNK = 4 };
+enum { KIND_STAGED = 0, KIND_GATHER = 1, KIND_TILED = 2, KIND_TMA = 3, KIND_CHUNK = 4, KIND_DMA = 5 };
 
 constexpr int kThreads = 256;
 constexpr int kVecPerThread = 4;
@@ -91,6 +91,37 @@ struct ChunkParams {
   ChunkDigit by_out[kChunkMaxInner];  // the same digits, output-fastest first
 };
 
+// DMA permute: the same pairs of layouts as the chunk-tiled kernel (a common contiguous run
+// shorter than a line), moved by the copy engine alone.  A tile is a box of digits; ONE tensor
+// map per side describes the whole buffer with those digits as dimensions, in the same order on
+// both sides (the order of the box in shared memory), each with its own stride on that side.  A
+// tile is then one tiled TMA load (rows as long as the input allows) and one tiled TMA store
+// from the same bytes: no thread touches the data.  Example, the 384^3 volume into 8^3 bricks:
+// the box is [z 8][y 8][bx 8][x 8] floats = 16 KiB; the load map sees it as (x + bx merged: 64
+// contiguous floats, y, z), the store map as (x, bx, y + z merged, by + bz merged).
+constexpr int kDmaMaxOuter = 8;
+struct DmaOuter {   // a digit of the tile id
+  FastDiv fd;
+  uint32_t radix;
+  int32_t ld_dim, ld_mul;  // tensor-map dimension it moves on the load side, coordinate units per step
+  int32_t st_dim, st_mul;  // the same on the store side
+};
+struct DmaParams {
+  int64_t n_tiles;
+  int32_t n_outer;
+  int32_t ld_rank, st_rank;
+  int32_t stages;
+  uint32_t tile_bytes;  // bytes of one box
+  uint32_t slot_bytes;  // pitch of the ring slots (tile_bytes rounded up to 128)
+  DmaOuter o[kDmaMaxOuter];
+};
+struct DmaMapSpec {     // host side: the arguments of the tensor-map encoder, in elements
+  int rank;
+  uint64_t size[5];
+  uint64_t stride[5];
+  uint32_t box[5];
+};
+
 struct Plan {
   int kind;
   bool by_order;  // tile ids are the ids of the caller's tile_order layout
@@ -102,6 +133,9 @@ struct Plan {
   TmaParams tma;
   GatherParams gather;
   ChunkParams chunk;
+  DmaParams dma;
+  DmaMapSpec dma_ld, dma_st;
+  int dma_elem_bytes;  // element size the maps are written in (16-byte elements count as two of 8)
   StagedProgram staged_src, staged_dst;
 };
 
@@ -214,6 +248,125 @@ chunk_permute_kernel(const __grid_constant__ ChunkParams P, const uint4* __restr
     }
     const uint32_t pos = r * (uint32_t)rv, tw = (q0 * (uint32_t)rv) & mask;
     for (int x = 0; x < rv; ++x) __stcs(dst + off + x, chunk_tile[(pos + x) ^ tw]);
+  }
+}
+
+// ---- DMA permute: tiled TMA load -> shared memory -> tiled TMA store ------------------
+//
+// Two threads per CTA do everything.  The loader walks this CTA's tiles (dealt round-robin),
+// waits for a free ring slot and issues one TMA load per tile; the storer waits for the
+// bytes, issues one TMA store from the same slot, and hands the slot back once the store has
+// read it (at most kDmaStoresInFlight stores are reading at a time, the rest of the ring is
+// loads in flight).  Several CTAs share an SM, so that issue latencies overlap.
+
+constexpr int kDmaThreads = 64;
+constexpr int kDmaMaxStages = 12;
+constexpr int kDmaStoresInFlight = 2;
+constexpr long long kDmaWaitLimit = 2000000000LL;  // SM cycles, about a second
+
+struct DmaCtl {
+  uint64_t full[kDmaMaxStages];
+  uint64_t empty[kDmaMaxStages];
+  uint32_t abort_flag;
+};
+
+template <bool STORE>
+__device__ __forceinline__ void dma_coords(const DmaParams& P, uint32_t t, int32_t (&c)[5]) {
+#pragma unroll
+  for (int k = 0; k < 5; ++k) c[k] = 0;
+  uint32_t rest = t;
+#pragma unroll
+  for (int j = 0; j < kDmaMaxOuter; ++j) {
+    if (j < P.n_outer) {
+      const DmaOuter& o = P.o[j];
+      const uint32_t q = (j + 1 < P.n_outer) ? fd_div(rest, o.fd) : 0u;
+      const uint32_t v = rest - q * o.radix;
+      rest = q;
+      const int dim = STORE ? o.st_dim : o.ld_dim;
+      const int32_t add = (int32_t)v * (STORE ? o.st_mul : o.ld_mul);
+#pragma unroll
+      for (int k = 0; k < 5; ++k) c[k] += (k == dim) ? add : 0;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kDmaThreads)
+dma_permute_kernel(const __grid_constant__ CUtensorMap ld_map, const __grid_constant__ CUtensorMap st_map,
+                   const __grid_constant__ DmaParams P, uint32_t* status) {
+  extern __shared__ uint8_t dsm_raw[];
+  const uint32_t raw = ptx::smem_u32(dsm_raw);
+  uint8_t* slots = dsm_raw + (((raw + 127u) & ~127u) - raw);
+  DmaCtl* ctl = reinterpret_cast<DmaCtl*>(slots + (size_t)P.stages * P.slot_bytes);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const int stages = P.stages;
+  const int64_t my_tiles =
+      P.n_tiles > blockIdx.x ? (P.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 1);
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  __syncthreads();
+  ptx::launch_dependents();
+  ptx::grid_dependency_wait();
+
+  if (threadIdx.x == 0) {
+    // ---------------- loader ----------------
+    int s = 0;
+    uint32_t use = 0;  // times the ring has wrapped
+    uint32_t t = blockIdx.x;
+    int64_t issued = 0;
+    for (int64_t n = 0; n < my_tiles; ++n, t += gridDim.x) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kDmaWaitLimit)) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, 0xA0000u | (uint32_t)s);
+        break;
+      }
+      int32_t c[5];
+      dma_coords<false>(P, t, c);
+      const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+      ptx::mbar_arrive_expect_tx(full, P.tile_bytes);
+      ptx::tma_load_nd(P.ld_rank, ptx::smem_u32(slots + (size_t)s * P.slot_bytes), &ld_map, c, full);
+      ++issued;
+      if (++s == stages) { s = 0; ++use; }
+    }
+    if (*abort_flag) {
+      // leave no load of ours in flight: the last one issued into every slot
+      uint32_t never = 0;
+      for (int k = 0; k < stages && k < issued; ++k) {
+        const int64_t last = issued - 1 - k;  // the k-th most recent load
+        ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[last % stages]), (uint32_t)((last / stages) & 1), &never,
+                               kDmaWaitLimit);
+      }
+    }
+  } else if (threadIdx.x == 32) {
+    // ---------------- storer ----------------
+    int s = 0, s_free = 0;
+    uint32_t use = 0;
+    uint32_t t = blockIdx.x;
+    for (int64_t n = 0; n < my_tiles; ++n, t += gridDim.x) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kDmaWaitLimit)) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, 0xB0000u | (uint32_t)s);
+        break;
+      }
+      int32_t c[5];
+      dma_coords<true>(P, t, c);
+      ptx::tma_store_nd(P.st_rank, &st_map, c, ptx::smem_u32(slots + (size_t)s * P.slot_bytes));
+      ptx::bulk_commit_group();
+      ptx::bulk_wait_group_read<kDmaStoresInFlight>();
+      if (n >= kDmaStoresInFlight) {  // the store of tile n - kDmaStoresInFlight has read its slot
+        ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s_free]));
+        if (++s_free == stages) s_free = 0;
+      }
+      if (++s == stages) { s = 0; ++use; }
+    }
+    ptx::bulk_wait_group<0>();  // shared memory must outlive the stores, and the writes end with the grid
   }
 }
 
@@ -691,6 +844,9 @@ bool finish_tiled(int64_t ti, int64_t to, int64_t s_out_i, int64_t s_in_o, int e
 // Most vectors per tile of the chunk-tiled permute (lego_tune): 3072 = 48 KiB lets three or four
 // CTAs share an SM, so that some load while others store.
 std::atomic<int> g_chunk_tile_vecs{3072};
+// DMA permute (lego_tune): most bytes per tile, 0 = never use it; CTAs per SM.
+std::atomic<int> g_dma_tile_bytes{16384};
+std::atomic<int> g_dma_ctas_per_sm{2};
 namespace {
 
 // Chunk-tiled plan (see ChunkParams); false when the pair of layouts has no common run of
@@ -845,8 +1001,173 @@ bool plan_chunk(const std::vector<PairDigit>& merged, int64_t size, int eb, cons
   return true;
 }
 
+// DMA plan (see DmaParams); false when the pair has no common run of whole 16-byte vectors,
+// when nothing continues it on one of the sides, or when one of the sides needs a tensor map
+// of more than five dimensions.
+bool plan_dma(const std::vector<PairDigit>& merged, int64_t size, int eb, const void* in, const void* out,
+              Plan* pl) {
+  const int64_t max_tile = g_dma_tile_bytes.load();
+  if (max_tile <= 0 || eb > 16 || !aligned(in, 16) || !aligned(out, 16) || size >= ((int64_t)1 << 40)) return false;
+  const int64_t unit = eb == 16 ? 2 : 1;  // 16-byte elements are written as two 8-byte ones
+  const int64_t ebx = eb == 16 ? 8 : eb;
+  struct D { int64_t radix, sa, sb, box; bool in_tile; };
+  std::vector<D> ds;
+  int c = -1;
+  for (const PairDigit& d : merged) {
+    if (d.radix == 1) continue;
+    if (d.sa == 1 && d.sb == 1) {
+      c = (int)ds.size();
+      ds.push_back({d.radix * unit, 1, 1, d.radix * unit, true});
+    } else {
+      ds.push_back({d.radix, d.sa * unit, d.sb * unit, 1, false});
+    }
+  }
+  if (c < 0) return false;
+  const int64_t run = ds[c].radix;  // elements of ebx bytes
+  if ((run * ebx) % 16 || run * ebx >= 128 || run > 256) return false;  // whole lines: the vector copy is coalesced already
+  const int64_t budget = max_tile / ebx;  // elements per tile
+  std::vector<int> order{c};              // the tile's digits, fastest in shared memory first
+  int64_t tile = run, len_i = run, len_o = run, piece_i = run, piece_o = run;
+  // Take the next digit of a side's contiguous chain into the tile, whole or the largest part
+  // (a divisor of its radix) that keeps the piece within max_len and the tile within budget.
+  // (keep_out_head: leave the digit that continues the run on the output side to that side.)
+  auto extend = [&](bool in_side, int64_t max_len, bool keep_out_head) {
+    int64_t& len = in_side ? len_i : len_o;
+    for (size_t j = 0; j < ds.size(); ++j) {
+      if (ds[j].in_tile || (in_side ? ds[j].sa : ds[j].sb) != len) continue;
+      if (keep_out_head && ds[j].sb == len_o) return false;
+      int64_t e = 0;
+      for (int64_t p = ds[j].radix; p >= 2; --p)
+        if (ds[j].radix % p == 0 && len * p <= max_len && tile * p <= budget) { e = p; break; }
+      if (e < 2) return false;
+      ds[j].box = e;
+      ds[j].in_tile = true;
+      order.push_back((int)j);
+      tile *= e;
+      (in_side ? piece_i : piece_o) *= e;
+      len = e == ds[j].radix ? len * e : -1;  // a digit taken in part ends the chain
+      return true;
+    }
+    return false;
+  };
+  // Rows of up to 256 bytes for the loads first (the copy engine fetches a box row by row),
+  // then whatever continues the run on the output side, then longer load rows if room is left.
+  const int64_t row = 256 / ebx;
+  int n_in = 0, n_out = 0;
+  while (len_i > 0 && len_i < row && extend(true, row, true)) ++n_in;
+  while (len_o > 0 && tile < budget && extend(false, budget, false)) ++n_out;
+  if (len_i < 0) {
+    // the input chain ended with part of a digit: a larger part of it, if room is left
+    const int j = [&] { int last = -1; for (int k : order) if (ds[k].box != ds[k].radix) { last = k; break; } return last; }();
+    if (j >= 0 && ds[j].sa * ds[j].box == piece_i) {
+      for (int64_t p = ds[j].radix; p > ds[j].box; --p)
+        if (ds[j].radix % p == 0 && piece_i / ds[j].box * p <= 256 && tile / ds[j].box * p <= budget) {
+          tile = tile / ds[j].box * p;
+          piece_i = piece_i / ds[j].box * p;
+          ds[j].box = p;
+          if (p == ds[j].radix) len_i = piece_i;
+          break;
+        }
+    }
+  }
+  while (len_i > 0 && tile < budget && extend(true, 256, false)) ++n_in;
+  if (n_in == 0 || n_out == 0) return false;
+  if (tile * ebx < 2048) return false;  // too little per copy to keep the engine busy
+
+  // One side's tensor map: consecutive tile digits whose strides continue one another share a
+  // dimension (the box is their product, at most 256 elements); digits outside the tile join a
+  // dimension they continue, or get one of their own with box 1.
+  struct Place { int dim; int64_t mul; };
+  auto build_side = [&](bool in_side, DmaMapSpec* spec, std::vector<Place>* place) {
+    struct Dim { int64_t stride, size, box; bool open; };
+    std::vector<Dim> dims;
+    place->assign(ds.size(), Place{-1, 0});
+    auto stride_of = [&](int j) { return in_side ? ds[j].sa : ds[j].sb; };
+    for (int j : order) {
+      const int64_t st = stride_of(j);
+      if (!dims.empty() && dims.back().open && st == dims.back().stride * dims.back().size &&
+          dims.back().box * ds[j].box <= 256) {
+        Dim& d = dims.back();
+        (*place)[j] = Place{(int)dims.size() - 1, d.size * ds[j].box};
+        d.box *= ds[j].box;
+        d.size *= ds[j].radix;
+        d.open = ds[j].box == ds[j].radix;
+      } else {
+        dims.push_back({st, ds[j].radix, ds[j].box, ds[j].box == ds[j].radix});
+        (*place)[j] = Place{(int)dims.size() - 1, ds[j].box};
+      }
+    }
+    std::vector<int> rest;
+    for (size_t j = 0; j < ds.size(); ++j)
+      if (!ds[j].in_tile) rest.push_back((int)j);
+    std::sort(rest.begin(), rest.end(), [&](int a, int b) { return stride_of(a) < stride_of(b); });
+    for (int j : rest) {
+      const int64_t st = stride_of(j);
+      bool joined = false;
+      for (size_t k = 0; k < dims.size() && !joined; ++k)
+        if (st == dims[k].stride * dims[k].size) {
+          (*place)[j] = Place{(int)k, dims[k].size};
+          dims[k].size *= ds[j].radix;
+          dims[k].open = false;
+          joined = true;
+        }
+      if (!joined) {
+        dims.push_back({st, ds[j].radix, 1, false});
+        (*place)[j] = Place{(int)dims.size() - 1, 1};
+      }
+    }
+    if (dims.size() < 2 || dims.size() > 5 || dims[0].stride != 1) return false;
+    spec->rank = (int)dims.size();
+    for (size_t k = 0; k < dims.size(); ++k) {
+      if (dims[k].size >= ((int64_t)1 << 31) || dims[k].box > 256) return false;
+      if (k > 0 && ((dims[k].stride * ebx) % 16 || dims[k].stride * ebx >= ((int64_t)1 << 40))) return false;
+      spec->size[k] = (uint64_t)dims[k].size;
+      spec->stride[k] = (uint64_t)dims[k].stride;
+      spec->box[k] = (uint32_t)dims[k].box;
+    }
+    return true;
+  };
+  std::vector<Place> pl_in, pl_out;
+  if (!build_side(true, &pl->dma_ld, &pl_in) || !build_side(false, &pl->dma_st, &pl_out)) return false;
+
+  DmaParams& dp = pl->dma;
+  std::memset(&dp, 0, sizeof(dp));
+  // the digits of the tile id: what is left of every digit outside the box; neighbouring ids
+  // walk the digit that is contiguous on the output side first
+  std::vector<int> outer;
+  for (size_t j = 0; j < ds.size(); ++j)
+    if (ds[j].radix / ds[j].box > 1) outer.push_back((int)j);
+  if ((int)outer.size() > kDmaMaxOuter) return false;
+  std::sort(outer.begin(), outer.end(), [&](int a, int b) { return ds[a].sb < ds[b].sb; });
+  int64_t n_tiles = 1;
+  for (int j : outer) {
+    DmaOuter& o = dp.o[dp.n_outer++];
+    const int64_t r = ds[j].radix / ds[j].box;
+    o.fd = make_fastdiv((uint64_t)r);
+    o.radix = (uint32_t)r;
+    if (pl_in[j].mul * r >= ((int64_t)1 << 31) || pl_out[j].mul * r >= ((int64_t)1 << 31)) return false;
+    o.ld_dim = pl_in[j].dim;
+    o.ld_mul = (int32_t)pl_in[j].mul;
+    o.st_dim = pl_out[j].dim;
+    o.st_mul = (int32_t)pl_out[j].mul;
+    n_tiles *= r;
+    if (n_tiles >= ((int64_t)1 << 31)) return false;
+  }
+  dp.n_tiles = n_tiles;
+  dp.ld_rank = pl->dma_ld.rank;
+  dp.st_rank = pl->dma_st.rank;
+  dp.tile_bytes = (uint32_t)(tile * ebx);
+  dp.slot_bytes = (dp.tile_bytes + 127u) & ~127u;
+  pl->dma_elem_bytes = (int)ebx;
+  pl->kind = KIND_DMA;
+  pl->vec_bytes = 16;
+  pl->tile_in = piece_i / unit;   // contiguous elements per piece read / written
+  pl->tile_out = piece_o / unit;
+  return true;
+}
+
 int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
-                  const lego_layout_t* order, const void* in, const void* out, Plan* pl) {
+                  const lego_layout_t* order, const void* in, const void* out, Plan* pl, bool allow_dma = true) {
   if (!src || !dst) return LEGO_ERR_NULL;
   if (eb != 1 && eb != 2 && eb != 4 && eb != 8 && eb != 16) return LEGO_ERR_SIZE;
   int64_t size = 0, osize = 0;
@@ -963,6 +1284,7 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
       if (finish_tiled(ti, to, merged[ii].sb, merged[oo].sa, eb, in, out, pl)) return LEGO_OK;
     }
   }
+  if (allow_dma && plan_dma(merged, size, eb, in, out, pl)) return LEGO_OK;
   if (plan_chunk(merged, size, eb, in, out, pl)) return LEGO_OK;
   plan_gather(merged, size, eb, in, out, pl);
   return LEGO_OK;
@@ -1066,6 +1388,64 @@ int32_t launch_chunk(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, 
   return cuda_status(cudaGetLastError());
 }
 
+// The tensor map of one side of a DMA plan.
+int32_t encode_dma_map(EncodeFn enc, CUtensorMap* map, const DmaMapSpec& sp, int ebx, const void* base) {
+  const CUtensorMapDataType dt = ebx == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                               : ebx == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                               : ebx == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT64;
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t box[5], estr[5];
+  for (int k = 0; k < sp.rank; ++k) {
+    dims[k] = sp.size[k];
+    box[k] = sp.box[k];
+    estr[k] = 1;
+    if (k > 0) strides[k - 1] = sp.stride[k] * (uint64_t)ebx;
+  }
+  const CUresult r = enc(map, dt, (cuuint32_t)sp.rank, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LEGO_OK : LEGO_ERR_UNSUPPORTED;
+}
+
+// LEGO_ERR_UNSUPPORTED (nothing launched) when the driver refuses one of the tensor maps: the
+// caller then plans again without this kernel.
+int32_t launch_dma(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
+  int32_t err = LEGO_OK;
+  EncodeFn enc = encode_fn(&err);
+  if (!enc) return err;
+  CUtensorMap ld_map, st_map;
+  err = encode_dma_map(enc, &ld_map, pl.dma_ld, pl.dma_elem_bytes, in);
+  if (err != LEGO_OK) return err;
+  err = encode_dma_map(enc, &st_map, pl.dma_st, pl.dma_elem_bytes, out);
+  if (err != LEGO_OK) return err;
+  DmaParams dp = pl.dma;
+  // Shared memory of an SM split among the CTAs that share it; every CTA keeps
+  // kDmaStoresInFlight slots for stores that are reading and the rest for loads in flight.
+  int ctas_per_sm = g_dma_ctas_per_sm.load();
+  const int64_t usable = (int64_t)ctx->smem_optin - 2048;
+  int64_t stages = 0;
+  for (; ctas_per_sm >= 1; --ctas_per_sm) {
+    stages = (usable / ctas_per_sm - (int64_t)sizeof(DmaCtl) - 1152) / dp.slot_bytes;
+    if (stages >= kDmaStoresInFlight + 2) break;
+  }
+  if (ctas_per_sm < 1) return LEGO_ERR_UNSUPPORTED;
+  if (stages > kDmaMaxStages) stages = kDmaMaxStages;
+  dp.stages = (int32_t)stages;
+  const size_t smem = (size_t)stages * dp.slot_bytes + sizeof(DmaCtl) + 128;
+  static PerDeviceFlag configured;
+  if (!configured.test(ctx->device)) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(dma_permute_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       ctx->smem_optin));
+    configured.set(ctx->device);
+  }
+  int64_t grid = (int64_t)ctx->sm_count * ctas_per_sm;
+  if (grid > dp.n_tiles) grid = dp.n_tiles;
+  const cudaError_t e = launch_overlapped(dma_permute_kernel, dim3((unsigned)grid), dim3(kDmaThreads), smem, s, ld_map,
+                                          st_map, dp, ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
+}
+
 template <int VB>
 int32_t launch_gather(const Plan& pl, const void* in, void* out, DeviceCtx* ctx, cudaStream_t s) {
   const GatherParams& gp = pl.gather;
@@ -1096,6 +1476,41 @@ int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const le
     if (kernel_kind) *kernel_kind = pl->kind;
     if (tile_in) *tile_in = pl->tile_in;
     if (tile_out) *tile_out = pl->tile_out;
+  }
+  delete pl;
+  return st;
+}
+
+int32_t lego_permute_dma_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
+                              lego_dma_plan_t* plan) {
+  if (!plan) return LEGO_ERR_NULL;
+  Plan* pl = new Plan();
+  int32_t st = make_plan(elem_bytes, src, dst, nullptr, nullptr, nullptr, pl);
+  if (st == LEGO_OK && pl->kind != KIND_DMA) st = LEGO_ERR_UNSUPPORTED;
+  if (st == LEGO_OK) {
+    std::memset(plan, 0, sizeof(*plan));
+    plan->elem_bytes = pl->dma_elem_bytes;
+    plan->n_outer = pl->dma.n_outer;
+    plan->n_tiles = pl->dma.n_tiles;
+    plan->tile_bytes = pl->dma.tile_bytes;
+    const DmaMapSpec* specs[2] = {&pl->dma_ld, &pl->dma_st};
+    lego_dma_side_t* sides[2] = {&plan->load, &plan->store};
+    for (int k = 0; k < 2; ++k) {
+      sides[k]->rank = specs[k]->rank;
+      for (int d = 0; d < specs[k]->rank; ++d) {
+        sides[k]->size[d] = (int64_t)specs[k]->size[d];
+        sides[k]->stride[d] = d == 0 ? 1 : (int64_t)specs[k]->stride[d];
+        sides[k]->box[d] = specs[k]->box[d];
+      }
+    }
+    for (int j = 0; j < pl->dma.n_outer; ++j) {
+      const DmaOuter& o = pl->dma.o[j];
+      plan->outer[j].radix = o.radix;
+      plan->outer[j].ld_dim = o.ld_dim;
+      plan->outer[j].ld_mul = o.ld_mul;
+      plan->outer[j].st_dim = o.st_dim;
+      plan->outer[j].st_mul = o.st_mul;
+    }
   }
   delete pl;
   return st;
@@ -1136,6 +1551,13 @@ static int32_t run_permute(const void* in, void* out, int32_t elem_bytes, const 
         case 4: st = launch_gather<4>(*pl, in, out, ctx, s); break;
         case 8: st = launch_gather<8>(*pl, in, out, ctx, s); break;
         default: st = launch_gather<16>(*pl, in, out, ctx, s); break;
+      }
+    } else if (pl->kind == KIND_DMA) {
+      st = launch_dma(*pl, in, out, ctx, s);
+      if (st == LEGO_ERR_UNSUPPORTED) {  // a tensor map the driver does not take: the kernels without one
+        st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl, false);
+        if (st == LEGO_OK && pl->kind == KIND_CHUNK) st = launch_chunk(*pl, in, out, ctx, s);
+        else if (st == LEGO_OK) st = LEGO_ERR_UNSUPPORTED;
       }
     } else if (pl->kind == KIND_CHUNK) {
       st = launch_chunk(*pl, in, out, ctx, s);

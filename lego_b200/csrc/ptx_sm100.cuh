@@ -150,6 +150,56 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t c0, int32
                : "memory");
 }
 
+// Tile load / store of a tensor map of rank 2 .. 5 (the rank is uniform over the launch);
+// coordinates innermost first, the ones beyond the rank are ignored.
+__device__ __forceinline__ void tma_load_nd(int rank, uint32_t dst, const void* tmap, const int32_t (&c)[5],
+                                            uint32_t bar) {
+  switch (rank) {
+    case 2:
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                   " [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(dst), "l"(tmap), "r"(c[0]), "r"(c[1]), "r"(bar) : "memory");
+      break;
+    case 3:
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                   " [%0], [%1, {%2, %3, %4}], [%5];"
+                   ::"r"(dst), "l"(tmap), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(bar) : "memory");
+      break;
+    case 4:
+      asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                   " [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                   ::"r"(dst), "l"(tmap), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(bar) : "memory");
+      break;
+    default:
+      asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                   " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                   ::"r"(dst), "l"(tmap), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]), "r"(bar)
+                   : "memory");
+      break;
+  }
+}
+
+__device__ __forceinline__ void tma_store_nd(int rank, const void* tmap, const int32_t (&c)[5], uint32_t src) {
+  switch (rank) {
+    case 2:
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                   ::"l"(tmap), "r"(c[0]), "r"(c[1]), "r"(src) : "memory");
+      break;
+    case 3:
+      asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                   ::"l"(tmap), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(src) : "memory");
+      break;
+    case 4:
+      asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+                   ::"l"(tmap), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(src) : "memory");
+      break;
+    default:
+      asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];"
+                   ::"l"(tmap), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]), "r"(src) : "memory");
+      break;
+  }
+}
+
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -158,6 +208,12 @@ __device__ __forceinline__ void bulk_commit_group() {
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// Wait until at most N of this thread's bulk groups are still incomplete (writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // 1-D bulk copy global -> this CTA's shared memory (16-byte aligned, size % 16 == 0).

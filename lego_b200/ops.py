@@ -27,7 +27,7 @@ from .layout import Col, GroupBy, OrderBy, Row
 from .lowering import lower, lower_optional
 
 __all__ = [
-    "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "transpose", "softmax",
+    "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "permute_dma_plan", "transpose", "softmax",
     "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "layer_norm_bwd", "matmul", "lego_group_gemm_fn",
     "grouped_swizzle_layout", "default_group_m", "default_tile_order", "row_tiling_layout", "device_status", "tune", "selftest_bounded_wait",
 ]
@@ -144,12 +144,22 @@ def selftest_bounded_wait(limit_cycles: int = 1_000_000) -> None:
 
 
 def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
-         gemm_lag: Optional[int] = None) -> None:
-    """Process-wide GEMM knobs: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
+         gemm_lag: Optional[int] = None, permute_dma_tile: Optional[int] = None,
+         permute_dma_ctas: Optional[int] = None, permute_tile_vecs: Optional[int] = None) -> None:
+    """Process-wide knobs.  GEMM: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
     pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` 0 / False keeps every tile whole,
     1 / True splits a poorly filled last wave along K, 2 splits any partial wave;
-    ``gemm_lag`` 0..4, the lead of the first accumulator block of a 512 x 256 tile."""
+    ``gemm_lag`` 0..4, the lead of the first accumulator block of a 512 x 256 tile.
+    Permute: ``permute_dma_tile`` most bytes per box of the DMA kernel (0: the chunk-tiled
+    kernel takes those layouts), ``permute_dma_ctas`` its CTAs per SM, ``permute_tile_vecs``
+    most 16-byte vectors per tile of the chunk-tiled kernel."""
     lib = _abi.lib()
+    if permute_dma_tile is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_DMA_TILE, int(permute_dma_tile)), "lego_tune")
+    if permute_dma_ctas is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_DMA_CTAS, int(permute_dma_ctas)), "lego_tune")
+    if permute_tile_vecs is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_TILE_VECS, int(permute_tile_vecs)), "lego_tune")
     if gemm_blocks is not None:
         _abi.check(lib.lego_tune(_abi.TUNE_GEMM_BLOCKS, int(gemm_blocks)), "lego_tune")
     if gemm_streamk is not None:
@@ -256,13 +266,30 @@ def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None, hos
 
 def permute_plan(elem_bytes: int, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None):
     """Which kernel ``permute`` would run: ``(kind, tile_in, tile_out)`` with kind
-    0 staged, 1 gather, 2 shared-memory tiled transpose, 3 TMA-fed tiled transpose.
-    Host-only; needs no GPU."""
+    0 staged, 1 gather, 2 shared-memory tiled transpose, 3 TMA-fed tiled transpose,
+    4 chunk-tiled permute, 5 DMA permute.  Host-only; needs no GPU."""
     kind, ti, to = C.c_int32(0), C.c_int64(0), C.c_int64(0)
     _abi.check(_abi.lib().lego_permute_plan(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)),
                                             lower_optional(tile_order), C.byref(kind), C.byref(ti), C.byref(to)),
                "lego_permute_plan")
     return kind.value, ti.value, to.value
+
+
+def permute_dma_plan(elem_bytes: int, src: GroupBy, dst: GroupBy) -> dict:
+    """The DMA permute's plan for a pair of layouts: both tensor maps (``size``, ``stride``,
+    ``box`` per dimension, innermost first, in elements of ``elem_bytes``) and the digits of
+    the tile id.  Raises ``ValueError`` when the pair is not moved that way.  Host-only."""
+    plan = _abi.DmaPlan()
+    _abi.check(_abi.lib().lego_permute_dma_plan(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)),
+                                                C.byref(plan)), "lego_permute_dma_plan")
+
+    def side(sd):
+        return {k: [int(getattr(sd, k)[i]) for i in range(sd.rank)] for k in ("size", "stride", "box")}
+
+    return {"elem_bytes": plan.elem_bytes, "n_tiles": plan.n_tiles, "tile_bytes": plan.tile_bytes,
+            "load": side(plan.load), "store": side(plan.store),
+            "outer": [{"radix": int(o.radix), "ld": (o.ld_dim, o.ld_mul), "st": (o.st_dim, o.st_mul)}
+                      for o in plan.outer[:plan.n_outer]]}
 
 
 def permute(x: torch.Tensor, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None,

@@ -145,35 +145,83 @@ def test_tile_ranges_assemble_the_whole_reorganisation(dtype, n, t):
         ops.permute(xd, src, dst, None, out=out, tiles=(0, 1))                # a range needs a tile order
 
 
-def test_brick_relayout_384_cubed(golden):
+@pytest.mark.parametrize("kernel", [5, 4])
+def test_brick_relayout_384_cubed(golden, kernel):
     """The reference's brick layouts (benchmarks/cuda/bricks_f3d.py:10-13): a 384^3 fp32
-    volume from row-major order into 8^3 bricks and back, each as ONE permute call on the
-    chunk-tiled kernel.  Checked three ways: against the reference's own index vectors for
-    both layouts (golden file), against the oracle on a 96^3 volume, and at full size against
-    the same re-layout written as reshape + transpose."""
+    volume from row-major order into 8^3 bricks and back, each as ONE permute call, on the
+    DMA kernel (two tensor maps, no thread touches the data) and on the chunk-tiled kernel.
+    Checked three ways: against the reference's own index vectors for both layouts (golden
+    file), against the oracle on a 96^3 volume, and at full size against the same re-layout
+    written as reshape + transpose."""
     n, b = 384, 8
     normal = L.OrderBy(L.Row(n, n, n)).TileBy([n // b] * 3, [b] * 3)
     bricks = L.OrderBy(L.Row(n // b, n // b, n // b), L.Row(b, b, b)).TileBy([n // b] * 3, [b] * 3)
-    assert ops.permute_plan(4, normal, bricks)[0] == 4 and ops.permute_plan(4, bricks, normal)[0] == 4
-    x = torch.rand(n, n, n, generator=torch.Generator().manual_seed(8))
-    xd = x.cuda()
-    out = ops.permute(xd, normal, bricks)
+    ops.tune(permute_dma_tile=16384 if kernel == 5 else 0)
+    try:
+        assert ops.permute_plan(4, normal, bricks)[0] == kernel and ops.permute_plan(4, bricks, normal)[0] == kernel
+        x = torch.rand(n, n, n, generator=torch.Generator().manual_seed(8))
+        xd = x.cuda()
+        out = ops.permute(xd, normal, bricks)
+        ops.device_status()
+        want = x.reshape(n // b, b, n // b, b, n // b, b).permute(0, 2, 4, 1, 3, 5).contiguous()
+        assert torch.equal(out.cpu().reshape(-1), want.reshape(-1))
+        assert torch.equal(ops.permute(out, bricks, normal).cpu(), x)          # and back
+        ops.device_status()
+        # the reference's vectors: the element with logical index (bx, by, bz, i, j, k), i.e. voxel
+        # (8 bx + i, 8 by + j, 8 bz + k), sits at normal(idx) before the call and at bricks(idx) after
+        for name, buf in (("bricks_normal_384", x), ("bricks_384", out.cpu())):
+            gl = golden["layouts"][name]
+            bx, by, bz, i, j, k = (torch.from_numpy(v) for v in np.unravel_index(np.asarray(gl["ids"]), gl["dims"]))
+            voxel = x[bx * b + i, by * b + j, bz * b + k]
+            assert torch.equal(buf.reshape(-1)[torch.tensor(gl["apply"])], voxel), name
+        # oracle on a volume it handles in seconds, several element sizes
+        m = 96
+        sn = L.OrderBy(L.Row(m, m, m)).TileBy([m // b] * 3, [b] * 3)
+        sb = L.OrderBy(L.Row(m // b, m // b, m // b), L.Row(b, b, b)).TileBy([m // b] * 3, [b] * 3)
+        for dtype in (torch.float16, torch.float32, torch.float64):
+            y = torch.rand(m, m, m, generator=torch.Generator().manual_seed(9)).to(dtype)
+            _check(y, sn, sb, kind=kernel)
+            _check(y, sb, sn, kind=kernel)
+        ops.device_status()
+    finally:
+        ops.tune(permute_dma_tile=16384)
+
+
+def test_dma_permute_other_shapes_and_sizes():
+    """Pairs with a short common run on the DMA kernel: blocks of a matrix, a swap of the
+    two middle axes of a 4-D array, a ragged volume; 2-, 8- and 16-byte elements; a grid
+    smaller than the machine and one many tiles deep; repeated back-to-back launches."""
+    g = torch.Generator().manual_seed(21)
+    r, c = 256, 1024
+    a = L.OrderBy(L.Row(r, c)).TileBy([r // 8, c // 8], [8, 8])
+    blk = L.OrderBy(L.Row(r // 8, c // 8), L.Row(8, 8)).TileBy([r // 8, c // 8], [8, 8])
+    x = torch.randn(r, c, generator=g).half()
+    _check(x, a, blk, kind=5)
+    _check(x, blk, a, kind=5)
+    p = L.OrderBy(L.Row(12, 40, 24, 4)).GroupBy([(12, 40, 24, 4)])
+    q = L.OrderBy(L.RegP([12, 40, 24, 4], [0, 2, 1, 3])).GroupBy([(12, 40, 24, 4)])
+    y = torch.randn(12, 40, 24, 4, generator=g, dtype=torch.float64)
+    got = _check(y, p, q, kind=5)
+    assert torch.equal(got.reshape(12, 24, 40, 4), y.transpose(1, 2).contiguous())
+    _check(y, q, p, kind=5)
+    # 16-byte elements (complex128): runs of two elements, written into the maps as four 8-byte ones
+    z = torch.randn(16, 24, 32, 2, generator=g, dtype=torch.float64).to(torch.complex128)
+    pz = L.OrderBy(L.Row(16, 24, 32, 2)).GroupBy([(16, 24, 32, 2)])
+    qz = L.OrderBy(L.RegP([16, 24, 32, 2], [0, 2, 1, 3])).GroupBy([(16, 24, 32, 2)])
+    assert ops.permute_plan(16, pz, qz)[0] == 5
+    gz = ops.permute(z.cuda(), pz, qz).cpu()
+    assert torch.equal(torch.view_as_real(gz.reshape(16, 32, 24, 2)),
+                       torch.view_as_real(z.transpose(1, 2).contiguous()))
+    # ragged volume, many launches in a row (ring slots and barriers start afresh each time)
+    dims, b = (64, 96, 160), 8
+    tiles = [d // b for d in dims]
+    sn = L.OrderBy(L.Row(*dims)).TileBy(tiles, [b] * 3)
+    sb = L.OrderBy(L.Row(*tiles), L.Row(b, b, b)).TileBy(tiles, [b] * 3)
+    v = torch.randn(*dims, generator=g)
+    vd = v.cuda()
+    want = v.reshape(tiles[0], b, tiles[1], b, tiles[2], b).permute(0, 2, 4, 1, 3, 5).contiguous().reshape(-1)
+    for _ in range(5):
+        out = ops.permute(vd, sn, sb)
+        back = ops.permute(out, sb, sn)
+    assert torch.equal(out.cpu().reshape(-1), want) and torch.equal(back.cpu(), v)
     ops.device_status()
-    want = x.reshape(n // b, b, n // b, b, n // b, b).permute(0, 2, 4, 1, 3, 5).contiguous()
-    assert torch.equal(out.cpu().reshape(-1), want.reshape(-1))
-    assert torch.equal(ops.permute(out, bricks, normal).cpu(), x)          # and back
-    # the reference's vectors: the element with logical index (bx, by, bz, i, j, k), i.e. voxel
-    # (8 bx + i, 8 by + j, 8 bz + k), sits at normal(idx) before the call and at bricks(idx) after
-    for name, buf in (("bricks_normal_384", x), ("bricks_384", out.cpu())):
-        gl = golden["layouts"][name]
-        bx, by, bz, i, j, k = (torch.from_numpy(v) for v in np.unravel_index(np.asarray(gl["ids"]), gl["dims"]))
-        voxel = x[bx * b + i, by * b + j, bz * b + k]
-        assert torch.equal(buf.reshape(-1)[torch.tensor(gl["apply"])], voxel), name
-    # oracle on a volume it handles in seconds, several element sizes
-    m = 96
-    sn = L.OrderBy(L.Row(m, m, m)).TileBy([m // b] * 3, [b] * 3)
-    sb = L.OrderBy(L.Row(m // b, m // b, m // b), L.Row(b, b, b)).TileBy([m // b] * 3, [b] * 3)
-    for dtype in (torch.float16, torch.float32, torch.float64):
-        y = torch.rand(m, m, m, generator=torch.Generator().manual_seed(9)).to(dtype)
-        _check(y, sn, sb, kind=4)
-        _check(y, sb, sn, kind=4)
