@@ -917,11 +917,14 @@ def run_workload(cls, args, dev, world, rank, timer, peaks, local_rank, headline
     w.setup(dev, rank, world)
     w.step(0)
     torch.cuda.synchronize()
-    full = gather(w.shard_result(), world)
     ok, parity = (True, "")
-    if rank == 0:
-        ok, parity = w.check(full)
-    del full
+    if args.as_rank0_of:
+        parity = f"not checked: one GPU running rank 0's shard of a world of {world}"
+    else:
+        full = gather(w.shard_result(), world)
+        if rank == 0:
+            ok, parity = w.check(full)
+        del full
     graph = w.graph_ok and not args.no_graph
     with ClockSampler(local_rank) as clocks:
         times = timer.run(w.step, launches, args.replays, args.warmup, graph=graph)
@@ -957,6 +960,10 @@ def run_workload(cls, args, dev, world, rank, timer, peaks, local_rank, headline
                             "frac": v / (peaks["tensor_sustained"] * w.peak_scale),
                             "peak_source": f"{peaks['source']}: cuBLAS bf16 back to back for seconds under the power cap",
                             "clocks": c2.summary()}
+    if args.as_rank0_of:
+        del w
+        torch.cuda.empty_cache()
+        return res
     if not args.no_e2e and (world == 1 or headline):   # N ranks' host staging shares one box: headline only
         h2d, d2h = w.e2e_setup()
         e_launches = 5
@@ -992,6 +999,45 @@ def run_workload(cls, args, dev, world, rank, timer, peaks, local_rank, headline
     del w
     torch.cuda.empty_cache()
     return res
+
+
+def sweep(args, dev, timer, peaks):
+    """The shapes of the reference's own result tables (result/triton/softmax.txt,
+    result/triton/layernorm.txt: 4096 rows, fp16, the widths below), one GPU: our kernel and the
+    library kernel for the same work, GB/s by the reference's byte count, buffer sets rotating
+    past L2.  One JSON line on stdout, a row per shape on stderr."""
+    rows = 4096
+    table = []
+    for cls, widths in ((Softmax, (512, 1024, 2048, 4096, 8192, 16384)),
+                        (LayerNorm, (1024, 2048, 4096, 8192, 16384)),
+                        (LayerNormBwd, (1024, 2048, 4096, 8192, 16384))):
+        for cols in widths:
+            w = cls()
+            w.rows, w.cols = rows, cols
+            w.setup(dev, 0, 1)
+            w.step(0)
+            torch.cuda.synchronize()
+            ok, _ = w.check(w.shard_result())
+            launches = max(args.steps, MIN_LAUNCHES)
+            t = statistics.median(timer.run(w.step, launches, args.replays, args.warmup, graph=True)) / launches
+            rec = {"op": getattr(w, "short", w.name.split("_f")[0]), "rows": rows, "cols": cols,
+                   "GB/s": round(_rate(w.work(), t, "GB/s"), 1), "us": round(t * 1e6, 2), "ok": bool(ok),
+                   "frac": round(_rate(w.work(), t, "GB/s") / peaks["hbm"], 3)}
+            for name, fn in w.comparators().items():
+                if name == "d2d_copy":
+                    continue
+                ring = [None] * 4
+
+                def call(i, fn=fn, ring=ring):
+                    ring[i % 4] = fn(i)
+                tc = statistics.median(timer.run(call, launches, 3, args.warmup, graph=True)) / launches
+                rec[name] = round(_rate(w.work(), tc, "GB/s"), 1)
+            table.append(rec)
+            log(json.dumps(rec))
+            del w
+            inputs.clear_cache()
+            torch.cuda.empty_cache()
+    print(json.dumps({"sweep": "reference result tables, 4096 rows fp16", "rows": table}), flush=True)
 
 
 def _rounded(x):
@@ -1100,6 +1146,11 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long leg of the GEMMs")
     ap.add_argument("--profile", action="store_true",
                     help="for profiler captures: exactly --steps launches in one replay, kernel legs only")
+    ap.add_argument("--as-rank0-of", type=int, default=0, metavar="N",
+                    help="one GPU, no process group: time rank 0's shard of a world of N (what a launch costs "
+                         "when the named shape is split N ways); kernel legs only, nothing is gathered or checked")
+    ap.add_argument("--sweep", action="store_true",
+                    help="one GPU: the shapes of the reference's result tables (4096 rows, widths 512 .. 16384)")
     ap.add_argument("--small", action="store_true",
                     help="halve the row / matrix sizes (for profiler captures; not a bench configuration)")
     args = ap.parse_args()
@@ -1111,6 +1162,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.as_rank0_of:
+        if world != 1:
+            raise SystemExit("--as-rank0-of is a one-GPU mode")
+        args.no_e2e = args.no_cpu = args.no_cmp = args.no_weak = args.no_sustained = True
 
     if args.impl == "reference":
         reference_arm(args, rank)
@@ -1121,6 +1176,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist_ctx = world > 1
+    if args.as_rank0_of:
+        world = args.as_rank0_of          # shard arithmetic only; this process is rank 0 and alone
     if dist_ctx:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=dev)
@@ -1133,6 +1190,11 @@ def main():
         Gemm.m = Gemm.n = Gemm.k = 4096
         Bricks.n = 192
     timer = Timer(dist_ctx)
+    if args.sweep:
+        if world != 1:
+            raise SystemExit("--sweep is a one-GPU mode")
+        sweep(args, dev, timer, peaks)
+        return
     names = [args.workload] + ([] if args.only else [n for n in WORKLOADS if n != args.workload])
     results = {}
     for name in names:
@@ -1164,6 +1226,10 @@ def main():
             if res.get("e2e") and res["unit"] == "GB/s":
                 line["e2e"]["frac_of_host_ceiling"] = res["e2e"]["value"] / ceiling
         line["workloads"] = {n: brief(r) for n, r in results.items() if n != args.workload}
+        if args.as_rank0_of:
+            line["n_gpus"] = 1
+            line["as_rank0_of"] = {"world": world, "what": "one GPU timing rank 0's shard; value = the named shape's "
+                                   "work / that time, i.e. what the world would deliver if every rank took as long"}
         print(json.dumps(_rounded(line)), flush=True)
     if dist_ctx:
         torch.distributed.barrier()

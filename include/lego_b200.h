@@ -137,7 +137,8 @@ int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const le
  * coordinate each one moves on either side.  Tile t = sum_j d_j * prod_{i<j} radix_i is
  * the box at load coordinates  c[outer[j].ld_dim] += d_j * outer[j].ld_mul  and store
  * coordinates  c[outer[j].st_dim] += d_j * outer[j].st_mul;  both boxes hold the same
- * bytes in the same order.  LEGO_ERR_UNSUPPORTED when the pair is not moved this way.
+ * bytes in the same order.  slab_count < 0: the whole re-layout; otherwise the plan of that
+ * many slabs (lego_permute_slabs).  LEGO_ERR_UNSUPPORTED when the pair is not moved this way.
  * No counterpart in the reference.                                              */
 typedef struct lego_dma_side {
   int32_t rank;
@@ -163,7 +164,7 @@ typedef struct lego_dma_plan {
 } lego_dma_plan_t;
 
 int32_t lego_permute_dma_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
-                              lego_dma_plan_t* plan);
+                              int64_t slab_count, lego_dma_plan_t* plan);
 
 /* ---- index-map evaluator -------------------------------------------------- */
 
@@ -204,6 +205,20 @@ int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_l
 int32_t lego_permute_tiles(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
                            const lego_layout_t* dst, const lego_layout_t* tile_order,
                            int64_t tile_begin, int64_t tile_count, void* stream);
+
+/* Slabs.  When the slowest-varying digit of the flat index is the same logical digit in
+ * both layouts (the outermost brick coordinate of benchmarks/cuda/bricks_f3d.py:10-13, the
+ * batch index of a batched transpose), the re-layout falls apart into *n_slabs independent
+ * pieces of *slab_elems elements, each contiguous in the input and in the output.
+ * lego_permute_slab_info reports them (host only; LEGO_ERR_UNSUPPORTED when the pair does
+ * not split).  lego_permute_slabs moves slab_count consecutive slabs: `in` and `out` hold
+ * those slabs only (slab_count * slab_elems elements each), so a caller can stage a large
+ * host buffer through the device piece by piece, or give every GPU its own range.  The
+ * reference has no counterpart: its CUDA programs move the whole volume in one kernel. */
+int32_t lego_permute_slab_info(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
+                               int64_t* n_slabs, int64_t* slab_elems);
+int32_t lego_permute_slabs(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                           const lego_layout_t* dst, int64_t slab_count, void* stream);
 
 /* ---- row-wise kernels ----------------------------------------------------- */
 

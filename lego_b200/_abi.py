@@ -33,6 +33,7 @@ TUNE_PERMUTE_TILE_VECS = 5
 TUNE_PERMUTE_DMA_TILE = 6
 TUNE_PERMUTE_DMA_CTAS = 7
 
+ERR_UNSUPPORTED = -8
 ERR_CUDA_BASE = 1000
 ERR_DEVICE_TIMEOUT = 2001
 
@@ -85,13 +86,15 @@ SIGNATURES = {
     "lego_layout_fold": (C.c_int32, [LayoutP, C.POINTER(Folded)]),
     "lego_permute_plan": (C.c_int32, [C.c_int32, LayoutP, LayoutP, LayoutP, C.POINTER(C.c_int32),
                                       C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
-    "lego_permute_dma_plan": (C.c_int32, [C.c_int32, LayoutP, LayoutP, C.POINTER(DmaPlan)]),
+    "lego_permute_dma_plan": (C.c_int32, [C.c_int32, LayoutP, LayoutP, C.c_int64, C.POINTER(DmaPlan)]),
     "lego_eval_apply": (C.c_int32, [LayoutP, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lego_eval_inv": (C.c_int32, [LayoutP, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "lego_eval_range": (C.c_int32, [LayoutP, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "lego_permute": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, LayoutP, LayoutP, LayoutP, C.c_void_p]),
     "lego_permute_tiles": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, LayoutP, LayoutP, LayoutP, C.c_int64,
                                        C.c_int64, C.c_void_p]),
+    "lego_permute_slab_info": (C.c_int32, [C.c_int32, LayoutP, LayoutP, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "lego_permute_slabs": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, LayoutP, LayoutP, C.c_int64, C.c_void_p]),
     "lego_softmax_f16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, LayoutP, C.c_void_p]),
     "lego_softmax_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, LayoutP, C.c_void_p]),
     "lego_layernorm_fwd_f16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -1167,7 +1167,8 @@ bool plan_dma(const std::vector<PairDigit>& merged, int64_t size, int eb, const 
 }
 
 int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
-                  const lego_layout_t* order, const void* in, const void* out, Plan* pl, bool allow_dma = true) {
+                  const lego_layout_t* order, const void* in, const void* out, Plan* pl, bool allow_dma = true,
+                  int64_t slab_count = -1, int64_t* n_slabs = nullptr, int64_t* slab_elems = nullptr) {
   if (!src || !dst) return LEGO_ERR_NULL;
   if (eb != 1 && eb != 2 && eb != 4 && eb != 8 && eb != 16) return LEGO_ERR_SIZE;
   int64_t size = 0, osize = 0;
@@ -1196,6 +1197,7 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
   if (fs != LEGO_OK || fd != LEGO_OK || !refine_pair(ds, dd, &pairs)) {
     if ((fs != LEGO_OK && fs != LEGO_ERR_UNSUPPORTED)) return fs;
     if ((fd != LEGO_OK && fd != LEGO_ERR_UNSUPPORTED)) return fd;
+    if (slab_count >= 0 || n_slabs) return LEGO_ERR_UNSUPPORTED;  // slabs are read off the folded digits
     pl->kind = KIND_STAGED;
     pl->vec_bytes = eb;
     st = build_staged(src, &pl->staged_src);
@@ -1205,7 +1207,7 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
   const int32_t wide = size > ((int64_t)1 << 31) ? 1 : 0;
 
   // (i) tiles named by tile_order: a tile is every index sharing the leading coordinates.
-  if (order && fold_layout(order, &dor) == LEGO_OK) {
+  if (order && slab_count < 0 && !n_slabs && fold_layout(order, &dor) == LEGO_OK) {
     int64_t tile_elems = 1;
     for (int k = order->rank; k < src->rank; ++k) tile_elems *= src->dims[k];
     std::vector<PairDigit> inner;
@@ -1235,6 +1237,25 @@ int32_t make_plan(int eb, const lego_layout_t* src, const lego_layout_t* dst,
   // (ii) tiles chosen here from the merged digit permutation.
   std::vector<PairDigit> merged = pairs;
   merge_pairs(&merged);
+  if (slab_count >= 0 || n_slabs) {
+    // The digit that is slowest in BOTH buffers cuts the re-layout into independent slabs, each
+    // contiguous on either side; `slab_count` of them are the same permutation with that digit's
+    // radix reduced (the buffers then hold those slabs only).
+    int top = -1;
+    for (size_t j = 0; j < merged.size(); ++j)
+      if (merged[j].radix > 1 && merged[j].sa * merged[j].radix == size && merged[j].sb * merged[j].radix == size)
+        top = (int)j;
+    if (top < 0) return LEGO_ERR_UNSUPPORTED;
+    if (n_slabs) *n_slabs = merged[top].radix;
+    if (slab_elems) *slab_elems = size / merged[top].radix;
+    if (slab_count >= 0) {
+      if (slab_count > merged[top].radix) return LEGO_ERR_SIZE;
+      size = size / merged[top].radix * slab_count;
+      merged[top].radix = slab_count;
+      pl->size = size;
+      if (slab_count == 0) return LEGO_OK;
+    }
+  }
   int ii = -1, oo = -1;
   for (size_t j = 0; j < merged.size(); ++j) {
     if (merged[j].sa == 1) ii = (int)j;
@@ -1482,10 +1503,10 @@ int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const le
 }
 
 int32_t lego_permute_dma_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
-                              lego_dma_plan_t* plan) {
+                              int64_t slab_count, lego_dma_plan_t* plan) {
   if (!plan) return LEGO_ERR_NULL;
   Plan* pl = new Plan();
-  int32_t st = make_plan(elem_bytes, src, dst, nullptr, nullptr, nullptr, pl);
+  int32_t st = make_plan(elem_bytes, src, dst, nullptr, nullptr, nullptr, pl, true, slab_count < 0 ? -1 : slab_count);
   if (st == LEGO_OK && pl->kind != KIND_DMA) st = LEGO_ERR_UNSUPPORTED;
   if (st == LEGO_OK) {
     std::memset(plan, 0, sizeof(*plan));
@@ -1520,13 +1541,13 @@ int32_t lego_permute_dma_plan(int32_t elem_bytes, const lego_layout_t* src, cons
 // tile_count - 1 of tile_order are moved, which needs a plan whose tiles are tile_order's.
 static int32_t run_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
                            const lego_layout_t* dst, const lego_layout_t* tile_order, int64_t tile_begin,
-                           int64_t tile_count, void* stream) {
+                           int64_t tile_count, void* stream, int64_t slab_count = -1) {
   if (!in || !out) return LEGO_ERR_NULL;
   if (in == out) return LEGO_ERR_UNSUPPORTED;  // in-place reorganisation is not defined
   if (!aligned(in, elem_bytes > 0 ? elem_bytes : 1) || !aligned(out, elem_bytes > 0 ? elem_bytes : 1))
     return LEGO_ERR_ALIGN;
   Plan* pl = new Plan();
-  int32_t st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl);
+  int32_t st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl, true, slab_count);
   if (st == LEGO_OK && tile_count >= 0) {
     if (!tile_order) st = LEGO_ERR_NULL;
     else if (!pl->by_order) st = LEGO_ERR_UNSUPPORTED;  // this pair of layouts is not moved tile_order-tile by tile
@@ -1555,7 +1576,7 @@ static int32_t run_permute(const void* in, void* out, int32_t elem_bytes, const 
     } else if (pl->kind == KIND_DMA) {
       st = launch_dma(*pl, in, out, ctx, s);
       if (st == LEGO_ERR_UNSUPPORTED) {  // a tensor map the driver does not take: the kernels without one
-        st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl, false);
+        st = make_plan(elem_bytes, src, dst, tile_order, in, out, pl, false, slab_count);
         if (st == LEGO_OK && pl->kind == KIND_CHUNK) st = launch_chunk(*pl, in, out, ctx, s);
         else if (st == LEGO_OK) st = LEGO_ERR_UNSUPPORTED;
       }
@@ -1584,6 +1605,21 @@ static int32_t run_permute(const void* in, void* out, int32_t elem_bytes, const 
 int32_t lego_permute(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
                      const lego_layout_t* dst, const lego_layout_t* tile_order, void* stream) {
   return run_permute(in, out, elem_bytes, src, dst, tile_order, 0, -1, stream);
+}
+
+int32_t lego_permute_slab_info(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
+                               int64_t* n_slabs, int64_t* slab_elems) {
+  if (!n_slabs || !slab_elems) return LEGO_ERR_NULL;
+  Plan* pl = new Plan();
+  const int32_t st = make_plan(elem_bytes, src, dst, nullptr, nullptr, nullptr, pl, true, -1, n_slabs, slab_elems);
+  delete pl;
+  return st;
+}
+
+int32_t lego_permute_slabs(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,
+                           const lego_layout_t* dst, int64_t slab_count, void* stream) {
+  if (slab_count < 0) return LEGO_ERR_SIZE;
+  return run_permute(in, out, elem_bytes, src, dst, nullptr, 0, -1, stream, slab_count);
 }
 
 int32_t lego_permute_tiles(const void* in, void* out, int32_t elem_bytes, const lego_layout_t* src,

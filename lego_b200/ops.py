@@ -27,7 +27,7 @@ from .layout import Col, GroupBy, OrderBy, Row
 from .lowering import lower, lower_optional
 
 __all__ = [
-    "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "permute_dma_plan", "transpose", "softmax",
+    "eval_apply", "eval_inv", "eval_range", "permute", "permute_plan", "permute_dma_plan", "permute_slabs", "permute_slab_info", "transpose", "softmax",
     "LEGOLayerNorm", "lego_layer_norm", "layer_norm_fwd", "layer_norm_bwd", "matmul", "lego_group_gemm_fn",
     "grouped_swizzle_layout", "default_group_m", "default_tile_order", "row_tiling_layout", "device_status", "tune", "selftest_bounded_wait",
 ]
@@ -114,10 +114,28 @@ class _HostPipeline:
         self.outbound.synchronize()
 
 
-def _row_blocks(rows: int, row_bytes: int, multiple: int = 1):
+def _row_blocks(rows: int, row_bytes: int, multiple: int = 1, taper: bool = False):
+    """Consecutive row ranges of about ``_HOST_BLOCK_BYTES`` each (whole multiples of ``multiple``
+    rows except the last).  With ``taper`` the first and last blocks are an eighth, a quarter and
+    a half of that: the first copy-in and the last copy-out are the only transfers nothing
+    overlaps, so a bandwidth-bound call gets them out of the way in small pieces."""
     step = max(1, _HOST_BLOCK_BYTES // max(1, row_bytes))
     step = max(multiple, step // multiple * multiple)
-    return [(r0, min(rows, r0 + step)) for r0 in range(0, rows, step)]
+    if not taper or rows < 4 * step or step < 8 * multiple:
+        return [(r0, min(rows, r0 + step)) for r0 in range(0, rows, step)]
+    ramp = [max(multiple, step // d // multiple * multiple) for d in (8, 4, 2)]
+    whole = rows // multiple * multiple          # a ragged end stays in the last block
+    sizes, left = list(ramp), whole - 2 * sum(ramp)
+    sizes += [step] * (left // step)
+    if left % step:
+        sizes.append(left % step)
+    sizes += ramp[::-1]
+    sizes[-1] += rows - whole
+    out, r0 = [], 0
+    for n in sizes:
+        out.append((r0, r0 + n))
+        r0 += n
+    return out
 
 
 def _pinned_like(shape, dtype) -> torch.Tensor:
@@ -247,7 +265,7 @@ def eval_range(layout: GroupBy, begin: int = 0, count: Optional[int] = None, hos
         res = _pinned_like((count,), torch.int64)
         bufs = [torch.empty(_HOST_BLOCK_BYTES // 8, dtype=torch.int64, device=pipe.dev) for _ in range(2)]
         done = [None, None]  # the copy-out that last read each buffer
-        for i, (r0, r1) in enumerate(_row_blocks(count, 8)):
+        for i, (r0, r1) in enumerate(_row_blocks(count, 8, taper=True)):
             buf = bufs[i & 1][: r1 - r0]
             if done[i & 1] is not None:
                 pipe.main.wait_event(done[i & 1])
@@ -275,12 +293,13 @@ def permute_plan(elem_bytes: int, src: GroupBy, dst: GroupBy, tile_order: Option
     return kind.value, ti.value, to.value
 
 
-def permute_dma_plan(elem_bytes: int, src: GroupBy, dst: GroupBy) -> dict:
+def permute_dma_plan(elem_bytes: int, src: GroupBy, dst: GroupBy, slabs: int = -1) -> dict:
     """The DMA permute's plan for a pair of layouts: both tensor maps (``size``, ``stride``,
     ``box`` per dimension, innermost first, in elements of ``elem_bytes``) and the digits of
-    the tile id.  Raises ``ValueError`` when the pair is not moved that way.  Host-only."""
+    the tile id; ``slabs >= 0``: the plan of that many slabs (``permute_slabs``).  Raises
+    ``ValueError`` when the pair is not moved that way.  Host-only."""
     plan = _abi.DmaPlan()
-    _abi.check(_abi.lib().lego_permute_dma_plan(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)),
+    _abi.check(_abi.lib().lego_permute_dma_plan(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)), int(slabs),
                                                 C.byref(plan)), "lego_permute_dma_plan")
 
     def side(sd):
@@ -292,6 +311,60 @@ def permute_dma_plan(elem_bytes: int, src: GroupBy, dst: GroupBy) -> dict:
                       for o in plan.outer[:plan.n_outer]]}
 
 
+def permute_slab_info(elem_bytes: int, src: GroupBy, dst: GroupBy):
+    """``(n_slabs, slab_elems)`` when the slowest digit of the flat index is the same logical
+    digit in both layouts -- the re-layout then is ``n_slabs`` independent pieces, each
+    contiguous in both buffers -- else ``None``.  Host-only."""
+    n, e = C.c_int64(0), C.c_int64(0)
+    st = _abi.lib().lego_permute_slab_info(elem_bytes, C.byref(lower(src)), C.byref(lower(dst)), C.byref(n),
+                                           C.byref(e))
+    if st == _abi.ERR_UNSUPPORTED:
+        return None
+    _abi.check(st, "lego_permute_slab_info")
+    return n.value, e.value
+
+
+def permute_slabs(x: torch.Tensor, src: GroupBy, dst: GroupBy, count: int,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The re-layout ``src -> dst`` restricted to ``count`` consecutive slabs (see
+    ``permute_slab_info``): ``x`` and the result hold those slabs only."""
+    d = _to_device(x).contiguous()
+    res = out if out is not None else torch.empty_like(d)
+    if not res.is_cuda or not res.is_contiguous() or res.numel() != d.numel() or res.dtype != d.dtype:
+        raise ValueError("out must be a contiguous CUDA tensor of x's size and dtype")
+    info = permute_slab_info(d.element_size(), src, dst)
+    if info is None:
+        raise ValueError("this pair of layouts does not split into slabs")
+    if count < 0 or count > info[0] or d.numel() != count * info[1]:
+        raise ValueError(f"{count} slabs of {info[1]} elements do not match a tensor of {d.numel()}")
+    _abi.check(_abi.lib().lego_permute_slabs(d.data_ptr(), res.data_ptr(), d.element_size(), C.byref(lower(src)),
+                                             C.byref(lower(dst)), int(count), _stream()), "lego_permute_slabs")
+    return _like_input(res, x)
+
+
+def _permute_from_host(x, src, dst, n_slabs, slab_elems):
+    """A re-layout that splits into slabs, on a host buffer: groups of slabs of about 16 MiB go
+    through the device on three streams (copy in / move / copy out), so the call costs about
+    one PCIe direction instead of copy-in + kernel + copy-out."""
+    eb = x.element_size()
+    pipe = _HostPipeline()
+    lib = _abi.lib()
+    flat = x.reshape(-1)
+    out = _pinned_like((x.numel(),), x.dtype)
+    d_in = torch.empty(x.numel(), dtype=x.dtype, device=pipe.dev)
+    d_out = torch.empty_like(d_in)
+    s_desc, d_desc = lower(src), lower(dst)
+    for k0, k1 in _row_blocks(n_slabs, slab_elems * eb, taper=True):
+        e0, e1 = k0 * slab_elems, k1 * slab_elems
+        pipe.feed(d_in[e0:e1], flat[e0:e1])
+        pipe.ready()
+        _abi.check(lib.lego_permute_slabs(d_in[e0:e1].data_ptr(), d_out[e0:e1].data_ptr(), eb, C.byref(s_desc),
+                                          C.byref(d_desc), k1 - k0, _stream()), "lego_permute_slabs")
+        pipe.drain(out[e0:e1], d_out[e0:e1])
+    pipe.finish()
+    return out.reshape(x.shape)
+
+
 def permute(x: torch.Tensor, src: GroupBy, dst: GroupBy, tile_order: Optional[GroupBy] = None,
             out: Optional[torch.Tensor] = None, tiles: Optional[Sequence[int]] = None) -> torch.Tensor:
     """``out_flat[dst(idx)] = x_flat[src(idx)]`` over the layouts' common logical
@@ -300,6 +373,11 @@ def permute(x: torch.Tensor, src: GroupBy, dst: GroupBy, tile_order: Optional[Gr
     slab of a reorganisation split across several) and leaves the rest of ``out`` alone."""
     if src.size() != x.numel():
         raise ValueError(f"layout covers {src.size()} elements, tensor has {x.numel()}")
+    if (not x.is_cuda and out is None and tiles is None and tile_order is None and x.is_contiguous()
+            and x.numel() * x.element_size() > 2 * _HOST_BLOCK_BYTES):
+        info = permute_slab_info(x.element_size(), src, dst)
+        if info is not None and info[0] * info[1] == x.numel() and info[1] * x.element_size() <= _HOST_BLOCK_BYTES:
+            return _permute_from_host(x, src, dst, *info)
     d = _to_device(x).contiguous()
     res = out if out is not None else torch.empty_like(d)
     if not res.is_cuda or not res.is_contiguous() or res.numel() != d.numel() or res.dtype != d.dtype:
@@ -382,7 +460,7 @@ def softmax(x: torch.Tensor, row_map: Optional[GroupBy] = None) -> torch.Tensor:
         d = torch.empty(x.shape, dtype=x.dtype, device=pipe.dev)
         y = torch.empty_like(d)
         out = _pinned_like(x.shape, x.dtype)
-        for r0, r1 in _row_blocks(x.shape[0], x.shape[1] * x.element_size()):
+        for r0, r1 in _row_blocks(x.shape[0], x.shape[1] * x.element_size(), taper=True):
             pipe.feed(d[r0:r1], x[r0:r1])
             pipe.ready()
             _abi.check(call(d[r0:r1].data_ptr(), y[r0:r1].data_ptr(), r1 - r0, x.shape[1], None, _stream()), fn)
@@ -419,7 +497,7 @@ def layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, ep
         mean = torch.empty(m, dtype=torch.float32, device=pipe.dev)
         rstd = torch.empty(m, dtype=torch.float32, device=pipe.dev)
         y_h, mean_h, rstd_h = _pinned_like(xh.shape, x.dtype), _pinned_like((m,), torch.float32), _pinned_like((m,), torch.float32)
-        for r0, r1 in _row_blocks(m, n * x.element_size()):
+        for r0, r1 in _row_blocks(m, n * x.element_size(), taper=True):
             pipe.feed(d[r0:r1], xh[r0:r1])
             pipe.ready()
             _abi.check(call(d[r0:r1].data_ptr(), w.data_ptr(), b.data_ptr(), y[r0:r1].data_ptr(),
@@ -512,7 +590,7 @@ def _layer_norm_bwd_from_host(dy, x, weight, mean, rstd):
     dw32 = torch.zeros(n, dtype=torch.float32, device=pipe.dev)
     db32 = torch.zeros(n, dtype=torch.float32, device=pipe.dev)
     dw_b, db_b = torch.empty_like(wd), torch.empty_like(wd)
-    blocks = _row_blocks(m, n * 2, multiple=4)
+    blocks = _row_blocks(m, n * 2, multiple=4, taper=True)
     prow = lib.lego_layernorm_bwd_partial_rows(max(r1 - r0 for r0, r1 in blocks), n)
     partial = torch.empty((2, prow, n), dtype=torch.float32, device=pipe.dev)
     for r0, r1 in blocks:

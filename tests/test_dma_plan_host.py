@@ -78,6 +78,32 @@ def test_brick_relayouts_as_tensor_map_pairs(dtype):
         _check_pair(bricks, normal, dtype)
 
 
+def test_slabs_are_the_same_permutation_with_a_smaller_top_digit():
+    """A volume splits along the outermost brick coordinate; a batched axis swap along the batch.
+    The plan of k slabs, run on the first k slabs' elements, gives the first k slabs of the result."""
+    b, dims = 8, (48, 32, 64)
+    tiles = [d // b for d in dims]
+    normal = L.OrderBy(L.Row(*dims)).TileBy(tiles, [b] * 3)
+    bricks = L.OrderBy(L.Row(*tiles), L.Row(b, b, b)).TileBy(tiles, [b] * 3)
+    assert ops.permute_slab_info(4, normal, bricks) == (6, 8 * 32 * 64)
+    p = L.OrderBy(L.Row(6, 40, 24, 4)).GroupBy([(6, 40, 24, 4)])
+    q = L.OrderBy(L.RegP([6, 40, 24, 4], [0, 2, 1, 3])).GroupBy([(6, 40, 24, 4)])
+    assert ops.permute_slab_info(8, p, q) == (6, 40 * 24 * 4)
+    t_src = L.OrderBy(L.Row(256, 256)).TileBy([8, 8], [32, 32])
+    t_dst = L.OrderBy(L.Col(256, 256)).TileBy([8, 8], [32, 32])
+    assert ops.permute_slab_info(4, t_src, t_dst) is None        # a transpose has no common slow digit
+    for src, dst, dtype in ((normal, bricks, np.uint32), (bricks, normal, np.uint32), (p, q, np.uint64)):
+        eb = np.dtype(dtype).itemsize
+        n_slabs, slab = ops.permute_slab_info(eb, src, dst)
+        x = (np.arange(src.size(), dtype=np.int64) * 2654435761 % (1 << 32)).astype(dtype)
+        want = O.permute(x, spec_of(src), spec_of(dst))
+        for k in (1, 2, n_slabs):
+            plan = ops.permute_dma_plan(eb, src, dst, slabs=k)
+            assert plan["n_tiles"] * plan["tile_bytes"] == k * slab * eb
+            got = _run_plan(plan, x[:k * slab])
+            assert np.array_equal(got, want[:k * slab]), (k, dtype)
+
+
 def test_full_size_brick_plan_shape():
     """384^3 fp32: 16 KiB boxes, loads in rows of 256 bytes, a rank-3 map on either side."""
     n, b = 384, 8

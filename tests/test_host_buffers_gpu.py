@@ -115,3 +115,53 @@ def test_layernorm_backward_host_rows():
     # the oracle comparison allows
     for got, want in ((dw, dw_d.cpu()), (db, db_d.cpu())):
         assert (got.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
+
+
+def test_brick_relayout_host_volume_is_staged_by_slabs():
+    """A volume on the host whose re-layout splits along the outermost brick coordinate goes
+    through the device slab group by slab group (lego_permute_slabs); bit-identical to the
+    one-call re-layout of the device-resident volume, both directions."""
+    b, dims = 8, (160, 192, 256)                             # 30 MiB fp32, 20 slabs of 1.5 MiB
+    tiles = [d // b for d in dims]
+    normal = L.OrderBy(L.Row(*dims)).TileBy(tiles, [b] * 3)
+    bricks = L.OrderBy(L.Row(*tiles), L.Row(b, b, b)).TileBy(tiles, [b] * 3)
+    assert ops.permute_slab_info(4, normal, bricks) == (20, 8 * 192 * 256)
+    x = torch.rand(*dims, generator=torch.Generator().manual_seed(14))
+    want = ops.permute(x.cuda(), normal, bricks).cpu()
+    assert torch.equal(want.reshape(-1), x.reshape(tiles[0], b, tiles[1], b, tiles[2], b).permute(0, 2, 4, 1, 3, 5)
+                       .contiguous().reshape(-1))
+    for name, xh in _both(x):
+        got = ops.permute(xh, normal, bricks)
+        assert not got.is_cuda and got.shape == x.shape, name
+        assert torch.equal(got, want), name
+        assert torch.equal(ops.permute(got, bricks, normal), x), name
+    # a range of slabs on device buffers: what one GPU of several would move
+    xd = x.cuda()
+    part = ops.permute_slabs(xd[3 * b:10 * b], normal, bricks, 7)
+    assert torch.equal(part.cpu().reshape(-1), want.reshape(-1)[3 * 8 * 192 * 256:10 * 8 * 192 * 256])
+    with pytest.raises(ValueError):
+        ops.permute_slabs(xd[:3 * b], normal, bricks, 4)     # tensor and count disagree
+    ops.device_status()
+
+
+def test_tapered_blocks_on_long_inputs():
+    """Inputs of four blocks or more are staged with small first and last blocks (an eighth, a
+    quarter, a half of a block).  A 128-row block runs on the kernel for few rows, whose sums are
+    taken in another order than the ring kernel's, so the comparison with the device-resident
+    call allows the last fp16 bit; everything else about the result is the same."""
+    g = torch.Generator().manual_seed(15)
+    x = (torch.randn(9001, 4096, generator=g) * 2).half()    # 70 MiB, 8 MiB blocks: tapered, ragged end
+    blocks = ops._row_blocks(9001, 8192, 1, True)
+    assert blocks[0] == (0, 128) and blocks[-1][1] == 9001 and len(blocks) > 8
+    got = ops.softmax(x.pin_memory())
+    want = ops.softmax(x.cuda()).cpu()
+    assert (got.float() - want.float()).abs().max().item() <= 2.0 ** -11
+    w = (1 + 0.1 * torch.randn(4096, generator=g)).half()
+    b = (0.1 * torch.randn(4096, generator=g)).half()
+    y, mean, rstd = ops.layer_norm_fwd(x.pin_memory(), w, b, 1e-5)
+    y_d, mean_d, rstd_d = ops.layer_norm_fwd(x.cuda(), w.cuda(), b.cuda(), 1e-5)
+    assert torch.allclose(mean, mean_d.cpu(), rtol=1e-5, atol=1e-6) and torch.allclose(rstd, rstd_d.cpu(), rtol=1e-5)
+    err = (y.float() - y_d.cpu().float()).abs()
+    assert bool((err <= y_d.cpu().float().abs() * 2.0 ** -10 + 1e-6).all())
+    ids = ops.eval_range(L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32]), host=True)   # 128 MiB of ids
+    assert torch.equal(ids, ops.eval_range(L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])).cpu())
