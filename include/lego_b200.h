@@ -318,9 +318,12 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *   LEGO_TUNE_PERMUTE_TILE_VECS  most 16-byte vectors per tile of the chunk-tiled permute (64 .. 6144)
  *   LEGO_TUNE_PERMUTE_DMA_TILE   most bytes per box of the DMA permute (2048 .. 49152); 0 = the
  *                           chunk-tiled kernel takes those pairs of layouts instead
- *   LEGO_TUNE_PERMUTE_DMA_CTAS   CTAs per SM of the DMA permute (1 .. 4) */
+ *   LEGO_TUNE_PERMUTE_DMA_CTAS   CTAs per SM of the DMA permute (1 .. 4)
+ *   LEGO_TUNE_PDL_LAST_WAVE      index-map kernels: 1 = only the last wave of a grid lets the next
+ *                           grid of the stream become resident, 0 = rule by grid depth */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
-       LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7 };
+       LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7,
+       LEGO_TUNE_PDL_LAST_WAVE = 8 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

@@ -144,7 +144,7 @@ __device__ __forceinline__ uint32_t eval_term(const TermRegs& r, uint32_t x) {
 // `p` holds the fast terms first (n_fast of them), then the slow ones.
 __global__ void __launch_bounds__(256)
 digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int64_t* __restrict__ out, int64_t begin,
-                        int64_t n, int vec, int trigger_early) {
+                        int64_t n, int vec, int trigger_early, int resident_ctas) {
   TermRegs fast[kWarpFast], slow[kWarpSlow];
 #pragma unroll
   for (int j = 0; j < kWarpFast; ++j) fast[j] = load_term(p, j, j < n_fast);
@@ -159,8 +159,13 @@ digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int6
   // which triggers at once, too) become resident on the SM slots this grid's own later CTAs
   // need -- 16 MiB of ids took 11.3 us that way against 4.4 us.  From about ten waves on the
   // early trigger wins (128 MiB: 21.9 against 22.8 us).
-  if (trigger_early) ptx::launch_dependents();
+  // resident_ctas > 0 selects the other rule: only the CTAs of the grid's last wave trigger
+  // early, and only after their own wait has returned -- the next grid then becomes resident
+  // on the slots this grid frees as it drains, and at most one grid waits behind the running one.
+  const bool last_wave = resident_ctas > 0 && (int64_t)blockIdx.x + resident_ctas >= (int64_t)gridDim.x;
+  if (trigger_early && resident_ctas == 0) ptx::launch_dependents();
   ptx::grid_dependency_wait();  // stores only once the previous grid is complete
+  if (last_wave) ptx::launch_dependents();
   for (int64_t blk = (begin >> 10) + warp; blk < block_end; blk += n_warps) {
     const uint32_t base = (uint32_t)(blk << 10);
     uint32_t run_sum = 0;
@@ -185,7 +190,7 @@ digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int6
       }
     }
   }
-  if (!trigger_early) ptx::launch_dependents();
+  if (resident_ctas > 0 ? !last_wave : !trigger_early) ptx::launch_dependents();
 }
 
 // inv over an array of flat positions, one thread per POSITION: a thread evaluates every term
@@ -197,7 +202,7 @@ digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int6
 template <int RANK>
 __global__ void __launch_bounds__(256)
 digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __restrict__ in,
-                      int64_t* __restrict__ out, int64_t n) {
+                      int64_t* __restrict__ out, int64_t n, int resident_ctas) {
   __shared__ __align__(16) int64_t turn[8][32 * RANK];
   // Term ranges per coordinate; the terms themselves are read from the parameter bank at
   // warp-uniform indices (no shared-memory or L1 traffic for them).
@@ -212,7 +217,9 @@ digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __r
   }
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   int64_t* mine = turn[wib];
+  const bool last_wave = resident_ctas > 0 && (int64_t)blockIdx.x + resident_ctas >= (int64_t)gridDim.x;
   ptx::grid_dependency_wait();
+  if (last_wave) ptx::launch_dependents();  // see digit_range_warp_kernel
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int64_t runs = (n + 31) >> 5;
   constexpr int CHUNKS = RANK * 16;  // 16-byte words a full warp's coordinates make
@@ -257,7 +264,7 @@ digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __r
     }
     __syncwarp();
   }
-  ptx::launch_dependents();  // only now: see digit_range_warp_kernel
+  if (!last_wave) ptx::launch_dependents();  // only now: see digit_range_warp_kernel
 }
 
 // inv over an array of flat positions, one thread per pair of OUTPUT words: output word e
@@ -352,6 +359,21 @@ staged_eval_kernel(const __grid_constant__ StagedProgram sp, const int64_t* __re
   }
 }
 
+// lego_tune(LEGO_TUNE_PDL_LAST_WAVE): 1 = the index kernels let only their last wave trigger the
+// next grid (after its own dependency wait), 0 = the grid-depth rule.
+std::atomic<int> g_pdl_last_wave{0};
+
+// CTAs of `kernel` (256 threads, no dynamic shared memory) the current device holds at once.
+template <typename K>
+static int resident_ctas_of(K kernel, const DeviceCtx* ctx) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return per_sm * ctx->sm_count;
+}
+
 template <int MODE>
 static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t* out, int64_t begin,
                         int64_t n, void* stream) {
@@ -392,8 +414,9 @@ static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t*
         const int64_t want = (id_blocks + 7) / 8, most = (int64_t)ctx->sm_count * 64;
         const int vec = (begin % 2 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) ? 1 : 0;
         const int early = want >= (int64_t)ctx->sm_count * 12 ? 1 : 0;
+        const int resident = g_pdl_last_wave.load() ? resident_ctas_of(digit_range_warp_kernel, ctx) : 0;
         const cudaError_t e = launch_overlapped(digit_range_warp_kernel, dim3((unsigned)(want < most ? want : most)),
-                                                dim3(threads), 0, s, w, n_fast, out, begin, n, vec, early);
+                                                dim3(threads), 0, s, w, n_fast, out, begin, n, vec, early, resident);
         if (e != cudaSuccess) (void)cudaGetLastError();
         return cuda_status(e);
       }
@@ -410,9 +433,16 @@ static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t*
         const int64_t want = (n + threads - 1) / threads, most = (int64_t)ctx->sm_count * 16;
         const dim3 grid((unsigned)(want < most ? want : most));
         cudaError_t e;
-        if (p.n_dst == 2) e = launch_overlapped(digit_inv_rows_kernel<2>, grid, dim3(threads), 0, s, w, in, out, n);
-        else if (p.n_dst == 3) e = launch_overlapped(digit_inv_rows_kernel<3>, grid, dim3(threads), 0, s, w, in, out, n);
-        else e = launch_overlapped(digit_inv_rows_kernel<4>, grid, dim3(threads), 0, s, w, in, out, n);
+        const bool lw = g_pdl_last_wave.load() != 0;
+        if (p.n_dst == 2)
+          e = launch_overlapped(digit_inv_rows_kernel<2>, grid, dim3(threads), 0, s, w, in, out, n,
+                                lw ? resident_ctas_of(digit_inv_rows_kernel<2>, ctx) : 0);
+        else if (p.n_dst == 3)
+          e = launch_overlapped(digit_inv_rows_kernel<3>, grid, dim3(threads), 0, s, w, in, out, n,
+                                lw ? resident_ctas_of(digit_inv_rows_kernel<3>, ctx) : 0);
+        else
+          e = launch_overlapped(digit_inv_rows_kernel<4>, grid, dim3(threads), 0, s, w, in, out, n,
+                                lw ? resident_ctas_of(digit_inv_rows_kernel<4>, ctx) : 0);
         if (e != cudaSuccess) (void)cudaGetLastError();
         return cuda_status(e);
       }
