@@ -1008,9 +1008,9 @@ def sweep(args, dev, timer, peaks):
     past L2.  One JSON line on stdout, a row per shape on stderr."""
     rows = 4096
     table = []
-    for cls, widths in ((Softmax, (512, 1024, 2048, 4096, 8192, 16384)),
-                        (LayerNorm, (1024, 2048, 4096, 8192, 16384)),
-                        (LayerNormBwd, (1024, 2048, 4096, 8192, 16384))):
+    for cls, widths in ((Softmax, (512, 1024, 2048, 4096, 8192)),           # result/triton/softmax.txt:4-8
+                        (LayerNorm, (1024, 2048, 4096, 8192)),              # result/triton/layernorm.txt:7-10
+                        (LayerNormBwd, (1024, 2048, 4096, 8192))):          # result/triton/layernorm.txt:16-19
         for cols in widths:
             w = cls()
             w.rows, w.cols = rows, cols
@@ -1150,7 +1150,7 @@ def main():
                     help="one GPU, no process group: time rank 0's shard of a world of N (what a launch costs "
                          "when the named shape is split N ways); kernel legs only, nothing is gathered or checked")
     ap.add_argument("--sweep", action="store_true",
-                    help="one GPU: the shapes of the reference's result tables (4096 rows, widths 512 .. 16384)")
+                    help="one GPU: the shapes of the reference's result tables (4096 rows, widths 512 .. 8192)")
     ap.add_argument("--small", action="store_true",
                     help="halve the row / matrix sizes (for profiler captures; not a bench configuration)")
     args = ap.parse_args()
