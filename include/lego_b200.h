@@ -321,12 +321,10 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *   LEGO_TUNE_PERMUTE_DMA_CTAS   CTAs per SM of the DMA permute (1 .. 4)
  *   LEGO_TUNE_PDL_LAST_WAVE      index-map kernels: 1 (default) = a grid that fills at most half of
  *                           the machine lets the next grid of the stream become resident beside
- *                           it, 0 = rule by grid depth alone
- *   LEGO_TUNE_INV_BULK_STORE     lego_eval_inv: 1 = a warp's coordinates leave by one bulk copy from
- *                           shared memory per 32 positions, 0 = by 128-bit stores from registers */
+ *                           it, 0 = rule by grid depth alone */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
        LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7,
-       LEGO_TUNE_PDL_LAST_WAVE = 8, LEGO_TUNE_INV_BULK_STORE = 9 };
+       LEGO_TUNE_PDL_LAST_WAVE = 8 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

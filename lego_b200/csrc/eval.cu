@@ -199,14 +199,14 @@ digit_range_warp_kernel(const __grid_constant__ DigitProgram p, int n_fast, int6
 // 16-byte words, 512 contiguous bytes per store instruction.  About a quarter of the
 // instructions per position of the per-output-word form below, which is issue-bound
 // (0.57 of the copy rate on 2^24 positions of a rank-4 layout).
-// BULK: the warp parks its coordinates in output order (two alternating 32 x RANK buffers) and one
-// lane hands the whole run -- 256 x RANK contiguous bytes -- to the copy engine (cp.async.bulk,
-// shared -> global); no thread reads the coordinates back or issues a global store.
-template <int RANK, bool BULK>
+// (Handing each warp's 256 x RANK contiguous bytes to the copy engine instead -- coordinates parked
+// in output order, one cp.async.bulk shared -> global per 32 positions -- was slower: rank 4
+// 126 against 115 us for 2^24 positions, rank 2 88 against 77.)
+template <int RANK>
 __global__ void __launch_bounds__(256)
 digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __restrict__ in,
                       int64_t* __restrict__ out, int64_t n, int resident_ctas) {
-  __shared__ __align__(128) int64_t turn[8][(BULK ? 2 : 1) * 32 * RANK];
+  __shared__ __align__(16) int64_t turn[8][32 * RANK];
   // Term ranges per coordinate; the terms themselves are read from the parameter bank at
   // warp-uniform indices (no shared-memory or L1 traffic for them).
   int lo[RANK + 1];
@@ -231,7 +231,6 @@ digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __r
   constexpr bool PAIRS = RANK % 2 == 0;
   int64_t run = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   uint32_t x_next = 0;
-  uint32_t flip = 0;
   if (run < runs && run * 32 + lane < n) x_next = (uint32_t)in[run * 32 + lane];
   for (; run < runs; run += n_warps) {
     const uint32_t x = x_next;
@@ -246,32 +245,6 @@ digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __r
     }
     const int64_t word0 = run * 32 * RANK;             // first output word of this run
     const int64_t words = (n - run * 32 < 32 ? n - run * 32 : 32) * RANK;
-    if (BULK && words == 32 * RANK) {
-      int64_t* buf = mine + flip * (32 * RANK);
-      flip ^= 1u;
-      // the copy that last read this buffer (two runs ago) must be done with it
-      if (lane == 0) ptx::bulk_wait_group_read<1>();
-      __syncwarp();
-      if (PAIRS) {
-#pragma unroll
-        for (int h = 0; h < RANK / 2; ++h)
-          *reinterpret_cast<longlong2*>(buf + lane * RANK + 2 * h) = make_longlong2(c[2 * h], c[2 * h + 1]);
-      } else {
-#pragma unroll
-        for (int k = 0; k < RANK; ++k) buf[lane * RANK + k] = c[k];
-      }
-      ptx::fence_proxy_async();  // this lane's generic-proxy writes -> visible to the copy engine
-      __syncwarp();
-      if (lane == 0) {
-        ptx::bulk_store(out + word0, ptx::smem_u32(buf), 32 * RANK * 8);
-        ptx::bulk_commit_group();
-      }
-      continue;
-    }
-    if (BULK) {  // the ragged last run goes out with plain stores; a copy may still be reading the buffer
-      if (lane == 0) ptx::bulk_wait_group_read<0>();
-      __syncwarp();
-    }
     if (PAIRS) {
 #pragma unroll
       for (int h = 0; h < RANK / 2; ++h) {
@@ -294,7 +267,6 @@ digit_inv_rows_kernel(const __grid_constant__ DigitProgram p, const int64_t* __r
     }
     __syncwarp();
   }
-  if (BULK && lane == 0) ptx::bulk_wait_group<0>();  // shared memory outlives the copies; the writes end with the grid
   if (!last_wave) ptx::launch_dependents();  // only now: see digit_range_warp_kernel
 }
 
@@ -397,9 +369,6 @@ staged_eval_kernel(const __grid_constant__ StagedProgram sp, const int64_t* __re
 // grid that nearly fills the machine must not do it (2^23 ids, 1024 CTAs on 1184 slots: 12.66 /
 // 13.37 -- the waiting CTAs take the slots as they free up and end up unevenly spread).
 std::atomic<int> g_pdl_last_wave{1};
-// lego_tune(LEGO_TUNE_INV_BULK_STORE): 1 = lego_eval_inv hands each warp's coordinates to the copy
-// engine (one bulk copy per 32 positions) instead of storing them from registers.
-std::atomic<int> g_inv_bulk_store{0};
 
 // CTAs of `kernel` (256 threads, no dynamic shared memory) the current device holds at once, if a
 // grid of `grid` CTAs leaves room for the next grid beside it; else 0 (the grid-depth rule applies).
@@ -475,14 +444,13 @@ static int32_t run_eval(const lego_layout_t* layout, const int64_t* in, int64_t*
         const dim3 grid((unsigned)(want < most ? want : most));
         cudaError_t e;
         const bool lw = g_pdl_last_wave.load() != 0;
-        const bool bulk = g_inv_bulk_store.load() != 0;
         auto go = [&](auto kernel) {
           return launch_overlapped(kernel, grid, dim3(threads), 0, s, w, in, out, n,
                                    lw ? resident_ctas_of(kernel, ctx, (int64_t)grid.x) : 0);
         };
-        if (p.n_dst == 2) e = bulk ? go(digit_inv_rows_kernel<2, true>) : go(digit_inv_rows_kernel<2, false>);
-        else if (p.n_dst == 3) e = bulk ? go(digit_inv_rows_kernel<3, true>) : go(digit_inv_rows_kernel<3, false>);
-        else e = bulk ? go(digit_inv_rows_kernel<4, true>) : go(digit_inv_rows_kernel<4, false>);
+        if (p.n_dst == 2) e = go(digit_inv_rows_kernel<2>);
+        else if (p.n_dst == 3) e = go(digit_inv_rows_kernel<3>);
+        else e = go(digit_inv_rows_kernel<4>);
         if (e != cudaSuccess) (void)cudaGetLastError();
         return cuda_status(e);
       }

@@ -1118,7 +1118,6 @@ extern std::atomic<int> g_chunk_tile_vecs;  // permute.cu
 extern std::atomic<int> g_dma_tile_bytes;   // permute.cu
 extern std::atomic<int> g_dma_ctas_per_sm;  // permute.cu
 extern std::atomic<int> g_pdl_last_wave;    // eval.cu
-extern std::atomic<int> g_inv_bulk_store;   // eval.cu
 namespace {
 // Tuning knobs (lego_tune), process-wide.
 std::atomic<int> g_tune_blocks{0};   // 0: choose, 1: 256 x 256 pair tiles, 2: 512 x 256
@@ -1355,10 +1354,6 @@ int32_t lego_tune(int32_t knob, int32_t value) {
     case LEGO_TUNE_PERMUTE_DMA_CTAS:
       if (value < 1 || value > 4) return LEGO_ERR_SIZE;
       g_dma_ctas_per_sm.store(value);
-      return LEGO_OK;
-    case LEGO_TUNE_INV_BULK_STORE:
-      if (value < 0 || value > 1) return LEGO_ERR_SIZE;
-      g_inv_bulk_store.store(value);
       return LEGO_OK;
     case LEGO_TUNE_PDL_LAST_WAVE:
       if (value < 0 || value > 1) return LEGO_ERR_SIZE;

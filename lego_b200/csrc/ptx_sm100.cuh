@@ -224,12 +224,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       : "memory");
 }
 
-// 1-D bulk copy this CTA's shared memory -> global (bulk async group; 16-byte aligned, size % 16 == 0).
-__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
-               : "memory");
-}
-
 // Packed fp32 arithmetic (two lanes per instruction, sm_100): halves the issue slots of
 // element-wise fp32 work.
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
