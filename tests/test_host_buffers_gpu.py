@@ -142,26 +142,3 @@ def test_brick_relayout_host_volume_is_staged_by_slabs():
     with pytest.raises(ValueError):
         ops.permute_slabs(xd[:3 * b], normal, bricks, 4)     # tensor and count disagree
     ops.device_status()
-
-
-def test_tapered_blocks_on_long_inputs():
-    """Inputs of four blocks or more are staged with small first and last blocks (an eighth, a
-    quarter, a half of a block).  A 128-row block runs on the kernel for few rows, whose sums are
-    taken in another order than the ring kernel's, so the comparison with the device-resident
-    call allows the last fp16 bit; everything else about the result is the same."""
-    g = torch.Generator().manual_seed(15)
-    x = (torch.randn(9001, 4096, generator=g) * 2).half()    # 70 MiB, 8 MiB blocks: tapered, ragged end
-    blocks = ops._row_blocks(9001, 8192, 1, True)
-    assert blocks[0] == (0, 128) and blocks[-1][1] == 9001 and len(blocks) > 8
-    got = ops.softmax(x.pin_memory())
-    want = ops.softmax(x.cuda()).cpu()
-    assert (got.float() - want.float()).abs().max().item() <= 2.0 ** -11
-    w = (1 + 0.1 * torch.randn(4096, generator=g)).half()
-    b = (0.1 * torch.randn(4096, generator=g)).half()
-    y, mean, rstd = ops.layer_norm_fwd(x.pin_memory(), w, b, 1e-5)
-    y_d, mean_d, rstd_d = ops.layer_norm_fwd(x.cuda(), w.cuda(), b.cuda(), 1e-5)
-    assert torch.allclose(mean, mean_d.cpu(), rtol=1e-5, atol=1e-6) and torch.allclose(rstd, rstd_d.cpu(), rtol=1e-5)
-    err = (y.float() - y_d.cpu().float()).abs()
-    assert bool((err <= y_d.cpu().float().abs() * 2.0 ** -10 + 1e-6).all())
-    ids = ops.eval_range(L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32]), host=True)   # 128 MiB of ids
-    assert torch.equal(ids, ops.eval_range(L.OrderBy(L.Col(4096, 4096)).TileBy([128, 128], [32, 32])).cpu())

@@ -233,13 +233,9 @@ def test_host_row_blocks_cover_the_rows_once():
     from lego_b200 import ops
     for rows, row_bytes, mult in ((16384, 16384, 1), (2600, 8192, 1), (2304, 8192, 256), (7, 1 << 30, 1),
                                   (1000, 3, 1), (512, 16384, 256), (1, 1, 1), (16387, 16384, 4), (9001, 4096, 4)):
-        for taper in (False, True):
-            blocks = ops._row_blocks(rows, row_bytes, mult, taper)
-            assert blocks[0][0] == 0 and blocks[-1][1] == rows
-            assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
-            assert all(r1 > r0 for r0, r1 in blocks)
-            assert all((r1 - r0) % mult == 0 for r0, r1 in blocks[:-1])
-            assert all((r1 - r0) * row_bytes <= max(ops._HOST_BLOCK_BYTES, mult * row_bytes) for r0, r1 in blocks)
-    # tapered: the first and the last block are an eighth of a full one
-    blocks = ops._row_blocks(16384, 16384, 1, True)
-    assert blocks[0] == (0, 128) and blocks[-1] == (16384 - 128, 16384) and max(b - a for a, b in blocks) == 1024
+        blocks = ops._row_blocks(rows, row_bytes, mult)
+        assert blocks[0][0] == 0 and blocks[-1][1] == rows
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+        assert all(r1 > r0 for r0, r1 in blocks)
+        assert all((r1 - r0) % mult == 0 for r0, r1 in blocks[:-1])
+        assert all((r1 - r0) * row_bytes <= max(ops._HOST_BLOCK_BYTES, mult * row_bytes) for r0, r1 in blocks)
