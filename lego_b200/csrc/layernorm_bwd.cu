@@ -133,18 +133,23 @@ struct BwdRing1Ctl {
   uint32_t abort_flag;
 };
 
+// EPT: columns per consumer thread, 8 or 16 with gamma in registers; 24 or 32 (rows of 8 Ki .. 16 Ki
+// columns) with gamma staged once per CTA in shared memory as fp16, because 64 accumulator
+// registers leave no room for it: three ring slots of 64 KiB then.
 template <int EPT>
 __global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
 ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
   constexpr int NV = EPT / 8;
   constexpr int NW = kBwd1Consumers / 32;
+  constexpr bool GSMEM = EPT > 16;
   extern __shared__ __align__(128) uint8_t bwd1_smem[];
   __shared__ __align__(16) float red[4][NW][2];  // [row & 3][warp] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
   const uint32_t half_slot = (row_bytes + 127u) & ~127u;
   const uint32_t slot_bytes = 2u * half_slot + 128u;  // x | dy | mean chunk, rstd chunk
-  BwdRing1Ctl* ctl = reinterpret_cast<BwdRing1Ctl*>(bwd1_smem + (size_t)stages * slot_bytes);
+  const uint4* gsm = reinterpret_cast<const uint4*>(bwd1_smem + (size_t)stages * slot_bytes);  // gamma (GSMEM)
+  BwdRing1Ctl* ctl = reinterpret_cast<BwdRing1Ctl*>(bwd1_smem + (size_t)stages * slot_bytes + (GSMEM ? half_slot : 0u));
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   const int tid = threadIdx.x;
   const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -214,16 +219,27 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   // every warp has finished phase 1 of row n, which follows its phase 2 of row n - 2.
   constexpr int P2 = EPT / 2;
   const int lane = tid & 31, warp = tid >> 5;
-  float2 g[P2], acc_w[P2], acc_b[P2];
+  float2 g[GSMEM ? 1 : P2], acc_w[P2], acc_b[P2];
+  if (GSMEM) {
+    uint4* gw = reinterpret_cast<uint4*>(bwd1_smem + (size_t)stages * slot_bytes);
+    for (int v = tid; v < (int)(half_slot / 16u); v += kBwd1Consumers)
+      gw[v] = v * 8 < cols ? __ldg(reinterpret_cast<const uint4*>(P.gamma) + v) : make_uint4(0u, 0u, 0u, 0u);
+    ptx::named_barrier<1, kBwd1Consumers>();  // consumers only: the producer is already streaming rows
+  } else {
 #pragma unroll
-  for (int k = 0; k < NV; ++k) {
-    const int c = (k * kBwd1Consumers + tid) * 8;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (c < cols) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
-    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * kBwd1Consumers + tid) * 8;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (c < cols) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
+      const __half2* hp = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) g[k * 4 + e] = __half22float2(hp[e]);
+      for (int e = 0; e < 4; ++e) g[k * 4 + e] = __half22float2(hp[e]);
+    }
   }
+  // gamma of this thread's e-th pair of its k-th vector
+  auto gamma_of = [&](const uint4& gv, int k, int e) -> float2 {
+    return GSMEM ? __half22float2(reinterpret_cast<const __half2*>(&gv)[e]) : g[GSMEM ? 0 : k * 4 + e];
+  };
 #pragma unroll
   for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
   const float inv_cols = 1.0f / (float)cols;
@@ -246,10 +262,11 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int v = k * kBwd1Consumers + tid;
-      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
+      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u), gv = make_uint4(0u, 0u, 0u, 0u);
       if (v * 8 < cols) {
         xr = reinterpret_cast<const uint4*>(slot)[v];
         dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+        if (GSMEM) gv = gsm[v];
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -257,7 +274,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
         const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
         acc_w[k * 4 + e] = ptx::fma2(d, h, acc_w[k * 4 + e]);
         acc_b[k * 4 + e] = ptx::add2(acc_b[k * 4 + e], d);
-        const float2 w = ptx::mul2(d, g[k * 4 + e]);
+        const float2 w = ptx::mul2(d, gamma_of(gv, k, e));
         s1 = ptx::fma2(h, w, s1);
         s2 = ptx::add2(s2, w);
       }
@@ -303,27 +320,32 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int v = k * kBwd1Consumers + tid;
-      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
+      uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u), gv = make_uint4(0u, 0u, 0u, 0u);
       if (v * 8 < cols) {
         xr = reinterpret_cast<const uint4*>(slot)[v];
         dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+        if (GSMEM) gv = gsm[v];
       }
       __half2* o2 = reinterpret_cast<__half2*>(&outv[k]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
         const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
-        const float2 w = ptx::mul2(d, g[k * 4 + e]);
+        const float2 w = ptx::mul2(d, gamma_of(gv, k, e));
         const float2 t = ptx::fma2(h, nc1, ptx::fma2(w, rstd2, nc2));
         o2[e] = __floats2half2_rn(t.x, t.y);
       }
+      // with 32 columns per thread the results leave at once: no registers to park four vectors in
+      if (GSMEM && v * 8 < cols) __stcs(reinterpret_cast<uint4*>(dx + v * 8), outv[k]);
     }
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
+    if (!GSMEM) {
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int c = (k * kBwd1Consumers + tid) * 8;
-      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * kBwd1Consumers + tid) * 8;
+        if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
+      }
     }
   };
 
@@ -370,11 +392,12 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
     configured.set(ctx->device);
   }
-  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128;
+  const size_t gamma_bytes = EPT > 16 ? half_slot : 0;  // gamma staged in shared memory
+  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128 - gamma_bytes;
   int stages = (int)(budget / slot);
   if (stages > kBwd1Ring) stages = kBwd1Ring;
-  if (stages < 2) return LEGO_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)stages * slot + sizeof(BwdRing1Ctl) + 128;
+  if (stages < 3) return LEGO_ERR_UNSUPPORTED;  // the rows in phase 1 and phase 2 hold two slots; one more for the load in flight
+  const size_t smem = (size_t)stages * slot + gamma_bytes + sizeof(BwdRing1Ctl) + 128;
   const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
   P.partial_rows = grid;
   const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(kBwd1Consumers + 32), smem, s, P, stages, ctx->status_word);
@@ -800,14 +823,17 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   int32_t err = LEGO_OK;
   DeviceCtx* ctx = device_ctx(&err);
   if (!ctx) return err;
-  // Ring-fed kernel: 16-byte aligned rows of 1 Ki .. 8 Ki columns, enough rows to fill the
+  // Ring-fed kernel: 16-byte aligned rows of 1 Ki .. 16 Ki columns, enough rows to fill the
   // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
-  if (vec && cols >= 1024 && cols <= kBwdConsumers * 16 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
+  // (Rows of 8 Ki .. 16 Ki columns, 8192 rows, same box: 24 / 32 columns per thread with gamma in
+  // shared memory 3.2 - 4.9 TB/s; the register kernel they ran on before 1.1; the library kernel 2.1.)
+  if (vec && cols >= 1024 && cols <= kBwdConsumers * 32 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
       a16(partial) && rows >= 2 * (int64_t)ctx->sm_count) {
     // Same box, GB/s, 16384 rows, both kernels with rows in two phases: one group of 512 threads /
     // groups of cols/16 threads: N = 2048: 2010 / 4180, N = 4096: 3850 / 5350, N = 6144: 4160 / 4670,
     // N = 8192: 5500 / 5250.
-    if (cols > g_lnbwd_split.load()) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
+    if (cols > kBwd1Consumers * 16) st = cols <= kBwd1Consumers * 24 ? launch_ring1_dx<24>(P, ctx, s) : launch_ring1_dx<32>(P, ctx, s);
+    else if (cols > g_lnbwd_split.load()) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
     else st = launch_ring_dx<16>(P, ctx, s);
   }
   if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
