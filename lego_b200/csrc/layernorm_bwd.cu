@@ -407,11 +407,17 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
 
 // ---- bulk-copy pipelined dx kernel, several groups (rows of up to 3 Ki columns) ------
 //
-// One CTA per SM.  A producer thread streams the rows of x and dy (and the 16-byte
-// chunks holding the row's mean and rstd) into a shared-memory ring with 1-D bulk
-// copies; up to 512 consumer threads in 1 .. 4 groups: a group of cols / 16 threads
-// (cols / 8 for the narrowest rows) takes every groups-th row of the CTA, each of its
-// threads owning 16 (8) fixed columns: gamma and the two column accumulators of those
+// One CTA per SM.  A producer thread streams x and dy into a shared-memory ring with 1-D
+// bulk copies, `groups` CONSECUTIVE rows per ring slot: one copy of x, one of dy and two
+// small ones for the rows' mean and rstd per slot, whatever the number of groups.  (With
+// one slot per row the lone producer thread was the limit for narrow rows: four copies per
+// row cost it about 0.4 us, which is what a row of 1 Ki columns took per SM.)  Up to 512
+// consumer threads in 1 .. 8 groups: a group of cols / 16 threads (cols / 8 for the
+// narrowest rows) takes one row of every slot, each of its threads owning 16 (8) fixed columns:
+// (BLOCKS = false is the form for one to three groups: one row per slot, group g takes rows g,
+// g + groups, ... of the CTA -- with few groups the per-row copies are large enough, and groups
+// that do not share a slot drift apart instead of waiting for the same barrier: rows of 3 Ki ..
+// 5 Ki columns lost 6 - 10 % in the block form, rows of 1 Ki / 2 Ki columns gain 52 % / 10 %.) gamma and the two column accumulators of those
 // columns stay in registers for the whole kernel, a row costs one two-value reduction
 // over the group (named barrier), and dx leaves in 128-bit streaming stores.  Every
 // group ends with its own partial row of column sums.  All element-wise fp32 work is
@@ -432,7 +438,7 @@ struct BwdRingCtl {
 };
 
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
-template <int EPT, int G>
+template <int EPT, int G, bool BLOCKS>
 __global__ void __launch_bounds__(kBwdConsumers + 32, 1)
 ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, uint32_t* status) {
   constexpr int NV = EPT / 8;
@@ -443,19 +449,22 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   __shared__ __align__(16) float2 red_all[kBwdMaxGroups][4][16];  // [group][row & 3][warp] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
-  const uint32_t half_slot = (row_bytes + 127u) & ~127u;
-  const uint32_t slot_bytes = 2u * half_slot + 128u;  // x | dy | mean chunk, rstd chunk
+  const uint32_t half_slot = ((BLOCKS ? (uint32_t)groups : 1u) * row_bytes + 127u) & ~127u;  // the slot's rows of x (or of dy)
+  const uint32_t slot_bytes = 2u * half_slot + 128u;  // x rows | dy rows | mean chunk (32 bytes), rstd chunk
   BwdRingCtl* ctl = reinterpret_cast<BwdRingCtl*>(bwd_smem + (size_t)stages * slot_bytes);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   const int tid = threadIdx.x;
   const int n_consumers = groups * gsize;
   const int nw = gsize >> 5;  // warps per group
-  const int64_t my_rows = P.rows > blockIdx.x ? (P.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  // slot fills (blocks of `groups` consecutive rows, or single rows) are dealt to the CTAs round-robin
+  const int per_fill = BLOCKS ? groups : 1;
+  const int64_t n_blocks = (P.rows + per_fill - 1) / per_fill;
+  const int64_t my_blocks = n_blocks > blockIdx.x ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), nw);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), BLOCKS ? n_consumers >> 5 : nw);  // the warps that read a slot
     }
     ctl->abort_flag = 0;
     for (int g = 0; g < kBwdMaxGroups; ++g) {
@@ -473,26 +482,33 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
 
   if (tid >= n_consumers) {
-    // ---------------- producer: rows in order, row n of this CTA into slot n mod stages ----------------
+    // ---------------- producer: blocks in order, block n of this CTA into slot n mod stages ----------------
     if (tid == n_consumers) {
       int64_t issued = 0;
       int s = 0;
       uint32_t use = 0;
-      for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
+      for (int64_t n = 0; n < my_blocks; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kBwdWaitLimit)) {
           *abort_flag = 1;
           atomicCAS(status, 0u, 0x60000u | (uint32_t)s);
           break;
         }
-        const int64_t row = blockIdx.x + n * (int64_t)gridDim.x;
-        ctl->row[s] = row;
+        const int64_t row0 = (blockIdx.x + n * (int64_t)gridDim.x) * per_fill;
+        const int64_t left = P.rows - row0;
+        const uint32_t bytes = (uint32_t)(left < per_fill ? left : per_fill) * row_bytes;
+        // the rows' statistics: the 16-byte chunks that hold rows row0 .. row0 + groups - 1 (the row
+        // count is a multiple of 4, so a chunk never reaches past the arrays)
+        const int64_t chunk0 = row0 & ~3LL;
+        const int64_t stat_rows = (row0 + (left < per_fill ? left : per_fill) - chunk0 + 3) & ~3LL;
+        const uint32_t stat_bytes = (uint32_t)stat_rows * 4u;
+        ctl->row[s] = row0;
         const uint32_t full = ptx::smem_u32(&ctl->full[s]);
         const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)s * slot_bytes);
-        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
-        ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
-        ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
-        ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
-        ptx::bulk_load(dst + 2u * half_slot + 16u, P.rstd + (row & ~3LL), 16u, full);
+        ptx::mbar_arrive_expect_tx(full, 2u * bytes + 2u * stat_bytes);
+        ptx::bulk_load(dst, P.x + row0 * cols, bytes, full);
+        ptx::bulk_load(dst + half_slot, P.dy + row0 * cols, bytes, full);
+        ptx::bulk_load(dst + 2u * half_slot, P.mean + chunk0, stat_bytes, full);
+        ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + chunk0, stat_bytes, full);
         ++issued;
       }
       if (*abort_flag) {
@@ -507,8 +523,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
     return;
   }
 
-  // ---------------- consumers: group g takes rows g, g + groups, ... of this CTA ----------------
-  // The slot count is a multiple of the group count, so a slot is always drained by the same group.
+  // ---------------- consumers: group g takes row g of every block of this CTA ----------------
   const int group = tid / gsize;
   const int gtid = tid - group * gsize;
   const int lane = tid & 31, warp_in_group = gtid >> 5;
@@ -541,9 +556,13 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
       return;
     }
     const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
-    const int64_t row = ctl->row[s];
-    const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
-    const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3];
+    const int64_t row0 = ctl->row[s];
+    const int64_t row = BLOCKS ? row0 + group : row0;
+    const bool exists = !BLOCKS || row < P.rows;  // the last block of the matrix may hold fewer rows than groups
+    const int at = (int)(row - (row0 & ~3LL));
+    const float mean = exists ? reinterpret_cast<const float*>(slot + 2u * half_slot)[at] : 0.f;
+    const float rstd = exists ? reinterpret_cast<const float*>(slot + 2u * half_slot + 64u)[at] : 0.f;
+    const uint8_t* xrow = BLOCKS ? slot + (size_t)group * row_bytes : slot;
     // xhat = x * rstd - mean * rstd; columns past the end hold dy = 0 and gamma = 0, so they add nothing
     const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
     float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
@@ -551,9 +570,9 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
     for (int k = 0; k < NV; ++k) {
       const int v = k * gsize + gtid;
       uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
-      if (v * 8 < cols) {
-        xr = reinterpret_cast<const uint4*>(slot)[v];
-        dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      if (exists && v * 8 < cols) {
+        xr = reinterpret_cast<const uint4*>(xrow)[v];
+        dr = reinterpret_cast<const uint4*>(xrow + half_slot)[v];
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -602,9 +621,13 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
       ss.y = ((a0.y + a0.w) + (a1.y + a1.w)) + ((a2.y + a2.w) + (a3.y + a3.w));
     }
     const uint8_t* slot = bwd_smem + (size_t)s * slot_bytes;
-    const int64_t row = ctl->row[s];
-    const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
-    const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 16u)[row & 3];
+    const int64_t row0 = ctl->row[s];
+    const int64_t row = BLOCKS ? row0 + group : row0;
+    const bool exists = !BLOCKS || row < P.rows;
+    const int at = (int)(row - (row0 & ~3LL));
+    const float mean = exists ? reinterpret_cast<const float*>(slot + 2u * half_slot)[at] : 0.f;
+    const float rstd = exists ? reinterpret_cast<const float*>(slot + 2u * half_slot + 64u)[at] : 0.f;
+    const uint8_t* xrow = BLOCKS ? slot + (size_t)group * row_bytes : slot;
     const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
     // dx = (wdy - (xhat * c1 + c2)) * rstd, as two fused steps per pair
     const float c1r = ss.x * inv_cols * rstd, c2r = ss.y * inv_cols * rstd;
@@ -615,9 +638,9 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
     for (int k = 0; k < NV; ++k) {
       const int v = k * gsize + gtid;
       uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u);
-      if (v * 8 < cols) {
-        xr = reinterpret_cast<const uint4*>(slot)[v];
-        dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+      if (exists && v * 8 < cols) {
+        xr = reinterpret_cast<const uint4*>(xrow)[v];
+        dr = reinterpret_cast<const uint4*>(xrow + half_slot)[v];
       }
       __half2* o2 = reinterpret_cast<__half2*>(&outv[k]);
 #pragma unroll
@@ -634,25 +657,28 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int c = (k * gsize + gtid) * 8;
-      if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
+      if (exists && c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
     }
   };
 
-  // ring cursors of the group's row in phase 1 (s1, use1) and in phase 2 (s2); the slot count is a
-  // multiple of the group count and at least twice it, so the two rows sit in different slots
-  const int64_t group_rows = my_rows > group ? (my_rows - group + groups - 1) / groups : 0;
-  int s1 = group, s2 = group;
+  // Ring cursors of the group's row in phase 1 (s1, use1) and in phase 2 (s2).  BLOCKS: every
+  // group walks every slot (at least three slots).  Else group g walks slots g, g + groups, ...;
+  // the slot count is a multiple of the group count and at least twice it.  Either way the two
+  // rows sit in different slots.
+  const int step = BLOCKS ? 1 : groups;
+  const int64_t group_rows = BLOCKS ? my_blocks : (my_blocks > group ? (my_blocks - group + groups - 1) / groups : 0);
+  int s1 = BLOCKS ? 0 : group, s2 = s1;
   uint32_t use1 = 0;
   if (group_rows > 0) phase1(0, s1, use1);
   for (int64_t j = 0; alive && j < group_rows; ++j) {
     if (j + 1 < group_rows) {
-      s1 += groups;
+      s1 += step;
       if (s1 >= stages) { s1 -= stages; ++use1; }
       phase1(j + 1, s1, use1);
       if (!alive) break;
     }
     phase2(j, s2);
-    s2 += groups;
+    s2 += step;
     if (s2 >= stages) s2 -= stages;
   }
   if (!alive) *group_abort = 1;
@@ -676,10 +702,10 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
 }
 
 // Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
-template <int EPT, int G>
+template <int EPT, int G, bool BLOCKS>
 int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int grid, int stages, int groups, int gsize,
                          size_t smem) {
-  auto kern = ln_bwd_ring_kernel<EPT, G>;
+  auto kern = ln_bwd_ring_kernel<EPT, G, BLOCKS>;
   static PerDeviceFlag configured;
   if (!configured.test(ctx->device)) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 8192));  // static part: 4 KiB of reduction slots
@@ -693,28 +719,36 @@ int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int
 
 template <int EPT>
 int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
-  const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
-  const size_t slot = 2 * half_slot + 128;
   // threads per row: EPT columns each, whole warps; as many groups as fit into 512 threads
   int gsize = (((P.cols + EPT - 1) / EPT) + 31) & ~31;
   if (gsize > kBwdConsumers) return LEGO_ERR_UNSUPPORTED;
-  const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
   int groups = kBwdConsumers / gsize;
   if (groups > kBwdMaxGroups) groups = kBwdMaxGroups;
+  const int64_t rows_cap = P.rows < ctx->sm_count ? P.rows : ctx->sm_count;
   // one partial row per group and CTA: no more than the caller's scratch holds
-  const int64_t room = (P.rows < kMaxPartialRows ? P.rows : kMaxPartialRows) / grid;
+  const int64_t room = (P.rows < kMaxPartialRows ? P.rows : kMaxPartialRows) / rows_cap;
   if (groups > room) groups = (int)room;
   if (groups < 1) return LEGO_ERR_UNSUPPORTED;
+  // A ring slot holds `groups` consecutive rows (see the kernel) from eight groups on, and from
+  // four when a CTA has many rows to go through (4 groups, 28 rows per SM: 18.5 against 18.2 us).
+  const bool blocks = groups >= 8 || (groups >= 4 && P.rows >= 64 * (int64_t)ctx->sm_count);
+  const int per_fill = blocks ? groups : 1;
+  const int64_t fills = (P.rows + per_fill - 1) / per_fill;
+  const int grid = (int)(fills < ctx->sm_count ? fills : ctx->sm_count);
+  const size_t half_slot = ((size_t)per_fill * P.cols * 2 + 127) & ~(size_t)127;
+  const size_t slot = 2 * half_slot + 128;
   const size_t budget = (size_t)ctx->smem_optin - 8192 - sizeof(BwdRingCtl) - 128;
   int stages = (int)((192 * 1024 + slot / 2) / slot);  // about 192 KiB of x and dy in flight
-  if (stages < 2 * groups) stages = 2 * groups;
+  const int least = blocks ? 3 : 2 * groups;  // the rows in phase 1 and phase 2 hold a slot each (per group)
+  if (stages < least) stages = least;
   if (stages > kBwdRing) stages = kBwdRing;
   if ((size_t)stages > budget / slot) stages = (int)(budget / slot);
-  stages -= stages % groups;
-  if (stages < 2 * groups) return LEGO_ERR_UNSUPPORTED;  // a group holds two slots: its rows in phase 1 and phase 2
+  if (!blocks) stages -= stages % groups;  // a slot always belongs to one group
+  if (stages < least) return LEGO_ERR_UNSUPPORTED;
   const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
   P.partial_rows = grid * groups;  // every group writes its row, all zeros if it saw no row of x
-  return launch_ring_dx_g<EPT, 0>(P, ctx, s, grid, stages, groups, gsize, smem);
+  return blocks ? launch_ring_dx_g<EPT, 0, true>(P, ctx, s, grid, stages, groups, gsize, smem)
+                : launch_ring_dx_g<EPT, 0, false>(P, ctx, s, grid, stages, groups, gsize, smem);
 }
 
 // Column reduction for widths that are a multiple of 4: a CTA of 32 warps sums 32 columns;
