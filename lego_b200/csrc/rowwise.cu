@@ -266,6 +266,10 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
     // back the first copy until the third slot is free.
     // (16384 x 8192 fp16, same box: one lane / lock-step rounds: softmax 6450 / 6470 GB/s,
     // LayerNorm 6480 / 6300.)
+    // (Fetching a round of `groups` consecutive rows by ONE copy into adjacent slots, which is what
+    // lifted the narrow rows of LayerNorm backward, loses here: LayerNorm 16384 x 1024 / 2048 / 4096
+    // 4369 / 5595 / 6291 -> 3732 / 4877 / 5597 GB/s -- all groups then wait for the same barrier and
+    // the producer for all of their slots, instead of each group drifting at its own pace.)
     const int chunk = groups > 4 ? groups : 1;
     const int lane = tid & 31;
     const T* __restrict__ x = reinterpret_cast<const T*>(P.x);
