@@ -321,10 +321,13 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *   LEGO_TUNE_PERMUTE_DMA_CTAS   CTAs per SM of the DMA permute (1 .. 4)
  *   LEGO_TUNE_PDL_LAST_WAVE      index-map kernels: 1 (default) = a grid that fills at most half of
  *                           the machine lets the next grid of the stream become resident beside
- *                           it, 0 = rule by grid depth alone */
+ *                           it, 0 = rule by grid depth alone
+ *   LEGO_TUNE_LNBWD_LANES        LayerNorm backward, grouped kernel: 0 = one producer thread, 1
+ *                           (default) = a producer lane per group where a ring slot holds one
+ *                           row, 2 = the same and never a block of rows per slot */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
        LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7,
-       LEGO_TUNE_PDL_LAST_WAVE = 8 };
+       LEGO_TUNE_PDL_LAST_WAVE = 8, LEGO_TUNE_LNBWD_LANES = 9 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

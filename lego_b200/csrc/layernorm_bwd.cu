@@ -14,6 +14,9 @@
 #include "rowwise.cuh"
 
 namespace lego {
+// lego_tune(LEGO_TUNE_LNBWD_LANES): producer of the grouped ring kernel.  0 = one thread; 1 = a lane
+// per group in lock step where a slot holds one row; 2 = the same, and never the block form.
+std::atomic<int> g_lnbwd_lanes{1};
 namespace {
 
 constexpr int kMaxPartialRows = 1184;  // 8 partial rows (one per consumer group) on each of 148 SMs
@@ -414,10 +417,11 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
 // row cost it about 0.4 us, which is what a row of 1 Ki columns took per SM.)  Up to 512
 // consumer threads in 1 .. 8 groups: a group of cols / 16 threads (cols / 8 for the
 // narrowest rows) takes one row of every slot, each of its threads owning 16 (8) fixed columns:
-// (BLOCKS = false is the form for one to three groups: one row per slot, group g takes rows g,
-// g + groups, ... of the CTA -- with few groups the per-row copies are large enough, and groups
-// that do not share a slot drift apart instead of waiting for the same barrier: rows of 3 Ki ..
-// 5 Ki columns lost 6 - 10 % in the block form, rows of 1 Ki / 2 Ki columns gain 52 % / 10 %.) gamma and the two column accumulators of those
+// (BLOCKS = false: one row per slot, group g takes rows g, g + groups, ... of the CTA, and the
+// producer warp feeds the groups with one lane each, in lock step.  Groups that do not share a
+// slot drift apart instead of waiting for the same barrier: rows of 3 Ki .. 5 Ki columns lost
+// 6 - 10 % in the block form; it pays only for the narrowest rows, where even a lane per group
+// cannot issue four copies per row fast enough.) gamma and the two column accumulators of those
 // columns stay in registers for the whole kernel, a row costs one two-value reduction
 // over the group (named barrier), and dx leaves in 128-bit streaming stores.  Every
 // group ends with its own partial row of column sums.  All element-wise fp32 work is
@@ -440,7 +444,8 @@ struct BwdRingCtl {
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
 template <int EPT, int G, bool BLOCKS>
 __global__ void __launch_bounds__(kBwdConsumers + 32, 1)
-ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, uint32_t* status) {
+ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, int lanes,
+                   uint32_t* status) {
   constexpr int NV = EPT / 8;
   const int gsize = G > 0 ? G : gsize_rt;
   const int groups = G == kBwdConsumers ? 1 : groups_rt;
@@ -483,6 +488,52 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
 
   if (tid >= n_consumers) {
     // ---------------- producer: blocks in order, block n of this CTA into slot n mod stages ----------------
+    if (!BLOCKS && lanes > 1) {
+      // One row per slot, several groups: `lanes` (= groups) lanes in lock step, lane l feeding
+      // group l -- their barrier polls and copy issues overlap instead of adding up in one thread.
+      const int lane = tid - n_consumers;
+      int slot0 = 0;
+      uint32_t lap = 0;
+      int64_t issued = 0;
+      bool failed = false;
+      for (int64_t base = 0; base < my_blocks; base += lanes) {
+        const int64_t n = base + lane;
+        const int sl = slot0 + lane;
+        if (lane < lanes && n < my_blocks) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[sl]), (lap & 1) ^ 1, abort_flag, kBwdWaitLimit)) {
+            *abort_flag = 1;
+            atomicCAS(status, 0u, 0x60000u | (uint32_t)sl);
+            failed = true;
+          } else {
+            const int64_t row = blockIdx.x + n * (int64_t)gridDim.x;
+            ctl->row[sl] = row;
+            const uint32_t full = ptx::smem_u32(&ctl->full[sl]);
+            const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)sl * slot_bytes);
+            ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+            ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
+            ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
+            ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+            ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + (row & ~3LL), 16u, full);
+          }
+        }
+        if (__any_sync(0xffffffffu, failed)) break;
+        issued = base + lanes < my_blocks ? base + lanes : my_blocks;
+        slot0 += lanes;
+        if (slot0 == stages) {
+          slot0 = 0;
+          ++lap;
+        }
+      }
+      if (*abort_flag && lane == 0) {
+        // leave no copy of ours in flight
+        uint32_t never = 0;
+        for (int sl = 0; sl < stages; ++sl) {
+          const int64_t uses = issued > sl ? (issued - sl + stages - 1) / stages : 0;
+          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[sl]), (uint32_t)((uses - 1) & 1), &never, kBwdWaitLimit);
+        }
+      }
+      return;
+    }
     if (tid == n_consumers) {
       int64_t issued = 0;
       int s = 0;
@@ -712,7 +763,7 @@ int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int
     configured.set(ctx->device);
   }
   const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32), smem, s, P, stages, groups, gsize,
-                                          ctx->status_word);
+                                          g_lnbwd_lanes.load() && !BLOCKS && groups > 1 ? groups : 1, ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
 }
@@ -729,9 +780,12 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const int64_t room = (P.rows < kMaxPartialRows ? P.rows : kMaxPartialRows) / rows_cap;
   if (groups > room) groups = (int)room;
   if (groups < 1) return LEGO_ERR_UNSUPPORTED;
-  // A ring slot holds `groups` consecutive rows (see the kernel) from eight groups on, and from
-  // four when a CTA has many rows to go through (4 groups, 28 rows per SM: 18.5 against 18.2 us).
-  const bool blocks = groups >= 8 || (groups >= 4 && P.rows >= 64 * (int64_t)ctx->sm_count);
+  // How the producer keeps up with narrow rows (16384 rows, same box, us per launch: one thread and
+  // a slot per row / a block of `groups` rows per slot / a producer lane per group, slot per row):
+  // N = 1024 (8 groups) 43.2 / 28.4 / 36.1; N = 2048 (4 groups) 47.9 / 43.5 / 40.8; N = 1536 (5) - /
+  // 35.4 / 35.8; 4096 rows: N = 1024 17.1 / 16.3 / 15.4, N = 2048 18.6 / - / 16.3.  So: blocks for
+  // eight groups when a CTA has many rows to go through, lanes otherwise.
+  const bool blocks = g_lnbwd_lanes.load() < 2 && groups >= 8 && P.rows >= 64 * (int64_t)ctx->sm_count;
   const int per_fill = blocks ? groups : 1;
   const int64_t fills = (P.rows + per_fill - 1) / per_fill;
   const int grid = (int)(fills < ctx->sm_count ? fills : ctx->sm_count);
