@@ -324,7 +324,8 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *                           it, 0 = rule by grid depth alone
  *   LEGO_TUNE_LNBWD_LANES        LayerNorm backward, grouped kernel: 0 = one producer thread, 1
  *                           (default) = a producer lane per group where a ring slot holds one
- *                           row, 2 = the same and never a block of rows per slot */
+ *                           row, 2 = the same and never a block of rows per slot; + 8 = every
+ *                           group writes its own partial row of column sums (no fold in the CTA) */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
        LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7,
        LEGO_TUNE_PDL_LAST_WAVE = 8, LEGO_TUNE_LNBWD_LANES = 9 };

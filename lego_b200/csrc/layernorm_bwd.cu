@@ -17,6 +17,8 @@ namespace lego {
 // lego_tune(LEGO_TUNE_LNBWD_LANES): producer of the grouped ring kernel.  0 = one thread; 1 = a lane
 // per group in lock step where a slot holds one row; 2 = the same, and never the block form.
 std::atomic<int> g_lnbwd_lanes{1};
+// 8 added to the knob's value: every group writes its own partial row (no fold inside the CTA)
+std::atomic<int> g_lnbwd_fold{1};
 namespace {
 
 constexpr int kMaxPartialRows = 1184;  // 8 partial rows (one per consumer group) on each of 148 SMs
@@ -444,7 +446,7 @@ struct BwdRingCtl {
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
 template <int EPT, int G, bool BLOCKS>
 __global__ void __launch_bounds__(kBwdConsumers + 32, 1)
-ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, int lanes,
+ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, int lanes, int fold,
                    uint32_t* status) {
   constexpr int NV = EPT / 8;
   const int gsize = G > 0 ? G : gsize_rt;
@@ -733,6 +735,44 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
     if (s2 >= stages) s2 -= stages;
   }
   if (!alive) *group_abort = 1;
+  if (fold) {
+    // The groups' column sums are added up inside the CTA, in group order, and ONE partial row per
+    // CTA goes to global memory: with eight groups their own rows were a third of the kernel's
+    // traffic.  The sums are parked in the ring's memory, which is free once EVERY group has left
+    // its loop (first barrier: every copy has landed and every slot has been read by then); every
+    // consumer thread reaches the barriers, also those of a group that gave up.
+    asm volatile("bar.sync 1, %0;" ::"r"(n_consumers) : "memory");
+    float* fw = reinterpret_cast<float*>(bwd_smem) + (size_t)group * 2 * cols;
+    float* fb = fw + cols;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = (k * gsize + gtid) * 8;
+      if (c < cols) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = k * 4 + 2 * e;
+          *reinterpret_cast<float4*>(fw + c + 4 * e) = make_float4(acc_w[j].x, acc_w[j].y, acc_w[j + 1].x, acc_w[j + 1].y);
+          *reinterpret_cast<float4*>(fb + c + 4 * e) = make_float4(acc_b[j].x, acc_b[j].y, acc_b[j + 1].x, acc_b[j + 1].y);
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(n_consumers) : "memory");
+    if (*abort_flag) return;
+    const float4* all = reinterpret_cast<const float4*>(bwd_smem);
+    const int quads = cols >> 2;  // float4 columns of one array
+    float* pw = P.partial + (size_t)blockIdx.x * cols;
+    float* pb = P.partial + ((size_t)P.partial_rows + blockIdx.x) * cols;
+    for (int i = tid; i < 2 * quads; i += n_consumers) {
+      const int arr = i >= quads ? 1 : 0, q = i - arr * quads;
+      float4 acc = all[(size_t)arr * quads + q];
+      for (int g2 = 1; g2 < groups; ++g2) {
+        const float4 v = all[((size_t)g2 * 2 + arr) * quads + q];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      *reinterpret_cast<float4*>((arr ? pb : pw) + 4 * q) = acc;
+    }
+    return;
+  }
   if (*group_abort) return;
   // this group's partial row of column sums
   const size_t prow = (size_t)blockIdx.x * groups + group;
@@ -755,7 +795,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
 // Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
 template <int EPT, int G, bool BLOCKS>
 int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int grid, int stages, int groups, int gsize,
-                         size_t smem) {
+                         size_t smem, int fold) {
   auto kern = ln_bwd_ring_kernel<EPT, G, BLOCKS>;
   static PerDeviceFlag configured;
   if (!configured.test(ctx->device)) {
@@ -763,7 +803,7 @@ int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int
     configured.set(ctx->device);
   }
   const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32), smem, s, P, stages, groups, gsize,
-                                          g_lnbwd_lanes.load() && !BLOCKS && groups > 1 ? groups : 1, ctx->status_word);
+                                          g_lnbwd_lanes.load() && !BLOCKS && groups > 1 ? groups : 1, fold, ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
 }
@@ -800,9 +840,12 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   if (!blocks) stages -= stages % groups;  // a slot always belongs to one group
   if (stages < least) return LEGO_ERR_UNSUPPORTED;
   const size_t smem = (size_t)stages * slot + sizeof(BwdRingCtl) + 128;
-  P.partial_rows = grid * groups;  // every group writes its row, all zeros if it saw no row of x
-  return blocks ? launch_ring_dx_g<EPT, 0, true>(P, ctx, s, grid, stages, groups, gsize, smem)
-                : launch_ring_dx_g<EPT, 0, false>(P, ctx, s, grid, stages, groups, gsize, smem);
+  // several groups: their column sums are folded in the ring's memory at the end, one partial row per CTA
+  const int fold = (groups > 1 && P.cols % 4 == 0 && (size_t)groups * 2 * P.cols * 4 <= (size_t)stages * slot &&
+                    g_lnbwd_fold.load()) ? 1 : 0;
+  P.partial_rows = fold ? grid : grid * groups;  // every group writes its row, all zeros if it saw no row of x
+  return blocks ? launch_ring_dx_g<EPT, 0, true>(P, ctx, s, grid, stages, groups, gsize, smem, fold)
+                : launch_ring_dx_g<EPT, 0, false>(P, ctx, s, grid, stages, groups, gsize, smem, fold);
 }
 
 // Column reduction for widths that are a multiple of 4: a CTA of 32 warps sums 32 columns;
