@@ -543,8 +543,11 @@ int32_t run_rows(RowParams& P, const lego_layout_t* row_map, void* stream) {
   bool vec = (P.cols % VEC == 0) && aligned16(P.x) && aligned16(P.y);
   if (OP == OP_LAYERNORM) vec = vec && aligned16(P.gamma) && aligned16(P.beta);
   // long aligned rows, enough of them to fill the machine: the bulk-copy pipeline
-  // (2 KiB rows: LayerNorm gains from the ring, 3.9 -> 4.4 TB/s; softmax loses, 5.9 -> 5.2, and starts at 4 KiB)
-  const size_t ring_from = OP == OP_SOFTMAX ? 4096 : 2048;
+  // (2 KiB rows: LayerNorm gains from the ring, 3.9 -> 4.4 TB/s; softmax loses, 5.9 -> 5.2 -- a warp per
+  // row suits 1024 fp16 values exactly -- and takes the ring from there on: 16384 x 1280 / 1536 27.9 / 28.8
+  // -> 19.9 / 20.1 us.  Several consecutive rows per ring slot, fetched by one copy, and three to six
+  // slots per group instead of two were tried for these narrow rows: no gain, or a loss.)
+  const size_t ring_from = OP == OP_SOFTMAX ? 2049 : 2048;
   if (vec && (size_t)P.cols * sizeof(T) >= ring_from && P.rows >= 2 * (int64_t)ctx->sm_count) {
     const int32_t st = launch_ring<OP, T>(P, ctx, s);
     if (st != LEGO_ERR_UNSUPPORTED) return st;
