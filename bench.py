@@ -946,7 +946,7 @@ def run_workload(cls, args, dev, world, rank, timer, peaks, local_rank, headline
                   "min_ms": min(times) * 1e3, "max_ms": max(times) * 1e3,
                   "as": "cuda graph replay" if graph else "stream launches"},
         "roofline": {"bound": w.bound, "achieved": per_gpu, "peak": peak, "unit": w.unit, "frac": per_gpu / peak,
-                     "traffic": recorded_traffic(w.name) if world == 1 else None,
+                     "traffic": recorded_traffic(w.name) if world == 1 and not args.shape else None,
                      "peak_source": f"{peaks['source']}: {which}"},
         "gpu_launches": launches * len(times) * w.kernels_per_step,
         "clocks": clocks.summary(),
@@ -1151,6 +1151,9 @@ def main():
                          "when the named shape is split N ways); kernel legs only, nothing is gathered or checked")
     ap.add_argument("--sweep", action="store_true",
                     help="one GPU: the shapes of the reference's result tables (4096 rows, widths 512 .. 8192)")
+    ap.add_argument("--shape", default="", metavar="ROWSxCOLS",
+                    help="row-wise workloads only: another matrix shape than the named one (for profiler captures "
+                         "and width studies; not a bench configuration)")
     ap.add_argument("--small", action="store_true",
                     help="halve the row / matrix sizes (for profiler captures; not a bench configuration)")
     args = ap.parse_args()
@@ -1185,6 +1188,8 @@ def main():
     if world > 1:   # the ranks of one box share its cores (input generation, parity checks)
         torch.set_num_threads(max(1, (os.cpu_count() or world) // world))
     peaks = measured_peaks()
+    if args.shape:
+        _Rows.rows, _Rows.cols = (int(v) for v in args.shape.lower().split("x"))
     if args.small:
         _Rows.rows = 8192
         Gemm.m = Gemm.n = Gemm.k = 4096
@@ -1226,6 +1231,8 @@ def main():
             if res.get("e2e") and res["unit"] == "GB/s":
                 line["e2e"]["frac_of_host_ceiling"] = res["e2e"]["value"] / ceiling
         line["workloads"] = {n: brief(r) for n, r in results.items() if n != args.workload}
+        if args.shape:
+            line["config"]["shape_override"] = args.shape + " (row-wise workloads; not the named configuration)"
         if args.as_rank0_of:
             line["n_gpus"] = 1
             line["as_rank0_of"] = {"world": world, "what": "one GPU timing rank 0's shard; value = the named shape's "
