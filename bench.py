@@ -175,6 +175,32 @@ class Softmax(_Rows):
                 "d2d_copy": _copy_comparator(self.x[0], self.sets)}
 
 
+class SoftmaxF32(Softmax):
+    """The precision the reference's own softmax table was measured in (softmax.py:238,271); used by --sweep."""
+    name = "softmax_f32"
+    short = "softmax_f32"
+    dtype = "f32"
+
+    def work(self):
+        return 2.0 * self.rows * self.cols * 4
+
+    def setup(self, dev, rank, world):
+        from lego_b200 import ops
+        self.ops = ops
+        self._rows_setup(rank, world)
+        self.sets = self.n_sets(2 * (self.r1 - self.r0) * self.cols * 4)
+        self.keep = [None] * (self.sets + 1)
+        self.x_host = inputs.softmax_input(self.rows, self.cols).float()
+        xs = self.x_host[self.r0:self.r1]
+        self.x = [xs.to(dev) for _ in range(self.sets)]
+        self.row_map = ops.row_tiling_layout(self.r1 - self.r0, 4)
+
+    def check(self, full):
+        sel = torch.arange(0, self.rows, 257)
+        err = (full[sel.to(full.device)].cpu() - torch.softmax(self.x_host[sel], dim=-1)).abs().max().item()
+        return err <= 1e-6, f"max-abs {err:.2e} on {len(sel)} rows vs torch CPU fp32 (tol 1e-6)"
+
+
 def _copy_comparator(like, sets):
     src = [torch.empty_like(like) for _ in range(sets)]
     dst = [torch.empty_like(like) for _ in range(sets)]
@@ -1008,7 +1034,8 @@ def sweep(args, dev, timer, peaks):
     past L2.  One JSON line on stdout, a row per shape on stderr."""
     rows = 4096
     table = []
-    for cls, widths in ((Softmax, (512, 1024, 2048, 4096, 8192)),           # result/triton/softmax.txt:4-8
+    for cls, widths in ((SoftmaxF32, (512, 1024, 2048, 4096, 8192)),        # result/triton/softmax.txt:4-8 (fp32, as there)
+                        (Softmax, (512, 1024, 2048, 4096, 8192)),           # the same widths in fp16
                         (LayerNorm, (1024, 2048, 4096, 8192)),              # result/triton/layernorm.txt:7-10
                         (LayerNormBwd, (1024, 2048, 4096, 8192))):          # result/triton/layernorm.txt:16-19
         for cols in widths:
