@@ -503,6 +503,7 @@ template <int OP, typename T, bool VECTOR>
 int32_t launch_vec(const RowParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const int c = P.cols;
   if (c <= 32 * 8) return launch_cfg<OP, T, 32, 8, VECTOR>(P, ctx, s);
+  if (c <= 32 * 16) return launch_cfg<OP, T, 32, 16, VECTOR>(P, ctx, s);
   if (c <= 32 * 32) return launch_cfg<OP, T, 32, 32, VECTOR>(P, ctx, s);
   if (c <= 256 * 8) return launch_cfg<OP, T, 256, 8, VECTOR>(P, ctx, s);
   if (c <= 256 * 16) return launch_cfg<OP, T, 256, 16, VECTOR>(P, ctx, s);
