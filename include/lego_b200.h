@@ -122,8 +122,8 @@ int32_t lego_layout_fold(const lego_layout_t* layout, lego_folded_t* out);
 /* Plan of a permute call, for inspection: which kernel lego_permute would pick
  * (0 staged interpreter, 1 output-order gather, 2 shared-memory tiled transpose,
  * 3 TMA-fed tiled transpose, 4 chunk-tiled permute for layouts that share a
- * contiguous run, e.g. a volume into bricks, 5 the same pairs moved by the copy
- * engine alone: one tiled TMA load and one tiled TMA store per box of digits; if
+ * contiguous run, e.g. a volume into bricks, 5 the same pairs (and large problems
+ * with longer common runs) moved by the copy engine alone: one tiled TMA load and one tiled TMA store per box of digits; if
  * the driver refuses a tensor map at call time, kernel 4 runs instead) and the
  * contiguous extents it reads and writes, in elements.                         */
 int32_t lego_permute_plan(int32_t elem_bytes, const lego_layout_t* src, const lego_layout_t* dst,
@@ -319,6 +319,9 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *   LEGO_TUNE_PERMUTE_DMA_TILE   most bytes per box of the DMA permute (2048 .. 49152); 0 = the
  *                           chunk-tiled kernel takes those pairs of layouts instead
  *   LEGO_TUNE_PERMUTE_DMA_CTAS   CTAs per SM of the DMA permute (1 .. 4)
+ *   LEGO_TUNE_PERMUTE_DMA_LONG   1 (default) = the DMA permute also takes pairs of layouts whose common
+ *                           run is a whole 128-byte line or more (problems of 4 MiB and more), 0 = the
+ *                           output-order vector copy keeps them
  *   LEGO_TUNE_PDL_LAST_WAVE      index-map kernels: 1 (default) = a grid that fills at most half of
  *                           the machine lets the next grid of the stream become resident beside
  *                           it, 0 = rule by grid depth alone
@@ -328,7 +331,7 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *                           group writes its own partial row of column sums (no fold in the CTA) */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
        LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7,
-       LEGO_TUNE_PDL_LAST_WAVE = 8, LEGO_TUNE_LNBWD_LANES = 9 };
+       LEGO_TUNE_PDL_LAST_WAVE = 8, LEGO_TUNE_LNBWD_LANES = 9, LEGO_TUNE_PERMUTE_DMA_LONG = 10 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

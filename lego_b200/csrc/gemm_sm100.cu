@@ -1119,6 +1119,7 @@ extern std::atomic<int> g_lnbwd_fold;       // layernorm_bwd.cu
 extern std::atomic<int> g_chunk_tile_vecs;  // permute.cu
 extern std::atomic<int> g_dma_tile_bytes;   // permute.cu
 extern std::atomic<int> g_dma_ctas_per_sm;  // permute.cu
+extern std::atomic<int> g_dma_long_runs;    // permute.cu
 extern std::atomic<int> g_pdl_last_wave;    // eval.cu
 namespace {
 // Tuning knobs (lego_tune), process-wide.
@@ -1356,6 +1357,10 @@ int32_t lego_tune(int32_t knob, int32_t value) {
     case LEGO_TUNE_PERMUTE_DMA_CTAS:
       if (value < 1 || value > 4) return LEGO_ERR_SIZE;
       g_dma_ctas_per_sm.store(value);
+      return LEGO_OK;
+    case LEGO_TUNE_PERMUTE_DMA_LONG:
+      if (value < 0 || value > 1) return LEGO_ERR_SIZE;
+      g_dma_long_runs.store(value);
       return LEGO_OK;
     case LEGO_TUNE_LNBWD_LANES:
       if (value < 0 || (value & 7) > 2 || value > 10) return LEGO_ERR_SIZE;

@@ -152,14 +152,15 @@ def selftest_bounded_wait(limit_cycles: int = 1_000_000) -> None:
 def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
          gemm_lag: Optional[int] = None, permute_dma_tile: Optional[int] = None,
          permute_dma_ctas: Optional[int] = None, permute_tile_vecs: Optional[int] = None,
-         pdl_last_wave: Optional[int] = None) -> None:
+         pdl_last_wave: Optional[int] = None, permute_dma_long: Optional[int] = None) -> None:
     """Process-wide knobs.  GEMM: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
     pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` 0 / False keeps every tile whole,
     1 / True splits a poorly filled last wave along K, 2 splits any partial wave;
     ``gemm_lag`` 0..4, the lead of the first accumulator block of a 512 x 256 tile.
     Permute: ``permute_dma_tile`` most bytes per box of the DMA kernel (0: the chunk-tiled
     kernel takes those layouts), ``permute_dma_ctas`` its CTAs per SM, ``permute_tile_vecs``
-    most 16-byte vectors per tile of the chunk-tiled kernel.  ``pdl_last_wave`` 1: only the last
+    most 16-byte vectors per tile of the chunk-tiled kernel, ``permute_dma_long`` 0: pairs whose
+    common run is a whole line or more stay with the vector copy.  ``pdl_last_wave`` 1: only the last
     wave of an index-map grid lets the next grid of the stream become resident."""
     lib = _abi.lib()
     if permute_dma_tile is not None:
@@ -168,6 +169,8 @@ def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
         _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_DMA_CTAS, int(permute_dma_ctas)), "lego_tune")
     if permute_tile_vecs is not None:
         _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_TILE_VECS, int(permute_tile_vecs)), "lego_tune")
+    if permute_dma_long is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_DMA_LONG, int(permute_dma_long)), "lego_tune")
     if pdl_last_wave is not None:
         _abi.check(lib.lego_tune(_abi.TUNE_PDL_LAST_WAVE, int(pdl_last_wave)), "lego_tune")
     if gemm_blocks is not None:

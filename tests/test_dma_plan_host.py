@@ -129,6 +129,32 @@ def test_other_pairs_with_a_short_common_run():
     _check_pair(q, p, np.uint64)
 
 
+def test_long_common_runs_on_large_problems():
+    """Problems of 4 MiB and more whose common run is a whole 128-byte line or longer also move by
+    DMA: a run of more than 256 elements is cut into box rows and a part that continues them."""
+    for dims, perm, dtype in (((16, 64, 2048), [1, 0, 2], np.uint32),       # runs of 8 KiB, cut into rows of 1 KiB
+                              ((64, 64, 256), [1, 0, 2], np.uint32),        # runs of 1 KiB
+                              ((256, 128, 64), [1, 0, 2], np.uint32),       # runs of 256 bytes
+                              ((40, 48, 1000), [1, 0, 2], np.uint32),       # 1000 = 5 x 200: rows of 800 bytes
+                              ((32, 16, 64, 128), [0, 2, 1, 3], np.uint16)):  # batched, 16-bit, runs of 256 bytes
+        src = L.OrderBy(L.Row(*dims)).GroupBy([tuple(dims)])
+        dst = L.OrderBy(L.RegP(list(dims), perm)).GroupBy([tuple(dims)])
+        eb = np.dtype(dtype).itemsize
+        if src.size() * eb < (4 << 20):
+            assert ops.permute_plan(eb, src, dst)[0] == 1
+            continue
+        _check_pair(src, dst, dtype)
+        _check_pair(dst, src, dtype)
+    ops.tune(permute_dma_long=0)
+    try:
+        big = (64, 64, 256)
+        a = L.OrderBy(L.Row(*big)).GroupBy([big])
+        b = L.OrderBy(L.RegP(list(big), [1, 0, 2])).GroupBy([big])
+        assert ops.permute_plan(4, a, b)[0] == 1
+    finally:
+        ops.tune(permute_dma_long=1)
+
+
 def test_pairs_the_dma_kernel_leaves_to_others():
     n = 256
     src = L.OrderBy(L.Row(n, n)).TileBy([8, 8], [32, 32])

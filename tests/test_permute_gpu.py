@@ -225,3 +225,25 @@ def test_dma_permute_other_shapes_and_sizes():
         back = ops.permute(out, sb, sn)
     assert torch.equal(out.cpu().reshape(-1), want) and torch.equal(back.cpu(), v)
     ops.device_status()
+
+
+def test_dma_permute_long_runs():
+    """Large problems whose common run is a whole line or more (batched permutations, axis swaps
+    with long innermost axes) also move by DMA; same results as the vector copy they replace."""
+    g = torch.Generator().manual_seed(31)
+    for dims, perm, dtype in (((16, 64, 2048), [1, 0, 2], torch.float32), ((256, 128, 64), [1, 0, 2], torch.float32),
+                              ((40, 48, 1000), [1, 0, 2], torch.float32), ((32, 16, 64, 128), [0, 2, 1, 3], torch.float16)):
+        src = L.OrderBy(L.Row(*dims)).GroupBy([tuple(dims)])
+        dst = L.OrderBy(L.RegP(list(dims), perm)).GroupBy([tuple(dims)])
+        x = torch.randn(*dims, generator=g).to(dtype)
+        assert ops.permute_plan(x.element_size(), src, dst)[0] == 5
+        got = ops.permute(x.cuda(), src, dst).cpu()
+        assert torch.equal(got.reshape(-1), x.permute(*perm).contiguous().reshape(-1)), dims
+        ops.tune(permute_dma_long=0)
+        try:
+            assert ops.permute_plan(x.element_size(), src, dst)[0] == 1
+            assert torch.equal(ops.permute(x.cuda(), src, dst).cpu(), got), dims
+        finally:
+            ops.tune(permute_dma_long=1)
+        assert torch.equal(ops.permute(got.cuda(), dst, src).cpu().reshape(-1), x.reshape(-1)), dims     # and back
+    ops.device_status()
