@@ -209,7 +209,12 @@ def test_permute_plans():
     assert ops.permute_plan(4, small, small_t, L.OrderBy(L.Row(3, 5)).TileBy([3, 5])) == (2, 16, 16)
     tm = L.OrderBy(L.Col(128, 128), L.Row(32, 32)).TileBy([128, 128], [32, 32])
     rm = L.OrderBy(L.Row(n, n)).TileBy([128, 128], [32, 32])
-    assert ops.permute_plan(4, rm, tm) == (1, 32, 32)                  # common 32-element runs: gather
+    assert ops.permute_plan(4, rm, tm)[0] == 5                         # common 32-element runs, 64 MiB: DMA permute
+    ops.tune(permute_dma_long=0)
+    try:
+        assert ops.permute_plan(4, rm, tm) == (1, 32, 32)              # without it: output-order vector copy
+    finally:
+        ops.tune(permute_dma_long=1)
     a = L.OrderBy(L.Col(3, 2)).GroupBy([(2, 3)])
     b = L.OrderBy(L.Row(2, 3)).GroupBy([(2, 3)])
     assert ops.permute_plan(4, a, b)[0] == 0                           # staged interpreter
