@@ -410,6 +410,294 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   return cuda_status(e);
 }
 
+// ---- rows of 16 Ki .. 32 Ki columns: a CTA pair per row ------------------------------
+//
+// The 64 accumulator registers of 32 columns per thread are all a thread can hold, so rows wider
+// than 512 x 32 columns are split between the two CTAs of a cluster: each runs the ring scheme of
+// ln_bwd_ring1_kernel<32> on its half of the columns of the SAME rows (gamma of its half in shared
+// memory, three ring slots), and the two halves of a row's sums meet in both CTAs: every warp
+// writes its two totals into its slot of red[] in its own and in the peer's shared memory and
+// arrives on both row barriers (32 arrivals: 16 warps of each CTA).  Everything else -- two phases
+// per row with the next row's first phase in between, fixed columns per thread, one partial row per
+// pair -- is as there.  No thread leaves before the final cluster barrier: the peer may still
+// store into this CTA's shared memory.
+
+struct BwdPairCtl {
+  uint64_t full[kBwd1Ring];
+  uint64_t empty[kBwd1Ring];
+  uint64_t rowbar[2];  // 32 arrivals: the 16 consumer warps of either CTA
+  int64_t row[kBwd1Ring];
+  uint32_t abort_flag;
+};
+
+__global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
+ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half, uint32_t* status) {
+  constexpr int EPT = 32;
+  constexpr int NV = EPT / 8;
+  constexpr int NW = kBwd1Consumers / 32;
+  constexpr int P2 = EPT / 2;
+  extern __shared__ __align__(128) uint8_t pair_smem[];
+  __shared__ __align__(16) float red[4][2 * NW][2];  // [row & 3][CTA rank * 16 + warp] -> (s1, s2)
+  const uint32_t rank = ptx::cluster_ctarank();
+  const uint32_t peer = rank ^ 1u;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int cols_full = P.cols;
+  const int col0 = (int)rank * col_half;
+  const int cols = cols_full - col0 < col_half ? cols_full - col0 : col_half;  // this CTA's columns
+  const uint32_t row_bytes = (uint32_t)cols * 2u;
+  const uint32_t half_slot = ((uint32_t)col_half * 2u + 127u) & ~127u;
+  const uint32_t slot_bytes = 2u * half_slot + 128u;  // x | dy | mean chunk, rstd chunk
+  uint4* gsm = reinterpret_cast<uint4*>(pair_smem + (size_t)stages * slot_bytes);  // gamma of this half
+  BwdPairCtl* ctl = reinterpret_cast<BwdPairCtl*>(pair_smem + (size_t)stages * slot_bytes + half_slot);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const int tid = threadIdx.x;
+  const int64_t my_rows = P.rows > pair ? (P.rows - pair + n_pairs - 1) / n_pairs : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), NW);
+    }
+    ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[0]), 2 * NW);
+    ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[1]), 2 * NW);
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  __syncthreads();
+  ptx::cluster_sync();  // the peer's barriers exist before anything arrives on them
+  ptx::launch_dependents();
+  ptx::grid_dependency_wait();
+
+  auto fail = [&](uint32_t code) {
+    *abort_flag = 1;
+    ptx::st_cluster_u32(ptx::mapa(ptx::smem_u32(const_cast<uint32_t*>(abort_flag)), peer), 1u);
+    atomicCAS(status, 0u, code);
+  };
+
+  if (tid >= kBwd1Consumers) {
+    // ---------------- producer ----------------
+    if (tid == kBwd1Consumers) {
+      int64_t issued = 0;
+      int s = 0;
+      uint32_t use = 0;
+      for (int64_t n = 0; n < my_rows; ++n, s = (s + 1 == stages ? 0 : s + 1), use += (s == 0)) {
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->empty[s]), (use & 1) ^ 1, abort_flag, kBwd1WaitLimit)) {
+          fail(0x60000u | 0x8000u | (uint32_t)s);
+          break;
+        }
+        const int64_t row = pair + n * (int64_t)n_pairs;
+        ctl->row[s] = row;
+        const uint32_t full = ptx::smem_u32(&ctl->full[s]);
+        const uint32_t dst = ptx::smem_u32(pair_smem + (size_t)s * slot_bytes);
+        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+        ptx::bulk_load(dst, P.x + row * cols_full + col0, row_bytes, full);
+        ptx::bulk_load(dst + half_slot, P.dy + row * cols_full + col0, row_bytes, full);
+        ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+        ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + (row & ~3LL), 16u, full);
+        ++issued;
+      }
+      if (*abort_flag) {
+        uint32_t never = 0;
+        for (int sl = 0; sl < stages; ++sl) {
+          const int64_t uses = issued > sl ? (issued - sl + stages - 1) / stages : 0;
+          if (uses) ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[sl]), (uint32_t)((uses - 1) & 1), &never, kBwd1WaitLimit);
+        }
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int v = tid; v < (int)(half_slot / 16u); v += kBwd1Consumers)
+      gsm[v] = v * 8 < cols ? __ldg(reinterpret_cast<const uint4*>(P.gamma + col0) + v) : make_uint4(0u, 0u, 0u, 0u);
+    ptx::named_barrier<1, kBwd1Consumers>();
+    float2 acc_w[P2], acc_b[P2];
+#pragma unroll
+    for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
+    const float inv_cols = 1.0f / (float)cols_full;
+    const uint32_t red_local = ptx::smem_u32(&red[0][0][0]);
+    const uint32_t red_peer = ptx::mapa(red_local, peer);
+    const uint32_t rowbar_local = ptx::smem_u32(&ctl->rowbar[0]);
+    const uint32_t rowbar_peer = ptx::mapa(rowbar_local, peer);
+
+    bool alive = true;
+    auto phase1 = [&](int64_t n, int s, uint32_t use) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->full[s]), use & 1, abort_flag, kBwd1WaitLimit)) {
+        fail(0x70000u | 0x8000u | (uint32_t)s);
+        alive = false;
+        return;
+      }
+      const uint8_t* slot = pair_smem + (size_t)s * slot_bytes;
+      const int64_t row = ctl->row[s];
+      const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
+      const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 64u)[row & 3];
+      const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
+      float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int v = k * kBwd1Consumers + tid;
+        uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u), gv = make_uint4(0u, 0u, 0u, 0u);
+        if (v * 8 < cols) {
+          xr = reinterpret_cast<const uint4*>(slot)[v];
+          dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+          gv = gsm[v];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
+          const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
+          acc_w[k * 4 + e] = ptx::fma2(d, h, acc_w[k * 4 + e]);
+          acc_b[k * 4 + e] = ptx::add2(acc_b[k * 4 + e], d);
+          const float2 w = ptx::mul2(d, __half22float2(reinterpret_cast<const __half2*>(&gv)[e]));
+          s1 = ptx::fma2(h, w, s1);
+          s2 = ptx::add2(s2, w);
+        }
+      }
+      float a = s1.x + s1.y, bsum = s2.x + s2.y;
+#pragma unroll
+      for (int o = 1; o <= 16; o <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        bsum += __shfl_xor_sync(0xffffffffu, bsum, o);
+      }
+      if (lane == 0) {
+        // this warp's totals into its slot of red[] in both CTAs, then one arrival on either row barrier
+        const uint32_t off = (uint32_t)((((n & 3) * 2 * NW) + (int)rank * NW + warp) * 2) * 4u;
+        red[n & 3][rank * NW + warp][0] = a;
+        red[n & 3][rank * NW + warp][1] = bsum;
+        ptx::st_cluster_f32x2(red_peer + off, a, bsum);
+        ptx::mbar_arrive_cluster(rowbar_local + (uint32_t)(n & 1) * 8u);
+        ptx::mbar_arrive_cluster(rowbar_peer + (uint32_t)(n & 1) * 8u);
+      }
+    };
+    auto phase2 = [&](int64_t n, int s) {
+      if (!ptx::mbar_wait_bounded_cluster(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
+                                          kBwd1WaitLimit)) {
+        fail(0x78000u | 0x4000u | (uint32_t)s);
+        alive = false;
+        return;
+      }
+      float2 ss = *reinterpret_cast<const float2*>(&red[n & 3][lane][0]);  // 32 warp totals, one per lane
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+        ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+      }
+      const uint8_t* slot = pair_smem + (size_t)s * slot_bytes;
+      const int64_t row = ctl->row[s];
+      const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
+      const float rstd = reinterpret_cast<const float*>(slot + 2u * half_slot + 64u)[row & 3];
+      const float2 rstd2 = make_float2(rstd, rstd), shift2 = make_float2(-mean * rstd, -mean * rstd);
+      const float c1r = ss.x * inv_cols * rstd, c2r = ss.y * inv_cols * rstd;
+      const float2 nc1 = make_float2(-c1r, -c1r), nc2 = make_float2(-c2r, -c2r);
+      __half* __restrict__ dx = P.dx + row * cols_full + col0;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int v = k * kBwd1Consumers + tid;
+        if (v * 8 < cols) {
+          const uint4 xr = reinterpret_cast<const uint4*>(slot)[v];
+          const uint4 dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
+          const uint4 gv = gsm[v];
+          uint4 outv;
+          __half2* o2 = reinterpret_cast<__half2*>(&outv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 d = __half22float2(reinterpret_cast<const __half2*>(&dr)[e]);
+            const float2 h = ptx::fma2(__half22float2(reinterpret_cast<const __half2*>(&xr)[e]), rstd2, shift2);
+            const float2 w = ptx::mul2(d, __half22float2(reinterpret_cast<const __half2*>(&gv)[e]));
+            const float2 t = ptx::fma2(h, nc1, ptx::fma2(w, rstd2, nc2));
+            o2[e] = __floats2half2_rn(t.x, t.y);
+          }
+          __stcs(reinterpret_cast<uint4*>(dx + v * 8), outv);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
+    };
+
+    int s1 = 0, s2 = 0;
+    uint32_t use1 = 0;
+    auto advance = [&](int& s) { s = (s + 1 == stages) ? 0 : s + 1; };
+    if (my_rows > 0) phase1(0, s1, use1);
+    for (int64_t n = 0; alive && n < my_rows; ++n) {
+      if (n + 1 < my_rows) {
+        advance(s1);
+        use1 += (s1 == 0);
+        phase1(n + 1, s1, use1);
+        if (!alive) break;
+      }
+      phase2(n, s2);
+      advance(s2);
+    }
+    if (!*abort_flag) {
+      float* pw = P.partial + (size_t)pair * cols_full + col0;
+      float* pb = P.partial + ((size_t)P.partial_rows + pair) * cols_full + col0;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int c = (k * kBwd1Consumers + tid) * 8;
+        if (c < cols) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = k * 4 + 2 * e;
+            *reinterpret_cast<float4*>(pw + c + 4 * e) = make_float4(acc_w[j].x, acc_w[j].y, acc_w[j + 1].x, acc_w[j + 1].y);
+            *reinterpret_cast<float4*>(pb + c + 4 * e) = make_float4(acc_b[j].x, acc_b[j].y, acc_b[j + 1].x, acc_b[j + 1].y);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  ptx::cluster_sync();  // neither CTA leaves while the other may still store into its shared memory
+}
+
+// The pair kernel for rows of more than 16 Ki columns; LEGO_ERR_UNSUPPORTED when the device cannot
+// schedule the clusters or the shape does not suit it.
+int32_t launch_pair_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
+  const int col_half = (int)((((int64_t)P.cols + 1) / 2 + 7) & ~7LL);  // columns of the first CTA, a multiple of 8
+  if (col_half > kBwd1Consumers * 32 || P.cols - col_half < 8) return LEGO_ERR_UNSUPPORTED;
+  const size_t half_slot = ((size_t)col_half * 2 + 127) & ~(size_t)127;
+  const size_t slot = 2 * half_slot + 128;
+  static PerDeviceFlag configured;
+  if (!configured.test(ctx->device)) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(ln_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
+    configured.set(ctx->device);
+  }
+  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdPairCtl) - 128 - half_slot;
+  int stages = (int)(budget / slot);
+  if (stages > kBwd1Ring) stages = kBwd1Ring;
+  if (stages < 3) return LEGO_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)stages * slot + half_slot + sizeof(BwdPairCtl) + 128;
+  int pairs = ctx->sm_count / 2;
+  if (pairs > P.rows) pairs = (int)P.rows;
+  if (pairs < 1) return LEGO_ERR_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kBwd1Consumers + 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  int max_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, ln_bwd_pair_kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+    (void)cudaGetLastError();
+    return LEGO_ERR_UNSUPPORTED;
+  }
+  if (pairs > max_clusters) {  // every pair must be resident: the grid is persistent
+    pairs = max_clusters;
+    cfg.gridDim = dim3(2 * pairs);
+  }
+  P.partial_rows = pairs;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, ln_bwd_pair_kernel, P, stages, col_half, ctx->status_word);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return cuda_status(e);
+}
+
 // ---- bulk-copy pipelined dx kernel, several groups (rows of up to 3 Ki columns) ------
 //
 // One CTA per SM.  A producer thread streams x and dy into a shared-memory ring with 1-D
@@ -958,12 +1246,13 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
   // (Rows of 8 Ki .. 16 Ki columns, 8192 rows, same box: 24 / 32 columns per thread with gamma in
   // shared memory 3.2 - 4.9 TB/s; the register kernel they ran on before 1.1; the library kernel 2.1.)
-  if (vec && cols >= 1024 && cols <= kBwdConsumers * 32 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
+  if (vec && cols >= 1024 && cols <= kBwdConsumers * 64 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
       a16(partial) && rows >= 2 * (int64_t)ctx->sm_count) {
     // Same box, GB/s, 16384 rows, both kernels with rows in two phases: one group of 512 threads /
     // groups of cols/16 threads: N = 2048: 2010 / 4180, N = 4096: 3850 / 5350, N = 6144: 4160 / 4670,
     // N = 8192: 5500 / 5250.
-    if (cols > kBwd1Consumers * 16) st = cols <= kBwd1Consumers * 24 ? launch_ring1_dx<24>(P, ctx, s) : launch_ring1_dx<32>(P, ctx, s);
+    if (cols > kBwd1Consumers * 32) st = launch_pair_dx(P, ctx, s);
+    else if (cols > kBwd1Consumers * 16) st = cols <= kBwd1Consumers * 24 ? launch_ring1_dx<24>(P, ctx, s) : launch_ring1_dx<32>(P, ctx, s);
     else if (cols > g_lnbwd_split.load()) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
     else st = launch_ring_dx<16>(P, ctx, s);
   }

@@ -172,9 +172,11 @@ def test_layernorm_backward_shapes_of_both_kernels():
     for neighbours that take the register kernel; tolerances of the reference's own test
     (atol 1e-2) for dx, 1e-2 of the largest entry for the column sums."""
     # (wide rows: 8 Ki < cols <= 16 Ki take the ring kernel with 32 columns per thread and gamma
-    # in shared memory; beyond, and for row counts below two per SM, the register kernel)
+    # in shared memory; 16 Ki < cols <= 32 Ki a CTA pair per row; row counts below two per SM the
+    # register kernel)
     for rows, cols in ((1152, 8192), (600, 4096), (2048, 2056), (1152, 1032), (1150, 8192), (512, 8200), (300, 1024),
-                       (1200, 1024), (600, 16384), (596, 12296), (300, 9000), (128, 16384), (320, 20480)):
+                       (1200, 1024), (600, 16384), (596, 12296), (300, 9000), (128, 16384), (320, 20480), (600, 32768),
+                       (296, 16400), (444, 30008)):
         g = torch.Generator().manual_seed(rows + cols)
         w = torch.rand(cols, generator=g).half()
         b = torch.rand(cols, generator=g).half()
