@@ -1116,6 +1116,7 @@ bool ids_share_columns(const Problem& p, int n) {
 extern std::atomic<int> g_lnbwd_split;      // layernorm_bwd.cu
 extern std::atomic<int> g_lnbwd_lanes;      // layernorm_bwd.cu
 extern std::atomic<int> g_lnbwd_fold;       // layernorm_bwd.cu
+extern std::atomic<int> g_lnbwd_min_rows;   // layernorm_bwd.cu
 extern std::atomic<int> g_chunk_tile_vecs;  // permute.cu
 extern std::atomic<int> g_dma_tile_bytes;   // permute.cu
 extern std::atomic<int> g_dma_ctas_per_sm;  // permute.cu
@@ -1366,6 +1367,10 @@ int32_t lego_tune(int32_t knob, int32_t value) {
       if (value < 0 || (value & 7) > 2 || value > 10) return LEGO_ERR_SIZE;
       g_lnbwd_lanes.store(value & 7);
       g_lnbwd_fold.store(value & 8 ? 0 : 1);
+      return LEGO_OK;
+    case LEGO_TUNE_LNBWD_MIN_ROWS:
+      if (value < 1) return LEGO_ERR_SIZE;
+      g_lnbwd_min_rows.store(value);
       return LEGO_OK;
     case LEGO_TUNE_PDL_LAST_WAVE:
       if (value < 0 || value > 1) return LEGO_ERR_SIZE;

@@ -16,6 +16,8 @@
 namespace lego {
 // lego_tune(LEGO_TUNE_LNBWD_LANES): producer of the grouped ring kernel.  0 = one thread; 1 = a lane
 // per group in lock step where a slot holds one row; 2 = the same, and never the block form.
+// fewest rows the ring-fed kernels take; below, the register kernel
+std::atomic<int> g_lnbwd_min_rows{1};
 std::atomic<int> g_lnbwd_lanes{1};
 // 8 added to the knob's value: every group writes its own partial row (no fold inside the CTA)
 std::atomic<int> g_lnbwd_fold{1};
@@ -126,6 +128,15 @@ ln_bwd_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dga
 // stores.  Memory-level parallelism comes from the ring (as many rows of x and dy in
 // flight per SM as fit, up to 12), not from occupancy.
 
+// The statistics of a row whose 16-byte chunk would reach past the arrays (the last rows & 3 rows of
+// a row count that is no multiple of four): the producer reads the two floats itself and stores
+// them where the chunk's copy would have put them (mean chunk at `stats`, rstd chunk `rstd_off`
+// bytes behind), before its arrive on the slot's barrier, which publishes them to the consumers.
+__device__ __forceinline__ void stats_by_hand(unsigned char* stats, uint32_t rstd_off, const BwdParams& P, int64_t row) {
+  reinterpret_cast<float*>(stats)[row & 3] = P.mean[row];
+  reinterpret_cast<float*>(stats + rstd_off)[row & 3] = P.rstd[row];
+}
+
 constexpr int kBwd1Consumers = 512;
 constexpr int kBwd1Ring = 12;  // two slots are held by the rows in phase 1 and phase 2, the rest are loads in flight
 constexpr long long kBwd1WaitLimit = 2000000000LL;  // SM cycles, about a second
@@ -191,11 +202,15 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
         ctl->row[s] = row;
         const uint32_t full = ptx::smem_u32(&ctl->full[s]);
         const uint32_t dst = ptx::smem_u32(bwd1_smem + (size_t)s * slot_bytes);
-        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+        const bool whole = (row | 3) < P.rows;  // else by plain loads: see stats_by_hand
+        if (!whole) stats_by_hand(bwd1_smem + (size_t)s * slot_bytes + 2u * half_slot, 16u, P, row);
+        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + (whole ? 32u : 0u));
         ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
         ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
-        ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
-        ptx::bulk_load(dst + 2u * half_slot + 16u, P.rstd + (row & ~3LL), 16u, full);
+        if (whole) {
+          ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+          ptx::bulk_load(dst + 2u * half_slot + 16u, P.rstd + (row & ~3LL), 16u, full);
+        }
         ++issued;
       }
       if (*abort_flag) {
@@ -490,11 +505,15 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
         ctl->row[s] = row;
         const uint32_t full = ptx::smem_u32(&ctl->full[s]);
         const uint32_t dst = ptx::smem_u32(pair_smem + (size_t)s * slot_bytes);
-        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+        const bool whole = (row | 3) < P.rows;
+        if (!whole) stats_by_hand(pair_smem + (size_t)s * slot_bytes + 2u * half_slot, 64u, P, row);
+        ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + (whole ? 32u : 0u));
         ptx::bulk_load(dst, P.x + row * cols_full + col0, row_bytes, full);
         ptx::bulk_load(dst + half_slot, P.dy + row * cols_full + col0, row_bytes, full);
-        ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
-        ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + (row & ~3LL), 16u, full);
+        if (whole) {
+          ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+          ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + (row & ~3LL), 16u, full);
+        }
         ++issued;
       }
       if (*abort_flag) {
@@ -799,11 +818,15 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
             ctl->row[sl] = row;
             const uint32_t full = ptx::smem_u32(&ctl->full[sl]);
             const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)sl * slot_bytes);
-            ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + 32u);
+            const bool whole = (row | 3) < P.rows;
+            if (!whole) stats_by_hand(bwd_smem + (size_t)sl * slot_bytes + 2u * half_slot, 64u, P, row);
+            ptx::mbar_arrive_expect_tx(full, 2u * row_bytes + (whole ? 32u : 0u));
             ptx::bulk_load(dst, P.x + row * cols, row_bytes, full);
             ptx::bulk_load(dst + half_slot, P.dy + row * cols, row_bytes, full);
-            ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
-            ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + (row & ~3LL), 16u, full);
+            if (whole) {
+              ptx::bulk_load(dst + 2u * half_slot, P.mean + (row & ~3LL), 16u, full);
+              ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + (row & ~3LL), 16u, full);
+            }
           }
         }
         if (__any_sync(0xffffffffu, failed)) break;
@@ -837,19 +860,27 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
         const int64_t row0 = (blockIdx.x + n * (int64_t)gridDim.x) * per_fill;
         const int64_t left = P.rows - row0;
         const uint32_t bytes = (uint32_t)(left < per_fill ? left : per_fill) * row_bytes;
-        // the rows' statistics: the 16-byte chunks that hold rows row0 .. row0 + groups - 1 (the row
-        // count is a multiple of 4, so a chunk never reaches past the arrays)
+        // the rows' statistics: the whole 16-byte chunks that hold rows row0 .. end - 1; the rows of a
+        // last chunk that would reach past the arrays by plain loads
+        const int64_t end = row0 + (left < per_fill ? left : per_fill);
         const int64_t chunk0 = row0 & ~3LL;
-        const int64_t stat_rows = (row0 + (left < per_fill ? left : per_fill) - chunk0 + 3) & ~3LL;
-        const uint32_t stat_bytes = (uint32_t)stat_rows * 4u;
+        const int64_t chunk_end = ((end + 3) & ~3LL) <= P.rows ? ((end + 3) & ~3LL) : (P.rows & ~3LL);
+        const uint32_t stat_bytes = (uint32_t)(chunk_end - chunk0) * 4u;
+        for (int64_t r = chunk_end > row0 ? chunk_end : row0; r < end; ++r) {
+          float* st = reinterpret_cast<float*>(bwd_smem + (size_t)s * slot_bytes + 2u * half_slot);
+          st[r - chunk0] = P.mean[r];
+          st[16 + (r - chunk0)] = P.rstd[r];
+        }
         ctl->row[s] = row0;
         const uint32_t full = ptx::smem_u32(&ctl->full[s]);
         const uint32_t dst = ptx::smem_u32(bwd_smem + (size_t)s * slot_bytes);
         ptx::mbar_arrive_expect_tx(full, 2u * bytes + 2u * stat_bytes);
         ptx::bulk_load(dst, P.x + row0 * cols, bytes, full);
         ptx::bulk_load(dst + half_slot, P.dy + row0 * cols, bytes, full);
-        ptx::bulk_load(dst + 2u * half_slot, P.mean + chunk0, stat_bytes, full);
-        ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + chunk0, stat_bytes, full);
+        if (stat_bytes) {
+          ptx::bulk_load(dst + 2u * half_slot, P.mean + chunk0, stat_bytes, full);
+          ptx::bulk_load(dst + 2u * half_slot + 64u, P.rstd + chunk0, stat_bytes, full);
+        }
         ++issued;
       }
       if (*abort_flag) {
@@ -1242,12 +1273,16 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
   int32_t err = LEGO_OK;
   DeviceCtx* ctx = device_ctx(&err);
   if (!ctx) return err;
-  // Ring-fed kernel: 16-byte aligned rows of 1 Ki .. 16 Ki columns, enough rows to fill the
-  // SMs, the row count a multiple of 4 (the statistics travel in 16-byte chunks).
+  // Ring-fed kernels: 16-byte aligned rows of 1 Ki .. 32 Ki columns, any number of rows (the rows'
+  // statistics travel in 16-byte chunks; the last rows & 3 rows, whose chunk would reach past the
+  // arrays, get theirs by plain loads -- the reference's own test shape has 1151 rows).
   // (Rows of 8 Ki .. 16 Ki columns, 8192 rows, same box: 24 / 32 columns per thread with gamma in
-  // shared memory 3.2 - 4.9 TB/s; the register kernel they ran on before 1.1; the library kernel 2.1.)
-  if (vec && cols >= 1024 && cols <= kBwdConsumers * 64 && rows % 4 == 0 && a16(mean) && a16(rstd) &&
-      a16(partial) && rows >= 2 * (int64_t)ctx->sm_count) {
+  // shared memory 3.2 - 4.9 TB/s; the register kernel they ran on before 1.1; the library kernel 2.1.
+  // Few rows, us per call, ring kernels / register kernel / library: 256 x 4096 7.3 / 16.4 / 7.7,
+  // 100 x 8192 9.1 / 17.2 / 11.2, 64 x 4096 5.9 / 9.0 / 6.3, 12 x 1024 3.9 / 5.2 / 4.4.)
+  if (vec && cols >= 1024 && cols <= kBwdConsumers * 64 && rows >= g_lnbwd_min_rows.load() && a16(mean) && a16(rstd) &&
+      a16(partial)) {
+    const int32_t room = P.partial_rows;
     // Same box, GB/s, 16384 rows, both kernels with rows in two phases: one group of 512 threads /
     // groups of cols/16 threads: N = 2048: 2010 / 4180, N = 4096: 3850 / 5350, N = 6144: 4160 / 4670,
     // N = 8192: 5500 / 5250.
@@ -1255,6 +1290,7 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
     else if (cols > kBwd1Consumers * 16) st = cols <= kBwd1Consumers * 24 ? launch_ring1_dx<24>(P, ctx, s) : launch_ring1_dx<32>(P, ctx, s);
     else if (cols > g_lnbwd_split.load()) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
     else st = launch_ring_dx<16>(P, ctx, s);
+    if (st == LEGO_ERR_UNSUPPORTED) P.partial_rows = room;
   }
   if (st == LEGO_ERR_UNSUPPORTED) st = vec ? launch_dx_by_cols<true>(P, s) : launch_dx_by_cols<false>(P, s);
   if (st != LEGO_OK) return st;

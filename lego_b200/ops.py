@@ -152,7 +152,8 @@ def selftest_bounded_wait(limit_cycles: int = 1_000_000) -> None:
 def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
          gemm_lag: Optional[int] = None, permute_dma_tile: Optional[int] = None,
          permute_dma_ctas: Optional[int] = None, permute_tile_vecs: Optional[int] = None,
-         pdl_last_wave: Optional[int] = None, permute_dma_long: Optional[int] = None) -> None:
+         pdl_last_wave: Optional[int] = None, permute_dma_long: Optional[int] = None,
+         lnbwd_min_rows: Optional[int] = None) -> None:
     """Process-wide knobs.  GEMM: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
     pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` 0 / False keeps every tile whole,
     1 / True splits a poorly filled last wave along K, 2 splits any partial wave;
@@ -161,8 +162,12 @@ def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
     kernel takes those layouts), ``permute_dma_ctas`` its CTAs per SM, ``permute_tile_vecs``
     most 16-byte vectors per tile of the chunk-tiled kernel, ``permute_dma_long`` 0: pairs whose
     common run is a whole line or more stay with the vector copy.  ``pdl_last_wave`` 1: only the last
-    wave of an index-map grid lets the next grid of the stream become resident."""
+    wave of an index-map grid lets the next grid of the stream become resident.
+    ``lnbwd_min_rows``: fewest rows for which LayerNorm backward uses its ring-fed kernels
+    (default 1; below, the kernel that holds a row in registers)."""
     lib = _abi.lib()
+    if lnbwd_min_rows is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_LNBWD_MIN_ROWS, int(lnbwd_min_rows)), "lego_tune")
     if permute_dma_tile is not None:
         _abi.check(lib.lego_tune(_abi.TUNE_PERMUTE_DMA_TILE, int(permute_dma_tile)), "lego_tune")
     if permute_dma_ctas is not None:

@@ -166,17 +166,8 @@ def test_layernorm_backward_matches_reference_test():
     assert torch.equal(y2, y)
 
 
-def test_layernorm_backward_shapes_of_both_kernels():
-    """dx / dweight / dbias against the oracle for row counts and widths that take the
-    ring-fed kernel (row count a multiple of 4, 1 Ki < cols <= 8 Ki, 16-byte rows) and
-    for neighbours that take the register kernel; tolerances of the reference's own test
-    (atol 1e-2) for dx, 1e-2 of the largest entry for the column sums."""
-    # (wide rows: 8 Ki < cols <= 16 Ki take the ring kernel with 32 columns per thread and gamma
-    # in shared memory; 16 Ki < cols <= 32 Ki a CTA pair per row; row counts below two per SM the
-    # register kernel)
-    for rows, cols in ((1152, 8192), (600, 4096), (2048, 2056), (1152, 1032), (1150, 8192), (512, 8200), (300, 1024),
-                       (1200, 1024), (600, 16384), (596, 12296), (300, 9000), (128, 16384), (320, 20480), (600, 32768),
-                       (296, 16400), (444, 30008)):
+def _check_layernorm_backward(shapes):
+    for rows, cols in shapes:
         g = torch.Generator().manual_seed(rows + cols)
         w = torch.rand(cols, generator=g).half()
         b = torch.rand(cols, generator=g).half()
@@ -192,6 +183,35 @@ def test_layernorm_backward_shapes_of_both_kernels():
         again = ops.layer_norm_bwd(dy.cuda(), x.cuda(), w.cuda(), mean.cuda(), rstd.cuda())
         assert all(torch.equal(a, b) for a, b in zip(again, (dx, dw, db))), (rows, cols)
     ops.device_status()
+
+
+def test_layernorm_backward_shapes_of_both_kernels():
+    """dx / dweight / dbias against the oracle for row counts and widths that take the
+    ring-fed kernels (16-byte rows of 1 Ki columns or more) and for neighbours that take the
+    register kernel (narrower rows, widths that are no multiple of 8); tolerances of the
+    reference's own test (atol 1e-2) for dx, 1e-2 of the largest entry for the column sums."""
+    # (wide rows: 8 Ki < cols <= 16 Ki take the ring kernel with 24 or 32 columns per thread and
+    # gamma in shared memory; 16 Ki < cols <= 32 Ki a CTA pair per row)
+    _check_layernorm_backward(((1152, 8192), (600, 4096), (2048, 2056), (1152, 1032), (1150, 8192), (512, 8200),
+                               (300, 1024), (1200, 1024), (600, 16384), (596, 12296), (300, 9000), (128, 16384),
+                               (320, 20480), (600, 32768), (296, 16400), (444, 30008), (37, 1000), (300, 777),
+                               (64, 4100)))
+
+
+def test_layernorm_backward_row_counts_that_are_no_multiple_of_four():
+    """The ring-fed kernels fetch the rows' statistics in 16-byte chunks; the rows of a last,
+    incomplete chunk get theirs by plain loads.  Every kernel of the family (groups of rows per
+    CTA with one row or a block of rows per slot, one group with 8 .. 32 columns per thread, a
+    CTA pair per row), with one to three rows left over, few rows and a single row; then the
+    same shapes through the register kernel."""
+    shapes = ((4095, 4096), (9479, 1024), (9474, 2048), (1201, 1536), (601, 20480), (131, 32768), (203, 3072),
+              (31, 8192), (7, 2048), (3, 4096), (1, 1024), (2, 16384), (149, 12288))
+    _check_layernorm_backward(shapes)
+    ops.tune(lnbwd_min_rows=1 << 30)
+    try:
+        _check_layernorm_backward(shapes[3:])
+    finally:
+        ops.tune(lnbwd_min_rows=1)
 
 
 def test_layernorm_errors():
