@@ -149,10 +149,12 @@ struct BwdRing1Ctl {
   uint32_t abort_flag;
 };
 
+// FULLW (EPT 24 or 32 only): the row is exactly 512 x EPT columns wide, so no vector of a thread
+// lies past its end: no bounds predicates and no zero fill of the vectors.
 // EPT: columns per consumer thread, 8 or 16 with gamma in registers; 24 or 32 (rows of 8 Ki .. 16 Ki
 // columns) with gamma staged once per CTA in shared memory as fp16, because 64 accumulator
 // registers leave no room for it: three ring slots of 64 KiB then.
-template <int EPT>
+template <int EPT, bool FULLW>
 __global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
 ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
   constexpr int NV = EPT / 8;
@@ -243,14 +245,14 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   if (GSMEM) {
     uint4* gw = reinterpret_cast<uint4*>(bwd1_smem + (size_t)stages * slot_bytes);
     for (int v = tid; v < (int)(half_slot / 16u); v += kBwd1Consumers)
-      gw[v] = v * 8 < cols ? __ldg(reinterpret_cast<const uint4*>(P.gamma) + v) : make_uint4(0u, 0u, 0u, 0u);
+      gw[v] = (FULLW || v * 8 < cols) ? __ldg(reinterpret_cast<const uint4*>(P.gamma) + v) : make_uint4(0u, 0u, 0u, 0u);
     ptx::named_barrier<1, kBwd1Consumers>();  // consumers only: the producer is already streaming rows
   } else {
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int c = (k * kBwd1Consumers + tid) * 8;
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (c < cols) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
+      if ((FULLW || c < cols)) raw = __ldg(reinterpret_cast<const uint4*>(P.gamma + c));
       const __half2* hp = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
       for (int e = 0; e < 4; ++e) g[k * 4 + e] = __half22float2(hp[e]);
@@ -283,7 +285,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
     for (int k = 0; k < NV; ++k) {
       const int v = k * kBwd1Consumers + tid;
       uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u), gv = make_uint4(0u, 0u, 0u, 0u);
-      if (v * 8 < cols) {
+      if ((FULLW || v * 8 < cols)) {
         xr = reinterpret_cast<const uint4*>(slot)[v];
         dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
         if (GSMEM) gv = gsm[v];
@@ -341,7 +343,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
     for (int k = 0; k < NV; ++k) {
       const int v = k * kBwd1Consumers + tid;
       uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u), gv = make_uint4(0u, 0u, 0u, 0u);
-      if (v * 8 < cols) {
+      if ((FULLW || v * 8 < cols)) {
         xr = reinterpret_cast<const uint4*>(slot)[v];
         dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
         if (GSMEM) gv = gsm[v];
@@ -356,7 +358,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
         o2[e] = __floats2half2_rn(t.x, t.y);
       }
       // with 32 columns per thread the results leave at once: no registers to park four vectors in
-      if (GSMEM && v * 8 < cols) __stcs(reinterpret_cast<uint4*>(dx + v * 8), outv[k]);
+      if (GSMEM && (FULLW || v * 8 < cols)) __stcs(reinterpret_cast<uint4*>(dx + v * 8), outv[k]);
     }
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[s]));  // slot may be refilled now
@@ -364,7 +366,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
         const int c = (k * kBwd1Consumers + tid) * 8;
-        if (c < cols) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
+        if ((FULLW || c < cols)) __stcs(reinterpret_cast<uint4*>(dx + c), outv[k]);
       }
     }
   };
@@ -390,7 +392,7 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
     const int c = (k * kBwd1Consumers + tid) * 8;
-    if (c < cols) {
+    if ((FULLW || c < cols)) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = k * 4 + 2 * e;
@@ -404,13 +406,17 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 // Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
 template <int EPT>
 int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
-  auto kern = ln_bwd_ring1_kernel<EPT>;
+  // Without the bounds predicates, same box: 8192 x 12288 (24 columns per thread) 135.7 -> 119 us,
+  // 8192 x 16384 (32) 176 -> 164 us; 16384 x 8192 (16) 150 -> 154 us with gamma in registers, 151 -> 158 us
+  // with gamma in shared memory, so not there.
+  const bool fullw = EPT > 16 && P.cols == EPT * kBwd1Consumers;
+  auto kern = fullw ? ln_bwd_ring1_kernel<EPT, (EPT > 16)> : ln_bwd_ring1_kernel<EPT, false>;
   const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
-  static PerDeviceFlag configured;
-  if (!configured.test(ctx->device)) {
+  static PerDeviceFlag configured[2];  // one per kernel
+  if (!configured[fullw].test(ctx->device)) {
     LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
-    configured.set(ctx->device);
+    configured[fullw].set(ctx->device);
   }
   const size_t gamma_bytes = EPT > 16 ? half_slot : 0;  // gamma staged in shared memory
   const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128 - gamma_bytes;
@@ -445,6 +451,7 @@ struct BwdPairCtl {
   uint32_t abort_flag;
 };
 
+template <bool FULLW>  // FULLW: 32768 columns, both halves exactly 512 x 32: no bounds predicates
 __global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
 ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half, uint32_t* status) {
   constexpr int EPT = 32;
@@ -528,7 +535,7 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
     // ---------------- consumers ----------------
     const int lane = tid & 31, warp = tid >> 5;
     for (int v = tid; v < (int)(half_slot / 16u); v += kBwd1Consumers)
-      gsm[v] = v * 8 < cols ? __ldg(reinterpret_cast<const uint4*>(P.gamma + col0) + v) : make_uint4(0u, 0u, 0u, 0u);
+      gsm[v] = (FULLW || v * 8 < cols) ? __ldg(reinterpret_cast<const uint4*>(P.gamma + col0) + v) : make_uint4(0u, 0u, 0u, 0u);
     ptx::named_barrier<1, kBwd1Consumers>();
     float2 acc_w[P2], acc_b[P2];
 #pragma unroll
@@ -556,7 +563,7 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
       for (int k = 0; k < NV; ++k) {
         const int v = k * kBwd1Consumers + tid;
         uint4 xr = make_uint4(0u, 0u, 0u, 0u), dr = make_uint4(0u, 0u, 0u, 0u), gv = make_uint4(0u, 0u, 0u, 0u);
-        if (v * 8 < cols) {
+        if ((FULLW || v * 8 < cols)) {
           xr = reinterpret_cast<const uint4*>(slot)[v];
           dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
           gv = gsm[v];
@@ -612,7 +619,7 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
         const int v = k * kBwd1Consumers + tid;
-        if (v * 8 < cols) {
+        if ((FULLW || v * 8 < cols)) {
           const uint4 xr = reinterpret_cast<const uint4*>(slot)[v];
           const uint4 dr = reinterpret_cast<const uint4*>(slot + half_slot)[v];
           const uint4 gv = gsm[v];
@@ -653,7 +660,7 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
         const int c = (k * kBwd1Consumers + tid) * 8;
-        if (c < cols) {
+        if ((FULLW || c < cols)) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int j = k * 4 + 2 * e;
@@ -675,10 +682,12 @@ int32_t launch_pair_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   if (col_half > kBwd1Consumers * 32 || P.cols - col_half < 8) return LEGO_ERR_UNSUPPORTED;
   const size_t half_slot = ((size_t)col_half * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
-  static PerDeviceFlag configured;
-  if (!configured.test(ctx->device)) {
-    LEGO_CUDA_TRY(cudaFuncSetAttribute(ln_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
-    configured.set(ctx->device);
+  const bool fullw = P.cols == 2 * kBwd1Consumers * 32;
+  auto kern = fullw ? ln_bwd_pair_kernel<true> : ln_bwd_pair_kernel<false>;
+  static PerDeviceFlag configured[2];  // one per kernel
+  if (!configured[fullw].test(ctx->device)) {
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
+    configured[fullw].set(ctx->device);
   }
   const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdPairCtl) - 128 - half_slot;
   int stages = (int)(budget / slot);
@@ -703,7 +712,7 @@ int32_t launch_pair_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   int max_clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&max_clusters, ln_bwd_pair_kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters < 1) {
     (void)cudaGetLastError();
     return LEGO_ERR_UNSUPPORTED;
   }
@@ -712,7 +721,7 @@ int32_t launch_pair_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
     cfg.gridDim = dim3(2 * pairs);
   }
   P.partial_rows = pairs;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, ln_bwd_pair_kernel, P, stages, col_half, ctx->status_word);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, P, stages, col_half, ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
 }
