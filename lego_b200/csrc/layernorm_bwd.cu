@@ -145,7 +145,9 @@ struct BwdRing1Ctl {
   uint64_t full[kBwd1Ring];
   uint64_t empty[kBwd1Ring];
   uint64_t rowbar[2];  // row n's warp totals are all in red[]: 16 arrivals (one per consumer warp)
+  uint64_t totbar[2];  // row n's totals are in tot[]: one arrival (the folding warp)
   int64_t row[kBwd1Ring];
+  float2 tot[4];       // [row & 3] -> the row's (s1, s2)
   uint32_t abort_flag;
 };
 
@@ -155,8 +157,9 @@ struct BwdRing1Ctl {
 // columns) with gamma staged once per CTA in shared memory as fp16, because 64 accumulator
 // registers leave no room for it: three ring slots of 64 KiB then.
 template <int EPT, bool FULLW>
-__global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
+__global__ void __launch_bounds__(kBwd1Consumers + (EPT <= 24 ? 64 : 32), 1)
 ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
+  constexpr bool fold_warp = EPT <= 24;  // a second helper warp folds the rows' totals (see there)
   constexpr int NV = EPT / 8;
   constexpr int NW = kBwd1Consumers / 32;
   constexpr bool GSMEM = EPT > 16;
@@ -179,6 +182,8 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
     }
     ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[0]), NW);
     ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[1]), NW);
+    ptx::mbar_init(ptx::smem_u32(&ctl->totbar[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&ctl->totbar[1]), 1);
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -187,6 +192,36 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   ptx::launch_dependents();     // the column reduction (or the next op) may set itself up now
   ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
 
+  if (tid >= kBwd1Consumers + 32) {
+    // ---------------- folding warp ----------------
+    // Folds the 16 warp totals of a row once for the whole CTA (the same shuffle tree every
+    // consumer thread runs for itself when fold_warp is 0) and publishes the result through
+    // totbar: the consumers' phase 2 then starts with one shared-memory load instead of a chain
+    // of four dependent shuffle levels.  Same box, 16384 x 8192: 152 -> 135 us; 16384 x 7168:
+    // 146 -> 128 us; 8192 x 10240: 125 -> 104 us; with the three ring slots of rows beyond
+    // 12 Ki columns (32 columns per thread) 160 -> 165 us, so those instances do without it.
+    const int lane = tid & 31;
+    for (int64_t n = 0; fold_warp && n < my_rows; ++n) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
+                                  kBwd1WaitLimit)) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, 0x78000u | (uint32_t)(n & 0xfff));
+        break;
+      }
+      float2 ss = *reinterpret_cast<const float2*>(&red[n & 3][lane & (NW - 1)][0]);
+#pragma unroll
+      for (int o = NW / 2; o > 0; o >>= 1) {
+        ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+        ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+      }
+      if (lane == 0) {
+        ctl->tot[n & 3] = ss;
+        ptx::mbar_arrive(ptx::smem_u32(&ctl->totbar[n & 1]));  // release: the store above is visible to the waiters
+      }
+      __syncwarp();
+    }
+    return;
+  }
   if (tid >= kBwd1Consumers) {
     // ---------------- producer ----------------
     if (tid == kBwd1Consumers) {
@@ -234,7 +269,8 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   // does useful work instead of waiting at a barrier:
   //   phase 1 (row n)  column accumulators, the row's two sums -> warp totals -> red[n & 3],
   //                    arrive on rowbar[n & 1];
-  //   phase 2 (row n)  wait for rowbar, fold the 16 warp totals, re-read x and dy from the
+  //   phase 2 (row n)  wait for the row's totals (totbar; or rowbar and fold the 16 warp
+  //                    totals oneself), re-read x and dy from the
   //                    ring slot, recompute xhat and dy * gamma (cheaper than keeping 32
   //                    registers alive across phase 1 of the next row), write dx, free the slot.
   // Four red[] buffers: a warp in phase 1 of row n + 2 has passed the barrier of row n, so
@@ -314,20 +350,25 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->rowbar[n & 1]));
   };
   auto phase2 = [&](int64_t n, int s) {
-    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
-                                kBwd1WaitLimit)) {
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(fold_warp ? &ctl->totbar[n & 1] : &ctl->rowbar[n & 1]),
+                                (uint32_t)((n >> 1) & 1), abort_flag, kBwd1WaitLimit)) {
       *abort_flag = 1;
-      atomicCAS(status, 0u, 0x78000u | (uint32_t)s);
+      atomicCAS(status, 0u, (fold_warp ? 0x7c000u : 0x78000u) | (uint32_t)s);
       alive = false;
       return;
     }
-    // Both half-warps fold the same 16 warp totals, so every lane ends with the row's totals
-    // after four shuffle levels.
-    float2 ss = *reinterpret_cast<const float2*>(&red[n & 3][lane & (NW - 1)][0]);
+    float2 ss;
+    if (fold_warp) {
+      ss = ctl->tot[n & 3];  // the row's totals, folded once for the CTA
+    } else {
+      // Both half-warps fold the same 16 warp totals, so every lane ends with the row's totals
+      // after four shuffle levels.
+      ss = *reinterpret_cast<const float2*>(&red[n & 3][lane & (NW - 1)][0]);
 #pragma unroll
-    for (int o = NW / 2; o > 0; o >>= 1) {
-      ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
-      ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+      for (int o = NW / 2; o > 0; o >>= 1) {
+        ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+        ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+      }
     }
     const uint8_t* slot = bwd1_smem + (size_t)s * slot_bytes;
     const int64_t row = ctl->row[s];
@@ -426,7 +467,8 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const size_t smem = (size_t)stages * slot + gamma_bytes + sizeof(BwdRing1Ctl) + 128;
   const int grid = (int)(P.rows < ctx->sm_count ? P.rows : ctx->sm_count);
   P.partial_rows = grid;
-  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(kBwd1Consumers + 32), smem, s, P, stages, ctx->status_word);
+  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(kBwd1Consumers + (EPT <= 24 ? 64 : 32)), smem, s, P, stages,
+                                          ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
 }
@@ -1253,7 +1295,7 @@ namespace {
 }  // namespace lego
 
 namespace lego {
-std::atomic<int> g_lnbwd_split{6144};  // rows wider than this take the one-group kernel
+std::atomic<int> g_lnbwd_split{4096};  // rows wider than this take the one-group kernel
 }
 
 using namespace lego;
