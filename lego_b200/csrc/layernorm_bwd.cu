@@ -159,12 +159,13 @@ struct BwdRing1Ctl {
 template <int EPT, bool FULLW>
 __global__ void __launch_bounds__(kBwd1Consumers + (EPT <= 24 ? 64 : 32), 1)
 ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* status) {
-  constexpr bool fold_warp = EPT <= 24;  // a second helper warp folds the rows' totals (see there)
+  constexpr bool fold_warp = EPT <= 24;  // a second helper warp sums the rows' totals (see there)
   constexpr int NV = EPT / 8;
   constexpr int NW = kBwd1Consumers / 32;
   constexpr bool GSMEM = EPT > 16;
   extern __shared__ __align__(128) uint8_t bwd1_smem[];
   __shared__ __align__(16) float red[4][NW][2];  // [row & 3][warp] -> (s1, s2)
+  __shared__ __align__(16) float2 part[fold_warp ? 2 : 1][fold_warp ? kBwd1Consumers : 1];  // [row & 1][thread] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
   const uint32_t half_slot = (row_bytes + 127u) & ~127u;
@@ -194,12 +195,13 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 
   if (tid >= kBwd1Consumers + 32) {
     // ---------------- folding warp ----------------
-    // Folds the 16 warp totals of a row once for the whole CTA (the same shuffle tree every
-    // consumer thread runs for itself when fold_warp is 0) and publishes the result through
-    // totbar: the consumers' phase 2 then starts with one shared-memory load instead of a chain
-    // of four dependent shuffle levels.  Same box, 16384 x 8192: 152 -> 135 us; 16384 x 7168:
-    // 146 -> 128 us; 8192 x 10240: 125 -> 104 us; with the three ring slots of rows beyond
-    // 12 Ki columns (32 columns per thread) 160 -> 165 us, so those instances do without it.
+    // Sums a row's 512 pairs of per-thread sums once for the whole CTA and publishes the totals
+    // through totbar.  The consumers' phase 1 then ends with one shared-memory store instead of
+    // six dependent shuffle levels, and their phase 2 starts with one load instead of four more.
+    // Same box, 16384 x 8192: folding the 16 warp totals here 152 -> 135 us, the threads' sums
+    // too 135 -> 129 us (6.25 TB/s); 8192 x 10240: 125 -> 104 -> 100 us.  The instances with 32
+    // columns per thread have three ring slots and no room for part[]; folding only the warp
+    // totals here made them 3 % slower, so they keep the fold in the consumers.
     const int lane = tid & 31;
     for (int64_t n = 0; fold_warp && n < my_rows; ++n) {
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
@@ -208,9 +210,17 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
         atomicCAS(status, 0u, 0x78000u | (uint32_t)(n & 0xfff));
         break;
       }
-      float2 ss = *reinterpret_cast<const float2*>(&red[n & 3][lane & (NW - 1)][0]);
+      // lane l adds the sums of threads l, l + 32, ... (a fixed tree), then five shuffle levels
+      float2 q[kBwd1Consumers / 32];
 #pragma unroll
-      for (int o = NW / 2; o > 0; o >>= 1) {
+      for (int i = 0; i < kBwd1Consumers / 32; ++i) q[i] = part[fold_warp ? (n & 1) : 0][fold_warp ? lane + 32 * i : 0];
+#pragma unroll
+      for (int w = kBwd1Consumers / 64; w > 0; w >>= 1)
+#pragma unroll
+        for (int i = 0; i < w; ++i) q[i] = ptx::add2(q[i], q[i + w]);
+      float2 ss = q[0];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
         ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
         ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
       }
@@ -267,8 +277,8 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
   // phases with the next row's first phase in between, so that the CTA-wide reduction of a
   // row (shuffles, a hop through shared memory, an mbarrier) is in flight while the thread
   // does useful work instead of waiting at a barrier:
-  //   phase 1 (row n)  column accumulators, the row's two sums -> warp totals -> red[n & 3],
-  //                    arrive on rowbar[n & 1];
+  //   phase 1 (row n)  column accumulators, the row's two sums -> part[n & 1] (or, without a
+  //                    folding warp, warp totals -> red[n & 3]), arrive on rowbar[n & 1];
   //   phase 2 (row n)  wait for the row's totals (totbar; or rowbar and fold the 16 warp
   //                    totals oneself), re-read x and dy from the
   //                    ring slot, recompute xhat and dy * gamma (cheaper than keeping 32
@@ -339,13 +349,17 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
     }
     // Even lanes fold the first sum, odd lanes the second: one shuffle per level instead of
     // two; lanes 0 and 1 end with the warp's two totals.
-    const bool odd = (lane & 1) != 0;
     const float a = s1.x + s1.y, bsum = s2.x + s2.y;
-    float keep = odd ? bsum : a;
-    keep += __shfl_xor_sync(0xffffffffu, odd ? a : bsum, 1);
+    if (fold_warp) {
+      part[fold_warp ? (n & 1) : 0][fold_warp ? tid : 0] = make_float2(a, bsum);  // the folding warp adds them up
+    } else {
+      const bool odd = (lane & 1) != 0;
+      float keep = odd ? bsum : a;
+      keep += __shfl_xor_sync(0xffffffffu, odd ? a : bsum, 1);
 #pragma unroll
-    for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-    if (lane < 2) red[n & 3][warp][lane] = keep;
+      for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+      if (lane < 2) red[n & 3][warp][lane] = keep;
+    }
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->rowbar[n & 1]));
   };
@@ -454,13 +468,14 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   auto kern = fullw ? ln_bwd_ring1_kernel<EPT, (EPT > 16)> : ln_bwd_ring1_kernel<EPT, false>;
   const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
+  const size_t part_bytes = EPT <= 24 ? 2 * kBwd1Consumers * sizeof(float2) : 0;  // static: the threads' row sums
   static PerDeviceFlag configured[2];  // one per kernel
   if (!configured[fullw].test(ctx->device)) {
-    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024));
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 1024 - part_bytes));
     configured[fullw].set(ctx->device);
   }
   const size_t gamma_bytes = EPT > 16 ? half_slot : 0;  // gamma staged in shared memory
-  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128 - gamma_bytes;
+  const size_t budget = (size_t)ctx->smem_optin - 1024 - sizeof(BwdRing1Ctl) - 128 - gamma_bytes - part_bytes;
   int stages = (int)(budget / slot);
   if (stages > kBwd1Ring) stages = kBwd1Ring;
   if (stages < 3) return LEGO_ERR_UNSUPPORTED;  // the rows in phase 1 and phase 2 hold two slots; one more for the load in flight
