@@ -816,6 +816,10 @@ struct BwdRingCtl {
   uint32_t group_abort[kBwdMaxGroups];  // set by a thread of the group that gave up
 };
 
+// (A folding warp as in ln_bwd_ring1_kernel was slower here, whether it served the groups in turn
+// or polled their barriers and served whichever had a row ready; same box: 16384 x 4096 72.6 ->
+// 77 us with two groups, 16384 x 2048 38.5 -> 57-60 us with four, 4096 x 1024 12.7 -> 18.6 us
+// with eight: a group of a few warps has little other work to cover the round trip.)
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
 template <int EPT, int G, bool BLOCKS>
 __global__ void __launch_bounds__(kBwdConsumers + 32, 1)
