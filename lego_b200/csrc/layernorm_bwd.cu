@@ -151,7 +151,7 @@ struct BwdRing1Ctl {
   uint32_t abort_flag;
 };
 
-// FULLW (EPT 24 or 32 only): the row is exactly 512 x EPT columns wide, so no vector of a thread
+// FULLW (EPT 16, 24 or 32): the row is exactly 512 x EPT columns wide, so no vector of a thread
 // lies past its end: no bounds predicates and no zero fill of the vectors.
 // EPT: columns per consumer thread, 8 or 16 with gamma in registers; 24 or 32 (rows of 8 Ki .. 16 Ki
 // columns) with gamma staged once per CTA in shared memory as fp16, because 64 accumulator
@@ -462,10 +462,10 @@ ln_bwd_ring1_kernel(const __grid_constant__ BwdParams P, int stages, uint32_t* s
 template <int EPT>
 int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   // Without the bounds predicates, same box: 8192 x 12288 (24 columns per thread) 135.7 -> 119 us,
-  // 8192 x 16384 (32) 176 -> 164 us; 16384 x 8192 (16) 150 -> 154 us with gamma in registers, 151 -> 158 us
-  // with gamma in shared memory, so not there.
-  const bool fullw = EPT > 16 && P.cols == EPT * kBwd1Consumers;
-  auto kern = fullw ? ln_bwd_ring1_kernel<EPT, (EPT > 16)> : ln_bwd_ring1_kernel<EPT, false>;
+  // 8192 x 16384 (32) 176 -> 164 us; 16384 x 8192 (16): 150 -> 154 us while the consumers still
+  // folded the row sums by shuffles, 135.5 -> 130.5 us since the folding warp does.
+  const bool fullw = EPT >= 16 && P.cols == EPT * kBwd1Consumers;
+  auto kern = fullw ? ln_bwd_ring1_kernel<EPT, (EPT >= 16)> : ln_bwd_ring1_kernel<EPT, false>;
   const size_t half_slot = ((size_t)P.cols * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
   const size_t part_bytes = EPT <= 24 ? 2 * kBwd1Consumers * sizeof(float2) : 0;  // static: the threads' row sums
