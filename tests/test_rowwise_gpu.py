@@ -190,12 +190,13 @@ def test_layernorm_backward_shapes_of_both_kernels():
     ring-fed kernels (16-byte rows of 1 Ki columns or more) and for neighbours that take the
     register kernel (narrower rows, widths that are no multiple of 8); tolerances of the
     reference's own test (atol 1e-2) for dx, 1e-2 of the largest entry for the column sums."""
-    # (wide rows: 8 Ki < cols <= 16 Ki take the ring kernel with 24 or 32 columns per thread and
-    # gamma in shared memory; 16 Ki < cols <= 32 Ki a CTA pair per row)
+    # (4 Ki < cols <= 8 Ki: one group of 512 threads with a folding warp; 8 Ki < cols <= 16 Ki the
+    # same kernel with 24 or 32 columns per thread and gamma in shared memory, without bounds
+    # predicates at exactly 8192, 12288 and 16384 columns; 16 Ki < cols <= 32 Ki a CTA pair per row)
     _check_layernorm_backward(((1152, 8192), (600, 4096), (2048, 2056), (1152, 1032), (1150, 8192), (512, 8200),
                                (300, 1024), (1200, 1024), (600, 16384), (596, 12296), (300, 9000), (128, 16384),
                                (320, 20480), (600, 32768), (296, 16400), (444, 30008), (37, 1000), (300, 777),
-                               (64, 4100)))
+                               (64, 4100), (700, 5120), (333, 6152), (400, 12288), (500, 7168)))
 
 
 def test_layernorm_backward_row_counts_that_are_no_multiple_of_four():
