@@ -341,6 +341,8 @@ row_ring_kernel(const __grid_constant__ RowParams P, int stages, int groups, int
     const uint4* slot = reinterpret_cast<const uint4*>(ring_smem + (size_t)s * slot_bytes);
     float v[EPT];
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.f;
+    // (An instance without the `c < cols` predicates for rows of exactly gsize x EPT values was
+    // slower, same box, 16384 x 8192 fp16: softmax 6501 -> 5879 GB/s, LayerNorm 6276-6544 -> 5700.)
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int c = (k * gsize + gtid) * VEC;
