@@ -503,20 +503,24 @@ int32_t launch_ring1_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
 struct BwdPairCtl {
   uint64_t full[kBwd1Ring];
   uint64_t empty[kBwd1Ring];
-  uint64_t rowbar[2];  // 32 arrivals: the 16 consumer warps of either CTA
+  uint64_t rowbar[2];   // 16 arrivals: this CTA's consumer warps have left their totals of the row in red[]
+  uint64_t peerbar[2];  // one arrival, from the peer's liaison warp: the peer's half of the row sums is in peer_tot[]
+  uint64_t totbar[2];   // one arrival, from this CTA's liaison warp: the whole row's sums are in tot[]
   int64_t row[kBwd1Ring];
+  float2 peer_tot[4];   // [row & 3], written by the peer
+  float2 tot[4];        // [row & 3]
   uint32_t abort_flag;
 };
 
 template <bool FULLW>  // FULLW: 32768 columns, both halves exactly 512 x 32: no bounds predicates
-__global__ void __launch_bounds__(kBwd1Consumers + 32, 1)
+__global__ void __launch_bounds__(kBwd1Consumers + 64, 1)
 ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half, uint32_t* status) {
   constexpr int EPT = 32;
   constexpr int NV = EPT / 8;
   constexpr int NW = kBwd1Consumers / 32;
   constexpr int P2 = EPT / 2;
   extern __shared__ __align__(128) uint8_t pair_smem[];
-  __shared__ __align__(16) float red[4][2 * NW][2];  // [row & 3][CTA rank * 16 + warp] -> (s1, s2)
+  __shared__ __align__(16) float red[4][NW][2];  // [row & 3][warp] -> (s1, s2) of this CTA's half of the row
   const uint32_t rank = ptx::cluster_ctarank();
   const uint32_t peer = rank ^ 1u;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
@@ -537,8 +541,11 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
       ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), NW);
     }
-    ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[0]), 2 * NW);
-    ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[1]), 2 * NW);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[i]), NW);
+      ptx::mbar_init(ptx::smem_u32(&ctl->peerbar[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->totbar[i]), 1);
+    }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -554,7 +561,51 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
     atomicCAS(status, 0u, code);
   };
 
-  if (tid >= kBwd1Consumers) {
+  if (tid >= kBwd1Consumers + 32) {
+    // ---------------- liaison warp ----------------
+    // The only role that talks to the peer CTA.  Per row: wait for this CTA's 16 warp totals, fold
+    // them, store the pair of sums into the peer's peer_tot[] and arrive on its peerbar (release at
+    // cluster scope), wait for the peer's pair (acquire at cluster scope), add the two halves in
+    // rank order (the same bits in both CTAs) and publish the row's sums to the consumers through
+    // totbar.  The consumers themselves synchronise at CTA scope only: when every consumer warp
+    // stored to the peer and arrived with a cluster-scope release, each such arrive first waited
+    // for the warp's outstanding dx stores (stall_membar 2.8 per issue, the top stall; 4096 x 32768:
+    // 216 us with that form).
+    const int lane = tid & 31;
+    const uint32_t peer_tot_remote = ptx::mapa(ptx::smem_u32(&ctl->peer_tot[0]), peer);
+    const uint32_t peerbar_remote = ptx::mapa(ptx::smem_u32(&ctl->peerbar[0]), peer);
+    for (int64_t n = 0; n < my_rows; ++n) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
+                                  kBwd1WaitLimit)) {
+        if (lane == 0) fail(0x78000u | 0x2000u);
+        break;
+      }
+      float2 mine = *reinterpret_cast<const float2*>(&red[n & 3][lane & (NW - 1)][0]);
+#pragma unroll
+      for (int o = NW / 2; o > 0; o >>= 1) {
+        mine.x += __shfl_xor_sync(0xffffffffu, mine.x, o);
+        mine.y += __shfl_xor_sync(0xffffffffu, mine.y, o);
+      }
+      int ok = 1;
+      if (lane == 0) {
+        ptx::st_cluster_f32x2(peer_tot_remote + (uint32_t)(n & 3) * 8u, mine.x, mine.y);
+        ptx::mbar_arrive_cluster(peerbar_remote + (uint32_t)(n & 1) * 8u);
+        ok = ptx::mbar_wait_bounded_cluster(ptx::smem_u32(&ctl->peerbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
+                                            kBwd1WaitLimit) ? 1 : 0;
+        if (ok) {
+          const volatile float* pt = reinterpret_cast<const volatile float*>(&ctl->peer_tot[n & 3]);
+          const float2 theirs = make_float2(pt[0], pt[1]);
+          const float2 r0 = rank == 0 ? mine : theirs, r1 = rank == 0 ? theirs : mine;
+          ctl->tot[n & 3] = make_float2(r0.x + r1.x, r0.y + r1.y);
+          ptx::mbar_arrive(ptx::smem_u32(&ctl->totbar[n & 1]));  // release: the store above is visible to the waiters
+        } else {
+          fail(0x78000u | 0x1000u);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+    }
+  } else if (tid >= kBwd1Consumers) {
     // ---------------- producer ----------------
     if (tid == kBwd1Consumers) {
       int64_t issued = 0;
@@ -598,10 +649,6 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
 #pragma unroll
     for (int k = 0; k < P2; ++k) acc_w[k] = acc_b[k] = make_float2(0.f, 0.f);
     const float inv_cols = 1.0f / (float)cols_full;
-    const uint32_t red_local = ptx::smem_u32(&red[0][0][0]);
-    const uint32_t red_peer = ptx::mapa(red_local, peer);
-    const uint32_t rowbar_local = ptx::smem_u32(&ctl->rowbar[0]);
-    const uint32_t rowbar_peer = ptx::mapa(rowbar_local, peer);
 
     bool alive = true;
     auto phase1 = [&](int64_t n, int s, uint32_t use) {
@@ -643,28 +690,19 @@ ln_bwd_pair_kernel(const __grid_constant__ BwdParams P, int stages, int col_half
         bsum += __shfl_xor_sync(0xffffffffu, bsum, o);
       }
       if (lane == 0) {
-        // this warp's totals into its slot of red[] in both CTAs, then one arrival on either row barrier
-        const uint32_t off = (uint32_t)((((n & 3) * 2 * NW) + (int)rank * NW + warp) * 2) * 4u;
-        red[n & 3][rank * NW + warp][0] = a;
-        red[n & 3][rank * NW + warp][1] = bsum;
-        ptx::st_cluster_f32x2(red_peer + off, a, bsum);
-        ptx::mbar_arrive_cluster(rowbar_local + (uint32_t)(n & 1) * 8u);
-        ptx::mbar_arrive_cluster(rowbar_peer + (uint32_t)(n & 1) * 8u);
+        // this warp's totals for the liaison warp; CTA scope only
+        red[n & 3][warp][0] = a;
+        red[n & 3][warp][1] = bsum;
+        ptx::mbar_arrive(ptx::smem_u32(&ctl->rowbar[n & 1]));
       }
     };
     auto phase2 = [&](int64_t n, int s) {
-      if (!ptx::mbar_wait_bounded_cluster(ptx::smem_u32(&ctl->rowbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag,
-                                          kBwd1WaitLimit)) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->totbar[n & 1]), (uint32_t)((n >> 1) & 1), abort_flag, kBwd1WaitLimit)) {
         fail(0x78000u | 0x4000u | (uint32_t)s);
         alive = false;
         return;
       }
-      float2 ss = *reinterpret_cast<const float2*>(&red[n & 3][lane][0]);  // 32 warp totals, one per lane
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
-        ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
-      }
+      const float2 ss = ctl->tot[n & 3];  // both halves of the row, added up by the liaison warp
       const uint8_t* slot = pair_smem + (size_t)s * slot_bytes;
       const int64_t row = ctl->row[s];
       const float mean = reinterpret_cast<const float*>(slot + 2u * half_slot)[row & 3];
@@ -756,7 +794,7 @@ int32_t launch_pair_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   if (pairs < 1) return LEGO_ERR_UNSUPPORTED;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(kBwd1Consumers + 32);
+  cfg.blockDim = dim3(kBwd1Consumers + 64);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
