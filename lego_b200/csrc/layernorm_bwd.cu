@@ -1395,9 +1395,9 @@ int32_t lego_layernorm_bwd_f16(const void* dy, const void* x, const void* gamma,
     // groups of cols/16 threads: N = 2048: 2010 / 4180, N = 4096: 3850 / 5350, N = 6144: 4160 / 4670,
     // N = 8192: 5500 / 5250.
     // (The pair kernel with 16 columns per thread for rows of 12 Ki .. 16 Ki columns, six ring slots
-    // instead of three: 8192 x 16384 157 -> 250 us, same box.  A pair turns one row around in 2.2 us or
-    // more whatever its width -- the exchange of the row sums between the two CTAs -- so it pays only
-    // where one CTA cannot hold the row.)
+    // instead of three: 8192 x 16384 157 -> 233 us, same box.  A pair turns one row around in about
+    // 2.1 us whatever its width -- the round trip of the row sums between the two CTAs, of which only
+    // one first phase is covered -- so it pays only where one CTA cannot hold the row.)
     if (cols > kBwd1Consumers * 32) st = launch_pair_dx(P, ctx, s);
     else if (cols > kBwd1Consumers * 16) st = cols <= kBwd1Consumers * 24 ? launch_ring1_dx<24>(P, ctx, s) : launch_ring1_dx<32>(P, ctx, s);
     else if (cols > g_lnbwd_split.load()) st = cols <= kBwd1Consumers * 8 ? launch_ring1_dx<8>(P, ctx, s) : launch_ring1_dx<16>(P, ctx, s);
