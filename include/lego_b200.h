@@ -330,11 +330,14 @@ int32_t lego_gemm_e5m2_ws(const void* A, const void* B, void* C, int64_t M, int6
  *                           row, 2 = the same and never a block of rows per slot; + 8 = every
  *                           group writes its own partial row of column sums (no fold in the CTA)
  *   LEGO_TUNE_LNBWD_MIN_ROWS     LayerNorm backward: fewest rows for which the ring-fed kernels are
- *                           used (below, one CTA per row with the row in registers) */
+ *                           used (below, one CTA per row with the row in registers)
+ *   LEGO_TUNE_LNBWD_FOLD_WARP    LayerNorm backward, rows of up to 4 Ki columns: most consumer groups
+ *                           for which an extra warp per group adds up the rows' sums (0 .. 3; 0:
+ *                           every consumer thread folds its group's sums itself) */
 enum { LEGO_TUNE_GEMM_BLOCKS = 1, LEGO_TUNE_GEMM_STREAMK = 2, LEGO_TUNE_GEMM_LAG = 3, LEGO_TUNE_LNBWD_SPLIT = 4,
        LEGO_TUNE_PERMUTE_TILE_VECS = 5, LEGO_TUNE_PERMUTE_DMA_TILE = 6, LEGO_TUNE_PERMUTE_DMA_CTAS = 7,
        LEGO_TUNE_PDL_LAST_WAVE = 8, LEGO_TUNE_LNBWD_LANES = 9, LEGO_TUNE_PERMUTE_DMA_LONG = 10,
-       LEGO_TUNE_LNBWD_MIN_ROWS = 11 };
+       LEGO_TUNE_LNBWD_MIN_ROWS = 11, LEGO_TUNE_LNBWD_FOLD_WARP = 12 };
 int32_t lego_tune(int32_t knob, int32_t value);
 
 /* G independent problems C_g = A_g . B_g (row-major, contiguous), walked by

@@ -36,6 +36,7 @@ TUNE_PDL_LAST_WAVE = 8
 TUNE_LNBWD_LANES = 9
 TUNE_PERMUTE_DMA_LONG = 10
 TUNE_LNBWD_MIN_ROWS = 11
+TUNE_LNBWD_FOLD_WARP = 12
 
 ERR_UNSUPPORTED = -8
 ERR_CUDA_BASE = 1000

@@ -1117,6 +1117,7 @@ extern std::atomic<int> g_lnbwd_split;      // layernorm_bwd.cu
 extern std::atomic<int> g_lnbwd_lanes;      // layernorm_bwd.cu
 extern std::atomic<int> g_lnbwd_fold;       // layernorm_bwd.cu
 extern std::atomic<int> g_lnbwd_min_rows;   // layernorm_bwd.cu
+extern std::atomic<int> g_lnbwd_foldw_groups;  // layernorm_bwd.cu
 extern std::atomic<int> g_chunk_tile_vecs;  // permute.cu
 extern std::atomic<int> g_dma_tile_bytes;   // permute.cu
 extern std::atomic<int> g_dma_ctas_per_sm;  // permute.cu
@@ -1367,6 +1368,10 @@ int32_t lego_tune(int32_t knob, int32_t value) {
       if (value < 0 || (value & 7) > 2 || value > 10) return LEGO_ERR_SIZE;
       g_lnbwd_lanes.store(value & 7);
       g_lnbwd_fold.store(value & 8 ? 0 : 1);
+      return LEGO_OK;
+    case LEGO_TUNE_LNBWD_FOLD_WARP:
+      if (value < 0 || value > 3) return LEGO_ERR_SIZE;
+      g_lnbwd_foldw_groups.store(value);
       return LEGO_OK;
     case LEGO_TUNE_LNBWD_MIN_ROWS:
       if (value < 1) return LEGO_ERR_SIZE;

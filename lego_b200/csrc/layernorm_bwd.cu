@@ -16,6 +16,8 @@
 namespace lego {
 // lego_tune(LEGO_TUNE_LNBWD_LANES): producer of the grouped ring kernel.  0 = one thread; 1 = a lane
 // per group in lock step where a slot holds one row; 2 = the same, and never the block form.
+// most consumer groups for which the grouped ring kernel runs a folding warp per group (0: never)
+std::atomic<int> g_lnbwd_foldw_groups{3};
 // fewest rows the ring-fed kernels take; below, the register kernel
 std::atomic<int> g_lnbwd_min_rows{1};
 std::atomic<int> g_lnbwd_lanes{1};
@@ -849,18 +851,24 @@ struct BwdRingCtl {
   uint64_t full[kBwdRing];
   uint64_t empty[kBwdRing];
   int64_t row[kBwdRing];
-  uint64_t rowbar[kBwdMaxGroups][2];    // [group][row & 1]: the row's warp totals are all in red_all
+  uint64_t rowbar[kBwdMaxGroups][2];    // [group][row & 1]: the row's warp totals are all in red_all (or the threads' sums in part[])
+  uint64_t totbar[kBwdMaxGroups][2];    // [group][row & 1]: the row's totals are in tot[] (one arrival: the group's folding warp)
+  float2 tot[kBwdMaxGroups][4];         // [group][row & 3] -> the row's (s1, s2)
   uint32_t abort_flag;                  // any role gave up: polled inside every bounded wait
   uint32_t group_abort[kBwdMaxGroups];  // set by a thread of the group that gave up
 };
 
-// (A folding warp as in ln_bwd_ring1_kernel was slower here, whether it served the groups in turn
-// or polled their barriers and served whichever had a row ready; same box: 16384 x 4096 72.6 ->
-// 77 us with two groups, 16384 x 2048 38.5 -> 57-60 us with four, 4096 x 1024 12.7 -> 18.6 us
-// with eight: a group of a few warps has little other work to cover the round trip.)
+// (ONE folding warp for all groups was slower than none, whether it served the groups in turn or
+// polled their barriers and served whichever had a row ready; same box: 16384 x 4096 72.6 -> 77 us
+// with two groups, 16384 x 2048 38.5 -> 57-60 us with four, 4096 x 1024 12.7 -> 18.6 us with eight.
+// A folding warp per group: 16384 x 4096 72.7 -> 67.7 us (5.54 -> 5.95 TB/s), 16384 x 3072 63 ->
+// 59.2 us, 4096 x 4096 23.1 -> 22.3 us; possible for up to three groups, see FOLDW.)
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
-template <int EPT, int G, bool BLOCKS>
-__global__ void __launch_bounds__(kBwdConsumers + 32, 1)
+// FOLDW: one folding warp PER GROUP (after the producer's warp; up to three groups, so that no
+// scheduler holds more than five warps) adds up the row sums the group's threads leave in part[],
+// as in ln_bwd_ring1_kernel; without it every consumer folds its group's warp totals itself.
+template <int EPT, int G, bool BLOCKS, bool FOLDW>
+__global__ void __launch_bounds__(FOLDW ? 640 : kBwdConsumers + 32, 1)
 ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_rt, int gsize_rt, int lanes, int fold,
                    uint32_t* status) {
   constexpr int NV = EPT / 8;
@@ -869,6 +877,7 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   constexpr int P2 = EPT / 2;  // packed pairs per thread and row
   extern __shared__ __align__(128) uint8_t bwd_smem[];
   __shared__ __align__(16) float2 red_all[kBwdMaxGroups][4][16];  // [group][row & 3][warp] -> (s1, s2)
+  __shared__ __align__(16) float2 part[FOLDW ? 2 : 1][FOLDW ? kBwdConsumers : 1];  // [row & 1][thread] -> (s1, s2)
   const int cols = P.cols;
   const uint32_t row_bytes = (uint32_t)cols * 2u;
   const uint32_t half_slot = ((BLOCKS ? (uint32_t)groups : 1u) * row_bytes + 127u) & ~127u;  // the slot's rows of x (or of dy)
@@ -893,6 +902,8 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
       ctl->group_abort[g] = 0;
       ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[g][0]), nw);
       ptx::mbar_init(ptx::smem_u32(&ctl->rowbar[g][1]), nw);
+      ptx::mbar_init(ptx::smem_u32(&ctl->totbar[g][0]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->totbar[g][1]), 1);
     }
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -903,6 +914,34 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
   ptx::launch_dependents();     // the column reduction (or the next op) may set itself up now
   ptx::grid_dependency_wait();  // global memory only once the previous grid is complete
 
+  if (FOLDW && tid >= n_consumers + 32) {
+    // ---------------- folding warps: warp g serves group g ----------------
+    const int lane = tid & 31;
+    const int g = (tid - n_consumers - 32) >> 5;
+    const int64_t g_rows = BLOCKS ? my_blocks : (my_blocks > g ? (my_blocks - g + groups - 1) / groups : 0);
+    for (int64_t j = 0; j < g_rows; ++j) {
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&ctl->rowbar[g][j & 1]), (uint32_t)((j >> 1) & 1), abort_flag,
+                                  kBwdWaitLimit)) {
+        *abort_flag = 1;
+        atomicCAS(status, 0u, 0x7a000u | (uint32_t)g);
+        return;
+      }
+      // lane l adds the sums of the group's threads l, l + 32, ... in order, then five shuffle levels
+      float2 ss = make_float2(0.f, 0.f);
+      for (int i = 0; i < nw; ++i) ss = ptx::add2(ss, part[FOLDW ? (j & 1) : 0][FOLDW ? g * gsize + 32 * i + lane : 0]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o);
+        ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+      }
+      if (lane == 0) {
+        ctl->tot[g][j & 3] = ss;
+        ptx::mbar_arrive(ptx::smem_u32(&ctl->totbar[g][j & 1]));  // release: the store above is visible to the waiters
+      }
+      __syncwarp();
+    }
+    return;
+  }
   if (tid >= n_consumers) {
     // ---------------- producer: blocks in order, block n of this CTA into slot n mod stages ----------------
     if (!BLOCKS && lanes > 1) {
@@ -1066,26 +1105,33 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
       }
     }
     // even lanes fold the first sum, odd lanes the second: one shuffle per level instead of two
-    const bool odd = (lane & 1) != 0;
     const float a = s1.x + s1.y, bsum = s2.x + s2.y;
-    float keep = odd ? bsum : a;
-    keep += __shfl_xor_sync(0xffffffffu, odd ? a : bsum, 1);
+    if (FOLDW) {
+      part[FOLDW ? (j & 1) : 0][FOLDW ? tid : 0] = make_float2(a, bsum);  // the group's folding warp adds them up
+    } else {
+      const bool odd = (lane & 1) != 0;
+      float keep = odd ? bsum : a;
+      keep += __shfl_xor_sync(0xffffffffu, odd ? a : bsum, 1);
 #pragma unroll
-    for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-    if (lane < 2) reinterpret_cast<float*>(&red[j & 3][warp_in_group])[lane] = keep;
+      for (int o = 2; o <= 16; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+      if (lane < 2) reinterpret_cast<float*>(&red[j & 3][warp_in_group])[lane] = keep;
+    }
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&rowbar[j & 1]));
   };
   auto phase2 = [&](int64_t j, int s) {
-    if (!ptx::mbar_wait_bounded(ptx::smem_u32(&rowbar[j & 1]), (uint32_t)((j >> 1) & 1), abort_flag, kBwdWaitLimit)) {
+    if (!ptx::mbar_wait_bounded(ptx::smem_u32(FOLDW ? &ctl->totbar[group][j & 1] : &rowbar[j & 1]), (uint32_t)((j >> 1) & 1),
+                                abort_flag, kBwdWaitLimit)) {
       *abort_flag = 1;
-      atomicCAS(status, 0u, 0x78000u | (uint32_t)s);
+      atomicCAS(status, 0u, (FOLDW ? 0x7c000u : 0x78000u) | (uint32_t)s);
       alive = false;
       return;
     }
     float2 ss;
     const float2* r = red[j & 3];
-    if (nw > 8) {
+    if (FOLDW) {
+      ss = ctl->tot[group][j & 3];  // folded once for the group by its folding warp
+    } else if (nw > 8) {
       // 16 partials: both half-warps fold the same 16 values by shuffles (few registers)
       ss = r[lane & 15];
 #pragma unroll
@@ -1220,17 +1266,19 @@ ln_bwd_ring_kernel(const __grid_constant__ BwdParams P, int stages, int groups_r
 }
 
 // Launches the ring kernel when the shape suits it; LEGO_ERR_UNSUPPORTED otherwise.
-template <int EPT, int G, bool BLOCKS>
+template <int EPT, int G, bool BLOCKS, bool FOLDW>
 int32_t launch_ring_dx_g(const BwdParams& P, DeviceCtx* ctx, cudaStream_t s, int grid, int stages, int groups, int gsize,
                          size_t smem, int fold) {
-  auto kern = ln_bwd_ring_kernel<EPT, G, BLOCKS>;
+  auto kern = ln_bwd_ring_kernel<EPT, G, BLOCKS, FOLDW>;
   static PerDeviceFlag configured;
   if (!configured.test(ctx->device)) {
-    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - 8192));  // static part: 4 KiB of reduction slots
+    // static part: 4 KiB of reduction slots, with folding warps 8 KiB of row sums too
+    LEGO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->smem_optin - (FOLDW ? 16384 : 8192)));
     configured.set(ctx->device);
   }
-  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32), smem, s, P, stages, groups, gsize,
-                                          g_lnbwd_lanes.load() && !BLOCKS && groups > 1 ? groups : 1, fold, ctx->status_word);
+  const cudaError_t e = launch_overlapped(kern, dim3(grid), dim3(groups * gsize + 32 + (FOLDW ? 32 * groups : 0)), smem, s, P, stages,
+                                          groups, gsize, g_lnbwd_lanes.load() && !BLOCKS && groups > 1 ? groups : 1, fold,
+                                          ctx->status_word);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return cuda_status(e);
 }
@@ -1258,7 +1306,10 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const int grid = (int)(fills < ctx->sm_count ? fills : ctx->sm_count);
   const size_t half_slot = ((size_t)per_fill * P.cols * 2 + 127) & ~(size_t)127;
   const size_t slot = 2 * half_slot + 128;
-  const size_t budget = (size_t)ctx->smem_optin - 8192 - sizeof(BwdRingCtl) - 128;
+  // a folding warp per group while consumers, producer and folding warps make 20 warps or fewer (five
+  // per scheduler, 96 registers); their 8 KiB of row sums come out of the ring's memory
+  const bool foldw = !blocks && groups <= g_lnbwd_foldw_groups.load() && groups * gsize + 32 + 32 * groups <= 640;
+  const size_t budget = (size_t)ctx->smem_optin - (foldw ? 16384 : 8192) - sizeof(BwdRingCtl) - 128;
   int stages = (int)((192 * 1024 + slot / 2) / slot);  // about 192 KiB of x and dy in flight
   const int least = blocks ? 3 : 2 * groups;  // the rows in phase 1 and phase 2 hold a slot each (per group)
   if (stages < least) stages = least;
@@ -1271,8 +1322,9 @@ int32_t launch_ring_dx(BwdParams& P, DeviceCtx* ctx, cudaStream_t s) {
   const int fold = (groups > 1 && P.cols % 4 == 0 && (size_t)groups * 2 * P.cols * 4 <= (size_t)stages * slot &&
                     g_lnbwd_fold.load()) ? 1 : 0;
   P.partial_rows = fold ? grid : grid * groups;  // every group writes its row, all zeros if it saw no row of x
-  return blocks ? launch_ring_dx_g<EPT, 0, true>(P, ctx, s, grid, stages, groups, gsize, smem, fold)
-                : launch_ring_dx_g<EPT, 0, false>(P, ctx, s, grid, stages, groups, gsize, smem, fold);
+  if (blocks) return launch_ring_dx_g<EPT, 0, true, false>(P, ctx, s, grid, stages, groups, gsize, smem, fold);
+  return foldw ? launch_ring_dx_g<EPT, 0, false, true>(P, ctx, s, grid, stages, groups, gsize, smem, fold)
+               : launch_ring_dx_g<EPT, 0, false, false>(P, ctx, s, grid, stages, groups, gsize, smem, fold);
 }
 
 // Column reduction for widths that are a multiple of 4: a CTA of 32 warps sums 32 columns;

@@ -153,7 +153,7 @@ def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
          gemm_lag: Optional[int] = None, permute_dma_tile: Optional[int] = None,
          permute_dma_ctas: Optional[int] = None, permute_tile_vecs: Optional[int] = None,
          pdl_last_wave: Optional[int] = None, permute_dma_long: Optional[int] = None,
-         lnbwd_min_rows: Optional[int] = None) -> None:
+         lnbwd_min_rows: Optional[int] = None, lnbwd_fold_warp: Optional[int] = None) -> None:
     """Process-wide knobs.  GEMM: ``gemm_blocks`` 0 library's choice / 1 (256 x 256 per SM
     pair) / 2 (512 x 256 per SM pair); ``gemm_streamk`` 0 / False keeps every tile whole,
     1 / True splits a poorly filled last wave along K, 2 splits any partial wave;
@@ -164,8 +164,11 @@ def tune(gemm_blocks: Optional[int] = None, gemm_streamk: Optional[bool] = None,
     common run is a whole line or more stay with the vector copy.  ``pdl_last_wave`` 1: only the last
     wave of an index-map grid lets the next grid of the stream become resident.
     ``lnbwd_min_rows``: fewest rows for which LayerNorm backward uses its ring-fed kernels
-    (default 1; below, the kernel that holds a row in registers)."""
+    (default 1; below, the kernel that holds a row in registers); ``lnbwd_fold_warp``: most
+    consumer groups for which its grouped kernel runs a folding warp per group (0 .. 3, default 3)."""
     lib = _abi.lib()
+    if lnbwd_fold_warp is not None:
+        _abi.check(lib.lego_tune(_abi.TUNE_LNBWD_FOLD_WARP, int(lnbwd_fold_warp)), "lego_tune")
     if lnbwd_min_rows is not None:
         _abi.check(lib.lego_tune(_abi.TUNE_LNBWD_MIN_ROWS, int(lnbwd_min_rows)), "lego_tune")
     if permute_dma_tile is not None:

@@ -215,6 +215,18 @@ def test_layernorm_backward_row_counts_that_are_no_multiple_of_four():
         ops.tune(lnbwd_min_rows=1)
 
 
+def test_layernorm_backward_grouped_kernel_with_and_without_folding_warps():
+    """Rows of up to 4 Ki columns: one, two and three consumer groups with a folding warp per
+    group, and the same shapes with every consumer folding its group's sums itself."""
+    shapes = ((600, 4096), (599, 3072), (333, 2560), (1200, 3584), (7, 4096), (150, 2304))
+    _check_layernorm_backward(shapes)
+    ops.tune(lnbwd_fold_warp=0)
+    try:
+        _check_layernorm_backward(shapes)
+    finally:
+        ops.tune(lnbwd_fold_warp=3)
+
+
 def test_layernorm_errors():
     x = torch.zeros(2, 40000, dtype=torch.float16, device="cuda")
     w = torch.zeros(40000, dtype=torch.float16, device="cuda")
