@@ -862,7 +862,8 @@ struct BwdRingCtl {
 // polled their barriers and served whichever had a row ready; same box: 16384 x 4096 72.6 -> 77 us
 // with two groups, 16384 x 2048 38.5 -> 57-60 us with four, 4096 x 1024 12.7 -> 18.6 us with eight.
 // A folding warp per group: 16384 x 4096 72.7 -> 67.7 us (5.54 -> 5.95 TB/s), 16384 x 3072 63 ->
-// 59.2 us, 4096 x 4096 23.1 -> 22.3 us; possible for up to three groups, see FOLDW.)
+// 59.2 us, 4096 x 4096 23.1 -> 22.3 us; possible for up to three groups, see FOLDW.  Two folding
+// warps for four groups, each serving two: 16384 x 2048 38.4 -> 41.7 us.)
 // G: threads per group when known at compile time, 0 = taken from `gsize_rt`.
 // FOLDW: one folding warp PER GROUP (after the producer's warp; up to three groups, so that no
 // scheduler holds more than five warps) adds up the row sums the group's threads leave in part[],
